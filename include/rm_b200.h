@@ -1,0 +1,148 @@
+/*
+ * rm_b200 — C ABI of the B200 (sm_100a) differentiable tetrahedral tile rasterizer.
+ *
+ * Drop-in boundary for the hot path of half-potato/radiance_meshes'
+ * delaunay_rasterization package.  Every entry point takes raw device
+ * pointers, explicit sizes and a CUDA stream; nothing here allocates or frees
+ * device memory (the caller owns outputs and workspaces), nothing keeps global
+ * mutable state unless an entry point says otherwise, and all work is
+ * stream-ordered on the stream passed in.  Return value: 0 on success, a
+ * negative RM_ERR_* code for host-detected errors (see rm_strerror).
+ * Device-detected conditions are reported through RmBinInfo.status.
+ *
+ * Citations are paths inside the reference project.
+ */
+#ifndef RM_B200_H_
+#define RM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RM_OK 0
+#define RM_ERR_INVALID_ARG (-1)
+#define RM_ERR_CUDA (-2)
+#define RM_ERR_TOO_MANY_KEYS (-3)
+#define RM_ERR_WORKSPACE (-4)
+
+/* bits of RmBinInfo.status */
+#define RM_STATUS_NAN_VERTEX 1u   /* a vertex coordinate is NaN (tile_shader_slang.py:78 asserts on this) */
+#define RM_STATUS_KEY_OVERFLOW 2u /* more than 2^31-1 (tile, tet) pairs (int32 cumsum, tile_shader_slang.py:36) */
+
+/* Floats per packed tet record / per record-gradient row. */
+#define RM_RECORD_FLOATS 24
+
+/*
+ * Camera, the reference's `tcam` dictionary (data/camera.py:72-91 plus the tile
+ * fields of utils/train_util.py:30-37; device-side view slang/camera.slang:13-29).
+ * The four arrays are DEVICE pointers exactly as the reference passes them
+ * (small CUDA tensors), so building this struct needs no host synchronisation.
+ */
+typedef struct RmCamera {
+  const float* world_view_transform; /* [4,4] row-major world->camera */
+  const float* K;                    /* [3,3] */
+  const float* cam_pos;              /* [3] */
+  const float* distortion_params;    /* [4] k1 k2 p1 p2 */
+  int32_t image_height, image_width;
+  int32_t camera_type;               /* 0 perspective, 1 fisheye */
+  float fovy, fovx, min_t;
+  int32_t tile_height, tile_width, grid_height, grid_width;
+  /* Screen-tile band [tile_row_begin, tile_row_end) this call is restricted to;
+   * 0, grid_height for the whole frame.  No counterpart in the reference (it is
+   * single-GPU); used to split one frame over several GPUs by tile rows. */
+  int32_t tile_row_begin, tile_row_end;
+} RmCamera;
+
+/* Written by rm_project_and_bin at the start of the info buffer (device memory). */
+typedef struct RmBinInfo {
+  int64_t n_keys;      /* N = sum of tiles_touched */
+  int32_t n_visible;   /* tets with tiles_touched > 0 */
+  uint32_t status;     /* RM_STATUS_* bits */
+} RmBinInfo;
+
+const char* rm_strerror(int code);
+int rm_version(void);
+
+/* Bytes of workspace rm_project_and_bin needs for T tets and G = grid_height*grid_width tiles. */
+size_t rm_bin_workspace_bytes(int64_t n_tets, int64_t n_tiles);
+
+/*
+ * Stage 1 + the size-independent half of stages 2-4.
+ * Replaces VertexShader.forward / vertex_shader (tile_shader_slang.py:77-125,
+ * slang/vertex_shader.slang:20-89), torch.cumsum (tile_shader_slang.py:36) and
+ * compute_tile_ranges (slang/tile_shader.slang:99-125).
+ *   indices[T,4] i32, vertices[V,3] f32 ->
+ *   tiles_touched[T] i32, rect_tile_space[T,4] i32, vs_tetra[T,3] f32 (column 2 =
+ *   clamped circumsphere power, the sort depth), circumcenter[T,3] f32 (zeros for
+ *   culled tets), tile_ranges[G,2] i32 (start,end of each tile's list; (0,0) if
+ *   empty), info (RmBinInfo).  Every output element is written.
+ * workspace must hold rm_bin_workspace_bytes(T, G) bytes, 256-byte aligned, and
+ * must stay untouched until rm_build_tile_lists has consumed it.
+ */
+int rm_project_and_bin(const int32_t* indices, int64_t n_tets, const float* vertices, int64_t n_vertices,
+                       const RmCamera* cam, int32_t* tiles_touched, int32_t* rect_tile_space, float* vs_tetra,
+                       float* circumcenter, int32_t* tile_ranges, RmBinInfo* info, void* workspace,
+                       size_t workspace_bytes, void* stream);
+
+/*
+ * Stages 2-3: per-tile tet lists ordered by (sort depth bits, tet id).
+ * Replaces generate_keys (slang/tile_shader.slang:49-97) + sort_by_keys
+ * (sort_by_keys/sort_by_keys.cu:9-53): the result equals the value array of a
+ * stable ascending sort of the keys (tile << 32 | sortable(depth)).
+ *   n_keys must be RmBinInfo.n_keys read back by the caller;
+ *   sorted_tetra_idx[N] i32 out; scratch[N] u32 caller-provided.
+ */
+int rm_build_tile_lists(const int32_t* rect_tile_space, const int32_t* tile_ranges, int64_t n_tets,
+                        const RmCamera* cam, int64_t n_keys, void* workspace, uint32_t* scratch,
+                        int32_t* sorted_tetra_idx, void* stream);
+
+/*
+ * Per-frame packed tet records (4 outward face planes relative to the camera
+ * position, colour field, density): the staged form of
+ * load_tet_alphablend_interp (slang/interp_version.slang:100-153).
+ * tiles_touched may be NULL (pack every tet) or [T] (skip culled tets).
+ * records[T, RM_RECORD_FLOATS] f32 out, 16-byte aligned.
+ */
+int rm_pack_records(const int32_t* indices, const float* vertices, const float* cell_values, int64_t n_tets,
+                    const RmCamera* cam, const int32_t* tiles_touched, float* records, void* stream);
+
+/*
+ * Forward integration.  Replaces splat_tiled (slang/alphablend_shader_interp.slang:371-431,
+ * host side alphablend_tiled_slang_interp.py:11-52).
+ *   ray_jitter[H,W,2] f32 -> output_img[H,W,4] (r,g,b,log-transmittance),
+ *   distortion_img[H,W,5], n_contributors[H,W] i32.  Every pixel of the band is written.
+ */
+int rm_forward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, const float* records,
+               const RmCamera* cam, const float* ray_jitter, float* output_img, float* distortion_img,
+               int32_t* n_contributors, void* stream);
+
+/*
+ * Backward integration.  Replaces splat_tiled.bwd / bwd_alpha_blend
+ * (slang/alphablend_shader_interp.slang:273-369, host side
+ * alphablend_tiled_slang_interp.py:70-112).
+ *   grad_records[T, RM_RECORD_FLOATS] is caller-provided scratch (zeroed here);
+ *   vertices_grad[V,3] and cell_values_grad[T,7] are fully written (zeroed here first).
+ */
+int rm_backward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, const float* records,
+                const RmCamera* cam, const float* ray_jitter, const float* output_img,
+                const float* distortion_img, const int32_t* n_contributors, const float* grad_output_img,
+                const float* grad_distortion_img, const int32_t* indices, const float* vertices,
+                const float* cell_values, int64_t n_tets, int64_t n_vertices, float* grad_records,
+                float* vertices_grad, float* cell_values_grad, void* stream);
+
+/*
+ * Reverse of stage 1 with respect to the vertices.  Replaces vertex_shader.bwd
+ * (tile_shader_slang.py:128-150).  grad_vs_tetra[T,3] (only column 2 is read)
+ * and grad_circumcenter[T,3] -> vertices_grad[V,3], zeroed here first.
+ */
+int rm_vertex_backward(const int32_t* indices, const float* vertices, int64_t n_tets, int64_t n_vertices,
+                       const RmCamera* cam, const int32_t* tiles_touched, const float* grad_vs_tetra,
+                       const float* grad_circumcenter, float* vertices_grad, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RM_B200_H_ */

@@ -1,0 +1,956 @@
+// CPU oracle for the differentiable tetrahedral tile rasterizer.
+//
+// TEST INFRASTRUCTURE ONLY.  This file is a plain C++ restatement of the
+// reference's shader arithmetic, stage by stage, used as the checker in the
+// test-suite, in the smoke test and as the timed CPU baseline of the bench.
+// Nothing in the product path (the CUDA library and its Python host code) may
+// import, link or call it.
+//
+// PARITY UNPINNED: the reference repository stores no golden images, tile
+// lists or gradients for this path, and neither its GPU implementation (needs
+// the Slang compiler) nor its CPU quadrature (needs JAX) can be executed where
+// this oracle was written.  The only known-answer value the reference holds,
+// compute_integral(1,1,2,1) == 1-exp(-2) (notebooks/integral.ipynb, cell 0),
+// is checked by the test-suite; everything else is pinned by construction
+// (each function below cites the reference lines it restates), by an fp64
+// central-difference check of this file's own forward pass, and by agreement
+// with the independent quadrature restatement in quad_oracle.cpp at the
+// reference's own 1e-1 tolerance.
+//
+// Conventions fixed here because the reference's generated CUDA is not
+// visible: normalize(v) = v / sqrt(dot(v,v)); lerp(a,b,t) = a + (b-a)*t;
+// dot and matrix products are evaluated left to right; the derivative of
+// max(x,y) goes to x when x > y, else to y; no floating-point contraction
+// (build with -ffp-contract=off).
+//
+// The forward/backward integration code is templated on the scalar type so
+// that the very same source can be instantiated in double for the
+// finite-difference check.
+
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <limits>
+#include <vector>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+namespace {
+
+template <class F>
+struct V3 {
+  F x, y, z;
+};
+template <class F>
+inline V3<F> operator+(V3<F> a, V3<F> b) { return {a.x + b.x, a.y + b.y, a.z + b.z}; }
+template <class F>
+inline V3<F> operator-(V3<F> a, V3<F> b) { return {a.x - b.x, a.y - b.y, a.z - b.z}; }
+template <class F>
+inline V3<F> operator*(V3<F> a, F s) { return {a.x * s, a.y * s, a.z * s}; }
+template <class F>
+inline V3<F> operator*(F s, V3<F> a) { return {a.x * s, a.y * s, a.z * s}; }
+template <class F>
+inline V3<F> operator-(V3<F> a) { return {-a.x, -a.y, -a.z}; }
+template <class F>
+inline F dot(V3<F> a, V3<F> b) { return a.x * b.x + a.y * b.y + a.z * b.z; }
+template <class F>
+inline V3<F> cross(V3<F> a, V3<F> b) {
+  return {a.y * b.z - a.z * b.y, a.z * b.x - a.x * b.z, a.x * b.y - a.y * b.x};
+}
+template <class F>
+inline V3<F> normalize(V3<F> a) {
+  F l = std::sqrt(dot(a, a));
+  return {a.x / l, a.y / l, a.z / l};
+}
+template <class F>
+inline V3<F> lerp(V3<F> a, V3<F> b, F t) { return a + (b - a) * t; }
+template <class F>
+inline V3<F> vmin(V3<F> a, V3<F> b) { return {std::fmin(a.x, b.x), std::fmin(a.y, b.y), std::fmin(a.z, b.z)}; }
+template <class F>
+inline V3<F> vmax(V3<F> a, V3<F> b) { return {std::fmax(a.x, b.x), std::fmax(a.y, b.y), std::fmax(a.z, b.z)}; }
+
+// ---------------------------------------------------------------------------
+// safe math: delaunay_rasterization/internal/slang/safe-math.slang:1-4,33-35,
+// 56-79,138-140,161-172
+// ---------------------------------------------------------------------------
+template <class F>
+inline F safe_clip(F v, F lo, F hi) { return std::fmax(std::fmin(v, hi), lo); }
+template <class F>
+inline F safe_div(F a, F b) {
+  const F TINY = F(1.0754944e-20f), MINV = F(-1e20f), MAXV = F(1e20f);
+  if (std::fabs(b) < TINY) return safe_clip(a / TINY, MINV, MAXV);
+  return safe_clip(a / b, MINV, MAXV);
+}
+template <class F>
+inline F safe_exp(F v) {
+  // exp(clip(v, -1e20, log(1e20)))
+  return std::exp(safe_clip(v, F(-1e20f), F(std::log(1e20f))));
+}
+
+// ---------------------------------------------------------------------------
+// Camera: data/camera.py:72-91 (dict layout), slang/camera.slang:13-76
+// ---------------------------------------------------------------------------
+}  // namespace
+
+extern "C" {
+struct OrCamera {
+  float world_view[16];  // row-major world->camera
+  float K[9];
+  float cam_pos[3];
+  float distortion[4];  // k1 k2 p1 p2
+  int image_height, image_width, camera_type;
+  float fovy, fovx, min_t;
+  int tile_height, tile_width, grid_height, grid_width;
+};
+}
+
+namespace {
+
+template <class F>
+struct Cam {
+  F W[4][4];
+  F K[3][3];
+  V3<F> pos;
+  F dist[4];
+  int H, Wd, type;
+  F min_t;
+  int tile_h, tile_w, grid_h, grid_w;
+};
+template <class F>
+Cam<F> load_cam(const OrCamera* c) {
+  Cam<F> r;
+  for (int i = 0; i < 4; ++i)
+    for (int j = 0; j < 4; ++j) r.W[i][j] = F(c->world_view[i * 4 + j]);
+  for (int i = 0; i < 3; ++i)
+    for (int j = 0; j < 3; ++j) r.K[i][j] = F(c->K[i * 3 + j]);
+  r.pos = {F(c->cam_pos[0]), F(c->cam_pos[1]), F(c->cam_pos[2])};
+  for (int i = 0; i < 4; ++i) r.dist[i] = F(c->distortion[i]);
+  r.H = c->image_height;
+  r.Wd = c->image_width;
+  r.type = c->camera_type;
+  r.min_t = F(c->min_t);
+  r.tile_h = c->tile_height;
+  r.tile_w = c->tile_width;
+  r.grid_h = c->grid_height;
+  r.grid_w = c->grid_width;
+  return r;
+}
+template <class F>
+inline F dist_norm2(const Cam<F>& c) {
+  return c.dist[0] * c.dist[0] + c.dist[1] * c.dist[1] + c.dist[2] * c.dist[2] + c.dist[3] * c.dist[3];
+}
+
+// slang/camera.slang:103-108 (point2camspace)
+template <class F>
+inline V3<F> point2camspace(V3<F> p, const Cam<F>& c) {
+  F h[4];
+  for (int i = 0; i < 4; ++i) h[i] = c.W[i][0] * p.x + c.W[i][1] * p.y + c.W[i][2] * p.z + c.W[i][3] * F(1);
+  return {safe_div(h[0], h[3]), safe_div(h[1], h[3]), safe_div(h[2], h[3])};
+}
+
+// slang/camera.slang:351-374 (distort)
+template <class F>
+inline void distort(F& x, F& y, const Cam<F>& c) {
+  if (dist_norm2(c) < F(1e-9f)) return;
+  F k1 = c.dist[0], k2 = c.dist[1], p1 = c.dist[2], p2 = c.dist[3];
+  F r2 = x * x + y * y;
+  F radial = r2 * (k1 + r2 * k2);
+  F tx = F(2) * p1 * x * y + p2 * (r2 + F(2) * x * x);
+  F ty = F(2) * p2 * x * y + p1 * (r2 + F(2) * y * y);
+  F nx = x + x * radial + tx;
+  F ny = y + y * radial + ty;
+  x = nx;
+  y = ny;
+}
+
+// slang/camera.slang:241-296 (undistort; Newton, at most 10 iterations)
+template <class F>
+inline void undistort(F& px, F& py, const Cam<F>& c) {
+  if (dist_norm2(c) < F(1e-9f)) return;
+  F k1 = c.dist[0], k2 = c.dist[1], p1 = c.dist[2], p2 = c.dist[3];
+  F x = px, y = py;
+  for (int i = 0; i < 10; ++i) {
+    F r2 = x * x + y * y;
+    F d = F(1) + r2 * (k1 + r2 * k2);
+    F fx = d * x + F(2) * p1 * x * y + p2 * (r2 + F(2) * x * x) - px;
+    F fy = d * y + F(2) * p2 * x * y + p1 * (r2 + F(2) * y * y) - py;
+    F d_r = k1 + r2 * (F(2) * k2);
+    F d_x = F(2) * x * d_r;
+    F d_y = F(2) * y * d_r;
+    F fx_x = d + d_x * x + F(2) * p1 * y + F(6) * p2 * x;
+    F fx_y = d_y * x + F(2) * p1 * x + F(2) * p2 * y;
+    F fy_x = d_x * y + F(2) * p2 * y + F(2) * p1 * x;
+    F fy_y = d + d_y * y + F(2) * p2 * x + F(6) * p1 * y;
+    F denom = fy_x * fx_y - fx_x * fy_y;
+    if (std::fabs(denom) < F(1e-9f)) break;
+    F xn = fx * fy_y - fy * fx_y;
+    F yn = fy * fx_x - fx * fy_x;
+    x += xn / denom;
+    y += yn / denom;
+  }
+  px = x;
+  py = y;
+}
+
+// slang/camera.slang:380-414 (camspace_to_image)
+template <class F>
+inline V3<F> camspace_to_image(V3<F> p, const Cam<F>& c) {
+  F ux, uy;
+  if (c.type == 1) {
+    V3<F> dir = normalize(p);
+    F sat = std::fmin(std::fmax(dir.z, F(0)), F(1));
+    F theta = std::acos(sat);
+    F st = std::sin(theta);
+    F k = (st < F(1e-6f)) ? F(1) : theta / st;
+    ux = dir.x * k;
+    uy = dir.y * k;
+  } else {
+    ux = p.x / p.z;
+    uy = p.y / p.z;
+  }
+  distort(ux, uy, c);
+  F px = ux * c.K[0][0] + c.K[0][2];
+  F py = uy * c.K[1][1] + c.K[1][2];
+  return {px, py, p.z};
+}
+
+// slang/camera.slang:418-440 (update_bounds_from_edge)
+template <class F>
+inline void update_bounds_from_edge(V3<F> a, V3<F> b, V3<F>& mn, V3<F>& mx, const Cam<F>& c) {
+  int n = 2;
+  bool distorted = dist_norm2(c) > F(1e-9f);
+  if (c.type == 1) n = 4;
+  else if (distorted) n = 3;
+  for (int i = 0; i < n; ++i) {
+    F t = F(i) / F(n - 1);
+    V3<F> s = lerp(a, b, t);
+    V3<F> pv = camspace_to_image(s, c);
+    mn = vmin(mn, pv);
+    mx = vmax(mx, pv);
+  }
+}
+
+// slang/camera.slang:443-508 (find_extent)
+template <class F>
+inline void find_extent(const V3<F> tet[4], V3<F>& mn, V3<F>& mx, const Cam<F>& c) {
+  const F BIG = F(1e20f);
+  mn = {BIG, BIG, BIG};
+  mx = {-BIG, -BIG, -BIG};
+  const F eps = F(1e-4f);
+  static const int faces[4][3] = {{0, 1, 2}, {0, 2, 3}, {0, 3, 1}, {1, 3, 2}};
+  for (int f = 0; f < 4; ++f) {
+    V3<F> fv[3] = {tet[faces[f][0]], tet[faces[f][1]], tet[faces[f][2]]};
+    V3<F> out[4];
+    int cnt = 0;
+    for (int j = 0; j < 3; ++j) {
+      V3<F> va = fv[j], vb = fv[(j + 1) % 3];
+      bool ain = va.z > eps, bin = vb.z > eps;
+      if (ain) {
+        bool found = false;
+        for (int k = 0; k < cnt; ++k)
+          if (out[k].x == va.x && out[k].y == va.y && out[k].z == va.z) found = true;
+        if (!found) out[cnt++] = va;
+      }
+      if (ain != bin) {
+        F t = (eps - va.z) / (vb.z - va.z);
+        out[cnt++] = lerp(va, vb, t);
+      }
+    }
+    if (cnt > 1)
+      for (int j = 0; j < cnt; ++j) update_bounds_from_edge(out[j], out[(j + 1) % cnt], mn, mx, c);
+  }
+}
+
+// slang/intersect.slang:76-89 (is_planar)
+template <class F>
+inline bool is_planar(const V3<F> v[4]) {
+  V3<F> n = normalize(cross(v[1] - v[0], v[2] - v[0]));
+  F d = dot(n, v[3] - v[0]);
+  return std::fabs(d) < F(1e-3f);
+}
+
+// slang/stable_power.slang:17-84 (power_of_circumsphere), always in double.
+inline double length3(V3<double> a) { return std::sqrt(dot(a, a)); }
+inline double power_of_circumsphere(V3<double> A, V3<double> B, V3<double> C, V3<double> D, V3<double> P,
+                                    V3<double>& center, int* branch) {
+  V3<double> a = B - A, b = C - A, c = D - A;
+  double aa = dot(a, a), bb = dot(b, b), cc = dot(c, c);
+  V3<double> cbc = cross(b, c), cca = cross(c, a), cab = cross(a, b);
+  double denominator = 2.0 * dot(a, cbc);
+  double radius;
+  if (std::fabs(denominator) < 1e-10) {
+    double m = std::fmax(length3(B - A),
+                         std::fmax(length3(C - A),
+                                   std::fmax(length3(D - A),
+                                             std::fmax(length3(C - B), std::fmax(length3(D - B), length3(D - C))))));
+    if (m < 1e-7) {
+      center = (A + B + C + D) * 0.25;
+      double dA = length3(A - center), dB = length3(B - center), dC = length3(C - center), dD = length3(D - center);
+      radius = std::fmin(dA, std::fmin(dB, std::fmin(dC, dD)));
+      V3<double> diff = center - P;
+      if (branch) *branch = 1;
+      return dot(diff, diff) - radius * radius;
+    }
+    if (branch) *branch = 2;
+    return -1e20;
+  }
+  V3<double> num = cbc * aa + cca * bb + cab * cc;
+  V3<double> rel = {num.x / denominator, num.y / denominator, num.z / denominator};
+  center = A + rel;
+  radius = length3(rel);
+  V3<double> diff = center - P;
+  if (branch) *branch = 0;
+  return dot(diff, diff) - radius * radius;
+}
+
+inline float clipf(float v, float lo, float hi) { return std::fmax(lo, std::fmin(hi, v)); }
+
+// slang/tile_shader.slang:18-47
+inline uint32_t float2sortable_key(float v) {
+  uint32_t bits;
+  std::memcpy(&bits, &v, 4);
+  if (bits & 0x80000000u) bits = ~bits;
+  else bits ^= 0x80000000u;
+  return bits;
+}
+
+template <class F>
+inline V3<F> load_v(const F* vertices, int64_t i) { return {vertices[3 * i], vertices[3 * i + 1], vertices[3 * i + 2]}; }
+
+// ---------------------------------------------------------------------------
+// Ray generation: slang/camera.slang:298-346 (get_ray), :200-207
+// ---------------------------------------------------------------------------
+template <class F>
+inline void get_ray(const Cam<F>& c, F px, F py, V3<F>& o, V3<F>& d) {
+  F fx = c.K[0][0], fy = c.K[1][1], cx = c.K[0][2], cy = c.K[1][2];
+  F x = (px - cx) / fx, y = (py - cy) / fy;
+  if (c.type == 0 || c.type == 1) undistort(x, y, c);
+  V3<F> dc;
+  if (c.type == 1) {
+    F theta = std::sqrt(x * x + y * y);
+    theta = std::fmin(F(3.14159265), theta);
+    F s = (theta < F(1e-6f)) ? F(1) : std::sin(theta) / theta;
+    dc = {x * s, y * s, std::cos(theta)};
+  } else {
+    dc = normalize(V3<F>{x, y, F(1)});
+  }
+  // V_rot = transpose of the top-left 3x3 of the world->camera matrix
+  V3<F> w = {c.W[0][0] * dc.x + c.W[1][0] * dc.y + c.W[2][0] * dc.z,
+             c.W[0][1] * dc.x + c.W[1][1] * dc.y + c.W[2][1] * dc.z,
+             c.W[0][2] * dc.x + c.W[1][2] * dc.y + c.W[2][2] * dc.z};
+  d = normalize(w);
+  o = c.pos + d * c.min_t;
+}
+
+// ---------------------------------------------------------------------------
+// Ray / tetrahedron: slang/intersect.slang:393-624 (ray_tetrahedron_intersect_fused)
+// Records which plane produced t_enter / t_exit so that the reverse pass can
+// route the gradient (what Slang's autodiff does through the branches).
+// ---------------------------------------------------------------------------
+template <class F>
+struct Planes {
+  V3<F> n[4];
+  F d[4];
+  int sgn[4];  // +1 / -1 applied to the raw cross product
+};
+template <class F>
+inline void make_planes(const V3<F> v[4], V3<F> orig, Planes<F>& p) {
+  // face i: (base, e1 end, e2 end, opposite)
+  static const int fa[4][4] = {{0, 1, 2, 3}, {0, 1, 3, 2}, {0, 2, 3, 1}, {1, 2, 3, 0}};
+  for (int i = 0; i < 4; ++i) {
+    V3<F> b = v[fa[i][0]];
+    V3<F> n = cross(v[fa[i][1]] - b, v[fa[i][2]] - b);
+    p.sgn[i] = 1;
+    if (dot(n, v[fa[i][3]] - b) > F(0)) {
+      n = -n;
+      p.sgn[i] = -1;
+    }
+    p.n[i] = n;
+    p.d[i] = -dot(n, b - orig);
+  }
+}
+template <class F>
+inline bool intersect(const Planes<F>& p, V3<F> dir, F& t_enter_raw, F& t_exit_raw, int& ie, int& ix) {
+  F te = F(-1e30f), tx = F(1e30f);
+  const F eps = F(1e-10f);
+  ie = -1;
+  ix = -1;
+  for (int i = 0; i < 4; ++i) {
+    F den = dot(p.n[i], dir);
+    if (std::fabs(den) < eps) {
+      if (p.d[i] > F(0)) return false;
+    } else {
+      F t = -p.d[i] / den;
+      if (den < F(0)) {
+        if (t > te) { te = t; ie = i; }
+      } else {
+        if (t < tx) { tx = t; ix = i; }
+      }
+    }
+  }
+  if (te > tx) return false;
+  if (tx <= F(0)) return false;
+  t_enter_raw = te;
+  t_exit_raw = tx;
+  return true;
+}
+
+// slang/interp_version.slang:21-40
+template <class F>
+inline F phi(F x) {
+  if (std::fabs(x) < F(1e-6f)) return F(1) - x / F(2);
+  return -std::expm1(-x) / x;
+}
+template <class F>
+inline F dphi(F x) {
+  if (std::fabs(x) < F(1e-6f)) return F(-0.5);
+  // d/dx [-expm1(-x)/x] with d expm1(v)/dv = exp(v) (safe-math.slang:161-172)
+  return std::exp(-x) / x + std::expm1(-x) / (x * x);
+}
+
+template <class F>
+struct Tet {
+  V3<F> v[4];
+  F density;
+  V3<F> base, grd;
+};
+template <class F>
+inline Tet<F> load_tet(int64_t g, const int32_t* indices, const F* vertices, const F* cell) {
+  // slang/interp_version.slang:100-153
+  Tet<F> t;
+  for (int k = 0; k < 4; ++k) t.v[k] = load_v(vertices, indices[4 * g + k]);
+  t.density = std::fmax(cell[7 * g], F(0));
+  t.base = {cell[7 * g + 1], cell[7 * g + 2], cell[7 * g + 3]};
+  t.grd = {cell[7 * g + 4], cell[7 * g + 5], cell[7 * g + 6]};
+  return t;
+}
+
+template <class F>
+struct Ctrl {
+  F r, g, b, a;  // a is the optical depth density*dt
+  F enter, exit, density;
+};
+
+// slang/interp_version.slang:42-98 (integrate_tetra_segment, evaluate_tetra_interp)
+template <class F>
+inline bool evaluate_tet(const Tet<F>& t, V3<F> o, V3<F> d, Ctrl<F>& c, Planes<F>* pl_out = nullptr, int* ie_out = nullptr,
+                         int* ix_out = nullptr, F* te_raw = nullptr, F* tx_raw = nullptr) {
+  Planes<F> pl;
+  make_planes(t.v, o, pl);
+  F te, tx;
+  int ie, ix;
+  if (!intersect(pl, d, te, tx, ie, ix)) return false;
+  F enter = std::fmax(te, F(0));
+  F exit = std::fmax(tx, enter);
+  F dt = std::fmax(exit - enter, F(0));
+  V3<F> ve = d * enter + o - t.v[0];
+  V3<F> vx = d * exit + o - t.v[0];
+  F oe = dot(t.grd, ve), ox = dot(t.grd, vx);
+  V3<F> ce = {oe + t.base.x, oe + t.base.y, oe + t.base.z};
+  V3<F> cx = {ox + t.base.x, ox + t.base.y, ox + t.base.z};
+  F ddt = dt * t.density;
+  F alpha = safe_exp(-ddt);
+  F ph = phi(ddt);
+  F w0 = ph - alpha, w1 = F(1) - ph;
+  c.r = w0 * cx.x + w1 * ce.x;
+  c.g = w0 * cx.y + w1 * ce.y;
+  c.b = w0 * cx.z + w1 * ce.z;
+  c.a = t.density * dt;
+  c.enter = enter;
+  c.exit = exit;
+  c.density = t.density;
+  if (pl_out) *pl_out = pl;
+  if (ie_out) *ie_out = ie;
+  if (ix_out) *ix_out = ix;
+  if (te_raw) *te_raw = te;
+  if (tx_raw) *tx_raw = tx;
+  return true;
+}
+
+// Pixel state: slang/alphablend_shader_interp.slang:26-32,83-126,153-183
+template <class F>
+struct State {
+  F r, g, b, logT;
+  F x, y, z, w, v;
+};
+template <class F>
+inline void update_state(State<F>& s, const Ctrl<F>& c) {
+  F T = safe_exp(s.logT);
+  s.r = s.r + c.r * T;
+  s.g = s.g + c.g * T;
+  s.b = s.b + c.b * T;
+  s.logT = s.logT - c.a;
+  F m0 = c.density;
+  F m1 = c.density * (c.exit + c.enter) / F(2);
+  F nx = s.x + F(2) * m1 * s.z;
+  F ny = s.y + F(2) * m0 * s.w;
+  F nz = s.z + m0;
+  F nw = s.w + m1;
+  F dtt = std::fmax(c.exit - c.enter, F(0));
+  F nv = s.v + c.density * c.density * dtt / F(3);
+  s.x = nx; s.y = ny; s.z = nz; s.w = nw; s.v = nv;
+}
+// slang/alphablend_shader_interp.slang:128-149,163-169,185-192
+template <class F>
+inline void undo_state(State<F>& s, const Ctrl<F>& c) {
+  F logTp = s.logT + c.a;
+  F Tp = safe_exp(logTp);
+  s.r = s.r - c.r * Tp;
+  s.g = s.g - c.g * Tp;
+  s.b = s.b - c.b * Tp;
+  s.logT = logTp;
+  F m0 = c.density;
+  F m1 = c.density * (c.exit + c.enter) / F(2);
+  F oz = s.z - m0;
+  F ow = s.w - m1;
+  F ox = s.x - F(2) * m1 * oz;
+  F oy = s.y - F(2) * m0 * ow;
+  F dtt = std::fmax(c.exit - c.enter, F(0));
+  F ov = s.v - c.density * c.density * dtt / F(3);
+  s.x = ox; s.y = oy; s.z = oz; s.w = ow; s.v = ov;
+}
+
+// ---------------------------------------------------------------------------
+// Forward integration of one pixel: slang/alphablend_shader_interp.slang:194-271
+// ---------------------------------------------------------------------------
+template <class F>
+inline int forward_pixel(const Cam<F>& cam, F px, F py, const int32_t* list, int64_t n, const int32_t* indices,
+                         const F* vertices, const F* cell, State<F>& s) {
+  V3<F> o, d;
+  get_ray(cam, px, py, o, d);
+  s = State<F>{0, 0, 0, 0, 0, 0, 0, 0, 0};
+  int contrib = 0;
+  for (int64_t j = 0; j < n; ++j) {
+    ++contrib;
+    Tet<F> t = load_tet<F>(list[j], indices, vertices, cell);
+    Ctrl<F> c;
+    if (evaluate_tet(t, o, d, c) && c.a > F(0)) {
+      update_state(s, c);
+      if (s.logT < F(-5.5)) break;
+    }
+  }
+  return contrib;
+}
+
+template <class F>
+inline void atomic_add(F* p, F v) {
+#pragma omp atomic
+  *p += v;
+}
+
+// ---------------------------------------------------------------------------
+// Backward of one pixel: slang/alphablend_shader_interp.slang:273-369 plus the
+// derivative code the Slang compiler generates for update_alpha_out,
+// evaluate_tetra_interp and load_tet_alphablend_interp, written by hand.
+// ---------------------------------------------------------------------------
+template <class F>
+inline void backward_pixel(const Cam<F>& cam, F px, F py, const int32_t* list, int64_t n, int n_contrib,
+                           const int32_t* indices, const F* vertices, const F* cell, State<F> s /* final */,
+                           State<F> ds /* grad of final */, F* vgrad, F* cgrad) {
+  V3<F> o, d;
+  get_ray(cam, px, py, o, d);
+  for (int64_t j = n - 1; j >= 0; --j) {
+    if (j >= n_contrib) continue;
+    int64_t g = list[j];
+    Tet<F> t = load_tet<F>(g, indices, vertices, cell);
+    Ctrl<F> c;
+    Planes<F> pl;
+    int ie, ix;
+    F te, tx;
+    if (!(evaluate_tet(t, o, d, c, &pl, &ie, &ix, &te, &tx) && c.a > F(0))) continue;
+    undo_state(s, c);  // s is now the state before this tet
+    // ---- reverse of update_alpha_out -------------------------------------
+    F T = safe_exp(s.logT);
+    F gcr = ds.r * T, gcg = ds.g * T, gcb = ds.b * T;  // grad wrt ctrl.rgb
+    F gT = ds.r * c.r + ds.g * c.g + ds.b * c.b;
+    F g_a = -ds.logT;  // grad wrt ctrl.a (optical depth)
+    F dlogT_prev = ds.logT + gT * T;
+    F m0 = c.density;
+    F m1 = c.density * (c.exit + c.enter) / F(2);
+    F g_m1 = F(2) * s.z * ds.x + ds.w;
+    F g_m0 = F(2) * s.w * ds.y + ds.z;
+    F dz_prev = ds.z + F(2) * m1 * ds.x;
+    F dw_prev = ds.w + F(2) * m0 * ds.y;
+    F dtt = std::fmax(c.exit - c.enter, F(0));
+    F g_cdens = g_m0 + g_m1 * (c.exit + c.enter) / F(2) + ds.v * F(2) * c.density * dtt / F(3);
+    F g_cexit = g_m1 * c.density / F(2);
+    F g_center = g_m1 * c.density / F(2);
+    if (c.exit - c.enter > F(0)) {
+      F k = ds.v * c.density * c.density / F(3);
+      g_cexit += k;
+      g_center -= k;
+    }
+    ds.logT = dlogT_prev;
+    ds.z = dz_prev;
+    ds.w = dw_prev;
+    // ---- reverse of integrate_tetra_segment -------------------------------
+    F enter = c.enter, exit = c.exit;
+    F dt = std::fmax(exit - enter, F(0));
+    V3<F> ve = d * enter + o - t.v[0];
+    V3<F> vx = d * exit + o - t.v[0];
+    F oe = dot(t.grd, ve), ox = dot(t.grd, vx);
+    V3<F> ce = {oe + t.base.x, oe + t.base.y, oe + t.base.z};
+    V3<F> cx = {ox + t.base.x, ox + t.base.y, ox + t.base.z};
+    F ddt = dt * t.density;
+    F alpha = safe_exp(-ddt);
+    F ph = phi(ddt);
+    F w0 = ph - alpha, w1 = F(1) - ph;
+    F g_w0 = gcr * cx.x + gcg * cx.y + gcb * cx.z;
+    F g_w1 = gcr * ce.x + gcg * ce.y + gcb * ce.z;
+    F G = gcr + gcg + gcb;
+    V3<F> g_base = {(w0 + w1) * gcr, (w0 + w1) * gcg, (w0 + w1) * gcb};
+    F g_ox = w0 * G, g_oe = w1 * G;
+    V3<F> g_grd = vx * g_ox + ve * g_oe;
+    V3<F> g_vx = t.grd * g_ox, g_ve = t.grd * g_oe;
+    V3<F> g_v0 = -(g_vx + g_ve);
+    F g_exit = dot(g_vx, d) + g_cexit;
+    F g_enter = dot(g_ve, d) + g_center;
+    F g_ph = g_w0 - g_w1;
+    F g_alpha = -g_w0;
+    F g_ddt = g_ph * dphi(ddt) - g_alpha * alpha;
+    F g_dens = g_ddt * dt + g_a * dt + g_cdens;
+    F g_dt = g_ddt * t.density + g_a * t.density;
+    if (exit - enter > F(0)) {
+      g_exit += g_dt;
+      g_enter -= g_dt;
+    }
+    // exit = max(t_exit_raw, enter); enter = max(t_enter_raw, 0)
+    F g_tx = F(0), g_te = F(0);
+    if (tx > enter) g_tx = g_exit;
+    else g_enter += g_exit;
+    if (te > F(0)) g_te = g_enter;
+    // ---- reverse of the plane intersection --------------------------------
+    V3<F> gv[4] = {g_v0, {0, 0, 0}, {0, 0, 0}, {0, 0, 0}};
+    static const int fa[4][4] = {{0, 1, 2, 3}, {0, 1, 3, 2}, {0, 2, 3, 1}, {1, 2, 3, 0}};
+    for (int pass = 0; pass < 2; ++pass) {
+      int i = pass == 0 ? ie : ix;
+      F gt = pass == 0 ? g_te : g_tx;
+      if (i < 0 || gt == F(0)) continue;
+      F den = dot(pl.n[i], d);
+      // t = -dist/den ; dist = -n.(b - o) ; den = n.d
+      F g_dist = -gt / den;
+      F g_den = gt * pl.d[i] / (den * den);
+      V3<F> b = t.v[fa[i][0]];
+      V3<F> g_n = (b - o) * (-g_dist) + d * g_den;
+      V3<F> g_b = pl.n[i] * (-g_dist);
+      // n = sgn * cross(e1, e2)
+      V3<F> e1 = t.v[fa[i][1]] - b, e2 = t.v[fa[i][2]] - b;
+      V3<F> g_raw = g_n * F(pl.sgn[i]);
+      V3<F> g_e1 = cross(e2, g_raw);
+      V3<F> g_e2 = cross(g_raw, e1);
+      gv[fa[i][1]] = gv[fa[i][1]] + g_e1;
+      gv[fa[i][2]] = gv[fa[i][2]] + g_e2;
+      gv[fa[i][0]] = gv[fa[i][0]] + g_b - g_e1 - g_e2;
+    }
+    // ---- reverse of load_tet_alphablend_interp: scatter --------------------
+    for (int k = 0; k < 4; ++k) {
+      int64_t vi = indices[4 * g + k];
+      atomic_add(&vgrad[3 * vi + 0], gv[k].x);
+      atomic_add(&vgrad[3 * vi + 1], gv[k].y);
+      atomic_add(&vgrad[3 * vi + 2], gv[k].z);
+    }
+    if (cell[7 * g] > F(0)) atomic_add(&cgrad[7 * g + 0], g_dens);
+    atomic_add(&cgrad[7 * g + 1], g_base.x);
+    atomic_add(&cgrad[7 * g + 2], g_base.y);
+    atomic_add(&cgrad[7 * g + 3], g_base.z);
+    atomic_add(&cgrad[7 * g + 4], g_grd.x);
+    atomic_add(&cgrad[7 * g + 5], g_grd.y);
+    atomic_add(&cgrad[7 * g + 6], g_grd.z);
+  }
+}
+
+template <class F>
+int forward_impl(const int32_t* sorted_idx, const int32_t* tile_ranges, const int32_t* indices, const F* vertices,
+                 const F* cell, const OrCamera* ocam, const F* jitter, F* out_img, F* dist_img, int32_t* n_contrib,
+                 int row0, int row1, int nthreads) {
+  Cam<F> cam = load_cam<F>(ocam);
+  const int H = cam.H, W = cam.Wd;
+  if (row0 < 0) row0 = 0;
+  if (row1 > H || row1 <= 0) row1 = H;
+#ifdef _OPENMP
+  if (nthreads > 0) omp_set_num_threads(nthreads);
+#endif
+#pragma omp parallel for schedule(dynamic, 16)
+  for (int64_t p = (int64_t)row0 * W; p < (int64_t)row1 * W; ++p) {
+    int y = int(p / W), x = int(p % W);
+    int tile = (y / cam.tile_h) * cam.grid_w + (x / cam.tile_w);
+    int64_t s0 = tile_ranges[2 * tile], s1 = tile_ranges[2 * tile + 1];
+    State<F> s;
+    F px = F(x) + jitter[2 * p], py = F(y) + jitter[2 * p + 1];
+    int nc = forward_pixel<F>(cam, px, py, sorted_idx + s0, s1 - s0, indices, vertices, cell, s);
+    n_contrib[p] = nc;
+    out_img[4 * p + 0] = s.r; out_img[4 * p + 1] = s.g; out_img[4 * p + 2] = s.b; out_img[4 * p + 3] = s.logT;
+    dist_img[5 * p + 0] = s.x; dist_img[5 * p + 1] = s.y; dist_img[5 * p + 2] = s.z; dist_img[5 * p + 3] = s.w;
+    dist_img[5 * p + 4] = s.v;
+  }
+  return 0;
+}
+
+template <class F>
+int backward_impl(const int32_t* sorted_idx, const int32_t* tile_ranges, const int32_t* indices, const F* vertices,
+                  const F* cell, const OrCamera* ocam, const F* jitter, const F* out_img, const F* dist_img,
+                  const int32_t* n_contrib, const F* g_img, const F* g_dist, F* vgrad, F* cgrad, int row0, int row1,
+                  int nthreads) {
+  Cam<F> cam = load_cam<F>(ocam);
+  const int H = cam.H, W = cam.Wd;
+  if (row0 < 0) row0 = 0;
+  if (row1 > H || row1 <= 0) row1 = H;
+#ifdef _OPENMP
+  if (nthreads > 0) omp_set_num_threads(nthreads);
+#endif
+#pragma omp parallel for schedule(dynamic, 16)
+  for (int64_t p = (int64_t)row0 * W; p < (int64_t)row1 * W; ++p) {
+    int y = int(p / W), x = int(p % W);
+    int tile = (y / cam.tile_h) * cam.grid_w + (x / cam.tile_w);
+    int64_t s0 = tile_ranges[2 * tile], s1 = tile_ranges[2 * tile + 1];
+    State<F> s = {out_img[4 * p], out_img[4 * p + 1], out_img[4 * p + 2], out_img[4 * p + 3], dist_img[5 * p],
+                  dist_img[5 * p + 1], dist_img[5 * p + 2], dist_img[5 * p + 3], dist_img[5 * p + 4]};
+    State<F> ds = {g_img[4 * p], g_img[4 * p + 1], g_img[4 * p + 2], g_img[4 * p + 3], g_dist[5 * p],
+                   g_dist[5 * p + 1], g_dist[5 * p + 2], g_dist[5 * p + 3], g_dist[5 * p + 4]};
+    F px = F(x) + jitter[2 * p], py = F(y) + jitter[2 * p + 1];
+    backward_pixel<F>(cam, px, py, sorted_idx + s0, s1 - s0, n_contrib[p], indices, vertices, cell, s, ds, vgrad,
+                      cgrad);
+  }
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+// Stage 1: per-tet projection, culling and tile counting.
+// slang/vertex_shader.slang:20-89 and the host wrapper tile_shader_slang.py:77-105.
+// Outputs of culled tets are zero.  Returns 1 if a NaN vertex was seen
+// (tile_shader_slang.py:78 asserts on it), else 0.
+int or_project(const int32_t* indices, int64_t T, const float* vertices, int64_t V, const OrCamera* ocam,
+               int32_t* tiles_touched, int32_t* rect, float* vs_tetra, float* circumcenter, int nthreads) {
+  Cam<float> cam = load_cam<float>(ocam);
+  int nan_seen = 0;
+  for (int64_t i = 0; i < 3 * V; ++i)
+    if (vertices[i] != vertices[i]) nan_seen = 1;
+#ifdef _OPENMP
+  if (nthreads > 0) omp_set_num_threads(nthreads);
+#endif
+#pragma omp parallel for schedule(static, 1024)
+  for (int64_t g = 0; g < T; ++g) {
+    tiles_touched[g] = 0;
+    for (int k = 0; k < 4; ++k) rect[4 * g + k] = 0;
+    for (int k = 0; k < 3; ++k) vs_tetra[3 * g + k] = 0.f, circumcenter[3 * g + k] = 0.f;
+    V3<float> v[4];
+    for (int k = 0; k < 4; ++k) v[k] = load_v(vertices, indices[4 * g + k]);
+    if (is_planar(v)) continue;
+    V3<float> cs[4];
+    for (int k = 0; k < 4; ++k) cs[k] = point2camspace(v[k], cam);
+    V3<float> mn, mx;
+    find_extent(cs, mn, mx, cam);
+    if (mx.z <= 0.0f) continue;
+    V3<double> A = {v[0].x, v[0].y, v[0].z}, B = {v[1].x, v[1].y, v[1].z}, C = {v[2].x, v[2].y, v[2].z},
+               D = {v[3].x, v[3].y, v[3].z}, P = {cam.pos.x, cam.pos.y, cam.pos.z};
+    V3<double> cc = {0, 0, 0};
+    float sort_depth = float(power_of_circumsphere(A, B, C, D, P, cc, nullptr));
+    if (sort_depth < -1e19f) continue;
+    int min_x = int(std::floor(clipf(mn.x / float(cam.tile_w), 0.f, float(cam.grid_w))));
+    int min_y = int(std::floor(clipf(mn.y / float(cam.tile_h), 0.f, float(cam.grid_h))));
+    int max_x = int(std::ceil(clipf(mx.x / float(cam.tile_w), 0.f, float(cam.grid_w))));
+    int max_y = int(std::ceil(clipf(mx.y / float(cam.tile_h), 0.f, float(cam.grid_h))));
+    int n_tiles = (max_x - min_x) * (max_y - min_y);
+    if (n_tiles == 0) continue;
+    tiles_touched[g] = n_tiles;
+    rect[4 * g + 0] = min_x; rect[4 * g + 1] = min_y; rect[4 * g + 2] = max_x; rect[4 * g + 3] = max_y;
+    vs_tetra[3 * g + 2] = std::fmin(std::fmax(sort_depth, -1e20f), 1e20f);
+    circumcenter[3 * g + 0] = float(cc.x);
+    circumcenter[3 * g + 1] = float(cc.y);
+    circumcenter[3 * g + 2] = float(cc.z);
+  }
+  return nan_seen;
+}
+
+// Number of (tile, tet) keys = last element of the int32 cumsum
+// (tile_shader_slang.py:36-38); returned as int64 so that overflow is visible.
+int64_t or_count_keys(const int32_t* tiles_touched, int64_t T) {
+  int64_t n = 0;
+  for (int64_t g = 0; g < T; ++g) n += tiles_touched[g];
+  return n;
+}
+
+// Stages 2-4: key emission (slang/tile_shader.slang:49-97), stable sort on the
+// low 32+msb key bits (sort_by_keys/sort_by_keys.cu:36-48; msb from
+// tile_shader_slang.py:57) and tile ranges (slang/tile_shader.slang:99-125).
+// keys_sorted may be null.
+int or_build_lists(const int32_t* tiles_touched, const int32_t* rect, const float* vs_tetra, int64_t T, int grid_h,
+                   int grid_w, int64_t N, int32_t* sorted_idx, int32_t* tile_ranges, int64_t* keys_sorted) {
+  std::vector<uint64_t> keys((size_t)N);
+  std::vector<int32_t> vals((size_t)N);
+  int64_t off = 0;
+  for (int64_t g = 0; g < T; ++g) {
+    if (tiles_touched[g] == 0) continue;
+    uint32_t fk = float2sortable_key(vs_tetra[3 * g + 2]);
+    for (int y = rect[4 * g + 1]; y < rect[4 * g + 3]; ++y)
+      for (int x = rect[4 * g + 0]; x < rect[4 * g + 2]; ++x) {
+        if (off >= N) return 1;
+        uint64_t key = (uint64_t)(uint32_t)(y * grid_w + x);
+        keys[off] = (key << 32) | fk;
+        vals[off] = (int32_t)g;
+        ++off;
+      }
+  }
+  if (off != N) return 1;
+  int msb = 0;
+  for (int64_t t = (int64_t)grid_w * grid_h; t > 0; t >>= 1) ++msb;  // int.bit_length()
+  int bits = 32 + msb;
+  uint64_t mask = bits >= 64 ? ~0ull : ((1ull << bits) - 1ull);
+  std::vector<int64_t> perm((size_t)N);
+  for (int64_t i = 0; i < N; ++i) perm[i] = i;
+  std::stable_sort(perm.begin(), perm.end(),
+                   [&](int64_t a, int64_t b) { return (keys[a] & mask) < (keys[b] & mask); });
+  int64_t G = (int64_t)grid_h * grid_w;
+  for (int64_t i = 0; i < 2 * G; ++i) tile_ranges[i] = 0;
+  for (int64_t i = 0; i < N; ++i) {
+    uint64_t k = keys[perm[i]];
+    sorted_idx[i] = vals[perm[i]];
+    if (keys_sorted) keys_sorted[i] = (int64_t)k;
+    uint32_t cur = (uint32_t)(k >> 32);
+    if (i == 0) tile_ranges[2 * cur] = 0;
+    else {
+      uint32_t prev = (uint32_t)(keys[perm[i - 1]] >> 32);
+      if (cur != prev) {
+        tile_ranges[2 * prev + 1] = (int32_t)i;
+        tile_ranges[2 * cur] = (int32_t)i;
+      }
+    }
+    if (i == N - 1) tile_ranges[2 * cur + 1] = (int32_t)N;
+  }
+  return 0;
+}
+
+// Stage 5 (fp32): slang/alphablend_shader_interp.slang:371-431 over pixel rows [row0,row1).
+int or_forward(const int32_t* sorted_idx, const int32_t* tile_ranges, const int32_t* indices, const float* vertices,
+               const float* cell, const OrCamera* cam, const float* jitter, float* out_img, float* dist_img,
+               int32_t* n_contrib, int row0, int row1, int nthreads) {
+  return forward_impl<float>(sorted_idx, tile_ranges, indices, vertices, cell, cam, jitter, out_img, dist_img,
+                             n_contrib, row0, row1, nthreads);
+}
+int or_forward_f64(const int32_t* sorted_idx, const int32_t* tile_ranges, const int32_t* indices,
+                   const double* vertices, const double* cell, const OrCamera* cam, const double* jitter,
+                   double* out_img, double* dist_img, int32_t* n_contrib, int row0, int row1, int nthreads) {
+  return forward_impl<double>(sorted_idx, tile_ranges, indices, vertices, cell, cam, jitter, out_img, dist_img,
+                              n_contrib, row0, row1, nthreads);
+}
+
+// Stage 6 (fp32): slang/alphablend_shader_interp.slang:273-369; gradients are ADDED
+// into vgrad[V,3] and cgrad[T,7] (the host zero-fills them,
+// alphablend_tiled_slang_interp.py:79-80).
+int or_backward(const int32_t* sorted_idx, const int32_t* tile_ranges, const int32_t* indices, const float* vertices,
+                const float* cell, const OrCamera* cam, const float* jitter, const float* out_img,
+                const float* dist_img, const int32_t* n_contrib, const float* g_img, const float* g_dist,
+                float* vgrad, float* cgrad, int row0, int row1, int nthreads) {
+  return backward_impl<float>(sorted_idx, tile_ranges, indices, vertices, cell, cam, jitter, out_img, dist_img,
+                              n_contrib, g_img, g_dist, vgrad, cgrad, row0, row1, nthreads);
+}
+int or_backward_f64(const int32_t* sorted_idx, const int32_t* tile_ranges, const int32_t* indices,
+                    const double* vertices, const double* cell, const OrCamera* cam, const double* jitter,
+                    const double* out_img, const double* dist_img, const int32_t* n_contrib, const double* g_img,
+                    const double* g_dist, double* vgrad, double* cgrad, int row0, int row1, int nthreads) {
+  return backward_impl<double>(sorted_idx, tile_ranges, indices, vertices, cell, cam, jitter, out_img, dist_img,
+                               n_contrib, g_img, g_dist, vgrad, cgrad, row0, row1, nthreads);
+}
+
+// Reverse of stage 1 with respect to the vertices: gradients of
+// vs_tetra[:,2] (clamped circumsphere power) and circumcenter, for tets that
+// were not culled (tiles_touched > 0).  Restates what Slang's autodiff derives
+// from slang/vertex_shader.slang:52-87 + slang/stable_power.slang:17-84; host
+// side tile_shader_slang.py:128-150.  Gradients are ADDED into vgrad[V,3].
+int or_vertex_backward(const int32_t* indices, int64_t T, const float* vertices, const OrCamera* ocam,
+                       const int32_t* tiles_touched, const float* g_vs, const float* g_cc, float* vgrad) {
+  V3<double> P = {ocam->cam_pos[0], ocam->cam_pos[1], ocam->cam_pos[2]};
+  for (int64_t g = 0; g < T; ++g) {
+    if (tiles_touched[g] == 0) continue;
+    V3<double> p[4];
+    for (int k = 0; k < 4; ++k) {
+      V3<float> v = load_v(vertices, indices[4 * g + k]);
+      p[k] = {v.x, v.y, v.z};
+    }
+    V3<double> center;
+    int branch;
+    double power = power_of_circumsphere(p[0], p[1], p[2], p[3], P, center, &branch);
+    float sd = float(power);
+    double g_power = (sd > -1e20f && sd < 1e20f) ? double(g_vs[3 * g + 2]) : 0.0;
+    V3<double> g_center = {g_cc[3 * g], g_cc[3 * g + 1], g_cc[3 * g + 2]};
+    V3<double> gp[4] = {{0, 0, 0}, {0, 0, 0}, {0, 0, 0}, {0, 0, 0}};
+    if (branch == 0) {
+      V3<double> a = p[1] - p[0], b = p[2] - p[0], c = p[3] - p[0];
+      double aa = dot(a, a), bb = dot(b, b), cc = dot(c, c);
+      V3<double> X = cross(b, c), Y = cross(c, a), Z = cross(a, b);
+      double den = 2.0 * dot(a, X);
+      V3<double> num = X * aa + Y * bb + Z * cc;
+      V3<double> rel = {num.x / den, num.y / den, num.z / den};
+      V3<double> diff = center - P;
+      V3<double> g_ct = g_center + diff * (2.0 * g_power);
+      V3<double> g_rel = g_ct - rel * (2.0 * g_power);
+      V3<double> g_A = g_ct;
+      V3<double> g_num = {g_rel.x / den, g_rel.y / den, g_rel.z / den};
+      double g_den = -dot(g_rel, rel) / den;
+      double g_aa = dot(g_num, X), g_bb = dot(g_num, Y), g_cc2 = dot(g_num, Z);
+      V3<double> g_X = g_num * aa + a * (2.0 * g_den);
+      V3<double> g_Y = g_num * bb, g_Z = g_num * cc;
+      V3<double> g_a = X * (2.0 * g_den) + a * (2.0 * g_aa);
+      V3<double> g_b = b * (2.0 * g_bb);
+      V3<double> g_c = c * (2.0 * g_cc2);
+      g_b = g_b + cross(c, g_X);  g_c = g_c + cross(g_X, b);   // X = b x c
+      g_c = g_c + cross(a, g_Y);  g_a = g_a + cross(g_Y, c);   // Y = c x a
+      g_a = g_a + cross(b, g_Z);  g_b = g_b + cross(g_Z, a);   // Z = a x b
+      gp[1] = g_a; gp[2] = g_b; gp[3] = g_c;
+      gp[0] = g_A - g_a - g_b - g_c;
+    } else if (branch == 1) {
+      V3<double> diff = center - P;
+      V3<double> g_ct = g_center + diff * (2.0 * g_power);
+      double dist[4];
+      int arg = 0;
+      for (int k = 0; k < 4; ++k) {
+        dist[k] = length3(p[k] - center);
+        if (dist[k] < dist[arg]) arg = k;
+      }
+      // power -= radius^2 with radius = |p[arg]-center|
+      V3<double> g_rv = (p[arg] - center) * (-2.0 * g_power);
+      gp[arg] = gp[arg] + g_rv;
+      g_ct = g_ct - g_rv;
+      for (int k = 0; k < 4; ++k) gp[k] = gp[k] + g_ct * 0.25;
+    }
+    for (int k = 0; k < 4; ++k) {
+      int64_t vi = indices[4 * g + k];
+      vgrad[3 * vi + 0] += float(gp[k].x);
+      vgrad[3 * vi + 1] += float(gp[k].y);
+      vgrad[3 * vi + 2] += float(gp[k].z);
+    }
+  }
+  return 0;
+}
+
+// Sort depth and circumcenter of one tet in double, for finite-difference
+// checks of or_vertex_backward.
+void or_power_f64(const double* v4x3, const double* P, double* power, double* center) {
+  V3<double> p[4];
+  for (int k = 0; k < 4; ++k) p[k] = {v4x3[3 * k], v4x3[3 * k + 1], v4x3[3 * k + 2]};
+  V3<double> c = {0, 0, 0};
+  *power = power_of_circumsphere(p[0], p[1], p[2], p[3], {P[0], P[1], P[2]}, c, nullptr);
+  center[0] = c.x; center[1] = c.y; center[2] = c.z;
+}
+
+// Known-answer hook: slang/interp_version.slang:31-40 (compute_integral) on scalars.
+float or_compute_integral(float c0, float c1, float ddt) {
+  float alpha = safe_exp(-ddt);
+  float ph = phi(ddt);
+  return (ph - alpha) * c0 + (1.0f - ph) * c1;
+}
+
+int or_num_threads() {
+#ifdef _OPENMP
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}
+
+}  // extern "C"

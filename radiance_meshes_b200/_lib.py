@@ -1,0 +1,66 @@
+"""ctypes binding of librm_b200.so (the C ABI declared in include/rm_b200.h).
+
+There is no CPU fallback: if the library is missing, loading raises.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "librm_b200.so")
+
+RM_RECORD_FLOATS = 24
+RM_STATUS_NAN_VERTEX = 1
+RM_STATUS_KEY_OVERFLOW = 2
+
+# every symbol include/rm_b200.h declares
+SYMBOLS = ["rm_strerror", "rm_version", "rm_bin_workspace_bytes", "rm_project_and_bin", "rm_build_tile_lists",
+           "rm_pack_records", "rm_forward", "rm_backward", "rm_vertex_backward"]
+
+
+class RmCamera(C.Structure):
+    _fields_ = [("world_view_transform", C.c_void_p), ("K", C.c_void_p), ("cam_pos", C.c_void_p),
+                ("distortion_params", C.c_void_p), ("image_height", C.c_int32), ("image_width", C.c_int32),
+                ("camera_type", C.c_int32), ("fovy", C.c_float), ("fovx", C.c_float), ("min_t", C.c_float),
+                ("tile_height", C.c_int32), ("tile_width", C.c_int32), ("grid_height", C.c_int32),
+                ("grid_width", C.c_int32), ("tile_row_begin", C.c_int32), ("tile_row_end", C.c_int32)]
+
+
+class RmBinInfo(C.Structure):
+    _fields_ = [("n_keys", C.c_int64), ("n_visible", C.c_int32), ("status", C.c_uint32)]
+
+
+_lib = None
+
+
+def load():
+    """Load the CUDA library, building nothing: a missing library is an error."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m radiance_meshes_b200.csrc.build` "
+            "(there is no CPU fallback for the rasterizer)")
+    lib = C.CDLL(LIB_PATH)
+    vp, i64, sz = C.c_void_p, C.c_int64, C.c_size_t
+    cam = C.POINTER(RmCamera)
+    lib.rm_strerror.restype = C.c_char_p
+    lib.rm_strerror.argtypes = [C.c_int]
+    lib.rm_version.restype = C.c_int
+    lib.rm_bin_workspace_bytes.restype = sz
+    lib.rm_bin_workspace_bytes.argtypes = [i64, i64]
+    lib.rm_project_and_bin.argtypes = [vp, i64, vp, i64, cam, vp, vp, vp, vp, vp, vp, vp, sz, vp]
+    lib.rm_build_tile_lists.argtypes = [vp, vp, i64, cam, i64, vp, vp, vp, vp]
+    lib.rm_pack_records.argtypes = [vp, vp, vp, i64, cam, vp, vp, vp]
+    lib.rm_forward.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, vp]
+    lib.rm_backward.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, vp, vp, vp, vp]
+    lib.rm_vertex_backward.argtypes = [vp, vp, i64, i64, cam, vp, vp, vp, vp, vp]
+    for name in SYMBOLS:
+        getattr(lib, name)
+    _lib = lib
+    return lib
+
+
+def check(rc):
+    if rc != 0:
+        raise RuntimeError(f"rm_b200: {load().rm_strerror(rc).decode()} (code {rc})")

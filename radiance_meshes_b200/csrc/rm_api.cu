@@ -1,0 +1,206 @@
+// extern "C" entry points of librm_b200.so: argument checks, device binding and
+// the launch sequence of each stage.  See include/rm_b200.h for the contract.
+
+#include <stdio.h>
+#include <string.h>
+
+#include "rm_common.cuh"
+
+// launchers defined in the kernel translation units
+int rm_launch_project(const int32_t*, int64_t, const float*, int64_t, const RmCamera*, int32_t*, int32_t*, float*,
+                      float*, uint32_t*, uint32_t*, int32_t*, RmBinInfo*, cudaStream_t);
+int rm_launch_vertex_backward(const int32_t*, const float*, int64_t, const RmCamera*, const int32_t*, const float*,
+                              const float*, float*, cudaStream_t);
+size_t rm_bin_layout_bytes(int64_t, int64_t);
+int rm_launch_bin_prepare(int64_t, const RmCamera*, void*, size_t, uint32_t**, uint32_t**, int32_t**, RmBinInfo*,
+                          cudaStream_t);
+int rm_launch_bin_finish(int64_t, const RmCamera*, const int32_t*, int32_t*, RmBinInfo*, void*, cudaStream_t);
+int rm_launch_build_lists(const int32_t*, const int32_t*, int64_t, const RmCamera*, int64_t, void*, uint32_t*,
+                          int32_t*, cudaStream_t);
+int rm_launch_pack(const int32_t*, const float*, const float*, int64_t, const RmCamera*, const int32_t*, float*,
+                   cudaStream_t);
+int rm_launch_forward(const int32_t*, const int32_t*, const float*, const RmCamera*, const float*, float*, float*,
+                      int32_t*, cudaStream_t);
+int rm_launch_backward(const int32_t*, const int32_t*, const float*, const RmCamera*, const float*, const float*,
+                       const float*, const int32_t*, const float*, const float*, const int32_t*, const float*,
+                       const float*, int64_t, int64_t, float*, float*, float*, cudaStream_t);
+
+static thread_local char g_last_error[256] = "";
+
+void rm_set_last_cuda_error(cudaError_t e, const char* file, int line) {
+  snprintf(g_last_error, sizeof(g_last_error), "CUDA error %d (%s) at %s:%d", (int)e, cudaGetErrorString(e), file,
+           line);
+}
+
+// Make the device that owns `device_ptr` current on this thread (the forward
+// pass runs on the caller's main thread, the backward pass on an autograd
+// worker thread).
+int rm_bind_device(const void* device_ptr) {
+  cudaPointerAttributes a;
+  cudaError_t e = cudaPointerGetAttributes(&a, device_ptr);
+  if (e != cudaSuccess) {
+    rm_set_last_cuda_error(e, __FILE__, __LINE__);
+    return RM_ERR_CUDA;
+  }
+  if (a.type != cudaMemoryTypeDevice && a.type != cudaMemoryTypeManaged) {
+    snprintf(g_last_error, sizeof(g_last_error), "pointer %p is not device memory", device_ptr);
+    return RM_ERR_INVALID_ARG;
+  }
+  int cur = -1;
+  RM_CUDA_CHECK(cudaGetDevice(&cur));
+  if (cur != a.device) RM_CUDA_CHECK(cudaSetDevice(a.device));
+  return RM_OK;
+}
+
+static int check_cam(const RmCamera* c) {
+  if (!c || !c->world_view_transform || !c->K || !c->cam_pos || !c->distortion_params) return RM_ERR_INVALID_ARG;
+  if (c->image_height <= 0 || c->image_width <= 0 || c->tile_height <= 0 || c->tile_width <= 0)
+    return RM_ERR_INVALID_ARG;
+  if (c->grid_height != (c->image_height + c->tile_height - 1) / c->tile_height ||
+      c->grid_width != (c->image_width + c->tile_width - 1) / c->tile_width)
+    return RM_ERR_INVALID_ARG;
+  if (c->tile_row_begin < 0 || c->tile_row_end > c->grid_height || c->tile_row_begin > c->tile_row_end)
+    return RM_ERR_INVALID_ARG;
+  if ((int64_t)c->grid_height * c->grid_width > 0x7fffffffll) return RM_ERR_INVALID_ARG;
+  return RM_OK;
+}
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+extern "C" {
+
+const char* rm_strerror(int code) {
+  switch (code) {
+    case RM_OK: return "ok";
+    case RM_ERR_INVALID_ARG: return g_last_error[0] ? g_last_error : "invalid argument";
+    case RM_ERR_CUDA: return g_last_error[0] ? g_last_error : "CUDA error";
+    case RM_ERR_TOO_MANY_KEYS: return "more than 2^31-1 (tile, tet) pairs";
+    case RM_ERR_WORKSPACE: return "workspace too small or misaligned";
+    default: return "unknown error";
+  }
+}
+
+int rm_version(void) { return 100; }
+
+size_t rm_bin_workspace_bytes(int64_t n_tets, int64_t n_tiles) {
+  if (n_tets < 0 || n_tiles < 0) return 0;
+  return rm_bin_layout_bytes(n_tets, n_tiles);
+}
+
+int rm_project_and_bin(const int32_t* indices, int64_t n_tets, const float* vertices, int64_t n_vertices,
+                       const RmCamera* cam, int32_t* tiles_touched, int32_t* rect_tile_space, float* vs_tetra,
+                       float* circumcenter, int32_t* tile_ranges, RmBinInfo* info, void* workspace,
+                       size_t workspace_bytes, void* stream) {
+  g_last_error[0] = 0;
+  int rc = check_cam(cam);
+  if (rc) return rc;
+  if (n_tets < 0 || n_vertices < 0 || n_tets > 0x7fffffffll || !info || !tile_ranges || !workspace)
+    return RM_ERR_INVALID_ARG;
+  if (n_tets > 0 && (!indices || !vertices || !tiles_touched || !rect_tile_space || !vs_tetra || !circumcenter))
+    return RM_ERR_INVALID_ARG;
+  if (!aligned16(indices) || !aligned16(rect_tile_space) || (reinterpret_cast<uintptr_t>(workspace) & 255))
+    return RM_ERR_WORKSPACE;
+  rc = rm_bind_device(workspace);
+  if (rc) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint32_t *depth_keys, *order_in;
+  int32_t* tile_diff;
+  rc = rm_launch_bin_prepare(n_tets, cam, workspace, workspace_bytes, &depth_keys, &order_in, &tile_diff, info, st);
+  if (rc) return rc;
+  rc = rm_launch_project(indices, n_tets, vertices, n_vertices, cam, tiles_touched, rect_tile_space, vs_tetra,
+                         circumcenter, depth_keys, order_in, tile_diff, info, st);
+  if (rc) return rc;
+  return rm_launch_bin_finish(n_tets, cam, tiles_touched, tile_ranges, info, workspace, st);
+}
+
+int rm_build_tile_lists(const int32_t* rect_tile_space, const int32_t* tile_ranges, int64_t n_tets,
+                        const RmCamera* cam, int64_t n_keys, void* workspace, uint32_t* scratch,
+                        int32_t* sorted_tetra_idx, void* stream) {
+  g_last_error[0] = 0;
+  int rc = check_cam(cam);
+  if (rc) return rc;
+  if (n_keys < 0 || n_tets < 0 || !workspace || !tile_ranges) return RM_ERR_INVALID_ARG;
+  if (n_keys > 0x7fffffffll) return RM_ERR_TOO_MANY_KEYS;
+  if (n_keys == 0) return RM_OK;
+  if (!rect_tile_space || !scratch || !sorted_tetra_idx) return RM_ERR_INVALID_ARG;
+  rc = rm_bind_device(workspace);
+  if (rc) return rc;
+  return rm_launch_build_lists(rect_tile_space, tile_ranges, n_tets, cam, n_keys, workspace, scratch,
+                               sorted_tetra_idx, static_cast<cudaStream_t>(stream));
+}
+
+int rm_pack_records(const int32_t* indices, const float* vertices, const float* cell_values, int64_t n_tets,
+                    const RmCamera* cam, const int32_t* tiles_touched, float* records, void* stream) {
+  g_last_error[0] = 0;
+  int rc = check_cam(cam);
+  if (rc) return rc;
+  if (n_tets < 0) return RM_ERR_INVALID_ARG;
+  if (n_tets == 0) return RM_OK;
+  if (!indices || !vertices || !cell_values || !records) return RM_ERR_INVALID_ARG;
+  if (!aligned16(indices) || !aligned16(records)) return RM_ERR_WORKSPACE;
+  rc = rm_bind_device(records);
+  if (rc) return rc;
+  return rm_launch_pack(indices, vertices, cell_values, n_tets, cam, tiles_touched, records,
+                        static_cast<cudaStream_t>(stream));
+}
+
+int rm_forward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, const float* records,
+               const RmCamera* cam, const float* ray_jitter, float* output_img, float* distortion_img,
+               int32_t* n_contributors, void* stream) {
+  g_last_error[0] = 0;
+  int rc = check_cam(cam);
+  if (rc) return rc;
+  if (!tile_ranges || !ray_jitter || !output_img || !distortion_img || !n_contributors) return RM_ERR_INVALID_ARG;
+  if (!aligned16(output_img) || !aligned16(records) || (reinterpret_cast<uintptr_t>(ray_jitter) & 7) ||
+      (reinterpret_cast<uintptr_t>(tile_ranges) & 7))
+    return RM_ERR_WORKSPACE;
+  rc = rm_bind_device(output_img);
+  if (rc) return rc;
+  return rm_launch_forward(sorted_tetra_idx, tile_ranges, records, cam, ray_jitter, output_img, distortion_img,
+                           n_contributors, static_cast<cudaStream_t>(stream));
+}
+
+int rm_backward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, const float* records,
+                const RmCamera* cam, const float* ray_jitter, const float* output_img,
+                const float* distortion_img, const int32_t* n_contributors, const float* grad_output_img,
+                const float* grad_distortion_img, const int32_t* indices, const float* vertices,
+                const float* cell_values, int64_t n_tets, int64_t n_vertices, float* grad_records,
+                float* vertices_grad, float* cell_values_grad, void* stream) {
+  g_last_error[0] = 0;
+  int rc = check_cam(cam);
+  if (rc) return rc;
+  if (n_tets < 0 || n_vertices < 0) return RM_ERR_INVALID_ARG;
+  if (!tile_ranges || !ray_jitter || !output_img || !distortion_img || !n_contributors || !grad_output_img ||
+      !grad_distortion_img || !vertices_grad)
+    return RM_ERR_INVALID_ARG;
+  if (n_tets > 0 && (!indices || !vertices || !cell_values || !grad_records || !cell_values_grad || !records))
+    return RM_ERR_INVALID_ARG;
+  if (!aligned16(output_img) || !aligned16(grad_output_img) || !aligned16(records) || !aligned16(grad_records) ||
+      !aligned16(indices))
+    return RM_ERR_WORKSPACE;
+  rc = rm_bind_device(vertices_grad);
+  if (rc) return rc;
+  return rm_launch_backward(sorted_tetra_idx, tile_ranges, records, cam, ray_jitter, output_img, distortion_img,
+                            n_contributors, grad_output_img, grad_distortion_img, indices, vertices, cell_values,
+                            n_tets, n_vertices, grad_records, vertices_grad, cell_values_grad,
+                            static_cast<cudaStream_t>(stream));
+}
+
+int rm_vertex_backward(const int32_t* indices, const float* vertices, int64_t n_tets, int64_t n_vertices,
+                       const RmCamera* cam, const int32_t* tiles_touched, const float* grad_vs_tetra,
+                       const float* grad_circumcenter, float* vertices_grad, void* stream) {
+  g_last_error[0] = 0;
+  int rc = check_cam(cam);
+  if (rc) return rc;
+  if (n_tets < 0 || n_vertices < 0 || !vertices_grad) return RM_ERR_INVALID_ARG;
+  if (n_tets > 0 && (!indices || !vertices || !tiles_touched || !grad_vs_tetra || !grad_circumcenter))
+    return RM_ERR_INVALID_ARG;
+  if (!aligned16(indices)) return RM_ERR_WORKSPACE;
+  rc = rm_bind_device(vertices_grad);
+  if (rc) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  RM_CUDA_CHECK(cudaMemsetAsync(vertices_grad, 0, sizeof(float) * 3 * (size_t)n_vertices, st));
+  return rm_launch_vertex_backward(indices, vertices, n_tets, cam, tiles_touched, grad_vs_tetra, grad_circumcenter,
+                                   vertices_grad, st);
+}
+
+}  // extern "C"

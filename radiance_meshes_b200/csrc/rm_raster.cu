@@ -1,0 +1,691 @@
+// Stages 5-6 on the GPU: per-pixel front-to-back integration of the tile lists
+// and its reverse pass.
+//
+// Reference behaviour reproduced: slang/alphablend_shader_interp.slang:83-431
+// (pixel state, distortion moments, forward loop with early termination at
+// log-transmittance < -5.5, backward replay with state undo),
+// slang/interp_version.slang:21-153 (closed-form segment integral of constant
+// density and linear colour), slang/intersect.slang:393-624 (ray/tet slab
+// test), slang/camera.slang:241-346 (ray generation).
+//
+// Design (not the reference's structure):
+//   * Tets are packed once per frame into 96-byte records holding the four
+//     outward face planes relative to the CAMERA POSITION (n_i, D_i) and the
+//     colour field folded to (grd, s0 = grd.(cam - v0), base, density).  The
+//     per-pixel origin offset o = cam + min_t*d only shifts each plane distance
+//     by min_t*(n_i.d), so the per-(pixel,tet) work drops from four cross
+//     products to four dot products.
+//   * A half-warp owns 16 pixels of one tile; a warp therefore walks two tile
+//     lists in lock-step.  Records are staged 16 at a time per half-warp into
+//     shared memory with 128-bit cp.async copies, double buffered, and a
+//     half-warp stops fetching as soon as all of its pixels have terminated.
+//   * Backward accumulates gradients with respect to the 24 record fields:
+//     a transposed butterfly reduction over the 16 pixels (23 shuffles) leaves
+//     each lane with at most two sums, added to a per-tet row with one atomic
+//     each; a per-tet kernel then applies the chain rule to vertices and cell
+//     values (12 vertex atomics per tet instead of 19 atomics per pixel hit).
+
+#include "rm_common.cuh"
+
+namespace rm {
+
+// ----------------------------------------------------------------------------
+// Record packing
+// ----------------------------------------------------------------------------
+struct PlaneSetup {
+  f3 n[4];
+  float D[4];
+  float sgn[4];
+};
+
+__device__ __forceinline__ void make_planes(const f3 v[4], f3 cam, PlaneSetup& p) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    // faces (v0,v1,v2) (v0,v1,v3) (v0,v2,v3) (v1,v2,v3); opposite vertex v3 v2 v1 v0
+    const int b = i == 3 ? 1 : 0;
+    const int e1 = i < 2 ? 1 : 2;
+    const int e2 = i == 0 ? 2 : 3;
+    const int op = 3 - i;
+    f3 n = cross(v[e1] - v[b], v[e2] - v[b]);
+    float s = 1.0f;
+    if (dot(n, v[op] - v[b]) > 0.0f) {
+      n = -n;
+      s = -1.0f;
+    }
+    p.n[i] = n;
+    p.sgn[i] = s;
+    p.D[i] = -dot(n, v[b] - cam);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+k_pack_records(const int32_t* __restrict__ indices, const float* __restrict__ vertices,
+               const float* __restrict__ cell, int64_t T, RmCamera rcam, const int32_t* __restrict__ tiles_touched,
+               float4* __restrict__ records) {
+  int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= T) return;
+  if (tiles_touched && tiles_touched[g] == 0) return;
+  f3 cam = {__ldg(rcam.cam_pos), __ldg(rcam.cam_pos + 1), __ldg(rcam.cam_pos + 2)};
+  int4 id = __ldg(reinterpret_cast<const int4*>(indices) + g);
+  f3 v[4] = {load3(vertices, id.x), load3(vertices, id.y), load3(vertices, id.z), load3(vertices, id.w)};
+  PlaneSetup p;
+  make_planes(v, cam, p);
+  const float* c = cell + 7 * g;
+  float density = fmaxf(__ldg(c), 0.0f);
+  f3 base = {__ldg(c + 1), __ldg(c + 2), __ldg(c + 3)};
+  f3 grd = {__ldg(c + 4), __ldg(c + 5), __ldg(c + 6)};
+  float s0 = dot(grd, cam - v[0]);
+  float4* r = records + 6 * g;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) r[i] = make_float4(p.n[i].x, p.n[i].y, p.n[i].z, p.D[i]);
+  r[4] = make_float4(grd.x, grd.y, grd.z, s0);
+  r[5] = make_float4(base.x, base.y, base.z, density);
+}
+
+// ----------------------------------------------------------------------------
+// Ray generation (fp32), slang/camera.slang:241-346
+// ----------------------------------------------------------------------------
+__device__ __forceinline__ void undistort(float& px, float& py, const float* dist) {
+  float k1 = dist[0], k2 = dist[1], p1 = dist[2], p2 = dist[3];
+  if (k1 * k1 + k2 * k2 + p1 * p1 + p2 * p2 < 1e-9f) return;
+  float x = px, y = py;
+  for (int i = 0; i < 10; ++i) {
+    float r2 = x * x + y * y;
+    float d = 1.0f + r2 * (k1 + r2 * k2);
+    float fx = d * x + 2.0f * p1 * x * y + p2 * (r2 + 2.0f * x * x) - px;
+    float fy = d * y + 2.0f * p2 * x * y + p1 * (r2 + 2.0f * y * y) - py;
+    float d_r = k1 + r2 * (2.0f * k2);
+    float d_x = 2.0f * x * d_r;
+    float d_y = 2.0f * y * d_r;
+    float fx_x = d + d_x * x + 2.0f * p1 * y + 6.0f * p2 * x;
+    float fx_y = d_y * x + 2.0f * p1 * x + 2.0f * p2 * y;
+    float fy_x = d_x * y + 2.0f * p2 * y + 2.0f * p1 * x;
+    float fy_y = d + d_y * y + 2.0f * p2 * x + 6.0f * p1 * y;
+    float denom = fy_x * fx_y - fx_x * fy_y;
+    if (fabsf(denom) < 1e-9f) break;
+    float xn = fx * fy_y - fy * fx_y;
+    float yn = fy * fx_x - fx * fy_x;
+    x += xn / denom;
+    y += yn / denom;
+  }
+  px = x;
+  py = y;
+}
+
+__device__ __forceinline__ f3 ray_direction(const RmCamera& c, float px, float py) {
+  float fx = __ldg(c.K + 0), cx = __ldg(c.K + 2), fy = __ldg(c.K + 4), cy = __ldg(c.K + 5);
+  float x = (px - cx) / fx, y = (py - cy) / fy;
+  float dist[4] = {__ldg(c.distortion_params), __ldg(c.distortion_params + 1), __ldg(c.distortion_params + 2),
+                   __ldg(c.distortion_params + 3)};
+  if (c.camera_type == 0 || c.camera_type == 1) undistort(x, y, dist);
+  f3 dc;
+  if (c.camera_type == 1) {
+    float theta = sqrtf(x * x + y * y);
+    theta = fminf(3.14159265f, theta);
+    float s = (theta < 1e-6f) ? 1.0f : sinf(theta) / theta;
+    dc = {x * s, y * s, cosf(theta)};
+  } else {
+    float l = sqrtf(x * x + y * y + 1.0f);
+    dc = {x / l, y / l, 1.0f / l};
+  }
+  const float* W = c.world_view_transform;
+  f3 w = {__ldg(W + 0) * dc.x + __ldg(W + 4) * dc.y + __ldg(W + 8) * dc.z,
+          __ldg(W + 1) * dc.x + __ldg(W + 5) * dc.y + __ldg(W + 9) * dc.z,
+          __ldg(W + 2) * dc.x + __ldg(W + 6) * dc.y + __ldg(W + 10) * dc.z};
+  float l = sqrtf(dot(w, w));
+  return {w.x / l, w.y / l, w.z / l};
+}
+
+// ----------------------------------------------------------------------------
+// Per (pixel, record) evaluation shared by forward and backward
+// ----------------------------------------------------------------------------
+struct Eval {
+  float enter, exit, te, tx;  // clamped and raw distances (from the offset origin)
+  int ie, ix;                 // planes that produced te / tx (-1: none)
+  float dt, tau, gd, oe, ox, alpha, phi, w0, w1;
+  float cr, cg, cb;           // colour contribution
+};
+
+__device__ __forceinline__ bool slab_test(const float4* __restrict__ rec, f3 d, float min_t, Eval& e) {
+  float te = -1e30f, tx = 1e30f;
+  int ie = -1, ix = -1;
+  bool miss = false;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float4 p = rec[i];
+    float den = p.x * d.x + p.y * d.y + p.z * d.z;
+    float dist = fmaf(min_t, den, p.w);
+    if (fabsf(den) < 1e-10f) {
+      miss = miss || (dist > 0.0f);
+    } else {
+      float t = -dist / den;
+      if (den < 0.0f) {
+        if (t > te) { te = t; ie = i; }
+      } else {
+        if (t < tx) { tx = t; ix = i; }
+      }
+    }
+  }
+  if (miss || te > tx || tx <= 0.0f) return false;
+  e.te = te; e.tx = tx; e.ie = ie; e.ix = ix;
+  e.enter = fmaxf(te, 0.0f);
+  e.exit = fmaxf(tx, e.enter);
+  e.dt = fmaxf(e.exit - e.enter, 0.0f);
+  return true;
+}
+
+// returns false if the segment contributes nothing (optical depth not > 0)
+__device__ __forceinline__ bool integrate(const float4* __restrict__ rec, f3 d, float min_t, Eval& e) {
+  float4 cg = rec[4], cb = rec[5];
+  e.tau = cb.w * e.dt;
+  if (!(e.tau > 0.0f)) return false;
+  e.gd = cg.x * d.x + cg.y * d.y + cg.z * d.z;
+  e.oe = fmaf(e.enter + min_t, e.gd, cg.w);
+  e.ox = fmaf(e.exit + min_t, e.gd, cg.w);
+  float em1 = expm1f(-e.tau);
+  e.alpha = 1.0f + em1;
+  e.phi = (e.tau < 1e-6f) ? 1.0f - 0.5f * e.tau : -em1 / e.tau;
+  e.w0 = e.phi - e.alpha;
+  e.w1 = 1.0f - e.phi;
+  e.cr = e.w0 * (cb.x + e.ox) + e.w1 * (cb.x + e.oe);
+  e.cg = e.w0 * (cb.y + e.ox) + e.w1 * (cb.y + e.oe);
+  e.cb = e.w0 * (cb.z + e.ox) + e.w1 * (cb.z + e.oe);
+  return true;
+}
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+constexpr int kWarpsPerBlock = 4;
+constexpr int kChunk = 16;  // records staged per half-warp per round
+
+struct Unit {
+  int tile;       // linear tile index
+  int x, y;       // pixel
+  bool inside;    // pixel exists
+  int start, len; // tile list
+};
+
+__device__ __forceinline__ Unit make_unit(const RmCamera& c, const int2* __restrict__ ranges, int64_t unit,
+                                          int64_t n_units, int subs, int lane16) {
+  Unit u;
+  u.inside = false;
+  u.start = 0;
+  u.len = 0;
+  u.tile = 0;
+  u.x = u.y = 0;
+  if (unit >= n_units) return u;
+  int64_t t = unit / subs;
+  int sub = (int)(unit - t * subs);
+  u.tile = c.tile_row_begin * c.grid_width + (int)t;
+  int ty = u.tile / c.grid_width, tx = u.tile - ty * c.grid_width;
+  int p = sub * 16 + lane16;
+  int ly = p / c.tile_width, lx = p - ly * c.tile_width;
+  u.x = tx * c.tile_width + lx;
+  u.y = ty * c.tile_height + ly;
+  u.inside = ly < c.tile_height && u.x < c.image_width && u.y < c.image_height;
+  int2 rg = __ldg(ranges + u.tile);
+  u.start = rg.x;
+  u.len = rg.y - rg.x;
+  return u;
+}
+
+// ----------------------------------------------------------------------------
+// Forward
+// ----------------------------------------------------------------------------
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, const float4* __restrict__ records,
+          RmCamera rcam, const float2* __restrict__ jitter, float4* __restrict__ out_img,
+          float* __restrict__ dist_img, int32_t* __restrict__ n_contrib, int subs, int64_t n_units) {
+  __shared__ __align__(16) float4 stage[kWarpsPerBlock][2][2][kChunk * 6];  // [warp][half][buffer]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int half = lane >> 4, lane16 = lane & 15;
+  const unsigned half_mask = 0xFFFFu << (16 * half);
+  const int64_t unit = ((int64_t)blockIdx.x * kWarpsPerBlock + warp) * 2 + half;
+  Unit u = make_unit(rcam, ranges, unit, n_units, subs, lane16);
+
+  f3 d = {0.f, 0.f, 1.f};
+  const int64_t pix = (int64_t)u.y * rcam.image_width + u.x;
+  if (u.inside) {
+    float2 j = __ldg(jitter + pix);
+    d = ray_direction(rcam, (float)u.x + j.x, (float)u.y + j.y);
+  }
+  const float min_t = rcam.min_t;
+
+  float sr = 0.f, sg = 0.f, sb = 0.f, logT = 0.f, T = 1.f;
+  float dx = 0.f, dy = 0.f, dz = 0.f, dw = 0.f, dv = 0.f;
+  int contrib = 0;
+  bool active = u.inside;
+
+  const int nchunks = (u.len + kChunk - 1) / kChunk;
+  // all lanes of the warp iterate up to the longer of the two lists
+  const int max_chunks = max(nchunks, __shfl_xor_sync(0xffffffffu, nchunks, 16));
+  bool fetching = __ballot_sync(0xffffffffu, active) & half_mask;
+
+  float4* buf0 = stage[warp][half][0];
+  float4* buf1 = stage[warp][half][1];
+  // prologue: stage chunk 0
+  if (fetching && lane16 < u.len) {
+    int id = __ldg(list + u.start + lane16);
+    const float4* src = records + 6 * (int64_t)id;
+#pragma unroll
+    for (int k = 0; k < 6; ++k) cp_async16(buf0 + lane16 * 6 + k, src + k);
+  }
+  cp_async_commit();
+
+  for (int c = 0; c < max_chunks; ++c) {
+    float4* cur = (c & 1) ? buf1 : buf0;
+    float4* nxt = (c & 1) ? buf0 : buf1;
+    // issue the next chunk
+    {
+      int e = (c + 1) * kChunk + lane16;
+      if (fetching && e < u.len) {
+        int id = __ldg(list + u.start + e);
+        const float4* src = records + 6 * (int64_t)id;
+#pragma unroll
+        for (int k = 0; k < 6; ++k) cp_async16(nxt + lane16 * 6 + k, src + k);
+      }
+      cp_async_commit();
+    }
+    cp_async_wait<1>();
+    __syncwarp();
+    if (active) {
+      const int cnt = min(kChunk, u.len - c * kChunk);
+      for (int j = 0; j < cnt; ++j) {
+        ++contrib;
+        const float4* rec = cur + j * 6;
+        Eval e;
+        if (slab_test(rec, d, min_t, e) && integrate(rec, d, min_t, e)) {
+          sr = fmaf(e.cr, T, sr);
+          sg = fmaf(e.cg, T, sg);
+          sb = fmaf(e.cb, T, sb);
+          logT -= e.tau;
+          T *= e.alpha;
+          float dens = rec[5].w;
+          float m1 = dens * (e.exit + e.enter) * 0.5f;
+          dx = fmaf(2.0f * m1, dz, dx);
+          dy = fmaf(2.0f * dens, dw, dy);
+          dz += dens;
+          dw += m1;
+          dv = fmaf(dens * dens, e.dt * (1.0f / 3.0f), dv);
+          if (logT < -5.5f) {
+            active = false;
+            break;
+          }
+        }
+      }
+    }
+    __syncwarp();
+    unsigned act = __ballot_sync(0xffffffffu, active);
+    fetching = act & half_mask;
+    if (act == 0) break;
+  }
+  cp_async_wait<0>();
+
+  if (u.inside) {
+    out_img[pix] = make_float4(sr, sg, sb, logT);
+    float* o = dist_img + 5 * pix;
+    o[0] = dx; o[1] = dy; o[2] = dz; o[3] = dw; o[4] = dv;
+    n_contrib[pix] = contrib;
+  }
+}
+
+// ----------------------------------------------------------------------------
+// Backward
+// ----------------------------------------------------------------------------
+// Sum v[0..N) over the 16 lanes of each half-warp.  On return lane l (0..15)
+// of a half holds at most two totals, written to out0/out1, whose field
+// indices are field0 and field0+1 (field0+1 may be >= N: padding).
+template <int N>
+__device__ __forceinline__ void halfwarp_transpose_reduce(float (&v)[N], int lane16, float& out0, float& out1,
+                                                          int& field0) {
+  static_assert(N == 24, "written for 24 fields");
+  int base = 0;
+  // 24 -> 12 (xor 8)
+  {
+    const bool up = lane16 & 8;
+#pragma unroll
+    for (int i = 0; i < 12; ++i) {
+      float send = up ? v[i] : v[i + 12];
+      float keep = up ? v[i + 12] : v[i];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+    }
+    base += up ? 12 : 0;
+  }
+  // 12 -> 6 (xor 4)
+  {
+    const bool up = lane16 & 4;
+#pragma unroll
+    for (int i = 0; i < 6; ++i) {
+      float send = up ? v[i] : v[i + 6];
+      float keep = up ? v[i + 6] : v[i];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+    }
+    base += up ? 6 : 0;
+  }
+  // 6 -> 3 (xor 2)
+  {
+    const bool up = lane16 & 2;
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      float send = up ? v[i] : v[i + 3];
+      float keep = up ? v[i + 3] : v[i];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+    }
+    base += up ? 3 : 0;
+  }
+  // 3 (+1 pad) -> 2 (xor 1)
+  {
+    const bool up = lane16 & 1;
+    float a0 = v[0], a1 = v[1], a2 = v[2], a3 = 0.0f;
+    float send0 = up ? a0 : a2, send1 = up ? a1 : a3;
+    float keep0 = up ? a2 : a0, keep1 = up ? a3 : a1;
+    out0 = keep0 + __shfl_xor_sync(0xffffffffu, send0, 1);
+    out1 = keep1 + __shfl_xor_sync(0xffffffffu, send1, 1);
+    base += up ? 2 : 0;
+    // lanes with up hold fields base (=+2) and a padding slot
+    field0 = base;
+    if (up) out1 = 0.0f;
+  }
+}
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, const float4* __restrict__ records,
+           RmCamera rcam, const float2* __restrict__ jitter, const float4* __restrict__ out_img,
+           const float* __restrict__ dist_img, const int32_t* __restrict__ n_contrib,
+           const float4* __restrict__ g_img, const float* __restrict__ g_dist, float* __restrict__ grec, int subs,
+           int64_t n_units) {
+  __shared__ __align__(16) float4 stage[kWarpsPerBlock][2][2][kChunk * 6];
+  __shared__ int stage_id[kWarpsPerBlock][2][2][kChunk];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int half = lane >> 4, lane16 = lane & 15;
+  const unsigned half_mask = 0xFFFFu << (16 * half);
+  const int64_t unit = ((int64_t)blockIdx.x * kWarpsPerBlock + warp) * 2 + half;
+  Unit u = make_unit(rcam, ranges, unit, n_units, subs, lane16);
+
+  f3 d = {0.f, 0.f, 1.f};
+  const int64_t pix = (int64_t)u.y * rcam.image_width + u.x;
+  float logT = 0.f, sz = 0.f, sw = 0.f;
+  float gr = 0.f, gg = 0.f, gb = 0.f, glogT = 0.f, gx = 0.f, gy = 0.f, gz = 0.f, gw = 0.f, gv = 0.f;
+  int nc = 0;
+  if (u.inside) {
+    float2 j = __ldg(jitter + pix);
+    d = ray_direction(rcam, (float)u.x + j.x, (float)u.y + j.y);
+    logT = __ldg(out_img + pix).w;
+    sz = __ldg(dist_img + 5 * pix + 2);
+    sw = __ldg(dist_img + 5 * pix + 3);
+    float4 g4 = __ldg(g_img + pix);
+    gr = g4.x; gg = g4.y; gb = g4.z; glogT = g4.w;
+    const float* gd = g_dist + 5 * pix;
+    gx = __ldg(gd); gy = __ldg(gd + 1); gz = __ldg(gd + 2); gw = __ldg(gd + 3); gv = __ldg(gd + 4);
+    nc = min(__ldg(n_contrib + pix), u.len);
+  }
+  const float min_t = rcam.min_t;
+
+  // entries at or beyond the largest n_contributors of the half are skipped by every pixel
+  int nmax = nc;
+#pragma unroll
+  for (int o = 8; o >= 1; o >>= 1) nmax = max(nmax, __shfl_xor_sync(0xffffffffu, nmax, o));
+  const int nchunks = (nmax + kChunk - 1) / kChunk;
+  const int max_chunks = max(nchunks, __shfl_xor_sync(0xffffffffu, nchunks, 16));
+
+  // chunk k of this half (k = 0 is the LAST chunk of its list) sits in buffer k&1
+  auto issue = [&](int k) {
+    int c = nchunks - 1 - k;
+    if (c >= 0) {
+      int e = c * kChunk + lane16;
+      if (e < nmax) {
+        int id = __ldg(list + u.start + e);
+        stage_id[warp][half][k & 1][lane16] = id;
+        const float4* src = records + 6 * (int64_t)id;
+        float4* dst = stage[warp][half][k & 1] + lane16 * 6;
+#pragma unroll
+        for (int q = 0; q < 6; ++q) cp_async16(dst + q, src + q);
+      }
+    }
+    cp_async_commit();
+  };
+  issue(0);
+  for (int k = 0; k < max_chunks; ++k) {
+    issue(k + 1);
+    cp_async_wait<1>();
+    __syncwarp();
+    const int c = nchunks - 1 - k;
+    const float4* cur = stage[warp][half][k & 1];
+    const int* cur_id = stage_id[warp][half][k & 1];
+    // both halves step through 16 slots; a half whose list is exhausted idles
+    for (int j = kChunk - 1; j >= 0; --j) {
+      const int e = c * kChunk + j;
+      const bool in_range = c >= 0 && e < nmax;
+      const float4* rec = cur + j * 6;
+      float g[24];
+#pragma unroll
+      for (int q = 0; q < 24; ++q) g[q] = 0.0f;
+      bool hit = false;
+      Eval ev;
+      if (in_range && u.inside && e < nc) {
+        if (slab_test(rec, d, min_t, ev) && integrate(rec, d, min_t, ev)) {
+          hit = true;
+          const float4 cgv = rec[4], cbv = rec[5];
+          const float dens = cbv.w;
+          // undo: state before this tet
+          logT += ev.tau;
+          const float Tp = __expf(fminf(logT, 46.0517f));
+          const float m0 = dens, m1 = dens * (ev.exit + ev.enter) * 0.5f;
+          sz -= m0;
+          sw -= m1;
+          // reverse of the state update
+          const float gcr = gr * Tp, gcg = gg * Tp, gcb = gb * Tp;
+          const float gT = gr * ev.cr + gg * ev.cg + gb * ev.cb;
+          const float g_a = -glogT;
+          const float g_m1 = 2.0f * sz * gx + gw;
+          const float g_m0 = 2.0f * sw * gy + gz;
+          float g_dens = g_m0 + g_m1 * (ev.exit + ev.enter) * 0.5f + gv * 2.0f * dens * ev.dt * (1.0f / 3.0f);
+          float g_exit = g_m1 * dens * 0.5f, g_enter = g_exit;
+          if (ev.exit - ev.enter > 0.0f) {
+            float kk = gv * dens * dens * (1.0f / 3.0f);
+            g_exit += kk;
+            g_enter -= kk;
+          }
+          glogT = fmaf(gT, Tp, glogT);
+          gz = fmaf(2.0f * m1, gx, gz);
+          gw = fmaf(2.0f * m0, gy, gw);
+          // reverse of the segment integral
+          const float cxr = cbv.x + ev.ox, cxg = cbv.y + ev.ox, cxb = cbv.z + ev.ox;
+          const float cer = cbv.x + ev.oe, ceg = cbv.y + ev.oe, ceb = cbv.z + ev.oe;
+          const float g_w0 = gcr * cxr + gcg * cxg + gcb * cxb;
+          const float g_w1 = gcr * cer + gcg * ceg + gcb * ceb;
+          const float G = gcr + gcg + gcb;
+          const float wsum = ev.w0 + ev.w1;
+          const float g_ox = ev.w0 * G, g_oe = ev.w1 * G;
+          const float g_gd = g_ox * (ev.exit + min_t) + g_oe * (ev.enter + min_t);
+          g_exit = fmaf(g_ox, ev.gd, g_exit);
+          g_enter = fmaf(g_oe, ev.gd, g_enter);
+          const float g_phi = g_w0 - g_w1;
+          float dphi;
+          if (ev.tau < 1e-6f) dphi = -0.5f;
+          else dphi = (ev.alpha - ev.phi) / ev.tau;  // exp(-x)/x + expm1(-x)/x^2
+          const float g_tau = g_phi * dphi + g_w0 * ev.alpha + g_a;
+          g_dens = fmaf(g_tau, ev.dt, g_dens);
+          const float g_dt = g_tau * dens;
+          if (ev.exit - ev.enter > 0.0f) {
+            g_exit += g_dt;
+            g_enter -= g_dt;
+          }
+          float g_tx = 0.0f, g_te = 0.0f;
+          if (ev.tx > ev.enter) g_tx = g_exit; else g_enter += g_exit;
+          if (ev.te > 0.0f) g_te = g_enter;
+          // planes
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float gt = (i == ev.ie ? g_te : 0.0f) + (i == ev.ix ? g_tx : 0.0f);
+            const float4 p = rec[i];
+            const float den = p.x * d.x + p.y * d.y + p.z * d.z;
+            const float r = (gt != 0.0f) ? 1.0f / den : 0.0f;
+            const float kD = -gt * r;
+            const float kn = gt * p.w * r * r;
+            g[4 * i + 0] = kn * d.x;
+            g[4 * i + 1] = kn * d.y;
+            g[4 * i + 2] = kn * d.z;
+            g[4 * i + 3] = kD;
+          }
+          g[16] = g_gd * d.x;
+          g[17] = g_gd * d.y;
+          g[18] = g_gd * d.z;
+          g[19] = g_ox + g_oe;
+          g[20] = wsum * gcr;
+          g[21] = wsum * gcg;
+          g[22] = wsum * gcb;
+          g[23] = g_dens;
+        }
+      }
+      const unsigned hits = __ballot_sync(0xffffffffu, hit);
+      if (hits) {
+        float o0, o1;
+        int f0;
+        halfwarp_transpose_reduce<24>(g, lane16, o0, o1, f0);
+        if (hits & half_mask) {
+          float* row = grec + (int64_t)cur_id[j] * 24;
+          if (o0 != 0.0f) atomicAdd(row + f0, o0);
+          if (f0 + 1 < 24 && !(lane16 & 1) && o1 != 0.0f) atomicAdd(row + f0 + 1, o1);
+        }
+      }
+    }
+    __syncwarp();
+  }
+  cp_async_wait<0>();
+}
+
+// Chain rule from record gradients to vertices and cell values; one thread per tet.
+__global__ void __launch_bounds__(256)
+k_backward_finish(const int32_t* __restrict__ indices, const float* __restrict__ vertices,
+                  const float* __restrict__ cell, int64_t T, RmCamera rcam, const float4* __restrict__ grec,
+                  float* __restrict__ vgrad, float* __restrict__ cgrad) {
+  int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= T) return;
+  float4 q[6];
+  bool any = false;
+#pragma unroll
+  for (int k = 0; k < 6; ++k) {
+    q[k] = __ldg(grec + 6 * g + k);
+    any = any || q[k].x != 0.f || q[k].y != 0.f || q[k].z != 0.f || q[k].w != 0.f;
+  }
+  float* co = cgrad + 7 * g;
+  if (!any) {
+#pragma unroll
+    for (int k = 0; k < 7; ++k) co[k] = 0.0f;
+    return;
+  }
+  f3 cam = {__ldg(rcam.cam_pos), __ldg(rcam.cam_pos + 1), __ldg(rcam.cam_pos + 2)};
+  int4 id = __ldg(reinterpret_cast<const int4*>(indices) + g);
+  const int vid[4] = {id.x, id.y, id.z, id.w};
+  f3 v[4] = {load3(vertices, id.x), load3(vertices, id.y), load3(vertices, id.z), load3(vertices, id.w)};
+  PlaneSetup p;
+  make_planes(v, cam, p);
+  f3 gvv[4] = {{0, 0, 0}, {0, 0, 0}, {0, 0, 0}, {0, 0, 0}};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int b = i == 3 ? 1 : 0;
+    const int e1 = i < 2 ? 1 : 2;
+    const int e2 = i == 0 ? 2 : 3;
+    const float gD = q[i].w;
+    f3 g_n = {q[i].x, q[i].y, q[i].z};
+    g_n = g_n + (v[b] - cam) * (-gD);  // D = -n.(b - cam)
+    f3 g_b = p.n[i] * (-gD);
+    f3 g_raw = g_n * p.sgn[i];
+    f3 E1 = v[e1] - v[b], E2 = v[e2] - v[b];
+    f3 g_e1 = cross(E2, g_raw);
+    f3 g_e2 = cross(g_raw, E1);
+    gvv[e1] = gvv[e1] + g_e1;
+    gvv[e2] = gvv[e2] + g_e2;
+    gvv[b] = gvv[b] + g_b - g_e1 - g_e2;
+  }
+  const float* c = cell + 7 * g;
+  f3 grd = {__ldg(c + 4), __ldg(c + 5), __ldg(c + 6)};
+  const float gs0 = q[4].w;
+  f3 g_grd = {q[4].x, q[4].y, q[4].z};
+  g_grd = g_grd + (cam - v[0]) * gs0;  // s0 = grd.(cam - v0)
+  gvv[0] = gvv[0] - grd * gs0;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    float* vp = vgrad + 3 * (int64_t)vid[k];
+    atomicAdd(vp + 0, gvv[k].x);
+    atomicAdd(vp + 1, gvv[k].y);
+    atomicAdd(vp + 2, gvv[k].z);
+  }
+  co[0] = __ldg(c) > 0.0f ? q[5].w : 0.0f;
+  co[1] = q[5].x;
+  co[2] = q[5].y;
+  co[3] = q[5].z;
+  co[4] = g_grd.x;
+  co[5] = g_grd.y;
+  co[6] = g_grd.z;
+}
+
+}  // namespace rm
+
+// ----------------------------------------------------------------------------
+// host-side launchers used by rm_api.cu
+// ----------------------------------------------------------------------------
+static inline void unit_grid(const RmCamera* cam, int* subs, int64_t* n_units, unsigned* blocks) {
+  int px = cam->tile_width * cam->tile_height;
+  *subs = (px + 15) / 16;
+  int64_t tiles = (int64_t)(cam->tile_row_end - cam->tile_row_begin) * cam->grid_width;
+  *n_units = tiles * *subs;
+  int64_t per_block = rm::kWarpsPerBlock * 2;
+  *blocks = (unsigned)((*n_units + per_block - 1) / per_block);
+}
+
+int rm_launch_pack(const int32_t* indices, const float* vertices, const float* cell, int64_t T, const RmCamera* cam,
+                   const int32_t* tiles_touched, float* records, cudaStream_t st) {
+  if (T == 0) return RM_OK;
+  rm::k_pack_records<<<(unsigned)((T + 255) / 256), 256, 0, st>>>(indices, vertices, cell, T, *cam, tiles_touched,
+                                                                  reinterpret_cast<float4*>(records));
+  RM_CUDA_CHECK(cudaPeekAtLastError());
+  return RM_OK;
+}
+
+int rm_launch_forward(const int32_t* list, const int32_t* ranges, const float* records, const RmCamera* cam,
+                      const float* jitter, float* out_img, float* dist_img, int32_t* n_contrib, cudaStream_t st) {
+  int subs;
+  int64_t n_units;
+  unsigned blocks;
+  unit_grid(cam, &subs, &n_units, &blocks);
+  if (n_units == 0) return RM_OK;
+  rm::k_forward<<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
+      list, reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam,
+      reinterpret_cast<const float2*>(jitter), reinterpret_cast<float4*>(out_img), dist_img, n_contrib, subs,
+      n_units);
+  RM_CUDA_CHECK(cudaPeekAtLastError());
+  return RM_OK;
+}
+
+int rm_launch_backward(const int32_t* list, const int32_t* ranges, const float* records, const RmCamera* cam,
+                       const float* jitter, const float* out_img, const float* dist_img, const int32_t* n_contrib,
+                       const float* g_img, const float* g_dist, const int32_t* indices, const float* vertices,
+                       const float* cell, int64_t T, int64_t V, float* grec, float* vgrad, float* cgrad,
+                       cudaStream_t st) {
+  RM_CUDA_CHECK(cudaMemsetAsync(vgrad, 0, sizeof(float) * 3 * (size_t)V, st));
+  if (T == 0) return RM_OK;
+  RM_CUDA_CHECK(cudaMemsetAsync(grec, 0, sizeof(float) * 24 * (size_t)T, st));
+  int subs;
+  int64_t n_units;
+  unsigned blocks;
+  unit_grid(cam, &subs, &n_units, &blocks);
+  if (n_units > 0) {
+    rm::k_backward<<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
+        list, reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam,
+        reinterpret_cast<const float2*>(jitter), reinterpret_cast<const float4*>(out_img), dist_img, n_contrib,
+        reinterpret_cast<const float4*>(g_img), g_dist, grec, subs, n_units);
+  }
+  rm::k_backward_finish<<<(unsigned)((T + 255) / 256), 256, 0, st>>>(indices, vertices, cell, T, *cam,
+                                                                     reinterpret_cast<const float4*>(grec), vgrad,
+                                                                     cgrad);
+  RM_CUDA_CHECK(cudaPeekAtLastError());
+  return RM_OK;
+}

@@ -1,0 +1,175 @@
+"""Host side of the rasterizer: torch tensors in, C-ABI calls, torch tensors out.
+
+PyTorch is used for device memory, streams and autograd plumbing only; every
+computation happens in the CUDA library.
+"""
+import ctypes as C
+
+import torch
+
+from . import _lib
+
+# launches of this library's kernels (memsets not counted) per call, for bench accounting
+LAUNCHES_PROJECT_AND_BIN = 1 + 12 + 2 + 3 + 1 + 3 + 1
+LAUNCHES_BUILD_LISTS = 1 + 3
+LAUNCHES_FORWARD = 2
+LAUNCHES_BACKWARD = 2
+
+
+def _ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream(device):
+    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _f32c(t, device):
+    if not isinstance(t, torch.Tensor):
+        t = torch.as_tensor(t)
+    return t.to(device=device, dtype=torch.float32).contiguous()
+
+
+class CameraArgs:
+    """RmCamera plus the device tensors it points at (kept alive with it)."""
+
+    def __init__(self, tcam, device, tile_rows=None):
+        self.keep = [_f32c(tcam["world_view_transform"], device), _f32c(tcam["K"], device),
+                     _f32c(tcam["cam_pos"], device), _f32c(tcam["distortion_params"], device)]
+        assert self.keep[0].numel() == 16 and self.keep[1].numel() == 9
+        assert self.keep[2].numel() == 3 and self.keep[3].numel() == 4
+        c = _lib.RmCamera()
+        c.world_view_transform, c.K, c.cam_pos, c.distortion_params = [t.data_ptr() for t in self.keep]
+        c.image_height = int(tcam["image_height"])
+        c.image_width = int(tcam["image_width"])
+        c.camera_type = int(tcam["camera_type"])
+        c.fovy = float(tcam["fovy"])
+        c.fovx = float(tcam["fovx"])
+        c.min_t = float(tcam["min_t"])
+        c.tile_height = int(tcam["tile_height"])
+        c.tile_width = int(tcam["tile_width"])
+        c.grid_height = int(tcam["grid_height"])
+        c.grid_width = int(tcam["grid_width"])
+        r0, r1 = tile_rows if tile_rows is not None else tcam.get("tile_rows", (0, c.grid_height))
+        c.tile_row_begin, c.tile_row_end = int(r0), int(r1)
+        self.c = c
+
+    @property
+    def ref(self):
+        return C.byref(self.c)
+
+
+def _require_cuda(t, name):
+    if not (isinstance(t, torch.Tensor) and t.is_cuda):
+        raise RuntimeError(f"{name} must be a CUDA tensor (the rasterizer has no CPU path)")
+
+
+def project_and_bin(indices, vertices, tcam, tile_rows=None):
+    """Stage 1 and tile populations. Returns a dict of outputs plus the binning context."""
+    _require_cuda(indices, "indices")
+    _require_cuda(vertices, "vertices")
+    lib = _lib.load()
+    dev = vertices.device
+    indices = indices.contiguous()
+    if indices.dtype != torch.int32:
+        indices = indices.to(torch.int32)
+    verts = vertices.detach().contiguous().float()
+    T, V = indices.shape[0], verts.shape[0]
+    cam = CameraArgs(tcam, dev, tile_rows)
+    G = cam.c.grid_height * cam.c.grid_width
+    with torch.cuda.device(dev):
+        tiles_touched = torch.empty((T,), dtype=torch.int32, device=dev)
+        rect = torch.empty((T, 4), dtype=torch.int32, device=dev)
+        vs_tetra = torch.empty((T, 3), dtype=torch.float32, device=dev)
+        circumcenter = torch.empty((T, 3), dtype=torch.float32, device=dev)
+        tile_ranges = torch.empty((G, 2), dtype=torch.int32, device=dev)
+        info = torch.empty((2,), dtype=torch.int64, device=dev)
+        ws_bytes = lib.rm_bin_workspace_bytes(T, G)
+        ws = torch.empty((ws_bytes,), dtype=torch.uint8, device=dev)
+        _lib.check(lib.rm_project_and_bin(_ptr(indices), T, _ptr(verts), V, cam.ref, _ptr(tiles_touched), _ptr(rect),
+                                          _ptr(vs_tetra), _ptr(circumcenter), _ptr(tile_ranges), _ptr(info),
+                                          _ptr(ws), ws_bytes, _stream(dev)))
+    return dict(indices=indices, vertices=verts, cam=cam, tiles_touched=tiles_touched, rect=rect, vs_tetra=vs_tetra,
+                circumcenter=circumcenter, tile_ranges=tile_ranges, info=info, workspace=ws, T=T, V=V, G=G)
+
+
+def read_info(ctx):
+    """The one host synchronisation of the binning stage: N, visible count, status."""
+    host = ctx["info"].cpu()
+    n_keys = int(host[0].item())
+    second = int(host[1].item())
+    n_visible = second & 0xFFFFFFFF
+    status = (second >> 32) & 0xFFFFFFFF
+    if status & _lib.RM_STATUS_NAN_VERTEX:
+        # same message as the reference's assert (tile_shader_slang.py:78)
+        raise AssertionError("Tensor contains NaN values!")
+    if status & _lib.RM_STATUS_KEY_OVERFLOW or n_keys > 2**31 - 1:
+        raise RuntimeError(f"rm_b200: {n_keys} (tile, tet) pairs exceed the int32 range of the tile lists")
+    return n_keys, n_visible
+
+
+def build_tile_lists(ctx, n_keys):
+    lib = _lib.load()
+    dev = ctx["vertices"].device
+    with torch.cuda.device(dev):
+        sorted_idx = torch.empty((n_keys,), dtype=torch.int32, device=dev)
+        if n_keys > 0:
+            scratch = torch.empty((n_keys,), dtype=torch.int32, device=dev)
+            _lib.check(lib.rm_build_tile_lists(_ptr(ctx["rect"]), _ptr(ctx["tile_ranges"]), ctx["T"], ctx["cam"].ref,
+                                               n_keys, _ptr(ctx["workspace"]), _ptr(scratch), _ptr(sorted_idx),
+                                               _stream(dev)))
+    return sorted_idx
+
+
+def pack_records(indices, vertices, cell_values, cam, tiles_touched=None):
+    lib = _lib.load()
+    dev = vertices.device
+    T = indices.shape[0]
+    with torch.cuda.device(dev):
+        records = torch.empty((T, _lib.RM_RECORD_FLOATS), dtype=torch.float32, device=dev)
+        _lib.check(lib.rm_pack_records(_ptr(indices), _ptr(vertices), _ptr(cell_values), T, cam.ref,
+                                       _ptr(tiles_touched), _ptr(records), _stream(dev)))
+    return records
+
+
+def forward(sorted_idx, tile_ranges, records, cam, ray_jitter):
+    lib = _lib.load()
+    dev = records.device
+    H, W = cam.c.image_height, cam.c.image_width
+    full = cam.c.tile_row_begin == 0 and cam.c.tile_row_end == cam.c.grid_height
+    alloc = torch.empty if full else torch.zeros
+    with torch.cuda.device(dev):
+        output_img = alloc((H, W, 4), dtype=torch.float32, device=dev)
+        distortion_img = alloc((H, W, 5), dtype=torch.float32, device=dev)
+        n_contributors = alloc((H, W, 1), dtype=torch.int32, device=dev)
+        _lib.check(lib.rm_forward(_ptr(sorted_idx), _ptr(tile_ranges), _ptr(records), cam.ref, _ptr(ray_jitter),
+                                  _ptr(output_img), _ptr(distortion_img), _ptr(n_contributors), _stream(dev)))
+    return output_img, distortion_img, n_contributors
+
+
+def backward(sorted_idx, tile_ranges, records, cam, ray_jitter, output_img, distortion_img, n_contributors,
+             grad_output_img, grad_distortion_img, indices, vertices, cell_values):
+    lib = _lib.load()
+    dev = records.device
+    T, V = indices.shape[0], vertices.shape[0]
+    with torch.cuda.device(dev):
+        grad_records = torch.empty((T, _lib.RM_RECORD_FLOATS), dtype=torch.float32, device=dev)
+        vertices_grad = torch.empty((V, 3), dtype=torch.float32, device=dev)
+        cell_grad = torch.empty((T, 7), dtype=torch.float32, device=dev)
+        _lib.check(lib.rm_backward(_ptr(sorted_idx), _ptr(tile_ranges), _ptr(records), cam.ref, _ptr(ray_jitter),
+                                   _ptr(output_img), _ptr(distortion_img), _ptr(n_contributors),
+                                   _ptr(grad_output_img), _ptr(grad_distortion_img), _ptr(indices), _ptr(vertices),
+                                   _ptr(cell_values), T, V, _ptr(grad_records), _ptr(vertices_grad), _ptr(cell_grad),
+                                   _stream(dev)))
+    return vertices_grad, cell_grad
+
+
+def vertex_backward(indices, vertices, cam, tiles_touched, grad_vs, grad_cc):
+    lib = _lib.load()
+    dev = vertices.device
+    T, V = indices.shape[0], vertices.shape[0]
+    with torch.cuda.device(dev):
+        vertices_grad = torch.empty((V, 3), dtype=torch.float32, device=dev)
+        _lib.check(lib.rm_vertex_backward(_ptr(indices), _ptr(vertices), T, V, cam.ref, _ptr(tiles_touched),
+                                          _ptr(grad_vs), _ptr(grad_cc), _ptr(vertices_grad), _stream(dev)))
+    return vertices_grad

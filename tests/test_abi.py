@@ -1,0 +1,55 @@
+"""The C-ABI library loads and exports every symbol include/rm_b200.h declares
+(no compute calls: there is no GPU on the CPU test box)."""
+import os
+import re
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "rm_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(rm_[a-z_0-9]+)\s*\(", text)))
+
+
+def test_header_symbols_exported(cuda_lib):
+    from radiance_meshes_b200 import _lib
+    declared = _declared_symbols()
+    assert declared, "no declarations found"
+    assert sorted(_lib.SYMBOLS) == declared
+    for name in declared:
+        assert hasattr(cuda_lib, name)
+    assert cuda_lib.rm_version() >= 100
+    assert cuda_lib.rm_strerror(0) == b"ok"
+    assert cuda_lib.rm_bin_workspace_bytes(1000, 64) > 0
+
+
+def test_struct_layout_matches_header():
+    import ctypes as C
+    from radiance_meshes_b200 import _lib
+    assert C.sizeof(_lib.RmBinInfo) == 16
+    assert C.sizeof(_lib.RmCamera) == 4 * 8 + 12 * 4
+    assert _lib.RM_RECORD_FLOATS == 24
+
+
+def test_host_path_rejects_cpu_tensors():
+    import pytest
+    import torch
+    from radiance_meshes_b200 import raster
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        raster.project_and_bin(torch.zeros((1, 4), dtype=torch.int32), torch.zeros((4, 3)), {})
+
+
+def test_render_grid_and_util():
+    import torch
+    from delaunay_rasterization.internal.render_grid import RenderGrid
+    from delaunay_rasterization.internal.util import recombine_tensors, split_tensors
+    g = RenderGrid(1080, 1920, tile_width=4, tile_height=4)
+    assert (g.grid_height, g.grid_width) == (270, 480)
+    g = RenderGrid(17, 33, tile_width=16, tile_height=8)
+    assert (g.grid_height, g.grid_width) == (3, 3)
+    d = dict(a=torch.ones(2), b=3, c=torch.zeros(1), min_t=0.1)
+    plain, tensors = split_tensors(d)
+    assert len(tensors) == 2 and plain["b"] == 3
+    back = recombine_tensors(plain, tensors)
+    assert set(back) == set(d) and back["a"] is d["a"]

@@ -1,0 +1,191 @@
+"""GPU parity tests: every stage of the CUDA path, called through the C ABI
+(via the drop-in delaunay_rasterization entry points), against the CPU oracle on
+the same seeded inputs.
+
+Gates: tile lists, rectangles, counts, sort depths bit-exact; images and
+distortion moments within 1e-4 relative L2 (fp32); gradients within 1e-3
+relative L2.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import scene_util
+from radiance_meshes_b200 import scenes
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "small_scene.npz")
+IMG_TOL = 1e-4
+GRAD_TOL = 1e-3
+
+
+def rel_l2(a, b):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    return np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30)
+
+
+def gpu_render(pts, tets, cell, tcam, jit, g_img=None, g_dist=None):
+    from radiance_meshes_b200.render import render, tcam_to_device
+    dev = torch.device("cuda:0")
+    v = torch.tensor(pts, device=dev, requires_grad=True)
+    c = torch.tensor(cell, device=dev, requires_grad=True)
+    idx = torch.tensor(tets, device=dev, dtype=torch.int32)
+    j = torch.tensor(jit, device=dev)
+    pkg = render(idx, v, c, tcam_to_device(tcam, dev), j)
+    out = {k: pkg[k].detach().cpu().numpy() for k in ("image", "distortion_img", "sorted_tetra_idx", "tile_ranges",
+                                                       "vs_tetra", "circumcenter", "rect", "mask")}
+    if g_img is not None:
+        loss = (pkg["image"] * torch.tensor(g_img, device=dev)).sum() + \
+               (pkg["distortion_img"] * torch.tensor(g_dist, device=dev)).sum()
+        loss.backward()
+        out["vertices_grad"] = v.grad.cpu().numpy()
+        out["cell_grad"] = c.grad.cpu().numpy()
+    return out
+
+
+def check_against_oracle(oracle, pts, tets, cell, tcam, jit, seed=0, check_grad=True, nc_slack=2e-4):
+    H, W = tcam["image_height"], tcam["image_width"]
+    rng = np.random.default_rng(seed)
+    g_img = rng.normal(size=(H, W, 4)).astype(np.float32)
+    g_dist = (0.05 * rng.normal(size=(H, W, 5))).astype(np.float32)
+    ref = oracle.render(tets, pts, cell, tcam, jit)
+    got = gpu_render(pts, tets, cell, tcam, jit, g_img if check_grad else None, g_dist)
+    # --- bit-exact integer / index work
+    np.testing.assert_array_equal(got["rect"], ref["project"]["rect"])
+    np.testing.assert_array_equal(got["mask"], ref["project"]["tiles_touched"] > 0)
+    np.testing.assert_array_equal(got["vs_tetra"].view(np.uint32), ref["project"]["vs_tetra"].view(np.uint32))
+    np.testing.assert_array_equal(got["circumcenter"].view(np.uint32),
+                                  ref["project"]["circumcenter"].view(np.uint32))
+    np.testing.assert_array_equal(got["tile_ranges"], ref["tile_ranges"])
+    np.testing.assert_array_equal(got["sorted_tetra_idx"], ref["sorted_idx"])
+    # --- floating point within tolerance
+    if ref["output_img"].any():
+        assert rel_l2(got["image"], ref["output_img"]) <= IMG_TOL
+        assert rel_l2(got["distortion_img"], ref["distortion_img"]) <= IMG_TOL
+    else:
+        assert not got["image"].any()
+    if check_grad:
+        vg, cg = oracle.backward(ref["sorted_idx"], ref["tile_ranges"], tets, pts, cell, tcam, jit,
+                                 ref["output_img"], ref["distortion_img"], ref["n_contributors"], g_img, g_dist)
+        if np.abs(vg).max() > 0:
+            assert rel_l2(got["vertices_grad"], vg) <= GRAD_TOL
+            assert rel_l2(got["cell_grad"], cg) <= GRAD_TOL
+        else:
+            assert not got["vertices_grad"].any() and not got["cell_grad"].any()
+    return ref, got
+
+
+@pytest.mark.parametrize("tile", [4, 8, 16])
+def test_small_scene_all_stages(oracle, cuda_lib, tile):
+    pts, tets, cell = scene_util.small_scene(300, seed=tile)
+    H, W = 64, 80
+    tcam = scene_util.camera(H=H, W=W, tile=tile)
+    check_against_oracle(oracle, pts, tets, cell, tcam, scene_util.jitter(H, W, 1))
+
+
+def test_ragged_image_and_odd_tile(oracle, cuda_lib):
+    # image not a multiple of the tile; tile sizes that are not multiples of 4
+    pts, tets, cell = scene_util.small_scene(200, seed=21)
+    for (H, W, tile) in [(37, 53, 4), (30, 30, 5), (33, 20, 3)]:
+        tcam = scene_util.camera(H=H, W=W, tile=tile)
+        check_against_oracle(oracle, pts, tets, cell, tcam, scene_util.jitter(H, W, 2))
+
+
+def test_camera_inside_mesh(oracle, cuda_lib):
+    pts, tets, cell = scene_util.small_scene(400, seed=5, zero_frac=0.4)
+    H = W = 48
+    tcam = scenes.make_tcam(scenes.look_at((0.05, 0.02, -0.1), (0.4, 0.1, 1.0)), H, W, 90.0, tile=4, min_t=0.02)
+    check_against_oracle(oracle, pts, tets, cell, tcam, scene_util.jitter(H, W, 3))
+
+
+def test_config1_cpu_runnable_reference_case(oracle, cuda_lib):
+    # 2,000 points uniform in [-1,1]^3, 128x128, fov 60, eye at distance 3
+    sc = scenes.make_scene(1)
+    tcam = scenes.config_camera(1)
+    ref, got = check_against_oracle(oracle, sc["vertices"], sc["indices"], sc["cell_values"], tcam,
+                                    np.full((128, 128, 2), 0.5, np.float32))
+    assert ref["sorted_idx"].shape[0] > 100_000
+
+
+def test_dense_scene_early_termination(oracle, cuda_lib):
+    # high densities: most pixels terminate early, exercising the per-tile fetch stop
+    pts, tets, cell = scene_util.small_scene(2000, seed=9, mu=3.0, sigma=0.5, zero_frac=0.0)
+    H = W = 64
+    tcam = scene_util.camera(H=H, W=W, tile=4)
+    ref, got = check_against_oracle(oracle, pts, tets, cell, tcam, scene_util.jitter(H, W, 4))
+    assert ref["output_img"][..., 3].min() < -5.5
+
+
+def test_empty_and_culled(oracle, cuda_lib):
+    pts, tets, cell = scene_util.small_scene(40, seed=4)
+    # looking away: N = 0
+    tcam = scenes.make_tcam(scenes.look_at((0, 0, 3.0), (0, 0, 6.0)), 16, 16, 60.0, tile=4)
+    check_against_oracle(oracle, pts, tets, cell, tcam, np.full((16, 16, 2), 0.5, np.float32))
+    # a planar tet next to a regular one
+    v = np.array([[0, 0, 0], [1, 0, 0], [0, 1, 0], [0.3, 0.3, 5e-4], [0.2, 0.2, 0.8]], np.float32)
+    t = np.array([[0, 1, 2, 3], [0, 1, 2, 4]], np.int32)
+    c = np.array([[1.0, .5, .5, .5, 0, 0, 0], [2.0, .2, .4, .6, .1, -.1, .2]], np.float32)
+    tcam = scene_util.camera(eye=(0.2, 0.2, 2.5), H=32, W=32)
+    check_against_oracle(oracle, v, t, c, tcam, np.full((32, 32, 2), 0.5, np.float32))
+
+
+def test_nan_vertices_raise(cuda_lib):
+    from radiance_meshes_b200.render import render, tcam_to_device
+    pts, tets, cell = scene_util.small_scene(40, seed=4)
+    pts[7, 2] = np.nan
+    dev = torch.device("cuda:0")
+    tcam = tcam_to_device(scene_util.camera(H=16, W=16), dev)
+    with pytest.raises(AssertionError, match="NaN"):
+        render(torch.tensor(tets, device=dev), torch.tensor(pts, device=dev), torch.tensor(cell, device=dev), tcam)
+
+
+def test_golden_fixture(cuda_lib):
+    g = np.load(GOLDEN)
+    tcam = scene_util.camera(eye=tuple(g["eye"]), H=int(g["H"]), W=int(g["W"]), tile=int(g["tile"]),
+                             fov=float(g["fov"]), min_t=float(g["min_t"]))
+    got = gpu_render(g["vertices"], g["indices"], g["cell_values"], tcam, g["jitter"], g["g_img"], g["g_dist"])
+    np.testing.assert_array_equal(got["rect"], g["rect"])
+    np.testing.assert_array_equal(got["sorted_tetra_idx"], g["sorted_idx"])
+    np.testing.assert_array_equal(got["tile_ranges"], g["tile_ranges"])
+    np.testing.assert_array_equal(got["vs_tetra"], g["vs_tetra"])
+    assert rel_l2(got["image"], g["output_img"]) <= IMG_TOL
+    assert rel_l2(got["distortion_img"], g["distortion_img"]) <= IMG_TOL
+    assert rel_l2(got["vertices_grad"], g["vertices_grad"]) <= GRAD_TOL
+    assert rel_l2(got["cell_grad"], g["cell_grad"]) <= GRAD_TOL
+
+
+def test_vertex_stage_backward(oracle, cuda_lib):
+    from delaunay_rasterization.internal.render_grid import RenderGrid
+    from delaunay_rasterization.internal.tile_shader_slang import vertex_and_tile_shader
+    from radiance_meshes_b200.render import tcam_to_device
+    pts, tets, cell = scene_util.small_scene(300, seed=13)
+    tcam = scene_util.camera(H=32, W=32)
+    dev = torch.device("cuda:0")
+    v = torch.tensor(pts, device=dev, requires_grad=True)
+    grid = RenderGrid(32, 32, tile_width=4, tile_height=4)
+    _, _, vs_tetra, circumcenter, mask, _ = vertex_and_tile_shader(torch.tensor(tets, device=dev), v,
+                                                                   tcam_to_device(tcam, dev), grid)
+    rng = np.random.default_rng(0)
+    g_vs = rng.normal(size=vs_tetra.shape).astype(np.float32)
+    g_cc = rng.normal(size=circumcenter.shape).astype(np.float32)
+    ((vs_tetra * torch.tensor(g_vs, device=dev)).sum() + (circumcenter * torch.tensor(g_cc, device=dev)).sum()
+     ).backward()
+    pr = oracle.project(tets, pts, tcam)
+    ref = oracle.vertex_backward(tets, pts, tcam, pr["tiles_touched"], g_vs, g_cc)
+    assert rel_l2(v.grad.cpu().numpy(), ref) <= GRAD_TOL
+
+
+def test_medium_scene_sort_classes(oracle, cuda_lib):
+    # 20k points at 256x256 with 16x16 tiles: tile lists of several thousand entries,
+    # exercising the large shared-memory sort class
+    pts = scenes.points_gaussians(20_000, seed=3)
+    tets = scenes.delaunay(pts)
+    cell = scenes._features(np.random.default_rng(3), tets.shape[0], -1.0, 1.5, 0.3)
+    H = W = 256
+    tcam = scenes.make_tcam(scenes.look_at((0.0, 0.3, 3.2)), H, W, 50.0, tile=16, min_t=0.1)
+    ref, got = check_against_oracle(oracle, pts, tets, cell, tcam, scene_util.jitter(H, W, 7), check_grad=True)
+    lens = ref["tile_ranges"][:, 1] - ref["tile_ranges"][:, 0]
+    assert lens.max() > 2048
