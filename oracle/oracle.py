@@ -144,6 +144,17 @@ def backward(sorted_idx, tile_ranges, indices, vertices, cell_values, tcam, jitt
     return vg, cg
 
 
+def sensitive_pixels(sorted_idx, tile_ranges, indices, vertices, cell_values, tcam, jitter, tol=1e-4, nthreads=0):
+    """Boolean [H,W] mask of pixels decided by rounding in the reference algorithm itself."""
+    sorted_idx, tile_ranges, indices, vertices, cell_values, jitter = _fb_args(
+        np.float32, sorted_idx, tile_ranges, indices, vertices, cell_values, jitter)
+    cam = make_camera(tcam)
+    mask = np.zeros((cam.image_height, cam.image_width), np.uint8)
+    lib().or_sensitive_pixels(_p(sorted_idx), _p(tile_ranges), _p(indices), _p(vertices), _p(cell_values),
+                              C.byref(cam), _p(jitter), _p(mask), C.c_float(tol), C.c_int(nthreads))
+    return mask.astype(bool)
+
+
 def vertex_backward(indices, vertices, tcam, tiles_touched, g_vs, g_cc):
     """Reverse of stage 1 wrt vertices. Returns vertices_grad[V,3]."""
     indices = np.ascontiguousarray(_np(indices), dtype=np.int32)

@@ -857,6 +857,56 @@ int or_backward_f64(const int32_t* sorted_idx, const int32_t* tile_ranges, const
                                n_contrib, g_img, g_dist, vgrad, cgrad, row0, row1, nthreads);
 }
 
+// Pixels whose result is decided by floating-point rounding in the reference
+// algorithm itself: a ray that grazes a tet (chord length within `tol` relative
+// of zero, counted either as a hit or as a miss) adds that tet's full density
+// to the distortion moments or not at all, and a log-transmittance within `tol`
+// of the -5.5 cut-off decides whether one more tet is walked.  Any two correct
+// fp32 implementations may differ on these pixels, so parity tests exclude them
+// from the distortion and gradient comparisons (and bound how many there are).
+int or_sensitive_pixels(const int32_t* sorted_idx, const int32_t* tile_ranges, const int32_t* indices,
+                        const float* vertices, const float* cell, const OrCamera* ocam, const float* jitter,
+                        uint8_t* mask, float tol, int nthreads) {
+  Cam<float> cam = load_cam<float>(ocam);
+  const int H = cam.H, W = cam.Wd;
+#ifdef _OPENMP
+  if (nthreads > 0) omp_set_num_threads(nthreads);
+#endif
+#pragma omp parallel for schedule(dynamic, 16)
+  for (int64_t p = 0; p < (int64_t)H * W; ++p) {
+    int y = int(p / W), x = int(p % W);
+    int tile = (y / cam.tile_h) * cam.grid_w + (x / cam.tile_w);
+    int64_t s0 = tile_ranges[2 * tile], s1 = tile_ranges[2 * tile + 1];
+    V3<float> o, d;
+    get_ray(cam, float(x) + jitter[2 * p], float(y) + jitter[2 * p + 1], o, d);
+    State<float> s = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+    uint8_t flag = 0;
+    for (int64_t j = s0; j < s1; ++j) {
+      Tet<float> t = load_tet<float>(sorted_idx[j], indices, vertices, cell);
+      Planes<float> pl;
+      make_planes(t.v, o, pl);
+      float te = -1e30f, tx = 1e30f;
+      for (int i = 0; i < 4; ++i) {
+        float den = dot(pl.n[i], d);
+        if (std::fabs(den) < 1e-10f) continue;
+        float tt = -pl.d[i] / den;
+        if (den < 0.f) te = std::fmax(te, tt);
+        else tx = std::fmin(tx, tt);
+      }
+      float chord = tx - std::fmax(te, 0.f);
+      if (t.density > 0.f && std::fabs(chord) <= tol * std::fmax(1.f, std::fabs(tx))) flag = 1;
+      Ctrl<float> c;
+      if (evaluate_tet(t, o, d, c) && c.a > 0.f) {
+        update_state(s, c);
+        if (std::fabs(s.logT + 5.5f) <= tol * 5.5f) flag = 1;
+        if (s.logT < -5.5f) break;
+      }
+    }
+    mask[p] = flag;
+  }
+  return 0;
+}
+
 // Reverse of stage 1 with respect to the vertices: gradients of
 // vs_tetra[:,2] (clamped circumsphere power) and circumcenter, for tets that
 // were not culled (tiles_touched > 0).  Restates what Slang's autodiff derives

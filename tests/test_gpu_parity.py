@@ -46,12 +46,22 @@ def gpu_render(pts, tets, cell, tcam, jit, g_img=None, g_dist=None):
     return out
 
 
-def check_against_oracle(oracle, pts, tets, cell, tcam, jit, seed=0, check_grad=True, nc_slack=2e-4):
+def check_against_oracle(oracle, pts, tets, cell, tcam, jit, seed=0, check_grad=True, max_flips=0.01):
+    """All stages against the oracle.
+
+    The image is compared on every pixel.  The distortion moments and the
+    gradients are compared with the rounding-decided pixels of the reference
+    algorithm masked out (oracle.sensitive_pixels: grazing ray/tet contacts add a
+    tet's whole density to the moments or nothing; a log-transmittance on the
+    -5.5 cut-off walks one more tet or not).  On the masked pixels the two sides
+    may legitimately differ; the share of pixels that actually do is bounded.
+    """
     H, W = tcam["image_height"], tcam["image_width"]
     rng = np.random.default_rng(seed)
-    g_img = rng.normal(size=(H, W, 4)).astype(np.float32)
-    g_dist = (0.05 * rng.normal(size=(H, W, 5))).astype(np.float32)
     ref = oracle.render(tets, pts, cell, tcam, jit)
+    keep = ~oracle.sensitive_pixels(ref["sorted_idx"], ref["tile_ranges"], tets, pts, cell, tcam, jit, tol=2e-5)
+    g_img = (rng.normal(size=(H, W, 4)) * keep[..., None]).astype(np.float32)
+    g_dist = (0.05 * rng.normal(size=(H, W, 5)) * keep[..., None]).astype(np.float32)
     got = gpu_render(pts, tets, cell, tcam, jit, g_img if check_grad else None, g_dist)
     # --- bit-exact integer / index work
     np.testing.assert_array_equal(got["rect"], ref["project"]["rect"])
@@ -64,7 +74,11 @@ def check_against_oracle(oracle, pts, tets, cell, tcam, jit, seed=0, check_grad=
     # --- floating point within tolerance
     if ref["output_img"].any():
         assert rel_l2(got["image"], ref["output_img"]) <= IMG_TOL
-        assert rel_l2(got["distortion_img"], ref["distortion_img"]) <= IMG_TOL
+        assert rel_l2(got["distortion_img"][keep], ref["distortion_img"][keep]) <= IMG_TOL
+        diff = np.abs(got["distortion_img"] - ref["distortion_img"]).max(-1)
+        flips = diff > 1e-3 * (np.abs(ref["distortion_img"]).max(-1) + 1e-6)
+        assert not (flips & keep).any()
+        assert flips.mean() <= max_flips
     else:
         assert not got["image"].any()
     if check_grad:
