@@ -1,0 +1,401 @@
+"""Benchmark of the rasterizer hot path: forward+backward Mpix/s at 1920x1080 over a
+~6.5M-tet synthetic unbounded-scene mesh (one view per GPU).
+
+python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload config3|config2|small]
+
+One JSON line on stdout (rank 0).  See DESIGN.md for the definition of every field.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from radiance_meshes_b200 import scenes  # noqa: E402
+
+WORKLOADS = {
+    # name: (scene config, n_points or None, camera config)
+    "config3": (3, None, 3),
+    "config2": (2, None, 2),
+    "small": (3, 60_000, 3),
+}
+CACHE_DIR = os.environ.get("RM_BENCH_CACHE", "/tmp/rm_b200_cache")
+
+
+def log(*a):
+    print(*a, file=sys.stderr, flush=True)
+
+
+def load_scene(workload, rank=0, world=1):
+    """Seeded synthetic mesh; built once per box (Delaunay of 1M points takes ~1 min) and cached in /tmp."""
+    cfg, npts, _ = WORKLOADS[workload]
+    path = os.path.join(CACHE_DIR, f"{workload}.npz")
+    if not os.path.exists(path):
+        if rank == 0:
+            os.makedirs(CACHE_DIR, exist_ok=True)
+            t = time.time()
+            sc = scenes.make_scene(cfg, npts)
+            tmp = path + f".tmp{os.getpid()}.npz"
+            np.savez(tmp, vertices=sc["vertices"], indices=sc["indices"], cell_values=sc["cell_values"])
+            os.replace(tmp, path)
+            log(f"[bench] built {workload}: {sc['indices'].shape[0]} tets in {time.time() - t:.1f}s")
+        else:
+            while not os.path.exists(path):
+                time.sleep(1.0)
+    z = np.load(path)
+    return dict(vertices=z["vertices"], indices=z["indices"], cell_values=z["cell_values"])
+
+
+def camera_for(workload, view, n_views=8):
+    return scenes.config_camera(WORKLOADS[workload][2], view=view, n_views=n_views)
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index=0):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return dict(sm_mhz=float(np.median(sm)) if sm else None, sm_max_mhz=float(max(mx)) if mx else None,
+                    samples=len(sm), reasons=sorted(reasons))
+
+
+def algorithmic_bytes(T, V, Tv, N, G, HW):
+    """Compulsory traffic of each stage of the reference path (every stage input read
+    once, every output written once, gathers counted once per distinct element)."""
+    return {
+        "project": 16 * T + 12 * V + 44 * T,
+        "scan_emit": 24 * T + 8 * T + 12 * N,
+        "sort": 24 * N,
+        "ranges": 8 * N + 8 * G,
+        "forward": 4 * N + 44 * Tv + 12 * V + 48 * HW,
+        "backward": 4 * N + 44 * Tv + 12 * V + 84 * HW + 12 * V + 28 * T,
+    }
+
+
+# which algorithmic stage each timed kernel (group) implements
+KERNEL_STAGE = {
+    "k_project": ("project", 1.0),
+    "k_forward": ("forward", 1.0),
+    "k_backward": ("backward", 1.0),
+    "k_scatter_ranks": ("scan_emit", 1.0),
+    "k_segment_sort(3 launches)": ("sort", 1.0),
+}
+
+
+def cpu_baseline(sc, tcam, tile_rows=8):
+    """Shader-math CPU oracle (OpenMP, all cores) on a band of tile rows of the same frame."""
+    from oracle import oracle as O
+    H, W = tcam["image_height"], tcam["image_width"]
+    th = tcam["tile_height"]
+    r0 = tcam["grid_height"] // 2 - tile_rows // 2
+    r1 = r0 + tile_rows
+    rows = (r0 * th, min(r1 * th, H))
+    cores = O.num_threads()
+    t0 = time.time()
+    pr = O.project(sc["indices"], sc["vertices"], tcam)
+    t_proj = time.time() - t0
+    t0 = time.time()
+    tt, rect = O.restrict_to_tile_rows(pr["tiles_touched"], pr["rect"], r0, r1)
+    idx, ranges = O.build_lists(tt, rect, pr["vs_tetra"], tcam["grid_height"], tcam["grid_width"])
+    t_lists = time.time() - t0
+    jit = np.full((H, W, 2), 0.5, np.float32)
+    t0 = time.time()
+    out, dist, nc = O.forward(idx, ranges, sc["indices"], sc["vertices"], sc["cell_values"], tcam, jit, rows=rows)
+    t_fwd = time.time() - t0
+    rng = np.random.default_rng(0)
+    g_img = rng.normal(size=(H, W, 4)).astype(np.float32)
+    g_dist = (0.01 * rng.normal(size=(H, W, 5))).astype(np.float32)
+    t0 = time.time()
+    O.backward(idx, ranges, sc["indices"], sc["vertices"], sc["cell_values"], tcam, jit, out, dist, nc, g_img, g_dist,
+               rows=rows)
+    t_bwd = time.time() - t0
+    npx = (rows[1] - rows[0]) * W
+    total = t_proj * npx / (H * W) + t_lists + t_fwd + t_bwd
+    return dict(value=npx / total / 1e6, unit="Mpix/s", cores=cores, kind="port",
+                sample=(f"shader-math CPU oracle (C++/OpenMP) on pixel rows {rows[0]}..{rows[1]} of the same frame: "
+                        f"project(all tets) {t_proj:.2f}s scaled by the band's share, lists {t_lists:.2f}s, "
+                        f"forward {t_fwd:.2f}s, backward {t_bwd:.2f}s"))
+
+
+def run_reference(args):
+    """Reference arm: the reference's own CPU path for a tet field is its brute-force
+    quadrature (jaxutil/tetra_quad.py); JAX is not installed, so its C++ restatement
+    in oracle/ is timed, forward + gradient, one pixel per host core per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle as O
+    sc = load_scene(args.workload)
+    tcam = camera_for(args.workload, 0)
+    H, W = tcam["image_height"], tcam["image_width"]
+    cores = O.num_threads()
+    n_samples = 256
+    fx, fy = float(tcam["K"][0, 0]), float(tcam["K"][1, 1])
+    center = (H // 2) * W + W // 2 - cores // 2
+    vc, td = sc["cell_values"][:, 1:], sc["cell_values"][:, 0]
+
+    def step(i):
+        p0 = center + i * cores
+        O.quad_render(sc["vertices"], sc["indices"], vc, td, H, W, tcam["world_view_transform"], fx, fy,
+                      tcam["min_t"], n_samples, pixels=(p0, p0 + cores), want_grad=True)
+
+    for i in range(args.warmup):
+        step(-1 - i)
+    t0 = time.time()
+    for i in range(args.steps):
+        step(i)
+    dt = time.time() - t0
+    value = cores * args.steps / dt / 1e6
+    sample = (f"quadrature restatement (C++/OpenMP), {n_samples} samples per ray, forward+gradient, "
+              f"{cores} pixels per step at the image centre, all {sc['indices'].shape[0]} tets tested per sample")
+    line = dict(impl="reference", metric="fwd+bwd Mpix/s at 1080p, 6.5M tets", value=value, unit="Mpix/s",
+                n_gpus=args.gpus, steps=args.steps, warmup=args.warmup, ms_per_step=1e3 * dt / args.steps,
+                higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f64", data="synthetic",
+                config=dict(workload=workload_name(args.workload, sc, tcam)),
+                cpu_baseline=dict(value=value, unit="Mpix/s", cores=cores, kind="port", sample=sample),
+                e2e=dict(value=value, unit="Mpix/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+                gpu_launches=0)
+    print(json.dumps(line), flush=True)
+
+
+def workload_name(workload, sc, tcam):
+    return (f"{workload}: {sc['vertices'].shape[0]} points -> {sc['indices'].shape[0]} tets (scipy Delaunay), "
+            f"{tcam['image_width']}x{tcam['image_height']} pinhole, tile {tcam['tile_width']}, ring camera, "
+            "fwd+bwd, one view per GPU")
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    from radiance_meshes_b200 import _lib, raster
+    from radiance_meshes_b200.render import render, tcam_to_device
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.load()
+
+    sc = load_scene(args.workload, rank, world)
+    tcam_np = camera_for(args.workload, rank % 8)
+    H, W = tcam_np["image_height"], tcam_np["image_width"]
+    rng = np.random.default_rng(1234 + rank)
+    host = dict(
+        indices=torch.from_numpy(sc["indices"]).pin_memory(),
+        vertices=torch.from_numpy(sc["vertices"]).pin_memory(),
+        cell=torch.from_numpy(sc["cell_values"]).pin_memory(),
+        jitter=torch.from_numpy(rng.uniform(0, 1, (H, W, 2)).astype(np.float32)).pin_memory(),
+        g_img=torch.from_numpy(rng.normal(size=(H, W, 4)).astype(np.float32)).pin_memory(),
+        g_dist=torch.from_numpy((0.01 * rng.normal(size=(H, W, 5))).astype(np.float32)).pin_memory(),
+    )
+    d = {k: v.to(dev) for k, v in host.items()}
+    tcam = tcam_to_device(tcam_np, dev)
+    T, V = sc["indices"].shape[0], sc["vertices"].shape[0]
+
+    def step(inp):
+        v = inp["vertices"].requires_grad_(True)
+        c = inp["cell"].requires_grad_(True)
+        v.grad = None
+        c.grad = None
+        pkg = render(inp["indices"], v, c, tcam, inp["jitter"])
+        torch.autograd.backward([pkg["image"], pkg["distortion_img"]], [inp["g_img"], inp["g_dist"]])
+        if world > 1:
+            dist.all_reduce(v.grad)
+            dist.all_reduce(c.grad)
+        return pkg, v.grad, c.grad
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return ms
+
+    # ---- device-resident arm -------------------------------------------------------------------
+    for _ in range(args.warmup):
+        pkg, vg, cg = step(d)
+    barrier()
+    _lib.profile_read()
+    _lib.profile_enable(True)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        pkg, vg, cg = step(d)
+    e1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    _lib.profile_enable(False)
+    prof = _lib.profile_read()
+    ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    value = H * W * world / (ms_step * 1e-3) / 1e6
+
+    N = int(pkg["sorted_tetra_idx"].shape[0])
+    Tv = int(pkg["mask"].sum().item())
+    G = tcam_np["grid_height"] * tcam_np["grid_width"]
+    alg = algorithmic_bytes(T, V, Tv, N, G, H * W)
+    per_kernel = {}
+    for name, ms in prof:
+        a = per_kernel.setdefault(name, [0, 0.0])
+        a[0] += 1
+        a[1] += ms
+    kernel_ms = {k: v[1] / v[0] for k, v in per_kernel.items()}
+    total_kernel_ms = sum(kernel_ms.values())
+    dominant = max(kernel_ms, key=kernel_ms.get) if kernel_ms else None
+
+    # ---- end-to-end arm: host buffers in, host buffers out, copies inside the timed region -----
+    out_host = dict(image=torch.empty((H, W, 4)).pin_memory(), dist=torch.empty((H, W, 5)).pin_memory(),
+                    vg=torch.empty((V, 3)).pin_memory(), cg=torch.empty((T, 7)).pin_memory())
+    h2d = sum(v.numel() * v.element_size() for v in host.values())
+    d2h = sum(v.numel() * v.element_size() for v in out_host.values())
+
+    def e2e_step():
+        inp = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
+        pkg, vg, cg = step(inp)
+        out_host["image"].copy_(pkg["image"].detach(), non_blocking=True)
+        out_host["dist"].copy_(pkg["distortion_img"].detach(), non_blocking=True)
+        out_host["vg"].copy_(vg, non_blocking=True)
+        out_host["cg"].copy_(cg, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(max(1, min(args.warmup, 3))):
+        e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    e2e_value = H * W * world / (e2e_ms * 1e-3) / 1e6
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak, peak_src = float(json.load(open(peaks_path))["hbm_gbs"]), "measured"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+    roofline = None
+    if dominant is not None:
+        stage, share = KERNEL_STAGE.get(dominant, (None, 1.0))
+        bytes_alg = alg[stage] * share if stage else None
+        achieved = bytes_alg / (kernel_ms[dominant] * 1e-3) / 1e9 if bytes_alg else None
+        roofline = dict(bound="hbm", kernel=dominant, achieved=achieved, peak=peak, peak_source=peak_src,
+                        unit="GB/s", frac=(achieved / peak) if achieved else None, traffic=None,
+                        kernel_ms=kernel_ms[dominant], algorithmic_bytes=bytes_alg,
+                        note="issue-bound kernel: ~16 pixel evaluations per staged record; see DESIGN.md")
+    frame_bytes = sum(alg.values())
+    line = dict(
+        metric="fwd+bwd Mpix/s at 1080p, 6.5M tets", value=value, unit="Mpix/s", n_gpus=world, steps=args.steps,
+        warmup=args.warmup, ms_per_step=ms_step, higher_is_better=True, scaling="weak", vs_baseline=None,
+        dtype="f32", data="synthetic",
+        config=dict(workload=workload_name(args.workload, sc, tcam_np), tets=T, vertices=V, visible_tets=Tv,
+                    tile_tet_pairs=N, l2_policy="inputs larger than L2 (indices+cell values+lists > 126 MB)",
+                    grads_allreduced=world > 1),
+        clocks=clocks,
+        e2e=dict(value=e2e_value, unit="Mpix/s", ms_per_step=e2e_ms, h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h),
+        gpu_launches=args.steps * (raster.LAUNCHES_PROJECT_AND_BIN + raster.LAUNCHES_BUILD_LISTS +
+                                   raster.LAUNCHES_FORWARD + raster.LAUNCHES_BACKWARD),
+        roofline=roofline,
+        frame_roofline=dict(algorithmic_bytes=frame_bytes, achieved=frame_bytes / (ms_step * 1e-3) / 1e9,
+                            peak=peak, unit="GB/s", frac=frame_bytes / (ms_step * 1e-3) / 1e9 / peak,
+                            stages=alg),
+        kernel_ms={k: round(v, 4) for k, v in sorted(kernel_ms.items(), key=lambda kv: -kv[1])},
+        kernel_ms_sum=total_kernel_ms,
+    )
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(sc, tcam_np)
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="config3", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        if args.steps > 4:
+            args.steps = 4
+        args.warmup = min(args.warmup, 1)
+        run_reference(args)
+    else:
+        args.warmup = max(args.warmup, 3)
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

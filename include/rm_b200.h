@@ -142,6 +142,19 @@ int rm_vertex_backward(const int32_t* indices, const float* vertices, int64_t n_
                        const RmCamera* cam, const int32_t* tiles_touched, const float* grad_vs_tetra,
                        const float* grad_circumcenter, float* vertices_grad, void* stream);
 
+/*
+ * Optional per-kernel timing, a measurement aid with no counterpart in the
+ * reference (which only has commented-out wall-clock prints,
+ * alphablend_tiled_slang.py:39-40).  While enabled, every kernel launch of the
+ * entry points above is bracketed by a CUDA event pair on its stream; this is
+ * process-global state.  rm_profile_read waits for the recorded events, writes
+ * up to max_records durations (milliseconds) to ms and the matching
+ * newline-separated kernel names to names, clears the records and returns how
+ * many it wrote.
+ */
+void rm_profile_enable(int on);
+int rm_profile_read(char* names, size_t names_bytes, float* ms, int max_records);
+
 #ifdef __cplusplus
 }
 #endif

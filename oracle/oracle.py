@@ -94,6 +94,19 @@ def build_lists(tiles_touched, rect, vs_tetra, grid_h, grid_w, want_keys=False):
     return (idx, ranges, keys) if want_keys else (idx, ranges)
 
 
+def restrict_to_tile_rows(tiles_touched, rect, row0, row1):
+    """Clamp every tet rectangle to tile rows [row0, row1): the lists built from the
+    result are the single-frame lists of those rows."""
+    rect = np.array(_np(rect), dtype=np.int32, copy=True)
+    rect[:, 1] = np.maximum(rect[:, 1], row0)
+    rect[:, 3] = np.minimum(rect[:, 3], row1)
+    h = np.maximum(rect[:, 3] - rect[:, 1], 0)
+    tt = ((rect[:, 2] - rect[:, 0]) * h).astype(np.int32)
+    tt[np.asarray(_np(tiles_touched)) == 0] = 0
+    rect[tt == 0] = 0
+    return tt, rect
+
+
 def _fb_args(dtype, sorted_idx, tile_ranges, indices, vertices, cell_values, jitter):
     return (np.ascontiguousarray(_np(sorted_idx), dtype=np.int32),
             np.ascontiguousarray(_np(tile_ranges), dtype=np.int32),

@@ -14,7 +14,8 @@ RM_STATUS_KEY_OVERFLOW = 2
 
 # every symbol include/rm_b200.h declares
 SYMBOLS = ["rm_strerror", "rm_version", "rm_bin_workspace_bytes", "rm_project_and_bin", "rm_build_tile_lists",
-           "rm_pack_records", "rm_forward", "rm_backward", "rm_vertex_backward"]
+           "rm_pack_records", "rm_forward", "rm_backward", "rm_vertex_backward", "rm_profile_enable",
+           "rm_profile_read"]
 
 
 class RmCamera(C.Structure):
@@ -55,6 +56,9 @@ def load():
     lib.rm_forward.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, vp]
     lib.rm_backward.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, vp, vp, vp, vp]
     lib.rm_vertex_backward.argtypes = [vp, vp, i64, i64, cam, vp, vp, vp, vp, vp]
+    lib.rm_profile_enable.restype = None
+    lib.rm_profile_enable.argtypes = [C.c_int]
+    lib.rm_profile_read.argtypes = [C.c_char_p, sz, C.POINTER(C.c_float), C.c_int]
     for name in SYMBOLS:
         getattr(lib, name)
     _lib = lib
@@ -64,3 +68,17 @@ def load():
 def check(rc):
     if rc != 0:
         raise RuntimeError(f"rm_b200: {load().rm_strerror(rc).decode()} (code {rc})")
+
+
+def profile_enable(on=True):
+    load().rm_profile_enable(1 if on else 0)
+
+
+def profile_read(max_records=4096):
+    """Returns [(kernel name, milliseconds)] recorded since the last read."""
+    lib = load()
+    names = C.create_string_buffer(64 * max_records)
+    ms = (C.c_float * max_records)()
+    n = lib.rm_profile_read(names, len(names), ms, max_records)
+    labels = names.value.decode().split("\n")[:n]
+    return list(zip(labels, [ms[i] for i in range(n)]))

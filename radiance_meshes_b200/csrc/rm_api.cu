@@ -27,6 +27,36 @@ int rm_launch_backward(const int32_t*, const int32_t*, const float*, const RmCam
 
 static thread_local char g_last_error[256] = "";
 
+// ---- optional per-kernel timing ---------------------------------------------
+#include <mutex>
+#include <vector>
+namespace {
+struct ProfRec {
+  const char* name;
+  cudaEvent_t a, b;
+};
+std::mutex g_prof_mu;
+bool g_prof_on = false;
+std::vector<ProfRec> g_prof;
+thread_local int g_prof_open = -1;
+}  // namespace
+
+void rm_prof_begin(const char* name, cudaStream_t st) {
+  if (!g_prof_on) return;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  ProfRec r{name, nullptr, nullptr};
+  if (cudaEventCreate(&r.a) != cudaSuccess || cudaEventCreate(&r.b) != cudaSuccess) return;
+  cudaEventRecord(r.a, st);
+  g_prof.push_back(r);
+  g_prof_open = (int)g_prof.size() - 1;
+}
+void rm_prof_end(cudaStream_t st) {
+  if (!g_prof_on) return;
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  if (g_prof_open >= 0 && g_prof_open < (int)g_prof.size()) cudaEventRecord(g_prof[g_prof_open].b, st);
+  g_prof_open = -1;
+}
+
 void rm_set_last_cuda_error(cudaError_t e, const char* file, int line) {
   snprintf(g_last_error, sizeof(g_last_error), "CUDA error %d (%s) at %s:%d", (int)e, cudaGetErrorString(e), file,
            line);
@@ -80,6 +110,37 @@ const char* rm_strerror(int code) {
 }
 
 int rm_version(void) { return 100; }
+
+void rm_profile_enable(int on) {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  g_prof_on = on != 0;
+}
+
+int rm_profile_read(char* names, size_t names_bytes, float* ms, int max_records) {
+  std::lock_guard<std::mutex> lk(g_prof_mu);
+  int n = 0;
+  size_t off = 0;
+  if (names && names_bytes) names[0] = 0;
+  for (auto& r : g_prof) {
+    float t = 0.f;
+    if (r.a && r.b && cudaEventSynchronize(r.b) == cudaSuccess) cudaEventElapsedTime(&t, r.a, r.b);
+    if (n < max_records) {
+      size_t len = strlen(r.name);
+      if (names && off + len + 2 <= names_bytes) {
+        memcpy(names + off, r.name, len);
+        names[off + len] = '\n';
+        names[off + len + 1] = 0;
+        off += len + 1;
+        if (ms) ms[n] = t;
+        ++n;
+      }
+    }
+    if (r.a) cudaEventDestroy(r.a);
+    if (r.b) cudaEventDestroy(r.b);
+  }
+  g_prof.clear();
+  return n;
+}
 
 size_t rm_bin_workspace_bytes(int64_t n_tets, int64_t n_tiles) {
   if (n_tets < 0 || n_tiles < 0) return 0;

@@ -501,6 +501,7 @@ int rm_launch_bin_finish(int64_t T, const RmCamera* cam, const int32_t* tiles_to
 
   // 1. rank tets by (depth bits, id): 4 stable passes; result ends in buffer 0
   if (T > 0) {
+    RmProfScope prof("rank_tets_radix_sort(12 launches)", st);
     for (int pass = 0; pass < 4; ++pass) {
       int src = pass & 1, dst = src ^ 1;
       int shift = pass * rm::kRadixBits;
@@ -513,6 +514,7 @@ int rm_launch_bin_finish(int64_t T, const RmCamera* cam, const int32_t* tiles_to
   }
   // 2. tile populations -> tile_ranges
   {
+    RmProfScope prof("tile_ranges(6 launches)", st);
     int rows_per_block = 4;  // 128 threads
     rm::k_diff_prefix_x<<<(gh + 1 + rows_per_block - 1) / rows_per_block, 32 * rows_per_block, 0, st>>>(diff, gh, gw);
     rm::k_diff_prefix_y<<<(gw + rows_per_block - 1) / rows_per_block, 32 * rows_per_block, 0, st>>>(diff, gh, gw,
@@ -525,6 +527,7 @@ int rm_launch_bin_finish(int64_t T, const RmCamera* cam, const int32_t* tiles_to
   }
   // 3. inclusive scan of tiles_touched in rank order (culled tets sort last with 0 tiles)
   {
+    RmProfScope prof("rank_order_scan(4 launches)", st);
     int rc = launch_scan(reinterpret_cast<const uint32_t*>(tiles_touched), ord[0], T, bsum, cum, 1, total_keys, st);
     if (rc) return rc;
     rm::k_finish_info<<<1, 1, 0, st>>>(info, total_keys);
@@ -546,14 +549,18 @@ int rm_launch_build_lists(const int32_t* rect, const int32_t* tile_ranges, int64
   const int2* ranges = reinterpret_cast<const int2*>(tile_ranges);
   RM_CUDA_CHECK(cudaMemsetAsync(cursor, 0, 4 * (size_t)(G + 1), st));
   int64_t nb = (n_keys + rm::kScatterTile - 1) / rm::kScatterTile;
-  rm::k_scatter_ranks<<<(unsigned)nb, rm::kScatterThreads, 0, st>>>(cum, order, (int32_t)T,
-                                                                     reinterpret_cast<const int4*>(rect), ranges,
-                                                                     cursor, gw, n_keys, scratch);
+  {
+    RmProfScope prof("k_scatter_ranks", st);
+    rm::k_scatter_ranks<<<(unsigned)nb, rm::kScatterThreads, 0, st>>>(cum, order, (int32_t)T,
+                                                                       reinterpret_cast<const int4*>(rect), ranges,
+                                                                       cursor, gw, n_keys, scratch);
+  }
   RM_CUDA_CHECK(cudaPeekAtLastError());
   // size classes: (0, 2048] in 8 KB of shared memory, (2048, 32768] in 128 KB, larger in global memory
   const uint32_t small_cap = 2048, big_cap = 32768;
   RM_CUDA_CHECK(cudaFuncSetAttribute(rm::k_segment_sort_smem, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)(big_cap * 4)));
+  RmProfScope prof("k_segment_sort(3 launches)", st);
   rm::k_segment_sort_smem<<<(unsigned)G, 256, small_cap * 4, st>>>(ranges, scratch, order, sorted_idx, 0, small_cap);
   rm::k_segment_sort_smem<<<(unsigned)G, 1024, big_cap * 4, st>>>(ranges, scratch, order, sorted_idx, small_cap,
                                                                   big_cap);

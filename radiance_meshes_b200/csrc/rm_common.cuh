@@ -18,6 +18,16 @@
 void rm_set_last_cuda_error(cudaError_t e, const char* file, int line);
 int rm_bind_device(const void* device_ptr);
 
+// Optional per-kernel timing (rm_profile_enable): a scope records a CUDA event
+// pair on the launch stream around the launches it encloses.
+void rm_prof_begin(const char* name, cudaStream_t st);
+void rm_prof_end(cudaStream_t st);
+struct RmProfScope {
+  cudaStream_t st;
+  RmProfScope(const char* name, cudaStream_t s) : st(s) { rm_prof_begin(name, s); }
+  ~RmProfScope() { rm_prof_end(st); }
+};
+
 namespace rm {
 
 constexpr int kRecordFloats = RM_RECORD_FLOATS;

@@ -331,6 +331,7 @@ int rm_launch_project(const int32_t* indices, int64_t T, const float* vertices, 
   int64_t n = T > 3 * V ? T : 3 * V;
   if (n == 0) return RM_OK;
   unsigned blocks = (unsigned)((n + 255) / 256);
+  RmProfScope prof("k_project", st);
   rm::k_project<<<blocks, 256, 0, st>>>(indices, T, vertices, V, *cam, tiles_touched, reinterpret_cast<int4*>(rect),
                                         vs_tetra, circumcenter, depth_keys, order_in, tile_diff, info);
   RM_CUDA_CHECK(cudaPeekAtLastError());
@@ -342,6 +343,7 @@ int rm_launch_vertex_backward(const int32_t* indices, const float* vertices, int
                               cudaStream_t st) {
   if (T == 0) return RM_OK;
   unsigned blocks = (unsigned)((T + 255) / 256);
+  RmProfScope prof("k_vertex_backward", st);
   rm::k_vertex_backward<<<blocks, 256, 0, st>>>(indices, vertices, T, *cam, tiles_touched, g_vs, g_cc, vgrad);
   RM_CUDA_CHECK(cudaPeekAtLastError());
   return RM_OK;

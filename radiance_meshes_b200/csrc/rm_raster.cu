@@ -471,7 +471,7 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
       if (in_range && u.inside && e < nc) {
         if (slab_test(rec, d, min_t, ev) && integrate(rec, d, min_t, ev)) {
           hit = true;
-          const float4 cgv = rec[4], cbv = rec[5];
+          const float4 cbv = rec[5];
           const float dens = cbv.w;
           // undo: state before this tet
           logT += ev.tau;
@@ -644,6 +644,7 @@ static inline void unit_grid(const RmCamera* cam, int* subs, int64_t* n_units, u
 int rm_launch_pack(const int32_t* indices, const float* vertices, const float* cell, int64_t T, const RmCamera* cam,
                    const int32_t* tiles_touched, float* records, cudaStream_t st) {
   if (T == 0) return RM_OK;
+  RmProfScope prof("k_pack_records", st);
   rm::k_pack_records<<<(unsigned)((T + 255) / 256), 256, 0, st>>>(indices, vertices, cell, T, *cam, tiles_touched,
                                                                   reinterpret_cast<float4*>(records));
   RM_CUDA_CHECK(cudaPeekAtLastError());
@@ -657,6 +658,7 @@ int rm_launch_forward(const int32_t* list, const int32_t* ranges, const float* r
   unsigned blocks;
   unit_grid(cam, &subs, &n_units, &blocks);
   if (n_units == 0) return RM_OK;
+  RmProfScope prof("k_forward", st);
   rm::k_forward<<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
       list, reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam,
       reinterpret_cast<const float2*>(jitter), reinterpret_cast<float4*>(out_img), dist_img, n_contrib, subs,
@@ -678,11 +680,13 @@ int rm_launch_backward(const int32_t* list, const int32_t* ranges, const float* 
   unsigned blocks;
   unit_grid(cam, &subs, &n_units, &blocks);
   if (n_units > 0) {
+    RmProfScope prof("k_backward", st);
     rm::k_backward<<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
         list, reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam,
         reinterpret_cast<const float2*>(jitter), reinterpret_cast<const float4*>(out_img), dist_img, n_contrib,
         reinterpret_cast<const float4*>(g_img), g_dist, grec, subs, n_units);
   }
+  RmProfScope prof2("k_backward_finish", st);
   rm::k_backward_finish<<<(unsigned)((T + 255) / 256), 256, 0, st>>>(indices, vertices, cell, T, *cam,
                                                                      reinterpret_cast<const float4*>(grec), vgrad,
                                                                      cgrad);
