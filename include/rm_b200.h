@@ -27,6 +27,7 @@ extern "C" {
 #define RM_ERR_CUDA (-2)
 #define RM_ERR_TOO_MANY_KEYS (-3)
 #define RM_ERR_WORKSPACE (-4)
+#define RM_ERR_STATIC_SCRATCH (-5)
 
 /* bits of RmBinInfo.status */
 #define RM_STATUS_NAN_VERTEX 1u   /* a vertex coordinate is NaN (tile_shader_slang.py:78 asserts on this) */
@@ -141,6 +142,37 @@ int rm_backward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, con
 int rm_vertex_backward(const int32_t* indices, const float* vertices, int64_t n_tets, int64_t n_vertices,
                        const RmCamera* cam, const int32_t* tiles_touched, const float* grad_vs_tetra,
                        const float* grad_circumcenter, float* vertices_grad, void* stream);
+
+/*
+ * Backward integration without any caller-provided or allocated scratch.
+ * No counterpart in the reference.
+ *
+ * Some hosts of this library cannot allocate device memory at the point where
+ * the backward pass runs: a plugin that is handed fixed input/output buffers by
+ * an engine that owns the allocator, code running under a memory budget that was
+ * fixed before the frame, or a callback in which cudaMalloc is forbidden.  This
+ * variant of rm_backward takes the same inputs and outputs but keeps its one
+ * scratch buffer (the per-tet record-gradient rows, RM_RECORD_FLOATS floats per
+ * tet) in a static device array inside the library, RM_STATIC_SCRATCH_MAX_TETS
+ * rows = 12 MiB, which every GPU that loads the library holds until the process
+ * exits.  It calls no cudaMalloc/cudaFree or other allocating routine.
+ *
+ *   - n_tets > RM_STATIC_SCRATCH_MAX_TETS is rejected with RM_ERR_STATIC_SCRATCH.
+ *   - The first call on each device looks up the array's device address; make
+ *     that first call outside any stream capture.
+ *   - All calls on a device share the array.  Each call clears the rows it
+ *     uses, but two calls whose kernels overlap on the GPU (different streams)
+ *     race on it: serialise them.
+ * Results equal rm_backward's up to the order of floating-point atomics.
+ */
+#define RM_STATIC_SCRATCH_MAX_TETS 131072
+int rm_backward_static_scratch(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, const float* records,
+                               const RmCamera* cam, const float* ray_jitter, const float* output_img,
+                               const float* distortion_img, const int32_t* n_contributors,
+                               const float* grad_output_img, const float* grad_distortion_img,
+                               const int32_t* indices, const float* vertices, const float* cell_values,
+                               int64_t n_tets, int64_t n_vertices, float* vertices_grad, float* cell_values_grad,
+                               void* stream);
 
 /*
  * Optional per-kernel timing, a measurement aid with no counterpart in the

@@ -105,6 +105,8 @@ const char* rm_strerror(int code) {
     case RM_ERR_CUDA: return g_last_error[0] ? g_last_error : "CUDA error";
     case RM_ERR_TOO_MANY_KEYS: return "more than 2^31-1 (tile, tet) pairs";
     case RM_ERR_WORKSPACE: return "workspace too small or misaligned";
+    case RM_ERR_STATIC_SCRATCH:
+      return "n_tets exceeds RM_STATIC_SCRATCH_MAX_TETS (131072): use rm_backward with a caller-provided scratch";
     default: return "unknown error";
   }
 }

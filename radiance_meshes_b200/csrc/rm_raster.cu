@@ -693,3 +693,79 @@ int rm_launch_backward(const int32_t* list, const int32_t* ranges, const float* 
   RM_CUDA_CHECK(cudaPeekAtLastError());
   return RM_OK;
 }
+
+// ----------------------------------------------------------------------------
+// rm_backward_static_scratch: the backward pass for callers that may not
+// allocate device memory.  Its only scratch, the per-tet record-gradient rows,
+// lives in the file-scope device array below instead of a caller buffer.
+// ----------------------------------------------------------------------------
+#include <mutex>
+
+static __device__ __align__(256) float g_static_grad_records[(size_t)RM_STATIC_SCRATCH_MAX_TETS * RM_RECORD_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+float* g_static_addr[kMaxDevices] = {nullptr};
+}  // namespace
+
+extern "C" int rm_backward_static_scratch(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges,
+                                          const float* records, const RmCamera* cam, const float* ray_jitter,
+                                          const float* output_img, const float* distortion_img,
+                                          const int32_t* n_contributors, const float* grad_output_img,
+                                          const float* grad_distortion_img, const int32_t* indices,
+                                          const float* vertices, const float* cell_values, int64_t n_tets,
+                                          int64_t n_vertices, float* vertices_grad, float* cell_values_grad,
+                                          void* stream) {
+  if (n_tets < 0 || n_vertices < 0 || !cam) return RM_ERR_INVALID_ARG;
+  if (n_tets > RM_STATIC_SCRATCH_MAX_TETS) return RM_ERR_STATIC_SCRATCH;
+  if (!tile_ranges || !ray_jitter || !output_img || !distortion_img || !n_contributors || !grad_output_img ||
+      !grad_distortion_img || !vertices_grad)
+    return RM_ERR_INVALID_ARG;
+  if (n_tets > 0 && (!indices || !vertices || !cell_values || !cell_values_grad || !records))
+    return RM_ERR_INVALID_ARG;
+  if (cam->image_height <= 0 || cam->image_width <= 0 || cam->tile_height <= 0 || cam->tile_width <= 0 ||
+      cam->tile_row_begin < 0 || cam->tile_row_end > cam->grid_height || cam->tile_row_begin > cam->tile_row_end)
+    return RM_ERR_INVALID_ARG;
+  auto misaligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; };
+  if (misaligned(output_img) || misaligned(grad_output_img) || misaligned(records) || misaligned(indices))
+    return RM_ERR_WORKSPACE;
+  int rc = rm_bind_device(vertices_grad);  // makes the device that owns the buffers current
+  if (rc) return rc;
+  // Set-up, once per device, with that device current: the array's name is a
+  // host-side handle, the kernels need its device address.
+  int dev = -1;
+  RM_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return RM_ERR_INVALID_ARG;
+  float* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (!g_static_addr[dev]) {
+      void* addr = nullptr;
+      RM_CUDA_CHECK(cudaGetSymbolAddress(&addr, g_static_grad_records));
+      g_static_addr[dev] = static_cast<float*>(addr);
+    }
+    scratch = g_static_addr[dev];
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The array keeps the previous call's sums: clear the rows this call accumulates into.
+  RM_CUDA_CHECK(cudaMemsetAsync(vertices_grad, 0, sizeof(float) * 3 * (size_t)n_vertices, st));
+  if (n_tets == 0) return RM_OK;
+  RM_CUDA_CHECK(cudaMemsetAsync(scratch, 0, sizeof(float) * RM_RECORD_FLOATS * (size_t)n_tets, st));
+  int subs;
+  int64_t n_units;
+  unsigned blocks;
+  unit_grid(cam, &subs, &n_units, &blocks);
+  if (n_units > 0) {
+    rm::k_backward<<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
+        sorted_tetra_idx, reinterpret_cast<const int2*>(tile_ranges), reinterpret_cast<const float4*>(records), *cam,
+        reinterpret_cast<const float2*>(ray_jitter), reinterpret_cast<const float4*>(output_img), distortion_img,
+        n_contributors, reinterpret_cast<const float4*>(grad_output_img), grad_distortion_img, scratch, subs,
+        n_units);
+  }
+  rm::k_backward_finish<<<(unsigned)((n_tets + 255) / 256), 256, 0, st>>>(
+      indices, vertices, cell_values, n_tets, *cam, reinterpret_cast<const float4*>(scratch), vertices_grad,
+      cell_values_grad);
+  RM_CUDA_CHECK(cudaPeekAtLastError());
+  return RM_OK;
+}
