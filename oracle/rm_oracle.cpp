@@ -907,6 +907,44 @@ int or_sensitive_pixels(const int32_t* sorted_idx, const int32_t* tile_ranges, c
   return 0;
 }
 
+// Work statistics of the forward walk, per pixel: list entries walked, ray/tet
+// hits with positive optical depth, and slab-test hits of zero-density tets.
+int or_walk_stats(const int32_t* sorted_idx, const int32_t* tile_ranges, const int32_t* indices,
+                  const float* vertices, const float* cell, const OrCamera* ocam, const float* jitter,
+                  int32_t* walked, int32_t* hits, int32_t* empty_hits, int row0, int row1, int nthreads) {
+  Cam<float> cam = load_cam<float>(ocam);
+  const int W = cam.Wd;
+#ifdef _OPENMP
+  if (nthreads > 0) omp_set_num_threads(nthreads);
+#endif
+#pragma omp parallel for schedule(dynamic, 16)
+  for (int64_t p = (int64_t)row0 * W; p < (int64_t)row1 * W; ++p) {
+    int y = int(p / W), x = int(p % W);
+    int tile = (y / cam.tile_h) * cam.grid_w + (x / cam.tile_w);
+    int64_t s0 = tile_ranges[2 * tile], s1 = tile_ranges[2 * tile + 1];
+    V3<float> o, d;
+    get_ray(cam, float(x) + jitter[2 * p], float(y) + jitter[2 * p + 1], o, d);
+    State<float> s = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+    int nw = 0, nh = 0, ne = 0;
+    for (int64_t j = s0; j < s1; ++j) {
+      ++nw;
+      Tet<float> t = load_tet<float>(sorted_idx[j], indices, vertices, cell);
+      Ctrl<float> c;
+      if (evaluate_tet(t, o, d, c)) {
+        if (c.a > 0.f) {
+          ++nh;
+          update_state(s, c);
+          if (s.logT < -5.5f) break;
+        } else {
+          ++ne;
+        }
+      }
+    }
+    walked[p] = nw; hits[p] = nh; empty_hits[p] = ne;
+  }
+  return 0;
+}
+
 // Reverse of stage 1 with respect to the vertices: gradients of
 // vs_tetra[:,2] (clamped circumsphere power) and circumcenter, for tets that
 // were not culled (tiles_touched > 0).  Restates what Slang's autodiff derives

@@ -147,31 +147,54 @@ struct Eval {
 };
 
 __device__ __forceinline__ bool slab_test(const float4* __restrict__ rec, f3 d, float min_t, Eval& e) {
-  float te = -1e30f, tx = 1e30f;
+  // Distances are first taken from the camera position (u = -D/den) and shifted
+  // by min_t afterwards: t = -(D + min_t*den)/den = u - min_t.
+  float ue = -1e30f, ux = 1e30f;
   int ie = -1, ix = -1;
   bool miss = false;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     float4 p = rec[i];
     float den = p.x * d.x + p.y * d.y + p.z * d.z;
-    float dist = fmaf(min_t, den, p.w);
     if (fabsf(den) < 1e-10f) {
-      miss = miss || (dist > 0.0f);
+      miss = miss || (fmaf(min_t, den, p.w) > 0.0f);
     } else {
-      float t = -dist / den;
+      float u = __fdividef(-p.w, den);
       if (den < 0.0f) {
-        if (t > te) { te = t; ie = i; }
+        if (u > ue) { ue = u; ie = i; }
       } else {
-        if (t < tx) { tx = t; ix = i; }
+        if (u < ux) { ux = u; ix = i; }
       }
     }
   }
+  const float te = ue - min_t, tx = ux - min_t;
   if (miss || te > tx || tx <= 0.0f) return false;
   e.te = te; e.tx = tx; e.ie = ie; e.ix = ix;
   e.enter = fmaxf(te, 0.0f);
   e.exit = fmaxf(tx, e.enter);
   e.dt = fmaxf(e.exit - e.enter, 0.0f);
   return true;
+}
+
+// Weights of the closed-form segment integral for optical depth x > 0:
+//   alpha = exp(-x), phi = (1 - alpha)/x, w0 = phi - alpha, w1 = 1 - phi.
+// Below x = 0.25 the differences cancel, so w0 and w1 come from their Taylor
+// series (truncation < 1e-7 relative); above, from the fast exponential.
+__device__ __forceinline__ void segment_weights(float x, float& alpha, float& phi, float& w0, float& w1) {
+  alpha = __expf(-x);
+  if (x < 0.25f) {
+    // w1 = x/2 - x^2/6 + x^3/24 - x^4/120 + x^5/720 - x^6/5040
+    w1 = x * fmaf(x, fmaf(x, fmaf(x, fmaf(x, fmaf(x, -1.0f / 5040.0f, 1.0f / 720.0f), -1.0f / 120.0f), 1.0f / 24.0f),
+                          -1.0f / 6.0f), 0.5f);
+    // w0 = x/2 - x^2/3 + x^3/8 - x^4/30 + x^5/144 - x^6/840
+    w0 = x * fmaf(x, fmaf(x, fmaf(x, fmaf(x, fmaf(x, -1.0f / 840.0f, 1.0f / 144.0f), -1.0f / 30.0f), 0.125f),
+                          -1.0f / 3.0f), 0.5f);
+    phi = 1.0f - w1;
+  } else {
+    phi = __fdividef(1.0f - alpha, x);
+    w0 = phi - alpha;
+    w1 = 1.0f - phi;
+  }
 }
 
 // returns false if the segment contributes nothing (optical depth not > 0)
@@ -182,11 +205,7 @@ __device__ __forceinline__ bool integrate(const float4* __restrict__ rec, f3 d, 
   e.gd = cg.x * d.x + cg.y * d.y + cg.z * d.z;
   e.oe = fmaf(e.enter + min_t, e.gd, cg.w);
   e.ox = fmaf(e.exit + min_t, e.gd, cg.w);
-  float em1 = expm1f(-e.tau);
-  e.alpha = 1.0f + em1;
-  e.phi = (e.tau < 1e-6f) ? 1.0f - 0.5f * e.tau : -em1 / e.tau;
-  e.w0 = e.phi - e.alpha;
-  e.w1 = 1.0f - e.phi;
+  segment_weights(e.tau, e.alpha, e.phi, e.w0, e.w1);
   e.cr = e.w0 * (cb.x + e.ox) + e.w1 * (cb.x + e.oe);
   e.cg = e.w0 * (cb.y + e.ox) + e.w1 * (cb.y + e.oe);
   e.cb = e.w0 * (cb.z + e.ox) + e.w1 * (cb.z + e.oe);
@@ -294,10 +313,14 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
     }
     cp_async_wait<1>();
     __syncwarp();
+    // Tets of zero density are walked (they count in n_contributors) but can never
+    // contribute or terminate a pixel: only the entries flagged here are evaluated.
+    const bool nonzero = (c * kChunk + lane16 < u.len) && cur[lane16 * 6 + 5].w > 0.0f;
+    unsigned todo = (__ballot_sync(0xffffffffu, nonzero) >> (16 * half)) & 0xFFFFu;
     if (active) {
-      const int cnt = min(kChunk, u.len - c * kChunk);
-      for (int j = 0; j < cnt; ++j) {
-        ++contrib;
+      while (todo) {
+        const int j = __ffs(todo) - 1;
+        todo &= todo - 1;
         const float4* rec = cur + j * 6;
         Eval e;
         if (slab_test(rec, d, min_t, e) && integrate(rec, d, min_t, e)) {
@@ -315,6 +338,7 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
           dv = fmaf(dens * dens, e.dt * (1.0f / 3.0f), dv);
           if (logT < -5.5f) {
             active = false;
+            contrib = c * kChunk + j + 1;  // entries walked, the terminating one included
             break;
           }
         }
@@ -326,6 +350,7 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
     if (act == 0) break;
   }
   cp_async_wait<0>();
+  if (active) contrib = u.len;  // walked the whole list
 
   if (u.inside) {
     out_img[pix] = make_float4(sr, sg, sb, logT);
@@ -458,19 +483,32 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
     const int c = nchunks - 1 - k;
     const float4* cur = stage[warp][half][k & 1];
     const int* cur_id = stage_id[warp][half][k & 1];
-    // both halves step through 16 slots; a half whose list is exhausted idles
-    for (int j = kChunk - 1; j >= 0; --j) {
+    // Staged entries with non-zero density, per half (zero-density tets never
+    // contribute).  Both halves step in lock-step through their own set bits,
+    // last entry first; a half that runs out idles.
+    const bool nonzero = c >= 0 && c * kChunk + lane16 < nmax && cur[lane16 * 6 + 5].w > 0.0f;
+    unsigned todo = (__ballot_sync(0xffffffffu, nonzero) >> (16 * half)) & 0xFFFFu;
+    const int steps = max(__popc(todo), __shfl_xor_sync(0xffffffffu, __popc(todo), 16));
+    for (int step = 0; step < steps; ++step) {
+      int j = 0;
+      bool in_range = false;
+      if (todo) {
+        j = 31 - __clz(todo);
+        todo &= ~(1u << j);
+        in_range = true;
+      }
       const int e = c * kChunk + j;
-      const bool in_range = c >= 0 && e < nmax;
       const float4* rec = cur + j * 6;
+      bool hit = false;
+      Eval ev;
+      if (in_range && u.inside && e < nc) hit = slab_test(rec, d, min_t, ev) && integrate(rec, d, min_t, ev);
+      const unsigned hits = __ballot_sync(0xffffffffu, hit);
+      if (hits == 0) continue;
       float g[24];
 #pragma unroll
       for (int q = 0; q < 24; ++q) g[q] = 0.0f;
-      bool hit = false;
-      Eval ev;
-      if (in_range && u.inside && e < nc) {
-        if (slab_test(rec, d, min_t, ev) && integrate(rec, d, min_t, ev)) {
-          hit = true;
+      {
+        if (hit) {
           const float4 cbv = rec[5];
           const float dens = cbv.w;
           // undo: state before this tet
@@ -507,9 +545,8 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
           g_exit = fmaf(g_ox, ev.gd, g_exit);
           g_enter = fmaf(g_oe, ev.gd, g_enter);
           const float g_phi = g_w0 - g_w1;
-          float dphi;
-          if (ev.tau < 1e-6f) dphi = -0.5f;
-          else dphi = (ev.alpha - ev.phi) / ev.tau;  // exp(-x)/x + expm1(-x)/x^2
+          float dphi;  // d phi / d tau = (alpha - phi) / tau = -w0 / tau
+          dphi = -__fdividef(ev.w0, ev.tau);
           const float g_tau = g_phi * dphi + g_w0 * ev.alpha + g_a;
           g_dens = fmaf(g_tau, ev.dt, g_dens);
           const float g_dt = g_tau * dens;
@@ -544,8 +581,15 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
           g[23] = g_dens;
         }
       }
-      const unsigned hits = __ballot_sync(0xffffffffu, hit);
-      if (hits) {
+      if (max(__popc(hits & 0xFFFFu), __popc(hits >> 16)) <= 2) {
+        // one or two pixels of a tile hit this tet: their lanes add the 24 sums directly
+        if (hit) {
+          float* row = grec + (int64_t)cur_id[j] * 24;
+#pragma unroll
+          for (int q = 0; q < 24; ++q)
+            if (g[q] != 0.0f) atomicAdd(row + q, g[q]);
+        }
+      } else {
         float o0, o1;
         int f0;
         halfwarp_transpose_reduce<24>(g, lane16, o0, o1, f0);
