@@ -13,7 +13,7 @@ RM_STATUS_NAN_VERTEX = 1
 RM_STATUS_KEY_OVERFLOW = 2
 
 # every symbol include/rm_b200.h declares
-SYMBOLS = ["rm_strerror", "rm_version", "rm_bin_workspace_bytes", "rm_project_and_bin", "rm_build_tile_lists",
+SYMBOLS = ["rm_strerror", "rm_version", "rm_bin_workspace_bytes", "rm_list_scratch_bytes", "rm_project_and_bin", "rm_build_tile_lists",
            "rm_pack_records", "rm_forward", "rm_backward", "rm_vertex_backward", "rm_profile_enable",
            "rm_profile_read", "rm_backward_static_scratch"]
 RM_STATIC_SCRATCH_MAX_TETS = 131072
@@ -53,7 +53,9 @@ def load():
     lib.rm_bin_workspace_bytes.restype = sz
     lib.rm_bin_workspace_bytes.argtypes = [i64, i64]
     lib.rm_project_and_bin.argtypes = [vp, i64, vp, i64, cam, vp, vp, vp, vp, vp, vp, vp, sz, vp]
-    lib.rm_build_tile_lists.argtypes = [vp, vp, i64, cam, i64, vp, vp, vp, vp]
+    lib.rm_list_scratch_bytes.restype = sz
+    lib.rm_list_scratch_bytes.argtypes = [i64, i64]
+    lib.rm_build_tile_lists.argtypes = [vp, vp, i64, cam, i64, vp, vp, sz, vp, vp]
     lib.rm_pack_records.argtypes = [vp, vp, vp, i64, cam, vp, vp, vp]
     lib.rm_forward.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, vp]
     lib.rm_backward.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, vp, vp, vp, vp]

@@ -11,10 +11,10 @@
 //   2. tile populations come from a 2-D difference array (4 atomics per tet,
 //      written by the projection kernel) and two prefix passes; an exclusive
 //      scan turns them into tile_ranges directly;
-//   3. every (tile, tet) pair writes the tet's 32-bit RANK into its tile's
-//      segment (load-balanced over pairs, slot taken with one atomic);
-//   4. each tile segment is sorted by rank in shared memory and mapped back to
-//      tet ids.
+//   3. the (tile, tet) pairs, generated in rank order and load-balanced over
+//      pairs, go through a stable two-pass counting sort on the tile id alone
+//      (17 bits at 1080p, against the reference's 49-bit keys); stability keeps
+//      every tile's segment in rank order, so nothing is sorted per tile.
 //
 // Ascending rank inside a tile is ascending (depth bits, tet id), which is what
 // the reference's stable sort produces because it emits pairs in tet order.
@@ -281,124 +281,262 @@ __global__ void k_finish_info(RmBinInfo* info, const unsigned long long* total_k
 }
 
 // ---------------------------------------------------------------------------
-// Scatter: one work item per (tile, tet) pair, items numbered in the
-// reference's emission order (tets by rank, tile rows then columns), so the
-// load is perfectly balanced whatever the rectangle sizes.
-//   cum[r]   inclusive scan of tiles_touched in rank order
-//   order[r] tet id of rank r
+// Tile lists by a stable two-pass counting sort on the tile id.
+//
+// Work items are the (tile, tet) pairs numbered in the reference's emission
+// order (tets by rank, then tile rows, then columns): item j belongs to the
+// rank r with cum[r-1] <= j < cum[r].  Because the items are generated in rank
+// order and both passes are stable, sorting them by tile id (low digit first,
+// then high digit) leaves every tile's segment ordered by rank, i.e. by
+// (depth bits, tet id): no per-tile sort, no atomics, deterministic.
+//   pass 1: generate items, stable split on the low  b1 bits of the tile id -> (rank, tile) pairs
+//   pass 2: stable split on the high b2 bits -> sorted_tetra_idx = order[rank]
+// Each pass is: per-block digit histogram, per-digit scan over the blocks,
+// stable scatter (warp-level match ranking, warps own consecutive item spans).
 // ---------------------------------------------------------------------------
-constexpr int kScatterThreads = 256;
-constexpr int kScatterItems = 8;
-constexpr int kScatterTile = kScatterThreads * kScatterItems;
+constexpr int kBinThreads = 256;
+constexpr int kBinItems = 16;
+constexpr int kBinTile = kBinThreads * kBinItems;  // items per block
+constexpr int kBinWarps = kBinThreads / 32;
+constexpr int kBinSpan = 32 * kBinItems;  // consecutive items owned by one warp
 
-__global__ void __launch_bounds__(kScatterThreads)
-k_scatter_ranks(const uint32_t* __restrict__ cum, const uint32_t* __restrict__ order, int32_t n_ranked,
-                const int4* __restrict__ rect, const int2* __restrict__ ranges, uint32_t* __restrict__ cursor,
-                int grid_w, int64_t n_keys, uint32_t* __restrict__ seg) {
-  __shared__ uint32_t win[kScatterTile + 1];
-  __shared__ int s_r0;
-  const int64_t j0 = (int64_t)blockIdx.x * kScatterTile;
-  const int64_t j1 = min(j0 + (int64_t)kScatterTile, n_keys);
+template <int THREADS>
+__device__ __forceinline__ uint32_t block_exclusive_maxscan(uint32_t v, uint32_t* smem /* THREADS/32 */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    uint32_t n = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc = max(inc, n);
+  }
+  if (lane == 31) smem[warp] = inc;
+  __syncthreads();
+  uint32_t prev = 0;
+  for (int w = 0; w < warp; ++w) prev = max(prev, smem[w]);
+  uint32_t up = __shfl_up_sync(0xffffffffu, inc, 1);
+  uint32_t ex = lane ? max(prev, up) : prev;
+  __syncthreads();
+  return ex;
+}
+
+// Owner table of the block's items: after this call item jl (0 <= jl < items of the
+// block) belongs to rank *r0 + own[jl]; win[i] = cum[*r0 + i].
+__device__ __forceinline__ void owners_of_items(const uint32_t* __restrict__ cum, int n_ranked, int64_t j0,
+                                                uint32_t* win /* kBinTile+1 */, uint16_t* own /* kBinTile */,
+                                                uint32_t* s_misc /* 16 words */) {
   if (threadIdx.x == 0) {
-    // first rank r with cum[r] > j0
-    int lo = 0, hi = n_ranked;
+    int lo = 0, hi = n_ranked;  // first rank with cum[r] > j0
     while (lo < hi) {
       int mid = (lo + hi) >> 1;
       if ((int64_t)cum[mid] > j0) hi = mid; else lo = mid + 1;
     }
-    s_r0 = lo;
+    s_misc[8] = (uint32_t)lo;
+    s_misc[9] = lo > 0 ? cum[lo - 1] : 0u;  // items before rank r0
+  }
+  for (int i = threadIdx.x; i < kBinTile; i += kBinThreads) own[i] = 0;
+  __syncthreads();
+  const int r0 = (int)s_misc[8];
+  for (int i = threadIdx.x; i <= kBinTile; i += kBinThreads) {
+    int r = r0 + i;
+    uint32_t c = r < n_ranked ? cum[r] : 0xFFFFFFFFu;
+    win[i] = c;
+    // rank r0+i+1 starts at item c (visible tets have at least one item, so starts are distinct)
+    int64_t start = (int64_t)c - j0;
+    if (c != 0xFFFFFFFFu && start < kBinTile && r + 1 < n_ranked) own[start] = (uint16_t)(i + 1);
   }
   __syncthreads();
-  const int r0 = s_r0;
-  // window of inclusive sums: at most one rank per item plus one
-  for (int i = threadIdx.x; i <= kScatterTile; i += kScatterThreads) {
-    int r = r0 + i;
-    win[i] = r < n_ranked ? cum[r] : 0xFFFFFFFFu;
+  // inclusive max-scan of own[], thread t owning items [16t, 16t+16)
+  uint32_t loc[kBinItems];
+  uint32_t m = 0;
+#pragma unroll
+  for (int k = 0; k < kBinItems; ++k) {
+    m = max(m, (uint32_t)own[threadIdx.x * kBinItems + k]);
+    loc[k] = m;
+  }
+  uint32_t ex = block_exclusive_maxscan<kBinThreads>(m, s_misc);
+#pragma unroll
+  for (int k = 0; k < kBinItems; ++k) own[threadIdx.x * kBinItems + k] = (uint16_t)max(ex, loc[k]);
+  __syncthreads();
+}
+
+// tile id and rank of local item jl
+__device__ __forceinline__ void item_tile(int jl, int64_t j0, int r0, uint32_t before_r0, const uint32_t* win,
+                                          const uint16_t* own, const uint32_t* __restrict__ order,
+                                          const int4* __restrict__ rect, int grid_w, uint32_t& tile, uint32_t& rank) {
+  const int i = own[jl];
+  rank = (uint32_t)(r0 + i);
+  const uint32_t excl = i > 0 ? win[i - 1] : before_r0;
+  const uint32_t local = (uint32_t)(j0 + jl - excl);
+  const int4 rc = __ldg(rect + order[rank]);
+  const uint32_t w = (uint32_t)(rc.z - rc.x);
+  const uint32_t dy = local / w;
+  tile = (rc.y + dy) * grid_w + rc.x + (local - dy * w);
+}
+
+__global__ void __launch_bounds__(kBinThreads)
+k_tile_hist1(const uint32_t* __restrict__ cum, const uint32_t* __restrict__ order, int n_ranked,
+             const int4* __restrict__ rect, int grid_w, int64_t n_keys, uint32_t bins, uint32_t* __restrict__ hist,
+             int nblk) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint32_t* win = reinterpret_cast<uint32_t*>(smem_raw);
+  uint32_t* s_misc = win + kBinTile + 4;
+  uint16_t* own = reinterpret_cast<uint16_t*>(s_misc + 16);
+  uint32_t* h = reinterpret_cast<uint32_t*>(own + kBinTile);
+  const int64_t j0 = (int64_t)blockIdx.x * kBinTile;
+  const int cnt = (int)min((int64_t)kBinTile, n_keys - j0);
+  for (uint32_t i = threadIdx.x; i < bins; i += kBinThreads) h[i] = 0;
+  owners_of_items(cum, n_ranked, j0, win, own, s_misc);
+  const int r0 = (int)s_misc[8];
+  const uint32_t before = s_misc[9];
+  for (int jl = threadIdx.x; jl < cnt; jl += kBinThreads) {
+    uint32_t tile, rank;
+    item_tile(jl, j0, r0, before, win, own, order, rect, grid_w, tile, rank);
+    atomicAdd(&h[tile & (bins - 1)], 1u);
+  }
+  __syncthreads();
+  for (uint32_t i = threadIdx.x; i < bins; i += kBinThreads) hist[(int64_t)i * nblk + blockIdx.x] = h[i];
+}
+
+__global__ void __launch_bounds__(kBinThreads)
+k_tile_hist2(const uint2* __restrict__ pairs, int64_t n, int shift, uint32_t bins, uint32_t* __restrict__ hist,
+             int nblk) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint32_t* h = reinterpret_cast<uint32_t*>(smem_raw);
+  for (uint32_t i = threadIdx.x; i < bins; i += kBinThreads) h[i] = 0;
+  __syncthreads();
+  const int64_t base = (int64_t)blockIdx.x * kBinTile;
+#pragma unroll
+  for (int k = 0; k < kBinItems; ++k) {
+    int64_t i = base + k * kBinThreads + threadIdx.x;
+    if (i < n) atomicAdd(&h[pairs[i].y >> shift], 1u);
+  }
+  __syncthreads();
+  for (uint32_t i = threadIdx.x; i < bins; i += kBinThreads) hist[(int64_t)i * nblk + blockIdx.x] = h[i];
+}
+
+// Stable placement of the block's items given their digits.  cnt is [kBinWarps][bins]
+// (zeroed by the caller), dbase [bins].  Returns each item's destination in pos[].
+__device__ __forceinline__ void stable_positions(const uint32_t (&digit)[kBinItems], const bool (&valid)[kBinItems],
+                                                 uint32_t bins, const uint32_t* __restrict__ hist,
+                                                 const uint32_t* __restrict__ digit_total, int nblk, uint32_t* cnt,
+                                                 uint32_t* dbase, uint32_t* s_scan, uint32_t (&pos)[kBinItems]) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // global base of each digit: exclusive scan of the digit totals + this block's offset in the digit's row
+  {
+    const uint32_t per = bins > kBinThreads ? bins / kBinThreads : 1;
+    uint32_t s = 0;
+    for (uint32_t q = 0; q < per; ++q) {
+      uint32_t dgt = threadIdx.x * per + q;
+      if (dgt < bins) s += digit_total[dgt];
+    }
+    uint32_t total;
+    uint32_t ex = block_exclusive_scan<kBinThreads>(s, &total, s_scan);
+    for (uint32_t q = 0; q < per; ++q) {
+      uint32_t dgt = threadIdx.x * per + q;
+      if (dgt < bins) {
+        dbase[dgt] = ex + hist[(int64_t)dgt * nblk + blockIdx.x];
+        ex += digit_total[dgt];
+      }
+    }
+  }
+  __syncthreads();
+  uint32_t* wc = cnt + (size_t)warp * bins;
+  uint32_t rnk[kBinItems];
+#pragma unroll
+  for (int k = 0; k < kBinItems; ++k) {
+    const uint32_t dgt = valid[k] ? digit[k] : 0xFFFFFFFFu;
+    const uint32_t peers = __match_any_sync(0xffffffffu, dgt);
+    const uint32_t before = __popc(peers & ((1u << lane) - 1u));
+    uint32_t prev = 0;
+    if (valid[k]) prev = wc[dgt];
+    __syncwarp();
+    if (valid[k] && before == 0) wc[dgt] = prev + __popc(peers);
+    __syncwarp();
+    rnk[k] = prev + before;
+  }
+  __syncthreads();
+  // per digit: exclusive scan over the warps, on top of the global base
+  for (uint32_t dgt = threadIdx.x; dgt < bins; dgt += kBinThreads) {
+    uint32_t run = dbase[dgt];
+#pragma unroll
+    for (int w = 0; w < kBinWarps; ++w) {
+      uint32_t c = cnt[(size_t)w * bins + dgt];
+      cnt[(size_t)w * bins + dgt] = run;
+      run += c;
+    }
   }
   __syncthreads();
 #pragma unroll
-  for (int k = 0; k < kScatterItems; ++k) {
-    int64_t j = j0 + k * kScatterThreads + threadIdx.x;
-    if (j >= j1) continue;
-    // first window entry with win[i] > j
-    int lo = 0, hi = kScatterTile;
-    while (lo < hi) {
-      int mid = (lo + hi) >> 1;
-      if ((int64_t)win[mid] > j) hi = mid; else lo = mid + 1;
-    }
-    int r = r0 + lo;
-    uint32_t excl = lo > 0 ? win[lo - 1] : (r0 > 0 ? cum[r0 - 1] : 0u);
-    uint32_t local = (uint32_t)(j - excl);
-    uint32_t tet = order[r];
-    int4 rc = __ldg(rect + tet);
-    uint32_t w = (uint32_t)(rc.z - rc.x);
-    uint32_t ty = rc.y + local / w, tx = rc.x + local % w;
-    uint32_t tile = ty * grid_w + tx;
-    uint32_t slot = atomicAdd(&cursor[tile], 1u);
-    seg[(uint32_t)ranges[tile].x + slot] = (uint32_t)r;
+  for (int k = 0; k < kBinItems; ++k) pos[k] = valid[k] ? wc[digit[k]] + rnk[k] : 0u;
+}
+
+// pass 1.  final != 0: the low digit is the whole tile id, write tet ids directly.
+__global__ void __launch_bounds__(kBinThreads)
+k_tile_scatter1(const uint32_t* __restrict__ cum, const uint32_t* __restrict__ order, int n_ranked,
+                const int4* __restrict__ rect, int grid_w, int64_t n_keys, uint32_t bins,
+                const uint32_t* __restrict__ hist, const uint32_t* __restrict__ digit_total, int nblk, int final,
+                uint2* __restrict__ pairs_out, int32_t* __restrict__ sorted_idx) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint32_t* win = reinterpret_cast<uint32_t*>(smem_raw);
+  uint32_t* s_misc = win + kBinTile + 4;
+  uint16_t* own = reinterpret_cast<uint16_t*>(s_misc + 16);
+  uint32_t* dbase = reinterpret_cast<uint32_t*>(own + kBinTile);
+  uint32_t* cnt = dbase + bins;
+  const int64_t j0 = (int64_t)blockIdx.x * kBinTile;
+  const int cntItems = (int)min((int64_t)kBinTile, n_keys - j0);
+  for (uint32_t i = threadIdx.x; i < kBinWarps * bins; i += kBinThreads) cnt[i] = 0;
+  owners_of_items(cum, n_ranked, j0, win, own, s_misc);
+  const int r0 = (int)s_misc[8];
+  const uint32_t before = s_misc[9];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  uint32_t tile[kBinItems], rank[kBinItems], digit[kBinItems], pos[kBinItems];
+  bool valid[kBinItems];
+#pragma unroll
+  for (int k = 0; k < kBinItems; ++k) {
+    const int jl = warp * kBinSpan + k * 32 + lane;
+    valid[k] = jl < cntItems;
+    tile[k] = 0;
+    rank[k] = 0;
+    if (valid[k]) item_tile(jl, j0, r0, before, win, own, order, rect, grid_w, tile[k], rank[k]);
+    digit[k] = tile[k] & (bins - 1);
+  }
+  __syncthreads();  // s_misc is reused by the scan below
+  stable_positions(digit, valid, bins, hist, digit_total, nblk, cnt, dbase, s_misc, pos);
+#pragma unroll
+  for (int k = 0; k < kBinItems; ++k) {
+    if (!valid[k]) continue;
+    if (final) sorted_idx[pos[k]] = (int32_t)order[rank[k]];
+    else pairs_out[pos[k]] = make_uint2(rank[k], tile[k]);
   }
 }
 
-// ---------------------------------------------------------------------------
-// Per-tile sort of the ranks (unique 32-bit integers) and mapping to tet ids.
-// Bitonic network in normalised form (every comparator ascending), so a
-// segment of any length sorts without padding: comparators whose upper index
-// falls beyond the segment are skipped, which is what +inf padding would do.
-// Three size classes share the code: shared memory for segments up to `cap`
-// entries, global memory (in place in `seg`) beyond.
-// ---------------------------------------------------------------------------
-template <bool SHARED>
-__device__ __forceinline__ void bitonic_sort(uint32_t* a, uint32_t len) {
-  uint32_t P = 1;
-  while (P < len) P <<= 1;
-  for (uint32_t k = 2; k <= P; k <<= 1) {
-    // flip step: i and its mirror inside blocks of k
-    for (uint32_t t = threadIdx.x; t < P / 2; t += blockDim.x) {
-      uint32_t blk = t / (k / 2), off = t % (k / 2);
-      uint32_t i = blk * k + off, l = blk * k + k - 1 - off;
-      if (l < len) {
-        uint32_t x = a[i], y = a[l];
-        if (x > y) { a[i] = y; a[l] = x; }
-      }
-    }
-    __syncthreads();
-    for (uint32_t j = k / 4; j >= 1; j >>= 1) {
-      for (uint32_t t = threadIdx.x; t < P / 2; t += blockDim.x) {
-        uint32_t i = 2 * j * (t / j) + (t % j), l = i + j;
-        if (l < len) {
-          uint32_t x = a[i], y = a[l];
-          if (x > y) { a[i] = y; a[l] = x; }
-        }
-      }
-      __syncthreads();
-    }
+// pass 2: stable split on tile >> shift; writes the tet ids.
+__global__ void __launch_bounds__(kBinThreads)
+k_tile_scatter2(const uint2* __restrict__ pairs, int64_t n, int shift, uint32_t bins,
+                const uint32_t* __restrict__ hist, const uint32_t* __restrict__ digit_total, int nblk,
+                const uint32_t* __restrict__ order, int32_t* __restrict__ sorted_idx) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint32_t* s_misc = reinterpret_cast<uint32_t*>(smem_raw);
+  uint32_t* dbase = s_misc + 16;
+  uint32_t* cnt = dbase + bins;
+  for (uint32_t i = threadIdx.x; i < kBinWarps * bins; i += kBinThreads) cnt[i] = 0;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t wbase = (int64_t)blockIdx.x * kBinTile + (int64_t)warp * kBinSpan;
+  uint32_t rank[kBinItems], digit[kBinItems], pos[kBinItems];
+  bool valid[kBinItems];
+#pragma unroll
+  for (int k = 0; k < kBinItems; ++k) {
+    const int64_t i = wbase + k * 32 + lane;
+    valid[k] = i < n;
+    uint2 pr = valid[k] ? pairs[i] : make_uint2(0u, 0u);
+    rank[k] = pr.x;
+    digit[k] = pr.y >> shift;
   }
-}
-
-// Segments with lo < len <= hi are handled by this launch (shared-memory variant).
-__global__ void k_segment_sort_smem(const int2* __restrict__ ranges, uint32_t* __restrict__ seg,
-                                    const uint32_t* __restrict__ order, int32_t* __restrict__ sorted_idx,
-                                    uint32_t lo, uint32_t hi) {
-  extern __shared__ uint32_t sbuf[];
-  int2 rg = ranges[blockIdx.x];
-  uint32_t len = (uint32_t)(rg.y - rg.x);
-  if (len <= lo || len > hi) return;
-  uint32_t* src = seg + rg.x;
-  for (uint32_t i = threadIdx.x; i < len; i += blockDim.x) sbuf[i] = src[i];
   __syncthreads();
-  bitonic_sort<true>(sbuf, len);
-  for (uint32_t i = threadIdx.x; i < len; i += blockDim.x) sorted_idx[rg.x + i] = (int32_t)order[sbuf[i]];
-}
-
-__global__ void k_segment_sort_gmem(const int2* __restrict__ ranges, uint32_t* __restrict__ seg,
-                                    const uint32_t* __restrict__ order, int32_t* __restrict__ sorted_idx,
-                                    uint32_t lo) {
-  int2 rg = ranges[blockIdx.x];
-  uint32_t len = (uint32_t)(rg.y - rg.x);
-  if (len <= lo) return;
-  uint32_t* a = seg + rg.x;
-  bitonic_sort<false>(a, len);
-  for (uint32_t i = threadIdx.x; i < len; i += blockDim.x) sorted_idx[rg.x + i] = (int32_t)order[a[i]];
+  stable_positions(digit, valid, bins, hist, digit_total, nblk, cnt, dbase, s_misc, pos);
+#pragma unroll
+  for (int k = 0; k < kBinItems; ++k)
+    if (valid[k]) sorted_idx[pos[k]] = (int32_t)order[rank[k]];
 }
 
 }  // namespace rm
@@ -536,35 +674,82 @@ int rm_launch_bin_finish(int64_t T, const RmCamera* cam, const int32_t* tiles_to
   return RM_OK;
 }
 
+namespace {
+struct ListPlan {
+  int bits1, bits2, nblk;
+  size_t pairs, hist, dtot, total;
+};
+// split of the tile-id bits into the two digits and the scratch layout
+bool make_list_plan(int64_t n_keys, int64_t G, ListPlan* P) {
+  int bits = 1;
+  while (((int64_t)1 << bits) < G) ++bits;
+  if (bits > 22) return false;
+  P->bits1 = bits <= 11 ? bits : (bits + 1) / 2;
+  P->bits2 = bits - P->bits1;
+  P->nblk = (int)((n_keys + rm::kBinTile - 1) / rm::kBinTile);
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    size_t o = off;
+    off = align256(off + bytes);
+    return o;
+  };
+  P->pairs = take(P->bits2 ? 8 * (size_t)n_keys : 0);
+  P->hist = take(4 * ((size_t)1 << P->bits1) * (size_t)(P->nblk > 0 ? P->nblk : 1));
+  P->dtot = take(4 * ((size_t)1 << P->bits1));
+  P->total = off;
+  return true;
+}
+}  // namespace
+
+size_t rm_list_plan_bytes(int64_t n_keys, int64_t G) {
+  ListPlan P;
+  if (!make_list_plan(n_keys, G, &P)) return 0;
+  return P.total;
+}
+
 int rm_launch_build_lists(const int32_t* rect, const int32_t* tile_ranges, int64_t T, const RmCamera* cam,
-                          int64_t n_keys, void* ws, uint32_t* scratch, int32_t* sorted_idx, cudaStream_t st) {
+                          int64_t n_keys, void* ws, void* scratch, size_t scratch_bytes, int32_t* sorted_idx,
+                          cudaStream_t st) {
+  (void)tile_ranges;
   if (n_keys == 0) return RM_OK;
   const int gh = cam->grid_height, gw = cam->grid_width;
   const int64_t G = (int64_t)gh * gw;
   BinLayout L = make_layout(T, G, gh, gw);
+  ListPlan P;
+  if (!make_list_plan(n_keys, G, &P)) return RM_ERR_INVALID_ARG;
+  if (P.total > scratch_bytes || (reinterpret_cast<uintptr_t>(scratch) & 255)) return RM_ERR_WORKSPACE;
   char* b = static_cast<char*>(ws);
   const uint32_t* order = reinterpret_cast<uint32_t*>(b + L.ord_a);
   const uint32_t* cum = reinterpret_cast<uint32_t*>(b + L.cum);
-  uint32_t* cursor = reinterpret_cast<uint32_t*>(b + L.cursor);
-  const int2* ranges = reinterpret_cast<const int2*>(tile_ranges);
-  RM_CUDA_CHECK(cudaMemsetAsync(cursor, 0, 4 * (size_t)(G + 1), st));
-  int64_t nb = (n_keys + rm::kScatterTile - 1) / rm::kScatterTile;
+  char* sb = static_cast<char*>(scratch);
+  uint2* pairs = reinterpret_cast<uint2*>(sb + P.pairs);
+  uint32_t* hist = reinterpret_cast<uint32_t*>(sb + P.hist);
+  uint32_t* dtot = reinterpret_cast<uint32_t*>(sb + P.dtot);
+  const uint32_t bins1 = 1u << P.bits1, bins2 = 1u << P.bits2;
+  const int4* rect4 = reinterpret_cast<const int4*>(rect);
+  const size_t gen = 4 * (rm::kBinTile + 4 + 16) + 2 * rm::kBinTile;
+  const size_t smem_h1 = gen + 4 * bins1;
+  const size_t smem_s1 = gen + 4 * bins1 * (1 + rm::kBinWarps);
+  const size_t smem_s2 = 64 + 4 * bins2 * (1 + rm::kBinWarps);
+  RM_CUDA_CHECK(cudaFuncSetAttribute(rm::k_tile_hist1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_h1));
+  RM_CUDA_CHECK(cudaFuncSetAttribute(rm::k_tile_scatter1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_s1));
+  RM_CUDA_CHECK(cudaFuncSetAttribute(rm::k_tile_scatter2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_s2));
   {
-    RmProfScope prof("k_scatter_ranks", st);
-    rm::k_scatter_ranks<<<(unsigned)nb, rm::kScatterThreads, 0, st>>>(cum, order, (int32_t)T,
-                                                                       reinterpret_cast<const int4*>(rect), ranges,
-                                                                       cursor, gw, n_keys, scratch);
+    RmProfScope prof("tile_split_pass1(3 launches)", st);
+    rm::k_tile_hist1<<<P.nblk, rm::kBinThreads, smem_h1, st>>>(cum, order, (int)T, rect4, gw, n_keys, bins1, hist,
+                                                              P.nblk);
+    rm::k_radix_rowscan<<<bins1, 1024, 0, st>>>(hist, P.nblk, dtot);
+    rm::k_tile_scatter1<<<P.nblk, rm::kBinThreads, smem_s1, st>>>(cum, order, (int)T, rect4, gw, n_keys, bins1, hist,
+                                                                 dtot, P.nblk, P.bits2 == 0, pairs, sorted_idx);
   }
   RM_CUDA_CHECK(cudaPeekAtLastError());
-  // size classes: (0, 2048] in 8 KB of shared memory, (2048, 32768] in 128 KB, larger in global memory
-  const uint32_t small_cap = 2048, big_cap = 32768;
-  RM_CUDA_CHECK(cudaFuncSetAttribute(rm::k_segment_sort_smem, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)(big_cap * 4)));
-  RmProfScope prof("k_segment_sort(3 launches)", st);
-  rm::k_segment_sort_smem<<<(unsigned)G, 256, small_cap * 4, st>>>(ranges, scratch, order, sorted_idx, 0, small_cap);
-  rm::k_segment_sort_smem<<<(unsigned)G, 1024, big_cap * 4, st>>>(ranges, scratch, order, sorted_idx, small_cap,
-                                                                  big_cap);
-  rm::k_segment_sort_gmem<<<(unsigned)G, 1024, 0, st>>>(ranges, scratch, order, sorted_idx, big_cap);
-  RM_CUDA_CHECK(cudaPeekAtLastError());
+  if (P.bits2) {
+    RmProfScope prof("tile_split_pass2(3 launches)", st);
+    rm::k_tile_hist2<<<P.nblk, rm::kBinThreads, 4 * bins2, st>>>(pairs, n_keys, P.bits1, bins2, hist, P.nblk);
+    rm::k_radix_rowscan<<<bins2, 1024, 0, st>>>(hist, P.nblk, dtot);
+    rm::k_tile_scatter2<<<P.nblk, rm::kBinThreads, smem_s2, st>>>(pairs, n_keys, P.bits1, bins2, hist, dtot, P.nblk,
+                                                                 order, sorted_idx);
+    RM_CUDA_CHECK(cudaPeekAtLastError());
+  }
   return RM_OK;
 }

@@ -11,7 +11,7 @@ from . import _lib
 
 # launches of this library's kernels (memsets not counted) per call, for bench accounting
 LAUNCHES_PROJECT_AND_BIN = 1 + 12 + 2 + 3 + 1 + 3 + 1
-LAUNCHES_BUILD_LISTS = 1 + 3
+LAUNCHES_BUILD_LISTS = 6
 LAUNCHES_FORWARD = 2
 LAUNCHES_BACKWARD = 2
 
@@ -114,10 +114,13 @@ def build_tile_lists(ctx, n_keys):
     with torch.cuda.device(dev):
         sorted_idx = torch.empty((n_keys,), dtype=torch.int32, device=dev)
         if n_keys > 0:
-            scratch = torch.empty((n_keys,), dtype=torch.int32, device=dev)
+            nbytes = lib.rm_list_scratch_bytes(n_keys, ctx["G"])
+            if nbytes == 0:
+                raise RuntimeError("rm_b200: tile grids above 2^22 tiles are not supported")
+            scratch = torch.empty((nbytes,), dtype=torch.uint8, device=dev)
             _lib.check(lib.rm_build_tile_lists(_ptr(ctx["rect"]), _ptr(ctx["tile_ranges"]), ctx["T"], ctx["cam"].ref,
-                                               n_keys, _ptr(ctx["workspace"]), _ptr(scratch), _ptr(sorted_idx),
-                                               _stream(dev)))
+                                               n_keys, _ptr(ctx["workspace"]), _ptr(scratch), nbytes,
+                                               _ptr(sorted_idx), _stream(dev)))
     return sorted_idx
 
 
