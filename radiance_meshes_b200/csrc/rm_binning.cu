@@ -414,129 +414,183 @@ k_tile_hist2(const uint2* __restrict__ pairs, int64_t n, int shift, uint32_t bin
   for (uint32_t i = threadIdx.x; i < bins; i += kBinThreads) hist[(int64_t)i * nblk + blockIdx.x] = h[i];
 }
 
-// Stable placement of the block's items given their digits.  cnt is [kBinWarps][bins]
-// (zeroed by the caller), dbase [bins].  Returns each item's destination in pos[].
-__device__ __forceinline__ void stable_positions(const uint32_t (&digit)[kBinItems], const bool (&valid)[kBinItems],
-                                                 uint32_t bins, const uint32_t* __restrict__ hist,
-                                                 const uint32_t* __restrict__ digit_total, int nblk, uint32_t* cnt,
-                                                 uint32_t* dbase, uint32_t* s_scan, uint32_t (&pos)[kBinItems]) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  // global base of each digit: exclusive scan of the digit totals + this block's offset in the digit's row
-  {
-    const uint32_t per = bins > kBinThreads ? bins / kBinThreads : 1;
-    uint32_t s = 0;
-    for (uint32_t q = 0; q < per; ++q) {
-      uint32_t dgt = threadIdx.x * per + q;
-      if (dgt < bins) s += digit_total[dgt];
-    }
-    uint32_t total;
-    uint32_t ex = block_exclusive_scan<kBinThreads>(s, &total, s_scan);
-    for (uint32_t q = 0; q < per; ++q) {
-      uint32_t dgt = threadIdx.x * per + q;
-      if (dgt < bins) {
-        dbase[dgt] = ex + hist[(int64_t)dgt * nblk + blockIdx.x];
-        ex += digit_total[dgt];
-      }
+// Stable placement of the block's items, in three steps shared by both passes:
+//   digit_bases   global base of each digit for this block -> dbase[]
+//   rank_round    one round of 32 consecutive items per warp: rank of each item
+//                 among the earlier items of the same digit in the warp's span
+//   warp_offsets  turns the per-warp digit counts into absolute offsets
+// cnt is [kBinWarps][bins], zeroed by the caller.
+__device__ __forceinline__ void digit_bases(uint32_t bins, const uint32_t* __restrict__ hist,
+                                            const uint32_t* __restrict__ digit_total, int nblk, uint32_t* dbase,
+                                            uint32_t* s_scan) {
+  const uint32_t per = bins > kBinThreads ? bins / kBinThreads : 1;
+  uint32_t s = 0;
+  for (uint32_t q = 0; q < per; ++q) {
+    uint32_t dgt = threadIdx.x * per + q;
+    if (dgt < bins) s += digit_total[dgt];
+  }
+  uint32_t total;
+  uint32_t ex = block_exclusive_scan<kBinThreads>(s, &total, s_scan);
+  for (uint32_t q = 0; q < per; ++q) {
+    uint32_t dgt = threadIdx.x * per + q;
+    if (dgt < bins) {
+      dbase[dgt] = ex + hist[(int64_t)dgt * nblk + blockIdx.x];
+      ex += digit_total[dgt];
     }
   }
-  __syncthreads();
-  uint32_t* wc = cnt + (size_t)warp * bins;
-  uint32_t rnk[kBinItems];
-#pragma unroll
-  for (int k = 0; k < kBinItems; ++k) {
-    const uint32_t dgt = valid[k] ? digit[k] : 0xFFFFFFFFu;
-    const uint32_t peers = __match_any_sync(0xffffffffu, dgt);
-    const uint32_t before = __popc(peers & ((1u << lane) - 1u));
-    uint32_t prev = 0;
-    if (valid[k]) prev = wc[dgt];
-    __syncwarp();
-    if (valid[k] && before == 0) wc[dgt] = prev + __popc(peers);
-    __syncwarp();
-    rnk[k] = prev + before;
-  }
-  __syncthreads();
-  // per digit: exclusive scan over the warps, on top of the global base
+}
+
+__device__ __forceinline__ uint32_t rank_round(uint32_t digit, bool valid, uint32_t* wc) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t peers = __match_any_sync(0xffffffffu, valid ? digit : 0xFFFFFFFFu);
+  const uint32_t before = __popc(peers & ((1u << lane) - 1u));
+  uint32_t prev = 0;
+  if (valid) prev = wc[digit];
+  __syncwarp();
+  if (valid && before == 0) wc[digit] = prev + __popc(peers);
+  __syncwarp();
+  return prev + before;
+}
+
+// After the ranking rounds: cnt[w][d] becomes the offset of warp w inside digit d's
+// run of this block, lstart[d] the run's start inside the block's reordered buffer,
+// and dbase[d] the difference (global position) - (position in the buffer).
+__device__ __forceinline__ void local_layout(uint32_t bins, uint32_t* cnt, uint32_t* dbase, uint32_t* lstart,
+                                             uint32_t* s_scan) {
   for (uint32_t dgt = threadIdx.x; dgt < bins; dgt += kBinThreads) {
-    uint32_t run = dbase[dgt];
+    uint32_t run = 0;
 #pragma unroll
     for (int w = 0; w < kBinWarps; ++w) {
       uint32_t c = cnt[(size_t)w * bins + dgt];
       cnt[(size_t)w * bins + dgt] = run;
       run += c;
     }
+    lstart[dgt] = run;  // run length for now
   }
   __syncthreads();
-#pragma unroll
-  for (int k = 0; k < kBinItems; ++k) pos[k] = valid[k] ? wc[digit[k]] + rnk[k] : 0u;
+  const uint32_t per = bins > kBinThreads ? bins / kBinThreads : 1;
+  uint32_t s = 0;
+  for (uint32_t q = 0; q < per; ++q) {
+    uint32_t dgt = threadIdx.x * per + q;
+    if (dgt < bins) s += lstart[dgt];
+  }
+  uint32_t total;
+  uint32_t ex = block_exclusive_scan<kBinThreads>(s, &total, s_scan);
+  for (uint32_t q = 0; q < per; ++q) {
+    uint32_t dgt = threadIdx.x * per + q;
+    if (dgt < bins) {
+      uint32_t len = lstart[dgt];
+      lstart[dgt] = ex;
+      dbase[dgt] -= ex;
+      ex += len;
+    }
+  }
+  __syncthreads();
 }
 
 // pass 1.  final != 0: the low digit is the whole tile id, write tet ids directly.
-__global__ void __launch_bounds__(kBinThreads)
+// Items are reordered by digit in shared memory first, so that the global
+// writes of one digit's run are contiguous.
+__global__ void __launch_bounds__(kBinThreads, 3)
 k_tile_scatter1(const uint32_t* __restrict__ cum, const uint32_t* __restrict__ order, int n_ranked,
                 const int4* __restrict__ rect, int grid_w, int64_t n_keys, uint32_t bins,
                 const uint32_t* __restrict__ hist, const uint32_t* __restrict__ digit_total, int nblk, int final,
                 uint2* __restrict__ pairs_out, int32_t* __restrict__ sorted_idx) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
+  // [ sbuf (8 B x kBinTile), aliased by win + s_misc + own during generation | dbase | lstart | cnt ]
+  uint2* sbuf = reinterpret_cast<uint2*>(smem_raw);
   uint32_t* win = reinterpret_cast<uint32_t*>(smem_raw);
   uint32_t* s_misc = win + kBinTile + 4;
   uint16_t* own = reinterpret_cast<uint16_t*>(s_misc + 16);
-  uint32_t* dbase = reinterpret_cast<uint32_t*>(own + kBinTile);
-  uint32_t* cnt = dbase + bins;
+  uint32_t* dbase = reinterpret_cast<uint32_t*>(smem_raw + 8 * kBinTile);
+  uint32_t* lstart = dbase + bins;
+  uint32_t* cnt = lstart + bins;
+  uint32_t* s_scan = cnt + (size_t)kBinWarps * bins;  // 16 words
   const int64_t j0 = (int64_t)blockIdx.x * kBinTile;
   const int cntItems = (int)min((int64_t)kBinTile, n_keys - j0);
   for (uint32_t i = threadIdx.x; i < kBinWarps * bins; i += kBinThreads) cnt[i] = 0;
   owners_of_items(cum, n_ranked, j0, win, own, s_misc);
   const int r0 = (int)s_misc[8];
   const uint32_t before = s_misc[9];
+  digit_bases(bins, hist, digit_total, nblk, dbase, s_scan);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  uint32_t tile[kBinItems], rank[kBinItems], digit[kBinItems], pos[kBinItems];
-  bool valid[kBinItems];
+  uint32_t* wc = cnt + (size_t)warp * bins;
+  uint32_t tile[kBinItems], rank[kBinItems];
+  uint32_t rnk[kBinItems / 2];  // two 16-bit ranks per word
 #pragma unroll
   for (int k = 0; k < kBinItems; ++k) {
     const int jl = warp * kBinSpan + k * 32 + lane;
-    valid[k] = jl < cntItems;
+    const bool valid = jl < cntItems;
     tile[k] = 0;
     rank[k] = 0;
-    if (valid[k]) item_tile(jl, j0, r0, before, win, own, order, rect, grid_w, tile[k], rank[k]);
-    digit[k] = tile[k] & (bins - 1);
+    if (valid) item_tile(jl, j0, r0, before, win, own, order, rect, grid_w, tile[k], rank[k]);
+    const uint32_t r = rank_round(tile[k] & (bins - 1), valid, wc);
+    if (k & 1) rnk[k >> 1] |= r << 16; else rnk[k >> 1] = r;
   }
-  __syncthreads();  // s_misc is reused by the scan below
-  stable_positions(digit, valid, bins, hist, digit_total, nblk, cnt, dbase, s_misc, pos);
+  __syncthreads();  // win / own are dead from here on: sbuf may overwrite them
+  local_layout(bins, cnt, dbase, lstart, s_scan);
 #pragma unroll
   for (int k = 0; k < kBinItems; ++k) {
-    if (!valid[k]) continue;
-    if (final) sorted_idx[pos[k]] = (int32_t)order[rank[k]];
-    else pairs_out[pos[k]] = make_uint2(rank[k], tile[k]);
+    const int jl = warp * kBinSpan + k * 32 + lane;
+    if (jl >= cntItems) continue;
+    const uint32_t dgt = tile[k] & (bins - 1);
+    const uint32_t lp = lstart[dgt] + wc[dgt] + ((rnk[k >> 1] >> (16 * (k & 1))) & 0xFFFFu);
+    sbuf[lp] = make_uint2(rank[k], tile[k]);
+  }
+  __syncthreads();
+  for (int lp = threadIdx.x; lp < cntItems; lp += kBinThreads) {
+    const uint2 pr = sbuf[lp];
+    const uint32_t g = dbase[pr.y & (bins - 1)] + (uint32_t)lp;
+    if (final) sorted_idx[g] = (int32_t)order[pr.x];
+    else pairs_out[g] = pr;
   }
 }
 
 // pass 2: stable split on tile >> shift; writes the tet ids.
-__global__ void __launch_bounds__(kBinThreads)
+__global__ void __launch_bounds__(kBinThreads, 3)
 k_tile_scatter2(const uint2* __restrict__ pairs, int64_t n, int shift, uint32_t bins,
                 const uint32_t* __restrict__ hist, const uint32_t* __restrict__ digit_total, int nblk,
                 const uint32_t* __restrict__ order, int32_t* __restrict__ sorted_idx) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  uint32_t* s_misc = reinterpret_cast<uint32_t*>(smem_raw);
-  uint32_t* dbase = s_misc + 16;
-  uint32_t* cnt = dbase + bins;
+  uint2* sbuf = reinterpret_cast<uint2*>(smem_raw);
+  uint32_t* dbase = reinterpret_cast<uint32_t*>(smem_raw + 8 * kBinTile);
+  uint32_t* lstart = dbase + bins;
+  uint32_t* cnt = lstart + bins;
+  uint32_t* s_scan = cnt + (size_t)kBinWarps * bins;
   for (uint32_t i = threadIdx.x; i < kBinWarps * bins; i += kBinThreads) cnt[i] = 0;
+  digit_bases(bins, hist, digit_total, nblk, dbase, s_scan);
+  __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int64_t wbase = (int64_t)blockIdx.x * kBinTile + (int64_t)warp * kBinSpan;
-  uint32_t rank[kBinItems], digit[kBinItems], pos[kBinItems];
-  bool valid[kBinItems];
+  uint32_t* wc = cnt + (size_t)warp * bins;
+  const int64_t base = (int64_t)blockIdx.x * kBinTile;
+  const int cntItems = (int)min((int64_t)kBinTile, n - base);
+  uint2 pr[kBinItems];
 #pragma unroll
   for (int k = 0; k < kBinItems; ++k) {
-    const int64_t i = wbase + k * 32 + lane;
-    valid[k] = i < n;
-    uint2 pr = valid[k] ? pairs[i] : make_uint2(0u, 0u);
-    rank[k] = pr.x;
-    digit[k] = pr.y >> shift;
+    const int jl = warp * kBinSpan + k * 32 + lane;
+    pr[k] = jl < cntItems ? pairs[base + jl] : make_uint2(0u, 0u);
+  }
+  uint32_t rnk[kBinItems / 2];
+#pragma unroll
+  for (int k = 0; k < kBinItems; ++k) {
+    const bool valid = warp * kBinSpan + k * 32 + lane < cntItems;
+    const uint32_t r = rank_round(pr[k].y >> shift, valid, wc);
+    if (k & 1) rnk[k >> 1] |= r << 16; else rnk[k >> 1] = r;
   }
   __syncthreads();
-  stable_positions(digit, valid, bins, hist, digit_total, nblk, cnt, dbase, s_misc, pos);
+  local_layout(bins, cnt, dbase, lstart, s_scan);
 #pragma unroll
-  for (int k = 0; k < kBinItems; ++k)
-    if (valid[k]) sorted_idx[pos[k]] = (int32_t)order[rank[k]];
+  for (int k = 0; k < kBinItems; ++k) {
+    if (warp * kBinSpan + k * 32 + lane >= cntItems) continue;
+    const uint32_t dgt = pr[k].y >> shift;
+    const uint32_t lp = lstart[dgt] + wc[dgt] + ((rnk[k >> 1] >> (16 * (k & 1))) & 0xFFFFu);
+    sbuf[lp] = pr[k];
+  }
+  __syncthreads();
+  for (int lp = threadIdx.x; lp < cntItems; lp += kBinThreads) {
+    const uint2 p2 = sbuf[lp];
+    sorted_idx[dbase[p2.y >> shift] + (uint32_t)lp] = (int32_t)order[p2.x];
+  }
 }
 
 }  // namespace rm
@@ -729,8 +783,8 @@ int rm_launch_build_lists(const int32_t* rect, const int32_t* tile_ranges, int64
   const int4* rect4 = reinterpret_cast<const int4*>(rect);
   const size_t gen = 4 * (rm::kBinTile + 4 + 16) + 2 * rm::kBinTile;
   const size_t smem_h1 = gen + 4 * bins1;
-  const size_t smem_s1 = gen + 4 * bins1 * (1 + rm::kBinWarps);
-  const size_t smem_s2 = 64 + 4 * bins2 * (1 + rm::kBinWarps);
+  const size_t smem_s1 = 8 * rm::kBinTile + 4 * bins1 * (2 + rm::kBinWarps) + 64;
+  const size_t smem_s2 = 8 * rm::kBinTile + 4 * bins2 * (2 + rm::kBinWarps) + 64;
   RM_CUDA_CHECK(cudaFuncSetAttribute(rm::k_tile_hist1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_h1));
   RM_CUDA_CHECK(cudaFuncSetAttribute(rm::k_tile_scatter1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_s1));
   RM_CUDA_CHECK(cudaFuncSetAttribute(rm::k_tile_scatter2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_s2));
