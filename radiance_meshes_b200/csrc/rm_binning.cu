@@ -187,8 +187,14 @@ k_radix_scatter(const uint32_t* __restrict__ keys_in, const uint32_t* __restrict
     bool valid = i < n;
     key[k] = valid ? keys_in[i] : 0xFFFFFFFFu;
     val[k] = valid ? vals_in[i] : 0u;
-    uint32_t d = valid ? ((key[k] >> shift) & (kRadix - 1)) : (uint32_t)kRadix;
-    uint32_t peers = __match_any_sync(0xffffffffu, d);
+    uint32_t d = (key[k] >> shift) & (kRadix - 1);
+    uint32_t peers = __ballot_sync(0xffffffffu, valid);
+#pragma unroll
+    for (int b = 0; b < kRadixBits; ++b) {
+      const bool bit = (d >> b) & 1u;
+      const uint32_t m = __ballot_sync(0xffffffffu, bit);
+      peers &= bit ? m : ~m;
+    }
     uint32_t before = __popc(peers & ((1u << lane) - 1u));
     uint32_t prev = 0;
     if (valid) prev = cnt[warp][d];
@@ -319,18 +325,30 @@ __device__ __forceinline__ uint32_t block_exclusive_maxscan(uint32_t v, uint32_t
   return ex;
 }
 
+// First rank of every block of kBinTile items (first r with cum[r] > block start),
+// one thread per block so that the dependent loads of the searches overlap.
+__global__ void k_block_start_ranks(const uint32_t* __restrict__ cum, int n_ranked, int nblk,
+                                    uint32_t* __restrict__ start_rank) {
+  int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= nblk) return;
+  const int64_t j0 = (int64_t)b * kBinTile;
+  int lo = 0, hi = n_ranked;
+  while (lo < hi) {
+    int mid = (lo + hi) >> 1;
+    if ((int64_t)__ldg(cum + mid) > j0) hi = mid; else lo = mid + 1;
+  }
+  start_rank[b] = (uint32_t)lo;
+}
+
 // Owner table of the block's items: after this call item jl (0 <= jl < items of the
 // block) belongs to rank *r0 + own[jl]; win[i] = cum[*r0 + i].
 __device__ __forceinline__ void owners_of_items(const uint32_t* __restrict__ cum, int n_ranked, int64_t j0,
+                                                const uint32_t* __restrict__ start_rank,
                                                 uint32_t* win /* kBinTile+1 */, uint16_t* own /* kBinTile */,
                                                 uint32_t* s_misc /* 16 words */) {
   if (threadIdx.x == 0) {
-    int lo = 0, hi = n_ranked;  // first rank with cum[r] > j0
-    while (lo < hi) {
-      int mid = (lo + hi) >> 1;
-      if ((int64_t)cum[mid] > j0) hi = mid; else lo = mid + 1;
-    }
-    s_misc[8] = (uint32_t)lo;
+    const uint32_t lo = start_rank[blockIdx.x];
+    s_misc[8] = lo;
     s_misc[9] = lo > 0 ? cum[lo - 1] : 0u;  // items before rank r0
   }
   for (int i = threadIdx.x; i < kBinTile; i += kBinThreads) own[i] = 0;
@@ -374,7 +392,8 @@ __device__ __forceinline__ void item_tile(int jl, int64_t j0, int r0, uint32_t b
 }
 
 __global__ void __launch_bounds__(kBinThreads)
-k_tile_hist1(const uint32_t* __restrict__ cum, const uint32_t* __restrict__ order, int n_ranked,
+k_tile_hist1(const uint32_t* __restrict__ cum, const uint32_t* __restrict__ start_rank,
+             const uint32_t* __restrict__ order, int n_ranked,
              const int4* __restrict__ rect, int grid_w, int64_t n_keys, uint32_t bins, uint32_t* __restrict__ hist,
              int nblk) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -385,7 +404,7 @@ k_tile_hist1(const uint32_t* __restrict__ cum, const uint32_t* __restrict__ orde
   const int64_t j0 = (int64_t)blockIdx.x * kBinTile;
   const int cnt = (int)min((int64_t)kBinTile, n_keys - j0);
   for (uint32_t i = threadIdx.x; i < bins; i += kBinThreads) h[i] = 0;
-  owners_of_items(cum, n_ranked, j0, win, own, s_misc);
+  owners_of_items(cum, n_ranked, j0, start_rank, win, own, s_misc);
   const int r0 = (int)s_misc[8];
   const uint32_t before = s_misc[9];
   for (int jl = threadIdx.x; jl < cnt; jl += kBinThreads) {
@@ -440,9 +459,22 @@ __device__ __forceinline__ void digit_bases(uint32_t bins, const uint32_t* __res
   }
 }
 
-__device__ __forceinline__ uint32_t rank_round(uint32_t digit, bool valid, uint32_t* wc) {
+// Lanes of the warp holding the same `nbits`-bit digit (valid lanes only), from one
+// ballot per bit: constant cost, where match.any slows down with the number of
+// distinct values.
+__device__ __forceinline__ uint32_t match_digit(uint32_t digit, bool valid, int nbits) {
+  uint32_t peers = __ballot_sync(0xffffffffu, valid);
+  for (int b = 0; b < nbits; ++b) {
+    const bool bit = (digit >> b) & 1u;
+    const uint32_t m = __ballot_sync(0xffffffffu, bit);
+    peers &= bit ? m : ~m;
+  }
+  return peers;
+}
+
+__device__ __forceinline__ uint32_t rank_round(uint32_t digit, bool valid, uint32_t* wc, int nbits) {
   const int lane = threadIdx.x & 31;
-  const uint32_t peers = __match_any_sync(0xffffffffu, valid ? digit : 0xFFFFFFFFu);
+  const uint32_t peers = match_digit(digit, valid, nbits);
   const uint32_t before = __popc(peers & ((1u << lane) - 1u));
   uint32_t prev = 0;
   if (valid) prev = wc[digit];
@@ -492,7 +524,8 @@ __device__ __forceinline__ void local_layout(uint32_t bins, uint32_t* cnt, uint3
 // Items are reordered by digit in shared memory first, so that the global
 // writes of one digit's run are contiguous.
 __global__ void __launch_bounds__(kBinThreads, 3)
-k_tile_scatter1(const uint32_t* __restrict__ cum, const uint32_t* __restrict__ order, int n_ranked,
+k_tile_scatter1(const uint32_t* __restrict__ cum, const uint32_t* __restrict__ start_rank,
+                const uint32_t* __restrict__ order, int n_ranked,
                 const int4* __restrict__ rect, int grid_w, int64_t n_keys, uint32_t bins,
                 const uint32_t* __restrict__ hist, const uint32_t* __restrict__ digit_total, int nblk, int final,
                 uint2* __restrict__ pairs_out, int32_t* __restrict__ sorted_idx) {
@@ -509,7 +542,7 @@ k_tile_scatter1(const uint32_t* __restrict__ cum, const uint32_t* __restrict__ o
   const int64_t j0 = (int64_t)blockIdx.x * kBinTile;
   const int cntItems = (int)min((int64_t)kBinTile, n_keys - j0);
   for (uint32_t i = threadIdx.x; i < kBinWarps * bins; i += kBinThreads) cnt[i] = 0;
-  owners_of_items(cum, n_ranked, j0, win, own, s_misc);
+  owners_of_items(cum, n_ranked, j0, start_rank, win, own, s_misc);
   const int r0 = (int)s_misc[8];
   const uint32_t before = s_misc[9];
   digit_bases(bins, hist, digit_total, nblk, dbase, s_scan);
@@ -524,7 +557,7 @@ k_tile_scatter1(const uint32_t* __restrict__ cum, const uint32_t* __restrict__ o
     tile[k] = 0;
     rank[k] = 0;
     if (valid) item_tile(jl, j0, r0, before, win, own, order, rect, grid_w, tile[k], rank[k]);
-    const uint32_t r = rank_round(tile[k] & (bins - 1), valid, wc);
+    const uint32_t r = rank_round(tile[k] & (bins - 1), valid, wc, 31 - __clz(bins));
     if (k & 1) rnk[k >> 1] |= r << 16; else rnk[k >> 1] = r;
   }
   __syncthreads();  // win / own are dead from here on: sbuf may overwrite them
@@ -574,7 +607,7 @@ k_tile_scatter2(const uint2* __restrict__ pairs, int64_t n, int shift, uint32_t 
 #pragma unroll
   for (int k = 0; k < kBinItems; ++k) {
     const bool valid = warp * kBinSpan + k * 32 + lane < cntItems;
-    const uint32_t r = rank_round(pr[k].y >> shift, valid, wc);
+    const uint32_t r = rank_round(pr[k].y >> shift, valid, wc, 31 - __clz(bins));
     if (k & 1) rnk[k >> 1] |= r << 16; else rnk[k >> 1] = r;
   }
   __syncthreads();
@@ -731,7 +764,7 @@ int rm_launch_bin_finish(int64_t T, const RmCamera* cam, const int32_t* tiles_to
 namespace {
 struct ListPlan {
   int bits1, bits2, nblk;
-  size_t pairs, hist, dtot, total;
+  size_t pairs, hist, dtot, starts, total;
 };
 // split of the tile-id bits into the two digits and the scratch layout
 bool make_list_plan(int64_t n_keys, int64_t G, ListPlan* P) {
@@ -750,6 +783,7 @@ bool make_list_plan(int64_t n_keys, int64_t G, ListPlan* P) {
   P->pairs = take(P->bits2 ? 8 * (size_t)n_keys : 0);
   P->hist = take(4 * ((size_t)1 << P->bits1) * (size_t)(P->nblk > 0 ? P->nblk : 1));
   P->dtot = take(4 * ((size_t)1 << P->bits1));
+  P->starts = take(4 * (size_t)(P->nblk > 0 ? P->nblk : 1));
   P->total = off;
   return true;
 }
@@ -779,6 +813,7 @@ int rm_launch_build_lists(const int32_t* rect, const int32_t* tile_ranges, int64
   uint2* pairs = reinterpret_cast<uint2*>(sb + P.pairs);
   uint32_t* hist = reinterpret_cast<uint32_t*>(sb + P.hist);
   uint32_t* dtot = reinterpret_cast<uint32_t*>(sb + P.dtot);
+  uint32_t* starts = reinterpret_cast<uint32_t*>(sb + P.starts);
   const uint32_t bins1 = 1u << P.bits1, bins2 = 1u << P.bits2;
   const int4* rect4 = reinterpret_cast<const int4*>(rect);
   const size_t gen = 4 * (rm::kBinTile + 4 + 16) + 2 * rm::kBinTile;
@@ -789,12 +824,14 @@ int rm_launch_build_lists(const int32_t* rect, const int32_t* tile_ranges, int64
   RM_CUDA_CHECK(cudaFuncSetAttribute(rm::k_tile_scatter1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_s1));
   RM_CUDA_CHECK(cudaFuncSetAttribute(rm::k_tile_scatter2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_s2));
   {
-    RmProfScope prof("tile_split_pass1(3 launches)", st);
-    rm::k_tile_hist1<<<P.nblk, rm::kBinThreads, smem_h1, st>>>(cum, order, (int)T, rect4, gw, n_keys, bins1, hist,
-                                                              P.nblk);
+    RmProfScope prof("tile_split_pass1(4 launches)", st);
+    rm::k_block_start_ranks<<<(P.nblk + 255) / 256, 256, 0, st>>>(cum, (int)T, P.nblk, starts);
+    rm::k_tile_hist1<<<P.nblk, rm::kBinThreads, smem_h1, st>>>(cum, starts, order, (int)T, rect4, gw, n_keys, bins1,
+                                                              hist, P.nblk);
     rm::k_radix_rowscan<<<bins1, 1024, 0, st>>>(hist, P.nblk, dtot);
-    rm::k_tile_scatter1<<<P.nblk, rm::kBinThreads, smem_s1, st>>>(cum, order, (int)T, rect4, gw, n_keys, bins1, hist,
-                                                                 dtot, P.nblk, P.bits2 == 0, pairs, sorted_idx);
+    rm::k_tile_scatter1<<<P.nblk, rm::kBinThreads, smem_s1, st>>>(cum, starts, order, (int)T, rect4, gw, n_keys,
+                                                                 bins1, hist, dtot, P.nblk, P.bits2 == 0, pairs,
+                                                                 sorted_idx);
   }
   RM_CUDA_CHECK(cudaPeekAtLastError());
   if (P.bits2) {

@@ -11,7 +11,7 @@ from . import _lib
 
 # launches of this library's kernels (memsets not counted) per call, for bench accounting
 LAUNCHES_PROJECT_AND_BIN = 1 + 12 + 2 + 3 + 1 + 3 + 1
-LAUNCHES_BUILD_LISTS = 6
+LAUNCHES_BUILD_LISTS = 7
 LAUNCHES_FORWARD = 2
 LAUNCHES_BACKWARD = 2
 
