@@ -33,8 +33,10 @@ extern "C" {
 #define RM_STATUS_NAN_VERTEX 1u   /* a vertex coordinate is NaN (tile_shader_slang.py:78 asserts on this) */
 #define RM_STATUS_KEY_OVERFLOW 2u /* more than 2^31-1 (tile, tet) pairs (int32 cumsum, tile_shader_slang.py:36) */
 
-/* Floats per packed tet record / per record-gradient row. */
-#define RM_RECORD_FLOATS 24
+/* Floats per packed tet record (24 used by the integration + 8 for the projected
+ * vertices used to cull whole tiles) and per record-gradient row. */
+#define RM_RECORD_FLOATS 32
+#define RM_GRAD_RECORD_FLOATS 24
 
 /*
  * Camera, the reference's `tcam` dictionary (data/camera.py:72-91 plus the tile
@@ -107,8 +109,9 @@ int rm_build_tile_lists(const int32_t* rect_tile_space, const int32_t* tile_rang
 
 /*
  * Per-frame packed tet records (4 outward face planes relative to the camera
- * position, colour field, density): the staged form of
- * load_tet_alphablend_interp (slang/interp_version.slang:100-153).
+ * position, colour field, density, and the 4 vertices projected to pixel
+ * coordinates): the staged form of load_tet_alphablend_interp
+ * (slang/interp_version.slang:100-153).
  * tiles_touched may be NULL (pack every tet) or [T] (skip culled tets).
  * records[T, RM_RECORD_FLOATS] f32 out, 16-byte aligned.
  */
@@ -129,7 +132,7 @@ int rm_forward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, cons
  * Backward integration.  Replaces splat_tiled.bwd / bwd_alpha_blend
  * (slang/alphablend_shader_interp.slang:273-369, host side
  * alphablend_tiled_slang_interp.py:70-112).
- *   grad_records[T, RM_RECORD_FLOATS] is caller-provided scratch (zeroed here);
+ *   grad_records[T, RM_GRAD_RECORD_FLOATS] is caller-provided scratch (zeroed here);
  *   vertices_grad[V,3] and cell_values_grad[T,7] are fully written (zeroed here first).
  */
 int rm_backward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, const float* records,
@@ -157,7 +160,7 @@ int rm_vertex_backward(const int32_t* indices, const float* vertices, int64_t n_
  * an engine that owns the allocator, code running under a memory budget that was
  * fixed before the frame, or a callback in which cudaMalloc is forbidden.  This
  * variant of rm_backward takes the same inputs and outputs but keeps its one
- * scratch buffer (the per-tet record-gradient rows, RM_RECORD_FLOATS floats per
+ * scratch buffer (the per-tet record-gradient rows, RM_GRAD_RECORD_FLOATS floats per
  * tet) in a static device array inside the library, RM_STATIC_SCRATCH_MAX_TETS
  * rows = 12 MiB, which every GPU that loads the library holds until the process
  * exits.  It calls no cudaMalloc/cudaFree or other allocating routine.

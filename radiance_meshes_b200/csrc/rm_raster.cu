@@ -29,6 +29,8 @@
 
 namespace rm {
 
+constexpr int kRecStride = RM_RECORD_FLOATS / 4;  // float4 per record in global memory (the first 6 are staged)
+
 // ----------------------------------------------------------------------------
 // Record packing
 // ----------------------------------------------------------------------------
@@ -75,11 +77,65 @@ k_pack_records(const int32_t* __restrict__ indices, const float* __restrict__ ve
   f3 base = {__ldg(c + 1), __ldg(c + 2), __ldg(c + 3)};
   f3 grd = {__ldg(c + 4), __ldg(c + 5), __ldg(c + 6)};
   float s0 = dot(grd, cam - v[0]);
-  float4* r = records + 6 * g;
+  float4* r = records + kRecStride * g;
 #pragma unroll
   for (int i = 0; i < 4; ++i) r[i] = make_float4(p.n[i].x, p.n[i].y, p.n[i].z, p.D[i]);
   r[4] = make_float4(grd.x, grd.y, grd.z, s0);
   r[5] = make_float4(base.x, base.y, base.z, density);
+  // Vertices in pixel coordinates, for the per-tile cull of the integration
+  // kernels.  Only meaningful for an undistorted pinhole with the whole tet in
+  // front of the camera; otherwise NaN, which makes every cull test fail.
+  const float* W = rcam.world_view_transform;
+  const float* D = rcam.distortion_params;
+  const float fx = __ldg(rcam.K + 0), cx = __ldg(rcam.K + 2), fy = __ldg(rcam.K + 4), cy = __ldg(rcam.K + 5);
+  const float d2 = __ldg(D) * __ldg(D) + __ldg(D + 1) * __ldg(D + 1) + __ldg(D + 2) * __ldg(D + 2) +
+                   __ldg(D + 3) * __ldg(D + 3);
+  bool ok = rcam.camera_type == 0 && d2 < 1e-9f;
+  float px[4], py[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    float X = __ldg(W + 0) * v[k].x + __ldg(W + 1) * v[k].y + __ldg(W + 2) * v[k].z + __ldg(W + 3);
+    float Y = __ldg(W + 4) * v[k].x + __ldg(W + 5) * v[k].y + __ldg(W + 6) * v[k].z + __ldg(W + 7);
+    float Z = __ldg(W + 8) * v[k].x + __ldg(W + 9) * v[k].y + __ldg(W + 10) * v[k].z + __ldg(W + 11);
+    ok = ok && Z > 1e-3f;
+    px[k] = fx * (X / Z) + cx;
+    py[k] = fy * (Y / Z) + cy;
+  }
+  const float qnan = __int_as_float(0x7fc00000);
+  if (!ok) px[0] = qnan;
+  r[6] = make_float4(px[0], py[0], px[1], py[1]);
+  r[7] = make_float4(px[2], py[2], px[3], py[3]);
+}
+
+// True if the convex hull of the four projected vertices (q0, q1) is separated
+// from the axis-aligned box [X0,X1] x [Y0,Y1] of a half-warp's sample positions
+// by one of the hull's edge lines, with a margin of 0.01 pixel.  Conservative:
+// a NaN anywhere makes it false.
+__device__ __forceinline__ bool hull_misses_box(float4 q0, float4 q1, float X0, float X1, float Y0, float Y1) {
+  const float vx[4] = {q0.x, q0.z, q1.x, q1.z};
+  const float vy[4] = {q0.y, q0.w, q1.y, q1.w};
+  // bounding boxes first
+  const float mnx = fminf(fminf(vx[0], vx[1]), fminf(vx[2], vx[3])), mxx = fmaxf(fmaxf(vx[0], vx[1]), fmaxf(vx[2], vx[3]));
+  const float mny = fminf(fminf(vy[0], vy[1]), fminf(vy[2], vy[3])), mxy = fmaxf(fmaxf(vy[0], vy[1]), fmaxf(vy[2], vy[3]));
+  const bool finite = vx[0] == vx[0];
+  bool sep = (mxx < X0 - 0.01f) || (mnx > X1 + 0.01f) || (mxy < Y0 - 0.01f) || (mny > Y1 + 0.01f);
+#pragma unroll
+  for (int a = 0; a < 4; ++a) {
+#pragma unroll
+    for (int b = a + 1; b < 4; ++b) {
+      const int c1 = (a != 0 && b != 0) ? 0 : ((a != 1 && b != 1) ? 1 : 2);
+      const int c2 = 6 - a - b - c1;
+      const float nx = -(vy[b] - vy[a]), ny = vx[b] - vx[a];
+      const float s1 = nx * (vx[c1] - vx[a]) + ny * (vy[c1] - vy[a]);
+      const float s2 = nx * (vx[c2] - vx[a]) + ny * (vy[c2] - vy[a]);
+      const float m = 0.01f * (fabsf(nx) + fabsf(ny));
+      // extreme values of n.(corner - a) over the box
+      const float hi = nx * ((nx > 0.0f ? X1 : X0) - vx[a]) + ny * ((ny > 0.0f ? Y1 : Y0) - vy[a]);
+      const float lo = nx * ((nx > 0.0f ? X0 : X1) - vx[a]) + ny * ((ny > 0.0f ? Y0 : Y1) - vy[a]);
+      sep = sep || (s1 >= 0.0f && s2 >= 0.0f && hi < -m) || (s1 <= 0.0f && s2 <= 0.0f && lo > m);
+    }
+  }
+  return finite && sep;
 }
 
 // ----------------------------------------------------------------------------
@@ -254,6 +310,22 @@ __device__ __forceinline__ Unit make_unit(const RmCamera& c, const int2* __restr
   return u;
 }
 
+// Bounding box of the sample positions (pixel + jitter) of the half-warp's pixels.
+__device__ __forceinline__ void halfwarp_sample_box(bool inside, float sx, float sy, float& X0, float& X1, float& Y0,
+                                                    float& Y1) {
+  X0 = inside ? sx : 3.0e38f;
+  X1 = inside ? sx : -3.0e38f;
+  Y0 = inside ? sy : 3.0e38f;
+  Y1 = inside ? sy : -3.0e38f;
+#pragma unroll
+  for (int o = 8; o >= 1; o >>= 1) {
+    X0 = fminf(X0, __shfl_xor_sync(0xffffffffu, X0, o));
+    X1 = fmaxf(X1, __shfl_xor_sync(0xffffffffu, X1, o));
+    Y0 = fminf(Y0, __shfl_xor_sync(0xffffffffu, Y0, o));
+    Y1 = fmaxf(Y1, __shfl_xor_sync(0xffffffffu, Y1, o));
+  }
+}
+
 // ----------------------------------------------------------------------------
 // Forward
 // ----------------------------------------------------------------------------
@@ -270,11 +342,18 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
 
   f3 d = {0.f, 0.f, 1.f};
   const int64_t pix = (int64_t)u.y * rcam.image_width + u.x;
+  float sx = 0.f, sy = 0.f;
   if (u.inside) {
     float2 j = __ldg(jitter + pix);
-    d = ray_direction(rcam, (float)u.x + j.x, (float)u.y + j.y);
+    sx = (float)u.x + j.x;
+    sy = (float)u.y + j.y;
+    d = ray_direction(rcam, sx, sy);
   }
   const float min_t = rcam.min_t;
+  float X0, X1, Y0, Y1;
+  halfwarp_sample_box(u.inside, sx, sy, X0, X1, Y0, Y1);
+  const float qnan = __int_as_float(0x7fc00000);
+  float4 nq0 = make_float4(qnan, qnan, qnan, qnan), nq1 = nq0;  // projected vertices of the record this lane stages
 
   float sr = 0.f, sg = 0.f, sb = 0.f, logT = 0.f, T = 1.f;
   float dx = 0.f, dy = 0.f, dz = 0.f, dw = 0.f, dv = 0.f;
@@ -291,23 +370,28 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
   // prologue: stage chunk 0
   if (fetching && lane16 < u.len) {
     int id = __ldg(list + u.start + lane16);
-    const float4* src = records + 6 * (int64_t)id;
+    const float4* src = records + kRecStride * (int64_t)id;
 #pragma unroll
     for (int k = 0; k < 6; ++k) cp_async16(buf0 + lane16 * 6 + k, src + k);
+    nq0 = __ldg(src + 6);
+    nq1 = __ldg(src + 7);
   }
   cp_async_commit();
 
   for (int c = 0; c < max_chunks; ++c) {
     float4* cur = (c & 1) ? buf1 : buf0;
     float4* nxt = (c & 1) ? buf0 : buf1;
+    const float4 cq0 = nq0, cq1 = nq1;
     // issue the next chunk
     {
       int e = (c + 1) * kChunk + lane16;
       if (fetching && e < u.len) {
         int id = __ldg(list + u.start + e);
-        const float4* src = records + 6 * (int64_t)id;
+        const float4* src = records + kRecStride * (int64_t)id;
 #pragma unroll
         for (int k = 0; k < 6; ++k) cp_async16(nxt + lane16 * 6 + k, src + k);
+        nq0 = __ldg(src + 6);
+        nq1 = __ldg(src + 7);
       }
       cp_async_commit();
     }
@@ -315,7 +399,9 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
     __syncwarp();
     // Tets of zero density are walked (they count in n_contributors) but can never
     // contribute or terminate a pixel: only the entries flagged here are evaluated.
-    const bool nonzero = (c * kChunk + lane16 < u.len) && cur[lane16 * 6 + 5].w > 0.0f;
+    // Neither are tets whose projection misses the box of this half-warp's samples.
+    const bool nonzero = (c * kChunk + lane16 < u.len) && cur[lane16 * 6 + 5].w > 0.0f &&
+                         !hull_misses_box(cq0, cq1, X0, X1, Y0, Y1);
     unsigned todo = (__ballot_sync(0xffffffffu, nonzero) >> (16 * half)) & 0xFFFFu;
     if (active) {
       while (todo) {
@@ -438,9 +524,12 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
   float logT = 0.f, sz = 0.f, sw = 0.f;
   float gr = 0.f, gg = 0.f, gb = 0.f, glogT = 0.f, gx = 0.f, gy = 0.f, gz = 0.f, gw = 0.f, gv = 0.f;
   int nc = 0;
+  float sx = 0.f, sy = 0.f;
   if (u.inside) {
     float2 j = __ldg(jitter + pix);
-    d = ray_direction(rcam, (float)u.x + j.x, (float)u.y + j.y);
+    sx = (float)u.x + j.x;
+    sy = (float)u.y + j.y;
+    d = ray_direction(rcam, sx, sy);
     logT = __ldg(out_img + pix).w;
     sz = __ldg(dist_img + 5 * pix + 2);
     sw = __ldg(dist_img + 5 * pix + 3);
@@ -451,6 +540,11 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
     nc = min(__ldg(n_contrib + pix), u.len);
   }
   const float min_t = rcam.min_t;
+
+  float X0, X1, Y0, Y1;
+  halfwarp_sample_box(u.inside, sx, sy, X0, X1, Y0, Y1);
+  const float qnan = __int_as_float(0x7fc00000);
+  float4 nq0 = make_float4(qnan, qnan, qnan, qnan), nq1 = nq0;
 
   // entries at or beyond the largest n_contributors of the half are skipped by every pixel
   int nmax = nc;
@@ -467,16 +561,19 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
       if (e < nmax) {
         int id = __ldg(list + u.start + e);
         stage_id[warp][half][k & 1][lane16] = id;
-        const float4* src = records + 6 * (int64_t)id;
+        const float4* src = records + kRecStride * (int64_t)id;
         float4* dst = stage[warp][half][k & 1] + lane16 * 6;
 #pragma unroll
         for (int q = 0; q < 6; ++q) cp_async16(dst + q, src + q);
+        nq0 = __ldg(src + 6);
+        nq1 = __ldg(src + 7);
       }
     }
     cp_async_commit();
   };
   issue(0);
   for (int k = 0; k < max_chunks; ++k) {
+    const float4 cq0 = nq0, cq1 = nq1;
     issue(k + 1);
     cp_async_wait<1>();
     __syncwarp();
@@ -486,7 +583,8 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
     // Staged entries with non-zero density, per half (zero-density tets never
     // contribute).  Both halves step in lock-step through their own set bits,
     // last entry first; a half that runs out idles.
-    const bool nonzero = c >= 0 && c * kChunk + lane16 < nmax && cur[lane16 * 6 + 5].w > 0.0f;
+    const bool nonzero = c >= 0 && c * kChunk + lane16 < nmax && cur[lane16 * 6 + 5].w > 0.0f &&
+                         !hull_misses_box(cq0, cq1, X0, X1, Y0, Y1);
     unsigned todo = (__ballot_sync(0xffffffffu, nonzero) >> (16 * half)) & 0xFFFFu;
     const int steps = max(__popc(todo), __shfl_xor_sync(0xffffffffu, __popc(todo), 16));
     for (int step = 0; step < steps; ++step) {
@@ -745,7 +843,7 @@ int rm_launch_backward(const int32_t* list, const int32_t* ranges, const float* 
 // ----------------------------------------------------------------------------
 #include <mutex>
 
-static __device__ __align__(256) float g_static_grad_records[(size_t)RM_STATIC_SCRATCH_MAX_TETS * RM_RECORD_FLOATS];
+static __device__ __align__(256) float g_static_grad_records[(size_t)RM_STATIC_SCRATCH_MAX_TETS * RM_GRAD_RECORD_FLOATS];
 
 namespace {
 constexpr int kMaxDevices = 64;
@@ -795,7 +893,7 @@ extern "C" int rm_backward_static_scratch(const int32_t* sorted_tetra_idx, const
   // The array keeps the previous call's sums: clear the rows this call accumulates into.
   RM_CUDA_CHECK(cudaMemsetAsync(vertices_grad, 0, sizeof(float) * 3 * (size_t)n_vertices, st));
   if (n_tets == 0) return RM_OK;
-  RM_CUDA_CHECK(cudaMemsetAsync(scratch, 0, sizeof(float) * RM_RECORD_FLOATS * (size_t)n_tets, st));
+  RM_CUDA_CHECK(cudaMemsetAsync(scratch, 0, sizeof(float) * RM_GRAD_RECORD_FLOATS * (size_t)n_tets, st));
   int subs;
   int64_t n_units;
   unsigned blocks;

@@ -156,7 +156,7 @@ def backward(sorted_idx, tile_ranges, records, cam, ray_jitter, output_img, dist
     dev = records.device
     T, V = indices.shape[0], vertices.shape[0]
     with torch.cuda.device(dev):
-        grad_records = torch.empty((T, _lib.RM_RECORD_FLOATS), dtype=torch.float32, device=dev)
+        grad_records = torch.empty((T, _lib.RM_GRAD_RECORD_FLOATS), dtype=torch.float32, device=dev)
         vertices_grad = torch.empty((V, 3), dtype=torch.float32, device=dev)
         cell_grad = torch.empty((T, 7), dtype=torch.float32, device=dev)
         _lib.check(lib.rm_backward(_ptr(sorted_idx), _ptr(tile_ranges), _ptr(records), cam.ref, _ptr(ray_jitter),

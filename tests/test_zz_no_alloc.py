@@ -59,7 +59,7 @@ def test_static_scratch_backward_matches_rm_backward(cuda_lib):
         g_img = torch.randn((H, W, 4), generator=gen).to(dev)
         g_dist = (0.05 * torch.randn((H, W, 5), generator=gen)).to(dev)
         # existing entry point, caller-provided scratch
-        scratch = torch.empty((T, _lib.RM_RECORD_FLOATS), device=dev)
+        scratch = torch.empty((T, _lib.RM_GRAD_RECORD_FLOATS), device=dev)
         vg_ref = torch.empty((V, 3), device=dev)
         cg_ref = torch.empty((T, 7), device=dev)
         _lib.check(cuda_lib.rm_backward(_p(sorted_idx), _p(bctx["tile_ranges"]), _p(records), cam.ref, _p(jitter),
