@@ -219,6 +219,7 @@ def run_gpu(args):
     import torch
     import torch.distributed as dist
     from radiance_meshes_b200 import _lib, raster
+    from radiance_meshes_b200 import dist as rmdist
     from radiance_meshes_b200.render import render, tcam_to_device
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -253,9 +254,7 @@ def run_gpu(args):
         c.grad = None
         pkg = render(inp["indices"], v, c, tcam, inp["jitter"])
         torch.autograd.backward([pkg["image"], pkg["distortion_img"]], [inp["g_img"], inp["g_dist"]])
-        if world > 1:
-            dist.all_reduce(v.grad)
-            dist.all_reduce(c.grad)
+        rmdist.allreduce_gradients([v.grad, c.grad])
         return pkg, v.grad, c.grad
 
     def barrier():

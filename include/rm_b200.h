@@ -33,9 +33,9 @@ extern "C" {
 #define RM_STATUS_NAN_VERTEX 1u   /* a vertex coordinate is NaN (tile_shader_slang.py:78 asserts on this) */
 #define RM_STATUS_KEY_OVERFLOW 2u /* more than 2^31-1 (tile, tet) pairs (int32 cumsum, tile_shader_slang.py:36) */
 
-/* Floats per packed tet record (24 used by the integration + 8 for the projected
- * vertices used to cull whole tiles) and per record-gradient row. */
-#define RM_RECORD_FLOATS 32
+/* Floats per packed tet record (24 used by the integration + 12 for the hull edge
+ * lines of the projected tet, used to cull whole tiles) and per record-gradient row. */
+#define RM_RECORD_FLOATS 36
 #define RM_GRAD_RECORD_FLOATS 24
 
 /*
@@ -109,7 +109,7 @@ int rm_build_tile_lists(const int32_t* rect_tile_space, const int32_t* tile_rang
 
 /*
  * Per-frame packed tet records (4 outward face planes relative to the camera
- * position, colour field, density, and the 4 vertices projected to pixel
+ * position, colour field, density, and the edge lines of the projected hull in pixel
  * coordinates): the staged form of load_tet_alphablend_interp
  * (slang/interp_version.slang:100-153).
  * tiles_touched may be NULL (pack every tet) or [T] (skip culled tets).

@@ -8,7 +8,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "librm_b200.so")
 
-RM_RECORD_FLOATS = 32
+RM_RECORD_FLOATS = 36
 RM_GRAD_RECORD_FLOATS = 24
 RM_STATUS_NAN_VERTEX = 1
 RM_STATUS_KEY_OVERFLOW = 2

@@ -101,41 +101,65 @@ k_pack_records(const int32_t* __restrict__ indices, const float* __restrict__ ve
     px[k] = fx * (X / Z) + cx;
     py[k] = fy * (Y / Z) + cy;
   }
-  const float qnan = __int_as_float(0x7fc00000);
-  if (!ok) px[0] = qnan;
-  r[6] = make_float4(px[0], py[0], px[1], py[1]);
-  r[7] = make_float4(px[2], py[2], px[3], py[3]);
-}
-
-// True if the convex hull of the four projected vertices (q0, q1) is separated
-// from the axis-aligned box [X0,X1] x [Y0,Y1] of a half-warp's sample positions
-// by one of the hull's edge lines, with a margin of 0.01 pixel.  Conservative:
-// a NaN anywhere makes it false.
-__device__ __forceinline__ bool hull_misses_box(float4 q0, float4 q1, float X0, float X1, float Y0, float Y1) {
-  const float vx[4] = {q0.x, q0.z, q1.x, q1.z};
-  const float vy[4] = {q0.y, q0.w, q1.y, q1.w};
-  // bounding boxes first
-  const float mnx = fminf(fminf(vx[0], vx[1]), fminf(vx[2], vx[3])), mxx = fmaxf(fmaxf(vx[0], vx[1]), fmaxf(vx[2], vx[3]));
-  const float mny = fminf(fminf(vy[0], vy[1]), fminf(vy[2], vy[3])), mxy = fmaxf(fmaxf(vy[0], vy[1]), fmaxf(vy[2], vy[3]));
-  const bool finite = vx[0] == vx[0];
-  bool sep = (mxx < X0 - 0.01f) || (mnx > X1 + 0.01f) || (mxy < Y0 - 0.01f) || (mny > Y1 + 0.01f);
+  // Edge lines of the convex hull of the four projected vertices, a*x + b*y + c >= 0
+  // inside, (a, b) of unit length.  A vertex pair is a hull edge iff the other two
+  // vertices lie on one side of its line; a tet projects to a quadrilateral (4 such
+  // pairs) or to a triangle with one vertex inside (3).  Anything else is degenerate
+  // and disables the cull for this tet.
+  float la[4], lb[4], lc[4];
+  int ne = 0;
 #pragma unroll
   for (int a = 0; a < 4; ++a) {
 #pragma unroll
     for (int b = a + 1; b < 4; ++b) {
       const int c1 = (a != 0 && b != 0) ? 0 : ((a != 1 && b != 1) ? 1 : 2);
       const int c2 = 6 - a - b - c1;
-      const float nx = -(vy[b] - vy[a]), ny = vx[b] - vx[a];
-      const float s1 = nx * (vx[c1] - vx[a]) + ny * (vy[c1] - vy[a]);
-      const float s2 = nx * (vx[c2] - vx[a]) + ny * (vy[c2] - vy[a]);
-      const float m = 0.01f * (fabsf(nx) + fabsf(ny));
-      // extreme values of n.(corner - a) over the box
-      const float hi = nx * ((nx > 0.0f ? X1 : X0) - vx[a]) + ny * ((ny > 0.0f ? Y1 : Y0) - vy[a]);
-      const float lo = nx * ((nx > 0.0f ? X0 : X1) - vx[a]) + ny * ((ny > 0.0f ? Y0 : Y1) - vy[a]);
-      sep = sep || (s1 >= 0.0f && s2 >= 0.0f && hi < -m) || (s1 <= 0.0f && s2 <= 0.0f && lo > m);
+      float nx = -(py[b] - py[a]), ny = px[b] - px[a];
+      const float len = sqrtf(nx * nx + ny * ny);
+      const float s1 = nx * (px[c1] - px[a]) + ny * (py[c1] - py[a]);
+      const float s2 = nx * (px[c2] - px[a]) + ny * (py[c2] - py[a]);
+      const bool pos = s1 >= 0.0f && s2 >= 0.0f && (s1 > 0.0f || s2 > 0.0f);
+      const bool neg = s1 <= 0.0f && s2 <= 0.0f && (s1 < 0.0f || s2 < 0.0f);
+      if ((pos || neg) && len > 0.0f) {
+        const float inv = (pos ? 1.0f : -1.0f) / len;
+        nx *= inv;
+        ny *= inv;
+        if (ne < 4) {
+          la[ne] = nx;
+          lb[ne] = ny;
+          lc[ne] = -(nx * px[a] + ny * py[a]);
+        }
+        ++ne;
+      }
     }
   }
-  return finite && sep;
+  ok = ok && (ne == 3 || ne == 4);
+  if (ne == 3) { la[3] = la[2]; lb[3] = lb[2]; lc[3] = lc[2]; }
+  const float qnan = __int_as_float(0x7fc00000);
+  if (!ok) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) la[k] = lb[k] = lc[k] = qnan;
+  }
+  r[6] = make_float4(la[0], lb[0], lc[0], la[1]);
+  r[7] = make_float4(lb[1], lc[1], la[2], lb[2]);
+  r[8] = make_float4(lc[2], la[3], lb[3], lc[3]);
+}
+
+// True if one of the four hull edge lines of a tet's projection (l0, l1, l2) has the
+// whole box [X0,X1] x [Y0,Y1] of a half-warp's sample positions on its outer side
+// by more than 0.01 pixel.  Conservative: NaN lines never separate.
+__device__ __forceinline__ bool hull_misses_box(float4 l0, float4 l1, float4 l2, float X0, float X1, float Y0,
+                                                float Y1) {
+  const float a[4] = {l0.x, l0.w, l1.z, l2.y};
+  const float b[4] = {l0.y, l1.x, l1.w, l2.z};
+  const float c[4] = {l0.z, l1.y, l2.x, l2.w};
+  bool sep = false;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float hi = fmaf(a[k], a[k] > 0.0f ? X1 : X0, fmaf(b[k], b[k] > 0.0f ? Y1 : Y0, c[k]));
+    sep = sep || hi < -0.01f;
+  }
+  return sep;
 }
 
 // ----------------------------------------------------------------------------
@@ -353,7 +377,7 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
   float X0, X1, Y0, Y1;
   halfwarp_sample_box(u.inside, sx, sy, X0, X1, Y0, Y1);
   const float qnan = __int_as_float(0x7fc00000);
-  float4 nq0 = make_float4(qnan, qnan, qnan, qnan), nq1 = nq0;  // projected vertices of the record this lane stages
+  float4 nq0 = make_float4(qnan, qnan, qnan, qnan), nq1 = nq0, nq2 = nq0;  // hull lines of the record this lane stages
 
   float sr = 0.f, sg = 0.f, sb = 0.f, logT = 0.f, T = 1.f;
   float dx = 0.f, dy = 0.f, dz = 0.f, dw = 0.f, dv = 0.f;
@@ -375,13 +399,14 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
     for (int k = 0; k < 6; ++k) cp_async16(buf0 + lane16 * 6 + k, src + k);
     nq0 = __ldg(src + 6);
     nq1 = __ldg(src + 7);
+    nq2 = __ldg(src + 8);
   }
   cp_async_commit();
 
   for (int c = 0; c < max_chunks; ++c) {
     float4* cur = (c & 1) ? buf1 : buf0;
     float4* nxt = (c & 1) ? buf0 : buf1;
-    const float4 cq0 = nq0, cq1 = nq1;
+    const float4 cq0 = nq0, cq1 = nq1, cq2 = nq2;
     // issue the next chunk
     {
       int e = (c + 1) * kChunk + lane16;
@@ -392,6 +417,7 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
         for (int k = 0; k < 6; ++k) cp_async16(nxt + lane16 * 6 + k, src + k);
         nq0 = __ldg(src + 6);
         nq1 = __ldg(src + 7);
+        nq2 = __ldg(src + 8);
       }
       cp_async_commit();
     }
@@ -401,7 +427,7 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
     // contribute or terminate a pixel: only the entries flagged here are evaluated.
     // Neither are tets whose projection misses the box of this half-warp's samples.
     const bool nonzero = (c * kChunk + lane16 < u.len) && cur[lane16 * 6 + 5].w > 0.0f &&
-                         !hull_misses_box(cq0, cq1, X0, X1, Y0, Y1);
+                         !hull_misses_box(cq0, cq1, cq2, X0, X1, Y0, Y1);
     unsigned todo = (__ballot_sync(0xffffffffu, nonzero) >> (16 * half)) & 0xFFFFu;
     if (active) {
       while (todo) {
@@ -544,7 +570,7 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
   float X0, X1, Y0, Y1;
   halfwarp_sample_box(u.inside, sx, sy, X0, X1, Y0, Y1);
   const float qnan = __int_as_float(0x7fc00000);
-  float4 nq0 = make_float4(qnan, qnan, qnan, qnan), nq1 = nq0;
+  float4 nq0 = make_float4(qnan, qnan, qnan, qnan), nq1 = nq0, nq2 = nq0;
 
   // entries at or beyond the largest n_contributors of the half are skipped by every pixel
   int nmax = nc;
@@ -567,13 +593,14 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
         for (int q = 0; q < 6; ++q) cp_async16(dst + q, src + q);
         nq0 = __ldg(src + 6);
         nq1 = __ldg(src + 7);
+        nq2 = __ldg(src + 8);
       }
     }
     cp_async_commit();
   };
   issue(0);
   for (int k = 0; k < max_chunks; ++k) {
-    const float4 cq0 = nq0, cq1 = nq1;
+    const float4 cq0 = nq0, cq1 = nq1, cq2 = nq2;
     issue(k + 1);
     cp_async_wait<1>();
     __syncwarp();
@@ -584,7 +611,7 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
     // contribute).  Both halves step in lock-step through their own set bits,
     // last entry first; a half that runs out idles.
     const bool nonzero = c >= 0 && c * kChunk + lane16 < nmax && cur[lane16 * 6 + 5].w > 0.0f &&
-                         !hull_misses_box(cq0, cq1, X0, X1, Y0, Y1);
+                         !hull_misses_box(cq0, cq1, cq2, X0, X1, Y0, Y1);
     unsigned todo = (__ballot_sync(0xffffffffu, nonzero) >> (16 * half)) & 0xFFFFu;
     const int steps = max(__popc(todo), __shfl_xor_sync(0xffffffffu, __popc(todo), 16));
     for (int step = 0; step < steps; ++step) {

@@ -1,0 +1,116 @@
+"""Multi-GPU host logic: one process per GPU, torch.distributed for the plumbing.
+
+The rasterizer shards two ways and needs no collective inside its kernels:
+
+* view-parallel: every rank renders its own view of a replicated mesh; the two
+  gradient tensors are summed over ranks afterwards (`allreduce_gradients`);
+* tile-row bands: one large frame is split into contiguous bands of tile rows,
+  every rank renders its band (the rasterizer clamps each tet's rectangle to the
+  band, so a band's tile lists are exactly the single-GPU lists of those rows),
+  and the image rows are combined (`combine_band_images`).
+
+The reference is single-GPU (nothing under delaunay_rasterization/ or train.py
+touches torch.distributed); this module has no counterpart there.
+The functions take the renderer as a callable so that the same logic runs on CPU
+ranks (gloo) in the tests.
+"""
+import numpy as np
+import torch
+import torch.distributed as dist
+
+
+def allreduce_gradients(grads, group=None):
+    """Sum each gradient tensor over the ranks, in place. Returns the list."""
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        for g in grads:
+            dist.all_reduce(g, op=dist.ReduceOp.SUM, group=group)
+    return grads
+
+
+def tile_row_bands(grid_height, world_size, row_weights=None):
+    """Split tile rows [0, grid_height) into world_size contiguous bands.
+
+    row_weights[r] is the work of tile row r (e.g. its number of (tile, tet)
+    pairs); bands are cut where the running weight crosses k/world_size of the
+    total, so every rank computes the same cuts from the same weights without
+    communicating. Without weights the rows are split evenly. Bands may be empty
+    when there are more ranks than rows.
+    """
+    if row_weights is None:
+        w = np.ones(grid_height, np.float64)
+    else:
+        w = np.asarray(row_weights, np.float64).reshape(-1)
+        assert w.shape[0] == grid_height
+        if w.sum() <= 0:
+            w = np.ones(grid_height, np.float64)
+    cum = np.concatenate([[0.0], np.cumsum(w)])
+    cuts = [0]
+    for k in range(1, world_size):
+        target = cum[-1] * k / world_size
+        r = int(np.searchsorted(cum, target, side="left"))
+        cuts.append(min(max(r, cuts[-1]), grid_height))
+    cuts.append(grid_height)
+    return [(cuts[k], cuts[k + 1]) for k in range(world_size)]
+
+
+def row_weights_from_rects(rect_tile_space, tiles_touched, grid_height):
+    """Work per tile row from the per-tet rectangles: sum over tets of the rectangle
+    width for every row the rectangle covers (a difference array over rows)."""
+    rect = rect_tile_space.to(torch.int64)
+    vis = tiles_touched > 0
+    width = (rect[:, 2] - rect[:, 0]) * vis
+    diff = torch.zeros(grid_height + 1, dtype=torch.int64, device=rect.device)
+    diff.index_add_(0, rect[:, 1].clamp(0, grid_height), width)
+    diff.index_add_(0, rect[:, 3].clamp(0, grid_height), -width)
+    return torch.cumsum(diff, 0)[:grid_height]
+
+
+def combine_band_images(local_image, band, tile_height, group=None):
+    """Full image from per-rank band images.
+
+    local_image is full-size [H, W, C] with valid rows only inside the rank's band
+    (other rows are ignored). Returns the full image on every rank.
+    """
+    H = local_image.shape[0]
+    r0, r1 = band
+    y0, y1 = min(r0 * tile_height, H), min(r1 * tile_height, H)
+    out = torch.zeros_like(local_image)
+    out[y0:y1] = local_image[y0:y1]
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(out, op=dist.ReduceOp.SUM, group=group)
+    return out
+
+
+def render_view_parallel(render_backward_fn, views, rank, world_size, group=None):
+    """Each rank renders views[rank::world_size] and the gradients are summed.
+
+    render_backward_fn(view) -> (image, vertices_grad, cell_values_grad).
+    Returns (list of local images, vertices_grad, cell_values_grad) with the
+    gradients summed over all views of all ranks.
+    """
+    images, vg, cg = [], None, None
+    for v in views[rank::world_size]:
+        img, g_v, g_c = render_backward_fn(v)
+        images.append(img)
+        vg = g_v.clone() if vg is None else vg + g_v
+        cg = g_c.clone() if cg is None else cg + g_c
+    allreduce_gradients([vg, cg], group)
+    return images, vg, cg
+
+
+def render_band_split(render_band_fn, grid_height, tile_height, rank, world_size, row_weights=None, group=None):
+    """One frame split over the ranks by tile-row bands.
+
+    render_band_fn((row_begin, row_end)) -> full-size image whose band rows are valid.
+    Returns (full image on every rank, this rank's band).
+    """
+    bands = tile_row_bands(grid_height, world_size, row_weights)
+    band = bands[rank]
+    if band[1] > band[0]:
+        local = render_band_fn(band)
+    else:
+        local = None
+    if local is None:
+        # a rank without rows still has to join the collective with the right shape
+        local = render_band_fn((0, 0))
+    return combine_band_images(local, band, tile_height, group), band

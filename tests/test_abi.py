@@ -29,7 +29,7 @@ def test_struct_layout_matches_header():
     from radiance_meshes_b200 import _lib
     assert C.sizeof(_lib.RmBinInfo) == 16
     assert C.sizeof(_lib.RmCamera) == 4 * 8 + 12 * 4
-    assert _lib.RM_RECORD_FLOATS == 32 and _lib.RM_GRAD_RECORD_FLOATS == 24
+    assert _lib.RM_RECORD_FLOATS == 36 and _lib.RM_GRAD_RECORD_FLOATS == 24
 
 
 def test_host_path_rejects_cpu_tensors():

@@ -203,3 +203,42 @@ def test_medium_scene_sort_classes(oracle, cuda_lib):
     ref, got = check_against_oracle(oracle, pts, tets, cell, tcam, scene_util.jitter(H, W, 7), check_grad=True)
     lens = ref["tile_ranges"][:, 1] - ref["tile_ranges"][:, 0]
     assert lens.max() > 2048
+
+
+def test_tile_row_bands_match_full_frame(oracle, cuda_lib):
+    # one frame rendered as two tile-row bands (the multi-GPU split of a large
+    # frame) equals the full-frame render: lists are the corresponding subsets,
+    # image rows are identical
+    from radiance_meshes_b200 import dist as rmdist
+    from radiance_meshes_b200.render import render, tcam_to_device
+    pts, tets, cell = scene_util.small_scene(500, seed=23)
+    H, W = 72, 64
+    tcam_np = scene_util.camera(H=H, W=W, tile=4)
+    dev = torch.device("cuda:0")
+    idx_t = torch.tensor(tets, device=dev)
+    v = torch.tensor(pts, device=dev)
+    c = torch.tensor(cell, device=dev)
+    jit = torch.tensor(scene_util.jitter(H, W, 9), device=dev)
+    full = render(idx_t, v, c, tcam_to_device(tcam_np, dev), jit)
+    gw, gh = tcam_np["grid_width"], tcam_np["grid_height"]
+    weights = rmdist.row_weights_from_rects(full["rect"], full["mask"].int(), gh)
+    lens = (full["tile_ranges"][:, 1] - full["tile_ranges"][:, 0]).reshape(gh, gw).sum(1)
+    assert torch.equal(weights.cpu(), lens.cpu().long())
+    bands = rmdist.tile_row_bands(gh, 2, weights.cpu().numpy())
+    combined = torch.zeros_like(full["image"])
+    combined_dist = torch.zeros_like(full["distortion_img"])
+    for band in bands:
+        tcam_b = dict(tcam_to_device(tcam_np, dev), tile_rows=band)
+        part = render(idx_t, v, c, tcam_b, jit)
+        y0, y1 = band[0] * 4, min(band[1] * 4, H)
+        combined[y0:y1] = part["image"][y0:y1]
+        combined_dist[y0:y1] = part["distortion_img"][y0:y1]
+        fr, pr = full["tile_ranges"].cpu().numpy(), part["tile_ranges"].cpu().numpy()
+        fi, pi = full["sorted_tetra_idx"].cpu().numpy(), part["sorted_tetra_idx"].cpu().numpy()
+        for t in range(band[0] * gw, band[1] * gw):
+            np.testing.assert_array_equal(pi[pr[t, 0]:pr[t, 1]], fi[fr[t, 0]:fr[t, 1]])
+        outside = np.ones(gh * gw, bool)
+        outside[band[0] * gw:band[1] * gw] = False
+        assert not pr[outside].any()
+    assert torch.equal(combined, full["image"])
+    assert torch.equal(combined_dist, full["distortion_img"])

@@ -1,0 +1,137 @@
+"""Multi-rank host logic on CPU ranks (gloo, world_size 2): gradient all-reduce
+for view-parallel rendering and tile-row band splitting of one frame.  The CPU
+oracle stands in for the renderer, so these run without a GPU."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import scene_util
+from radiance_meshes_b200 import dist as rmdist
+from radiance_meshes_b200 import scenes
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _scene():
+    pts, tets, cell = scene_util.small_scene(150, seed=17)
+    return pts, tets, cell
+
+
+def _view(k, H=32, W=40):
+    return scenes.ring_camera(k, 4, H, W, 60.0, radius=2.6, tile=4, min_t=0.1)
+
+
+def _oracle_render_backward(O, pts, tets, cell, tcam, rows=None):
+    H, W = tcam["image_height"], tcam["image_width"]
+    jit = np.full((H, W, 2), 0.5, np.float32)
+    pr = O.project(tets, pts, tcam)
+    tt, rect = pr["tiles_touched"], pr["rect"]
+    if rows is not None:
+        tt, rect = O.restrict_to_tile_rows(tt, rect, rows[0], rows[1])
+    idx, ranges = O.build_lists(tt, rect, pr["vs_tetra"], tcam["grid_height"], tcam["grid_width"])
+    prow = None if rows is None else (rows[0] * tcam["tile_height"], min(rows[1] * tcam["tile_height"], H))
+    if prow is not None and prow[1] <= prow[0]:
+        return np.zeros((H, W, 4), np.float32), None, None, idx, ranges
+    out, dist_img, nc = O.forward(idx, ranges, tets, pts, cell, tcam, jit, rows=prow)
+    g_img = np.ones((H, W, 4), np.float32)
+    vg, cg = O.backward(idx, ranges, tets, pts, cell, tcam, jit, out, dist_img, nc, g_img,
+                        np.zeros((H, W, 5), np.float32), rows=prow)
+    return out, vg, cg, idx, ranges
+
+
+def _worker(rank, world, port, results):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import oracle as O
+        pts, tets, cell = _scene()
+        # --- view-parallel: 4 views over 2 ranks, gradients summed
+        def rb(view):
+            out, vg, cg, _, _ = _oracle_render_backward(O, pts, tets, cell, _view(view))
+            return torch.from_numpy(out), torch.from_numpy(vg), torch.from_numpy(cg)
+        images, vg, cg = rmdist.render_view_parallel(rb, [0, 1, 2, 3], rank, world)
+        # --- band split of view 0
+        tcam = _view(0)
+        pr = O.project(tets, pts, tcam)
+        weights = rmdist.row_weights_from_rects(torch.from_numpy(pr["rect"]), torch.from_numpy(pr["tiles_touched"]),
+                                                tcam["grid_height"])
+        def band_fn(band):
+            out, _, _, _, _ = _oracle_render_backward(O, pts, tets, cell, tcam, rows=band)
+            return torch.from_numpy(out)
+        full, band = rmdist.render_band_split(band_fn, tcam["grid_height"], tcam["tile_height"], rank, world,
+                                              row_weights=weights.numpy())
+        results[rank] = dict(vg=vg.numpy(), cg=cg.numpy(), n_images=len(images), full=full.numpy(), band=band,
+                             weights=weights.numpy())
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_view_parallel_and_band_split(oracle):
+    world = 2
+    port = _free_port()
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_worker, args=(world, port, results), nprocs=world, join=True)
+    pts, tets, cell = _scene()
+    # serial reference: sum of the four views' gradients
+    vg_ref = cg_ref = None
+    for v in range(4):
+        _, vg, cg, _, _ = _oracle_render_backward(oracle, pts, tets, cell, _view(v))
+        vg_ref = vg if vg_ref is None else vg_ref + vg
+        cg_ref = cg if cg_ref is None else cg_ref + cg
+    for r in range(world):
+        assert results[r]["n_images"] == 2
+        np.testing.assert_allclose(results[r]["vg"], vg_ref, rtol=1e-5, atol=1e-5 * np.abs(vg_ref).max())
+        np.testing.assert_allclose(results[r]["cg"], cg_ref, rtol=1e-5, atol=1e-5 * np.abs(cg_ref).max())
+    # band split: the combined image equals the single-rank image bit for bit
+    full_ref, _, _, idx_full, ranges_full = _oracle_render_backward(oracle, pts, tets, cell, _view(0))
+    np.testing.assert_array_equal(results[0]["full"], full_ref)
+    np.testing.assert_array_equal(results[1]["full"], full_ref)
+    b0, b1 = results[0]["band"], results[1]["band"]
+    assert b0[0] == 0 and b0[1] == b1[0] and b1[1] == _view(0)["grid_height"]
+    # weights are the per-row key counts
+    lens = (ranges_full[:, 1] - ranges_full[:, 0]).reshape(_view(0)["grid_height"], -1).sum(1)
+    np.testing.assert_array_equal(results[0]["weights"], lens)
+
+
+def test_band_lists_are_subsets_of_full_lists(oracle):
+    pts, tets, cell = _scene()
+    tcam = _view(1)
+    pr = oracle.project(tets, pts, tcam)
+    idx, ranges = oracle.build_lists(pr["tiles_touched"], pr["rect"], pr["vs_tetra"], tcam["grid_height"],
+                                     tcam["grid_width"])
+    gw = tcam["grid_width"]
+    for band in rmdist.tile_row_bands(tcam["grid_height"], 3):
+        tt, rect = oracle.restrict_to_tile_rows(pr["tiles_touched"], pr["rect"], *band)
+        bidx, branges = oracle.build_lists(tt, rect, pr["vs_tetra"], tcam["grid_height"], gw)
+        for t in range(band[0] * gw, band[1] * gw):
+            np.testing.assert_array_equal(bidx[branges[t, 0]:branges[t, 1]], idx[ranges[t, 0]:ranges[t, 1]])
+        outside = np.ones(len(branges), bool)
+        outside[band[0] * gw:band[1] * gw] = False
+        assert not branges[outside].any()
+
+
+def test_tile_row_bands_partition():
+    for gh, world in [(270, 8), (7, 3), (2, 4), (540, 8)]:
+        bands = rmdist.tile_row_bands(gh, world)
+        assert bands[0][0] == 0 and bands[-1][1] == gh
+        assert all(bands[k][1] == bands[k + 1][0] for k in range(world - 1))
+    w = np.zeros(100)
+    w[40:60] = 1.0
+    bands = rmdist.tile_row_bands(100, 4, w)
+    sums = [w[a:b].sum() for a, b in bands]
+    assert max(sums) - min(sums) <= 1.0 and sum(sums) == 20
