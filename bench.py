@@ -231,7 +231,13 @@ def run_gpu(args):
         dist.init_process_group("nccl", device_id=dev)
     _lib.load()
 
-    sc = load_scene(args.workload, rank, world)
+    # rank 0 builds (or finds) the cached mesh first; the others read it after the barrier
+    if rank == 0:
+        sc = load_scene(args.workload, 0, world)
+    if world > 1:
+        dist.barrier()
+    if rank != 0:
+        sc = load_scene(args.workload, rank, world)
     tcam_np = camera_for(args.workload, rank % 8)
     H, W = tcam_np["image_height"], tcam_np["image_width"]
     rng = np.random.default_rng(1234 + rank)
