@@ -302,6 +302,7 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 
 constexpr int kWarpsPerBlock = 4;
 constexpr int kChunk = 16;  // records staged per half-warp per round
+constexpr int kButterflyMinHits = 4;  // fewer hit pixels in a tile: direct atomics instead of the shuffle reduction
 
 struct Unit {
   int tile;       // linear tile index
@@ -475,62 +476,6 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
 // ----------------------------------------------------------------------------
 // Backward
 // ----------------------------------------------------------------------------
-// Sum v[0..N) over the 16 lanes of each half-warp.  On return lane l (0..15)
-// of a half holds at most two totals, written to out0/out1, whose field
-// indices are field0 and field0+1 (field0+1 may be >= N: padding).
-template <int N>
-__device__ __forceinline__ void halfwarp_transpose_reduce(float (&v)[N], int lane16, float& out0, float& out1,
-                                                          int& field0) {
-  static_assert(N == 24, "written for 24 fields");
-  int base = 0;
-  // 24 -> 12 (xor 8)
-  {
-    const bool up = lane16 & 8;
-#pragma unroll
-    for (int i = 0; i < 12; ++i) {
-      float send = up ? v[i] : v[i + 12];
-      float keep = up ? v[i + 12] : v[i];
-      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
-    }
-    base += up ? 12 : 0;
-  }
-  // 12 -> 6 (xor 4)
-  {
-    const bool up = lane16 & 4;
-#pragma unroll
-    for (int i = 0; i < 6; ++i) {
-      float send = up ? v[i] : v[i + 6];
-      float keep = up ? v[i + 6] : v[i];
-      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
-    }
-    base += up ? 6 : 0;
-  }
-  // 6 -> 3 (xor 2)
-  {
-    const bool up = lane16 & 2;
-#pragma unroll
-    for (int i = 0; i < 3; ++i) {
-      float send = up ? v[i] : v[i + 3];
-      float keep = up ? v[i + 3] : v[i];
-      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
-    }
-    base += up ? 3 : 0;
-  }
-  // 3 (+1 pad) -> 2 (xor 1)
-  {
-    const bool up = lane16 & 1;
-    float a0 = v[0], a1 = v[1], a2 = v[2], a3 = 0.0f;
-    float send0 = up ? a0 : a2, send1 = up ? a1 : a3;
-    float keep0 = up ? a2 : a0, keep1 = up ? a3 : a1;
-    out0 = keep0 + __shfl_xor_sync(0xffffffffu, send0, 1);
-    out1 = keep1 + __shfl_xor_sync(0xffffffffu, send1, 1);
-    base += up ? 2 : 0;
-    // lanes with up hold fields base (=+2) and a padding slot
-    field0 = base;
-    if (up) out1 = 0.0f;
-  }
-}
-
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, const float4* __restrict__ records,
            RmCamera rcam, const float2* __restrict__ jitter, const float4* __restrict__ out_img,
@@ -541,7 +486,6 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
   __shared__ int stage_id[kWarpsPerBlock][2][2][kChunk];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int half = lane >> 4, lane16 = lane & 15;
-  const unsigned half_mask = 0xFFFFu << (16 * half);
   const int64_t unit = ((int64_t)blockIdx.x * kWarpsPerBlock + warp) * 2 + half;
   Unit u = make_unit(rcam, ranges, unit, n_units, subs, lane16);
 
@@ -629,9 +573,13 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
       if (in_range && u.inside && e < nc) hit = slab_test(rec, d, min_t, ev) && integrate(rec, d, min_t, ev);
       const unsigned hits = __ballot_sync(0xffffffffu, hit);
       if (hits == 0) continue;
-      float g[24];
+      // Per lane: gradient of the entering plane (v[0..3] -> row[4*pe..]), of the
+      // exit plane (v[4..7] -> row[4*px..]) and of the colour fields (v[8..15] ->
+      // row[16..23]); zero for lanes without a hit.
+      float v[16];
 #pragma unroll
-      for (int q = 0; q < 24; ++q) g[q] = 0.0f;
+      for (int q = 0; q < 16; ++q) v[q] = 0.0f;
+      int pe = -1, px = -1;  // planes that receive v[0..3] / v[4..7]; -1: none
       {
         if (hit) {
           const float4 cbv = rec[5];
@@ -682,47 +630,76 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
           float g_tx = 0.0f, g_te = 0.0f;
           if (ev.tx > ev.enter) g_tx = g_exit; else g_enter += g_exit;
           if (ev.te > 0.0f) g_te = g_enter;
-          // planes
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float gt = (i == ev.ie ? g_te : 0.0f) + (i == ev.ix ? g_tx : 0.0f);
-            const float4 p = rec[i];
-            const float den = p.x * d.x + p.y * d.y + p.z * d.z;
-            const float r = (gt != 0.0f) ? 1.0f / den : 0.0f;
-            const float kD = -gt * r;
-            const float kn = gt * p.w * r * r;
-            g[4 * i + 0] = kn * d.x;
-            g[4 * i + 1] = kn * d.y;
-            g[4 * i + 2] = kn * d.z;
-            g[4 * i + 3] = kD;
+          // planes: t = -D/den - min_t  =>  dt/dD = -1/den, dt/dn = (D/den^2) d
+          if (g_te != 0.0f && ev.ie >= 0) {
+            const float4 p = rec[ev.ie];
+            const float r = __fdividef(1.0f, p.x * d.x + p.y * d.y + p.z * d.z);
+            const float kn = g_te * p.w * r * r;
+            v[0] = kn * d.x; v[1] = kn * d.y; v[2] = kn * d.z; v[3] = -g_te * r;
+            pe = ev.ie;
           }
-          g[16] = g_gd * d.x;
-          g[17] = g_gd * d.y;
-          g[18] = g_gd * d.z;
-          g[19] = g_ox + g_oe;
-          g[20] = wsum * gcr;
-          g[21] = wsum * gcg;
-          g[22] = wsum * gcb;
-          g[23] = g_dens;
+          if (g_tx != 0.0f && ev.ix >= 0) {
+            const float4 p = rec[ev.ix];
+            const float r = __fdividef(1.0f, p.x * d.x + p.y * d.y + p.z * d.z);
+            const float kn = g_tx * p.w * r * r;
+            v[4] = kn * d.x; v[5] = kn * d.y; v[6] = kn * d.z; v[7] = -g_tx * r;
+            px = ev.ix;
+          }
+          v[8] = g_gd * d.x;
+          v[9] = g_gd * d.y;
+          v[10] = g_gd * d.z;
+          v[11] = g_ox + g_oe;
+          v[12] = wsum * gcr;
+          v[13] = wsum * gcg;
+          v[14] = wsum * gcb;
+          v[15] = g_dens;
         }
       }
-      if (max(__popc(hits & 0xFFFFu), __popc(hits >> 16)) <= 2) {
-        // one or two pixels of a tile hit this tet: their lanes add the 24 sums directly
-        if (hit) {
-          float* row = grec + (int64_t)cur_id[j] * 24;
+      // Reduction over the pixels of a tile.  If every contributing lane of a half
+      // enters through the same face and leaves through the same face, and enough
+      // lanes hit, the 16 sums are formed with a transposed butterfly (15 shuffles,
+      // one atomic per lane); otherwise each hit lane adds its own 16 values.
+      const unsigned my_hits = (hits >> (16 * half)) & 0xFFFFu;
+      const unsigned e_lanes = (__ballot_sync(0xffffffffu, pe >= 0) >> (16 * half)) & 0xFFFFu;
+      const unsigned x_lanes = (__ballot_sync(0xffffffffu, px >= 0) >> (16 * half)) & 0xFFFFu;
+      const int src_e = e_lanes ? (__ffs(e_lanes) - 1) + 16 * half : lane;
+      const int src_x = x_lanes ? (__ffs(x_lanes) - 1) + 16 * half : lane;
+      const int pe_ref = __shfl_sync(0xffffffffu, pe, src_e);
+      const int px_ref = __shfl_sync(0xffffffffu, px, src_x);
+      const bool odd = (pe >= 0 && pe != pe_ref) || (px >= 0 && px != px_ref);
+      const bool use_butterfly =
+          __ballot_sync(0xffffffffu, odd || (my_hits != 0 && __popc(my_hits) < kButterflyMinHits)) == 0;
+      if (use_butterfly) {
+        // 16 -> 8 -> 4 -> 2 -> 1; lane l of a half ends with the total of field l
 #pragma unroll
-          for (int q = 0; q < 24; ++q)
-            if (g[q] != 0.0f) atomicAdd(row + q, g[q]);
+        for (int w = 8; w >= 1; w >>= 1) {
+          const bool up = lane16 & w;
+#pragma unroll
+          for (int i = 0; i < w; ++i) {
+            const float send = up ? v[i] : v[i + w];
+            const float keep = up ? v[i + w] : v[i];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, w);
+          }
         }
-      } else {
-        float o0, o1;
-        int f0;
-        halfwarp_transpose_reduce<24>(g, lane16, o0, o1, f0);
-        if (hits & half_mask) {
+        if (my_hits && v[0] != 0.0f) {
           float* row = grec + (int64_t)cur_id[j] * 24;
-          if (o0 != 0.0f) atomicAdd(row + f0, o0);
-          if (f0 + 1 < 24 && !(lane16 & 1) && o1 != 0.0f) atomicAdd(row + f0 + 1, o1);
+          const int f = lane16;
+          const int dst = f < 4 ? 4 * pe_ref + f : (f < 8 ? 4 * px_ref + (f - 4) : f + 8);
+          if (dst >= 0) atomicAdd(row + dst, v[0]);
         }
+      } else if (hit) {
+        float* row = grec + (int64_t)cur_id[j] * 24;
+        if (pe >= 0) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) atomicAdd(row + 4 * pe + q, v[q]);
+        }
+        if (px >= 0) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) atomicAdd(row + 4 * px + q, v[4 + q]);
+        }
+#pragma unroll
+        for (int q = 8; q < 16; ++q)
+          if (v[q] != 0.0f) atomicAdd(row + 8 + q, v[q]);
       }
     }
     __syncwarp();
