@@ -226,7 +226,7 @@ struct Eval {
   float cr, cg, cb;           // colour contribution
 };
 
-__device__ __forceinline__ bool slab_test(const float4* __restrict__ rec, f3 d, float min_t, Eval& e) {
+__device__ __forceinline__ bool slab_test(const float4 (&rec)[4], f3 d, float min_t, Eval& e) {
   // Distances are first taken from the camera position (u = -D/den) and shifted
   // by min_t afterwards: t = -(D + min_t*den)/den = u - min_t.
   float ue = -1e30f, ux = 1e30f;
@@ -392,7 +392,8 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
 
   float4* buf0 = stage[warp][half][0];
   float4* buf1 = stage[warp][half][1];
-  // prologue: stage chunk 0
+  // prologue: stage chunk 0; the list entry of the chunk after next is always
+  // loaded one iteration before it is needed
   if (fetching && lane16 < u.len) {
     int id = __ldg(list + u.start + lane16);
     const float4* src = records + kRecStride * (int64_t)id;
@@ -403,6 +404,7 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
     nq2 = __ldg(src + 8);
   }
   cp_async_commit();
+  int id_next = (fetching && kChunk + lane16 < u.len) ? __ldg(list + u.start + kChunk + lane16) : 0;
 
   for (int c = 0; c < max_chunks; ++c) {
     float4* cur = (c & 1) ? buf1 : buf0;
@@ -412,8 +414,7 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
     {
       int e = (c + 1) * kChunk + lane16;
       if (fetching && e < u.len) {
-        int id = __ldg(list + u.start + e);
-        const float4* src = records + kRecStride * (int64_t)id;
+        const float4* src = records + kRecStride * (int64_t)id_next;
 #pragma unroll
         for (int k = 0; k < 6; ++k) cp_async16(nxt + lane16 * 6 + k, src + k);
         nq0 = __ldg(src + 6);
@@ -421,6 +422,7 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
         nq2 = __ldg(src + 8);
       }
       cp_async_commit();
+      if (fetching && e + kChunk < u.len) id_next = __ldg(list + u.start + e + kChunk);
     }
     cp_async_wait<1>();
     __syncwarp();
@@ -430,13 +432,17 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
     const bool nonzero = (c * kChunk + lane16 < u.len) && cur[lane16 * 6 + 5].w > 0.0f &&
                          !hull_misses_box(cq0, cq1, cq2, X0, X1, Y0, Y1);
     unsigned todo = (__ballot_sync(0xffffffffu, nonzero) >> (16 * half)) & 0xFFFFu;
-    if (active) {
-      while (todo) {
-        const int j = __ffs(todo) - 1;
+    if (active && todo) {
+      int j = __ffs(todo) - 1;
+      float4 pl[4] = {cur[j * 6], cur[j * 6 + 1], cur[j * 6 + 2], cur[j * 6 + 3]};
+      while (true) {
         todo &= todo - 1;
+        // planes of the next record to evaluate, loaded while this one is tested
+        const int jn = todo ? __ffs(todo) - 1 : j;
+        const float4 nx[4] = {cur[jn * 6], cur[jn * 6 + 1], cur[jn * 6 + 2], cur[jn * 6 + 3]};
         const float4* rec = cur + j * 6;
         Eval e;
-        if (slab_test(rec, d, min_t, e) && integrate(rec, d, min_t, e)) {
+        if (slab_test(pl, d, min_t, e) && integrate(rec, d, min_t, e)) {
           sr = fmaf(e.cr, T, sr);
           sg = fmaf(e.cg, T, sg);
           sb = fmaf(e.cb, T, sb);
@@ -455,6 +461,10 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
             break;
           }
         }
+        if (!todo) break;
+        j = jn;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) pl[q] = nx[q];
       }
     }
     __syncwarp();
@@ -524,12 +534,19 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
   const int max_chunks = max(nchunks, __shfl_xor_sync(0xffffffffu, nchunks, 16));
 
   // chunk k of this half (k = 0 is the LAST chunk of its list) sits in buffer k&1
+  // list entry this lane stages for chunk k+1, loaded while chunk k is issued
+  int id_next = 0;
+  {
+    const int e0 = (nchunks - 1) * kChunk + lane16;
+    if (nchunks >= 1 && e0 < nmax) id_next = __ldg(list + u.start + e0);
+  }
   auto issue = [&](int k) {
     int c = nchunks - 1 - k;
     if (c >= 0) {
       int e = c * kChunk + lane16;
+      const int id = id_next;
+      if (c >= 1) id_next = __ldg(list + u.start + e - kChunk);  // always < nmax
       if (e < nmax) {
-        int id = __ldg(list + u.start + e);
         stage_id[warp][half][k & 1][lane16] = id;
         const float4* src = records + kRecStride * (int64_t)id;
         float4* dst = stage[warp][half][k & 1] + lane16 * 6;
@@ -568,9 +585,10 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
       }
       const int e = c * kChunk + j;
       const float4* rec = cur + j * 6;
+      const float4 pl[4] = {rec[0], rec[1], rec[2], rec[3]};
       bool hit = false;
       Eval ev;
-      if (in_range && u.inside && e < nc) hit = slab_test(rec, d, min_t, ev) && integrate(rec, d, min_t, ev);
+      if (in_range && u.inside && e < nc) hit = slab_test(pl, d, min_t, ev) && integrate(rec, d, min_t, ev);
       const unsigned hits = __ballot_sync(0xffffffffu, hit);
       if (hits == 0) continue;
       // Per lane: gradient of the entering plane (v[0..3] -> row[4*pe..]), of the
