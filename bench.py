@@ -26,6 +26,7 @@ WORKLOADS = {
     "config3": (3, None, 3),
     "config2": (2, None, 2),
     "small": (3, 60_000, 3),
+    "medium": (3, 300_000, 3),
 }
 CACHE_DIR = os.environ.get("RM_BENCH_CACHE", "/tmp/rm_b200_cache")
 

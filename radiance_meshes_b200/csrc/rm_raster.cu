@@ -706,18 +706,12 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
           if (dst >= 0) atomicAdd(row + dst, v[0]);
         }
       } else if (hit) {
-        float* row = grec + (int64_t)cur_id[j] * 24;
-        if (pe >= 0) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) atomicAdd(row + 4 * pe + q, v[q]);
-        }
-        if (px >= 0) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) atomicAdd(row + 4 * px + q, v[4 + q]);
-        }
-#pragma unroll
-        for (int q = 8; q < 16; ++q)
-          if (v[q] != 0.0f) atomicAdd(row + 8 + q, v[q]);
+        // 128-bit reductions: a plane's four sums and the colour sums are 16-byte aligned
+        float4* row = reinterpret_cast<float4*>(grec + (int64_t)cur_id[j] * 24);
+        if (pe >= 0) atomicAdd(row + pe, make_float4(v[0], v[1], v[2], v[3]));
+        if (px >= 0) atomicAdd(row + px, make_float4(v[4], v[5], v[6], v[7]));
+        atomicAdd(row + 4, make_float4(v[8], v[9], v[10], v[11]));
+        atomicAdd(row + 5, make_float4(v[12], v[13], v[14], v[15]));
       }
     }
     __syncwarp();
