@@ -226,6 +226,10 @@ struct Eval {
   float cr, cg, cb;           // colour contribution
 };
 
+// TRACK = false (forward): only the distances are needed, so the entering and exit
+// distances are plain max/min chains; TRACK = true (backward) also records which
+// plane produced each of them.
+template <bool TRACK>
 __device__ __forceinline__ bool slab_test(const float4 (&rec)[4], f3 d, float min_t, Eval& e) {
   // Distances are first taken from the camera position (u = -D/den) and shifted
   // by min_t afterwards: t = -(D + min_t*den)/den = u - min_t.
@@ -234,17 +238,23 @@ __device__ __forceinline__ bool slab_test(const float4 (&rec)[4], f3 d, float mi
   bool miss = false;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    float4 p = rec[i];
-    float den = p.x * d.x + p.y * d.y + p.z * d.z;
-    if (fabsf(den) < 1e-10f) {
-      miss = miss || (fmaf(min_t, den, p.w) > 0.0f);
-    } else {
-      float u = __fdividef(-p.w, den);
-      if (den < 0.0f) {
-        if (u > ue) { ue = u; ie = i; }
-      } else {
-        if (u < ux) { ux = u; ix = i; }
+    const float4 p = rec[i];
+    const float den = p.x * d.x + p.y * d.y + p.z * d.z;
+    const float u = __fdividef(-p.w, den);
+    const bool par = fabsf(den) < 1e-10f;  // ray parallel to the plane: ignored unless outside
+    miss = miss || (par && fmaf(min_t, den, p.w) > 0.0f);
+    const bool entering = den < 0.0f;
+    if (TRACK) {
+      if (!par) {
+        if (entering) {
+          if (u > ue) { ue = u; ie = i; }
+        } else {
+          if (u < ux) { ux = u; ix = i; }
+        }
       }
+    } else {
+      ue = fmaxf(ue, (entering && !par) ? u : -1e30f);
+      ux = fminf(ux, (entering || par) ? 1e30f : u);
     }
   }
   const float te = ue - min_t, tx = ux - min_t;
@@ -442,7 +452,7 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
         const float4 nx[4] = {cur[jn * 6], cur[jn * 6 + 1], cur[jn * 6 + 2], cur[jn * 6 + 3]};
         const float4* rec = cur + j * 6;
         Eval e;
-        if (slab_test(pl, d, min_t, e) && integrate(rec, d, min_t, e)) {
+        if (slab_test<false>(pl, d, min_t, e) && integrate(rec, d, min_t, e)) {
           sr = fmaf(e.cr, T, sr);
           sg = fmaf(e.cg, T, sg);
           sb = fmaf(e.cb, T, sb);
@@ -588,7 +598,7 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
       const float4 pl[4] = {rec[0], rec[1], rec[2], rec[3]};
       bool hit = false;
       Eval ev;
-      if (in_range && u.inside && e < nc) hit = slab_test(pl, d, min_t, ev) && integrate(rec, d, min_t, ev);
+      if (in_range && u.inside && e < nc) hit = slab_test<true>(pl, d, min_t, ev) && integrate(rec, d, min_t, ev);
       const unsigned hits = __ballot_sync(0xffffffffu, hit);
       if (hits == 0) continue;
       // Per lane: gradient of the entering plane (v[0..3] -> row[4*pe..]), of the
