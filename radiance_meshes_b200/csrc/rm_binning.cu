@@ -824,10 +824,13 @@ int rm_launch_build_lists(const int32_t* rect, const int32_t* tile_ranges, int64
   RM_CUDA_CHECK(cudaFuncSetAttribute(rm::k_tile_scatter1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_s1));
   RM_CUDA_CHECK(cudaFuncSetAttribute(rm::k_tile_scatter2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_s2));
   {
-    RmProfScope prof("tile_split_pass1(4 launches)", st);
+    RmProfScope prof("k_block_start_ranks+k_tile_hist1", st);
     rm::k_block_start_ranks<<<(P.nblk + 255) / 256, 256, 0, st>>>(cum, (int)T, P.nblk, starts);
     rm::k_tile_hist1<<<P.nblk, rm::kBinThreads, smem_h1, st>>>(cum, starts, order, (int)T, rect4, gw, n_keys, bins1,
                                                               hist, P.nblk);
+  }
+  {
+    RmProfScope prof("k_radix_rowscan+k_tile_scatter1", st);
     rm::k_radix_rowscan<<<bins1, 1024, 0, st>>>(hist, P.nblk, dtot);
     rm::k_tile_scatter1<<<P.nblk, rm::kBinThreads, smem_s1, st>>>(cum, starts, order, (int)T, rect4, gw, n_keys,
                                                                  bins1, hist, dtot, P.nblk, P.bits2 == 0, pairs,
@@ -835,11 +838,16 @@ int rm_launch_build_lists(const int32_t* rect, const int32_t* tile_ranges, int64
   }
   RM_CUDA_CHECK(cudaPeekAtLastError());
   if (P.bits2) {
-    RmProfScope prof("tile_split_pass2(3 launches)", st);
-    rm::k_tile_hist2<<<P.nblk, rm::kBinThreads, 4 * bins2, st>>>(pairs, n_keys, P.bits1, bins2, hist, P.nblk);
-    rm::k_radix_rowscan<<<bins2, 1024, 0, st>>>(hist, P.nblk, dtot);
-    rm::k_tile_scatter2<<<P.nblk, rm::kBinThreads, smem_s2, st>>>(pairs, n_keys, P.bits1, bins2, hist, dtot, P.nblk,
-                                                                 order, sorted_idx);
+    {
+      RmProfScope prof("k_tile_hist2", st);
+      rm::k_tile_hist2<<<P.nblk, rm::kBinThreads, 4 * bins2, st>>>(pairs, n_keys, P.bits1, bins2, hist, P.nblk);
+    }
+    {
+      RmProfScope prof("k_radix_rowscan+k_tile_scatter2", st);
+      rm::k_radix_rowscan<<<bins2, 1024, 0, st>>>(hist, P.nblk, dtot);
+      rm::k_tile_scatter2<<<P.nblk, rm::kBinThreads, smem_s2, st>>>(pairs, n_keys, P.bits1, bins2, hist, dtot,
+                                                                   P.nblk, order, sorted_idx);
+    }
     RM_CUDA_CHECK(cudaPeekAtLastError());
   }
   return RM_OK;

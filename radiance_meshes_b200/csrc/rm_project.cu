@@ -121,6 +121,32 @@ __device__ __forceinline__ void find_extent(const f3 tet[4], f3& mn, f3& mx, con
   }
 }
 
+// Extent of a tet that lies entirely in front of the near plane, seen by an
+// undistorted pinhole camera.  The general routine then clips nothing and samples
+// every directed face edge a->b at its two ends, a + (b-a)*0 and a + (b-a)*1; the
+// first is the vertex itself (up to the sign of a zero, which no later step can
+// see), so 4 vertex projections and 12 end samples give the same minima and
+// maxima as its 24 projections, without loops or local arrays.
+__device__ __forceinline__ void find_extent_unclipped(const f3 cs[4], f3& mn, f3& mx, const DevCam& c) {
+  const float BIG = 1e20f;
+  mn = {BIG, BIG, BIG};
+  mx = {-BIG, -BIG, -BIG};
+  auto add = [&](f3 p) {
+    const float ux = p.x / p.z, uy = p.y / p.z;
+    const float px = ux * c.K[0] + c.K[2];
+    const float py = uy * c.K[4] + c.K[5];
+    mn = {fminf(mn.x, px), fminf(mn.y, py), fminf(mn.z, p.z)};
+    mx = {fmaxf(mx.x, px), fmaxf(mx.y, py), fmaxf(mx.z, p.z)};
+  };
+#pragma unroll
+  for (int k = 0; k < 4; ++k) add(cs[k]);
+  // directed edges of the faces (0,1,2) (0,2,3) (0,3,1) (1,3,2)
+  const int ea[12] = {0, 1, 2, 0, 2, 3, 0, 3, 1, 1, 3, 2};
+  const int eb[12] = {1, 2, 0, 2, 3, 0, 3, 1, 0, 3, 2, 1};
+#pragma unroll
+  for (int e = 0; e < 12; ++e) add(lerp3(cs[ea[e]], cs[eb[e]], 1.0f));
+}
+
 __device__ __forceinline__ bool is_planar(const f3 v[4]) {
   f3 n = normalize3(cross(v[1] - v[0], v[2] - v[0]));
   float d = dot(n, v[3] - v[0]);
@@ -193,7 +219,10 @@ k_project(const int32_t* __restrict__ indices, int64_t T, const float* __restric
 #pragma unroll
     for (int k = 0; k < 4; ++k) cs[k] = point2camspace(v[k], cam);
     f3 mn, mx;
-    find_extent(cs, mn, mx, cam);
+    const bool simple = cam.type == 0 && dist_norm2(cam) < 1e-9f && cs[0].z > 1e-4f && cs[1].z > 1e-4f &&
+                        cs[2].z > 1e-4f && cs[3].z > 1e-4f;
+    if (simple) find_extent_unclipped(cs, mn, mx, cam);
+    else find_extent(cs, mn, mx, cam);
     if (mx.z <= 0.0f) break;
     d3 A = {v[0].x, v[0].y, v[0].z}, B = {v[1].x, v[1].y, v[1].z}, C = {v[2].x, v[2].y, v[2].z},
        D = {v[3].x, v[3].y, v[3].z}, P = {cam.pos[0], cam.pos[1], cam.pos[2]};

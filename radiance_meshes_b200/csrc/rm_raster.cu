@@ -60,89 +60,103 @@ __device__ __forceinline__ void make_planes(const f3 v[4], f3 cam, PlaneSetup& p
   }
 }
 
-__global__ void __launch_bounds__(256)
+constexpr int kPackThreads = 128;
+
+// One thread per tet builds the record in registers; the block then writes its
+// records through shared memory so that the global stores are contiguous.
+__global__ void __launch_bounds__(kPackThreads)
 k_pack_records(const int32_t* __restrict__ indices, const float* __restrict__ vertices,
                const float* __restrict__ cell, int64_t T, RmCamera rcam, const int32_t* __restrict__ tiles_touched,
                float4* __restrict__ records) {
-  int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (g >= T) return;
-  if (tiles_touched && tiles_touched[g] == 0) return;
-  f3 cam = {__ldg(rcam.cam_pos), __ldg(rcam.cam_pos + 1), __ldg(rcam.cam_pos + 2)};
-  int4 id = __ldg(reinterpret_cast<const int4*>(indices) + g);
-  f3 v[4] = {load3(vertices, id.x), load3(vertices, id.y), load3(vertices, id.z), load3(vertices, id.w)};
-  PlaneSetup p;
-  make_planes(v, cam, p);
-  const float* c = cell + 7 * g;
-  float density = fmaxf(__ldg(c), 0.0f);
-  f3 base = {__ldg(c + 1), __ldg(c + 2), __ldg(c + 3)};
-  f3 grd = {__ldg(c + 4), __ldg(c + 5), __ldg(c + 6)};
-  float s0 = dot(grd, cam - v[0]);
-  float4* r = records + kRecStride * g;
+  __shared__ __align__(16) float4 sm[kPackThreads * kRecStride];
+  const int64_t g0 = (int64_t)blockIdx.x * kPackThreads;
+  const int64_t g = g0 + threadIdx.x;
+  float4 r[kRecStride];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) r[i] = make_float4(p.n[i].x, p.n[i].y, p.n[i].z, p.D[i]);
-  r[4] = make_float4(grd.x, grd.y, grd.z, s0);
-  r[5] = make_float4(base.x, base.y, base.z, density);
-  // Vertices in pixel coordinates, for the per-tile cull of the integration
-  // kernels.  Only meaningful for an undistorted pinhole with the whole tet in
-  // front of the camera; otherwise NaN, which makes every cull test fail.
-  const float* W = rcam.world_view_transform;
-  const float* D = rcam.distortion_params;
-  const float fx = __ldg(rcam.K + 0), cx = __ldg(rcam.K + 2), fy = __ldg(rcam.K + 4), cy = __ldg(rcam.K + 5);
-  const float d2 = __ldg(D) * __ldg(D) + __ldg(D + 1) * __ldg(D + 1) + __ldg(D + 2) * __ldg(D + 2) +
-                   __ldg(D + 3) * __ldg(D + 3);
-  bool ok = rcam.camera_type == 0 && d2 < 1e-9f;
-  float px[4], py[4];
+  for (int k = 0; k < kRecStride; ++k) r[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (g < T && !(tiles_touched && tiles_touched[g] == 0)) {
+    f3 cam = {__ldg(rcam.cam_pos), __ldg(rcam.cam_pos + 1), __ldg(rcam.cam_pos + 2)};
+    int4 id = __ldg(reinterpret_cast<const int4*>(indices) + g);
+    f3 v[4] = {load3(vertices, id.x), load3(vertices, id.y), load3(vertices, id.z), load3(vertices, id.w)};
+    PlaneSetup p;
+    make_planes(v, cam, p);
+    const float* c = cell + 7 * g;
+    float density = fmaxf(__ldg(c), 0.0f);
+    f3 base = {__ldg(c + 1), __ldg(c + 2), __ldg(c + 3)};
+    f3 grd = {__ldg(c + 4), __ldg(c + 5), __ldg(c + 6)};
+    float s0 = dot(grd, cam - v[0]);
 #pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    float X = __ldg(W + 0) * v[k].x + __ldg(W + 1) * v[k].y + __ldg(W + 2) * v[k].z + __ldg(W + 3);
-    float Y = __ldg(W + 4) * v[k].x + __ldg(W + 5) * v[k].y + __ldg(W + 6) * v[k].z + __ldg(W + 7);
-    float Z = __ldg(W + 8) * v[k].x + __ldg(W + 9) * v[k].y + __ldg(W + 10) * v[k].z + __ldg(W + 11);
-    ok = ok && Z > 1e-3f;
-    px[k] = fx * (X / Z) + cx;
-    py[k] = fy * (Y / Z) + cy;
-  }
-  // Edge lines of the convex hull of the four projected vertices, a*x + b*y + c >= 0
-  // inside, (a, b) of unit length.  A vertex pair is a hull edge iff the other two
-  // vertices lie on one side of its line; a tet projects to a quadrilateral (4 such
-  // pairs) or to a triangle with one vertex inside (3).  Anything else is degenerate
-  // and disables the cull for this tet.
-  float la[4], lb[4], lc[4];
-  int ne = 0;
+    for (int i = 0; i < 4; ++i) r[i] = make_float4(p.n[i].x, p.n[i].y, p.n[i].z, p.D[i]);
+    r[4] = make_float4(grd.x, grd.y, grd.z, s0);
+    r[5] = make_float4(base.x, base.y, base.z, density);
+    // Vertices in pixel coordinates, for the per-tile cull of the integration
+    // kernels.  Only meaningful for an undistorted pinhole with the whole tet in
+    // front of the camera; otherwise the cull is disabled for this tet (NaN lines).
+    const float* W = rcam.world_view_transform;
+    const float* D = rcam.distortion_params;
+    const float fx = __ldg(rcam.K + 0), cx = __ldg(rcam.K + 2), fy = __ldg(rcam.K + 4), cy = __ldg(rcam.K + 5);
+    const float d2 = __ldg(D) * __ldg(D) + __ldg(D + 1) * __ldg(D + 1) + __ldg(D + 2) * __ldg(D + 2) +
+                     __ldg(D + 3) * __ldg(D + 3);
+    bool ok = rcam.camera_type == 0 && d2 < 1e-9f;
+    float px[4], py[4];
 #pragma unroll
-  for (int a = 0; a < 4; ++a) {
+    for (int k = 0; k < 4; ++k) {
+      float X = __ldg(W + 0) * v[k].x + __ldg(W + 1) * v[k].y + __ldg(W + 2) * v[k].z + __ldg(W + 3);
+      float Y = __ldg(W + 4) * v[k].x + __ldg(W + 5) * v[k].y + __ldg(W + 6) * v[k].z + __ldg(W + 7);
+      float Z = __ldg(W + 8) * v[k].x + __ldg(W + 9) * v[k].y + __ldg(W + 10) * v[k].z + __ldg(W + 11);
+      ok = ok && Z > 1e-3f;
+      px[k] = fx * (X / Z) + cx;
+      py[k] = fy * (Y / Z) + cy;
+    }
+    // Edge lines of the convex hull of the four projected vertices, a*x + b*y + c >= 0
+    // inside, (a, b) of unit length.  A vertex pair is a hull edge iff the other two
+    // vertices lie on one side of its line; a tet projects to a quadrilateral (4 such
+    // pairs) or to a triangle with one vertex inside (3).  Anything else is degenerate
+    // and disables the cull for this tet.
+    float la[4] = {0, 0, 0, 0}, lb[4] = {0, 0, 0, 0}, lc[4] = {0, 0, 0, 0};
+    int ne = 0;
 #pragma unroll
-    for (int b = a + 1; b < 4; ++b) {
-      const int c1 = (a != 0 && b != 0) ? 0 : ((a != 1 && b != 1) ? 1 : 2);
-      const int c2 = 6 - a - b - c1;
-      float nx = -(py[b] - py[a]), ny = px[b] - px[a];
-      const float len = sqrtf(nx * nx + ny * ny);
-      const float s1 = nx * (px[c1] - px[a]) + ny * (py[c1] - py[a]);
-      const float s2 = nx * (px[c2] - px[a]) + ny * (py[c2] - py[a]);
-      const bool pos = s1 >= 0.0f && s2 >= 0.0f && (s1 > 0.0f || s2 > 0.0f);
-      const bool neg = s1 <= 0.0f && s2 <= 0.0f && (s1 < 0.0f || s2 < 0.0f);
-      if ((pos || neg) && len > 0.0f) {
-        const float inv = (pos ? 1.0f : -1.0f) / len;
-        nx *= inv;
-        ny *= inv;
-        if (ne < 4) {
-          la[ne] = nx;
-          lb[ne] = ny;
-          lc[ne] = -(nx * px[a] + ny * py[a]);
+    for (int a = 0; a < 4; ++a) {
+#pragma unroll
+      for (int b = a + 1; b < 4; ++b) {
+        const int c1 = (a != 0 && b != 0) ? 0 : ((a != 1 && b != 1) ? 1 : 2);
+        const int c2 = 6 - a - b - c1;
+        float nx = -(py[b] - py[a]), ny = px[b] - px[a];
+        const float len = sqrtf(nx * nx + ny * ny);
+        const float s1 = nx * (px[c1] - px[a]) + ny * (py[c1] - py[a]);
+        const float s2 = nx * (px[c2] - px[a]) + ny * (py[c2] - py[a]);
+        const bool pos = s1 >= 0.0f && s2 >= 0.0f && (s1 > 0.0f || s2 > 0.0f);
+        const bool neg = s1 <= 0.0f && s2 <= 0.0f && (s1 < 0.0f || s2 < 0.0f);
+        if ((pos || neg) && len > 0.0f) {
+          const float inv = (pos ? 1.0f : -1.0f) / len;
+          nx *= inv;
+          ny *= inv;
+          const float cc = -(nx * px[a] + ny * py[a]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {  // slot `ne`, without dynamic indexing
+            if (q == ne) { la[q] = nx; lb[q] = ny; lc[q] = cc; }
+          }
+          ++ne;
         }
-        ++ne;
       }
     }
-  }
-  ok = ok && (ne == 3 || ne == 4);
-  if (ne == 3) { la[3] = la[2]; lb[3] = lb[2]; lc[3] = lc[2]; }
-  const float qnan = __int_as_float(0x7fc00000);
-  if (!ok) {
+    ok = ok && (ne == 3 || ne == 4);
+    if (ne == 3) { la[3] = la[2]; lb[3] = lb[2]; lc[3] = lc[2]; }
+    const float qnan = __int_as_float(0x7fc00000);
+    if (!ok) {
 #pragma unroll
-    for (int k = 0; k < 4; ++k) la[k] = lb[k] = lc[k] = qnan;
+      for (int k = 0; k < 4; ++k) la[k] = lb[k] = lc[k] = qnan;
+    }
+    r[6] = make_float4(la[0], lb[0], lc[0], la[1]);
+    r[7] = make_float4(lb[1], lc[1], la[2], lb[2]);
+    r[8] = make_float4(lc[2], la[3], lb[3], lc[3]);
   }
-  r[6] = make_float4(la[0], lb[0], lc[0], la[1]);
-  r[7] = make_float4(lb[1], lc[1], la[2], lb[2]);
-  r[8] = make_float4(lc[2], la[3], lb[3], lc[3]);
+#pragma unroll
+  for (int k = 0; k < kRecStride; ++k) sm[threadIdx.x * kRecStride + k] = r[k];
+  __syncthreads();
+  const int64_t n_rec = min((int64_t)kPackThreads, T - g0);
+  float4* out = records + g0 * kRecStride;
+  for (int i = threadIdx.x; i < n_rec * kRecStride; i += kPackThreads) out[i] = sm[i];
 }
 
 // True if one of the four hull edge lines of a tet's projection (l0, l1, l2) has the
@@ -813,7 +827,7 @@ int rm_launch_pack(const int32_t* indices, const float* vertices, const float* c
                    const int32_t* tiles_touched, float* records, cudaStream_t st) {
   if (T == 0) return RM_OK;
   RmProfScope prof("k_pack_records", st);
-  rm::k_pack_records<<<(unsigned)((T + 255) / 256), 256, 0, st>>>(indices, vertices, cell, T, *cam, tiles_touched,
+  rm::k_pack_records<<<(unsigned)((T + rm::kPackThreads - 1) / rm::kPackThreads), rm::kPackThreads, 0, st>>>(indices, vertices, cell, T, *cam, tiles_touched,
                                                                   reinterpret_cast<float4*>(records));
   RM_CUDA_CHECK(cudaPeekAtLastError());
   return RM_OK;
