@@ -337,6 +337,23 @@ def run_gpu(args):
     e2e_ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
     e2e_value = H * W * world / (e2e_ms * 1e-3) / 1e6
 
+    # ---- densification statistics (the next row after the fwd+bwd path), timed separately ----
+    tet_err_ms = None
+    if rank == 0:
+        from delaunay_rasterization.internal.render_err import tet_error_stats
+        perr = torch.randn((H, W), device=dev) * 0.1
+        serr = torch.rand((H, W), device=dev)
+        tt = pkg["mask"].to(torch.int32)
+        _lib.profile_read()
+        _lib.profile_enable(True)
+        for _ in range(4):
+            tet_error_stats(pkg["sorted_tetra_idx"], pkg["tile_ranges"], d["indices"], d["vertices"], d["cell"], tcam,
+                            perr, serr, tt)
+        torch.cuda.synchronize()
+        _lib.profile_enable(False)
+        ms = [t for n, t in _lib.profile_read() if n == "k_tet_err"]
+        tet_err_ms = float(np.mean(ms[1:])) if len(ms) > 1 else None
+
     if rank != 0:
         if world > 1:
             dist.barrier()
@@ -375,6 +392,9 @@ def run_gpu(args):
                             stages=alg),
         kernel_ms={k: round(v, 4) for k, v in sorted(kernel_ms.items(), key=lambda kv: -kv[1])},
         kernel_ms_sum=total_kernel_ms,
+        densification_stats=dict(kernel="k_tet_err", ms=tet_err_ms,
+                                 mpix_per_s=(H * W / (tet_err_ms * 1e-3) / 1e6) if tet_err_ms else None,
+                                 note="calc_tet_err pass over the same lists; not part of `value`"),
     )
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(sc, tcam_np)

@@ -143,6 +143,19 @@ int rm_backward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, con
                 float* vertices_grad, float* cell_values_grad, void* stream);
 
 /*
+ * Densification statistics.  Replaces calc_tet_err (slang/alphablend_shader_interp.slang:433-599,
+ * host side internal/render_err.py:119-150): every pixel walks its tile list from the
+ * pixel centre and every hit adds its weight T (transmittance in front of the tet times
+ * the tet's optical depth, with the reference's initial log-transmittance of 1) times
+ * (1, err, err^2, -, -, ssim, entry point xyz, exit point xyz, 1, mid point xyz) to
+ * tet_err[T,16] and (1, max int(65535*T)) to tet_count[T,2].  Both outputs are zeroed here.
+ *   pixel_err[H,W], ssim_err[H,W] f32; records from rm_pack_records.
+ */
+int rm_tet_err(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, const float* records,
+               const RmCamera* cam, const float* pixel_err, const float* ssim_err, int64_t n_tets, float* tet_err,
+               int32_t* tet_count, void* stream);
+
+/*
  * Reverse of stage 1 with respect to the vertices.  Replaces vertex_shader.bwd
  * (tile_shader_slang.py:128-150).  grad_vs_tetra[T,3] (only column 2 is read)
  * and grad_circumcenter[T,3] -> vertices_grad[V,3], zeroed here first.

@@ -168,6 +168,22 @@ def sensitive_pixels(sorted_idx, tile_ranges, indices, vertices, cell_values, tc
     return mask.astype(bool)
 
 
+def tet_err(sorted_idx, tile_ranges, indices, vertices, cell_values, tcam, pixel_err, ssim_err, nthreads=0):
+    """Densification statistics. Returns (tet_err[T,16] f32, tet_count[T,2] i32)."""
+    jit = np.zeros((1, 1, 2), np.float32)
+    sorted_idx, tile_ranges, indices, vertices, cell_values, _ = _fb_args(
+        np.float32, sorted_idx, tile_ranges, indices, vertices, cell_values, jit)
+    cam = make_camera(tcam)
+    pe = np.ascontiguousarray(_np(pixel_err), dtype=np.float32)
+    se = np.ascontiguousarray(_np(ssim_err), dtype=np.float32)
+    T = indices.shape[0]
+    err = np.zeros((T, 16), np.float32)
+    cnt = np.zeros((T, 2), np.int32)
+    lib().or_tet_err(_p(sorted_idx), _p(tile_ranges), _p(indices), _p(vertices), _p(cell_values), C.byref(cam),
+                     _p(pe), _p(se), C.c_int64(T), _p(err), _p(cnt), C.c_int(nthreads))
+    return err, cnt
+
+
 def vertex_backward(indices, vertices, tcam, tiles_touched, g_vs, g_cc):
     """Reverse of stage 1 wrt vertices. Returns vertices_grad[V,3]."""
     indices = np.ascontiguousarray(_np(indices), dtype=np.int32)

@@ -945,6 +945,63 @@ int or_walk_stats(const int32_t* sorted_idx, const int32_t* tile_ranges, const i
   return 0;
 }
 
+// Densification statistics: slang/alphablend_shader_interp.slang:433-599
+// (kern_calc_tet_err / calc_tet_err), host side internal/render_err.py:119-150.
+// Every pixel walks its tile list from the pixel centre (+0.5, no jitter) with the
+// pixel state starting at log-transmittance 1.0 (as the reference initialises it),
+// and every hit with positive optical depth adds, to row g of tet_err[T,16]:
+//   [0] T  [1] T*pixel_err  [2] T*pixel_err^2  [5] T*ssim_err  [6..8] T*p_enter
+//   [9..11] T*p_exit  [12] T  [13..15] T*p_mid          (columns 3, 4 stay zero)
+// with T = exp(logT_before) * optical_depth, and to tet_count[T,2]: [0] += 1,
+// [1] = max(., int(65535*T)).  Sums are formed in double and rounded once.
+int or_tet_err(const int32_t* sorted_idx, const int32_t* tile_ranges, const int32_t* indices, const float* vertices,
+               const float* cell, const OrCamera* ocam, const float* pixel_err, const float* ssim_err, int64_t T,
+               float* tet_err, int32_t* tet_count, int nthreads) {
+  Cam<float> cam = load_cam<float>(ocam);
+  const int H = cam.H, W = cam.Wd;
+  std::vector<double> acc((size_t)T * 16, 0.0);
+  for (int64_t i = 0; i < 2 * T; ++i) tet_count[i] = 0;
+#ifdef _OPENMP
+  if (nthreads > 0) omp_set_num_threads(nthreads);
+#endif
+#pragma omp parallel for schedule(dynamic, 16)
+  for (int64_t p = 0; p < (int64_t)H * W; ++p) {
+    int y = int(p / W), x = int(p % W);
+    int tile = (y / cam.tile_h) * cam.grid_w + (x / cam.tile_w);
+    int64_t s0 = tile_ranges[2 * tile], s1 = tile_ranges[2 * tile + 1];
+    V3<float> o, d;
+    get_ray(cam, float(x) + 0.5f, float(y) + 0.5f, o, d);
+    State<float> s = {0, 0, 0, 1.0f, 0, 0, 0, 0, 0};
+    const float perr = pixel_err[p], serr = ssim_err[p];
+    for (int64_t j = s0; j < s1; ++j) {
+      const int64_t g = sorted_idx[j];
+      Tet<float> t = load_tet<float>(g, indices, vertices, cell);
+      Ctrl<float> c;
+      if (!(evaluate_tet(t, o, d, c) && c.a > 0.f)) continue;
+      const float trans = std::exp(s.logT);
+      const float Tw = trans * c.a;
+      update_state(s, c);
+      V3<float> p1 = d * c.enter + o, p2 = d * c.exit + o, pc = d * (0.5f * (c.enter + c.exit)) + o;
+      const double vals[16] = {Tw, Tw * perr, Tw * perr * perr, 0, 0, Tw * serr, Tw * p1.x, Tw * p1.y, Tw * p1.z,
+                               Tw * p2.x, Tw * p2.y, Tw * p2.z, Tw, Tw * pc.x, Tw * pc.y, Tw * pc.z};
+      for (int k = 0; k < 16; ++k) {
+        if (vals[k] == 0) continue;
+#pragma omp atomic
+        acc[16 * g + k] += vals[k];
+      }
+      const int Ti = int(65535.f * Tw);
+#pragma omp critical
+      {
+        tet_count[2 * g] += 1;
+        if (Ti > tet_count[2 * g + 1]) tet_count[2 * g + 1] = Ti;
+      }
+      if (s.logT < -5.5f) break;
+    }
+  }
+  for (size_t i = 0; i < (size_t)T * 16; ++i) tet_err[i] = float(acc[i]);
+  return 0;
+}
+
 // Reverse of stage 1 with respect to the vertices: gradients of
 // vs_tetra[:,2] (clamped circumsphere power) and circumcenter, for tets that
 // were not culled (tiles_touched > 0).  Restates what Slang's autodiff derives

@@ -26,6 +26,9 @@ int rm_launch_backward(const int32_t*, const int32_t*, const float*, const RmCam
                        const float*, const int32_t*, const float*, const float*, const int32_t*, const float*,
                        const float*, int64_t, int64_t, float*, float*, float*, cudaStream_t);
 
+int rm_launch_tet_err(const int32_t*, const int32_t*, const float*, const RmCamera*, const float*, const float*,
+                      int64_t, float*, int32_t*, cudaStream_t);
+
 static thread_local char g_last_error[256] = "";
 
 // ---- optional per-kernel timing ---------------------------------------------
@@ -252,6 +255,23 @@ int rm_backward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, con
                             n_contributors, grad_output_img, grad_distortion_img, indices, vertices, cell_values,
                             n_tets, n_vertices, grad_records, vertices_grad, cell_values_grad,
                             static_cast<cudaStream_t>(stream));
+}
+
+int rm_tet_err(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, const float* records,
+               const RmCamera* cam, const float* pixel_err, const float* ssim_err, int64_t n_tets, float* tet_err,
+               int32_t* tet_count, void* stream) {
+  g_last_error[0] = 0;
+  int rc = check_cam(cam);
+  if (rc) return rc;
+  if (n_tets < 0 || !tile_ranges || !pixel_err || !ssim_err) return RM_ERR_INVALID_ARG;
+  if (n_tets == 0) return RM_OK;
+  if (!records || !tet_err || !tet_count) return RM_ERR_INVALID_ARG;
+  if (!aligned16(records) || !aligned16(tet_err) || (reinterpret_cast<uintptr_t>(tile_ranges) & 7))
+    return RM_ERR_WORKSPACE;
+  rc = rm_bind_device(tet_err);
+  if (rc) return rc;
+  return rm_launch_tet_err(sorted_tetra_idx, tile_ranges, records, cam, pixel_err, ssim_err, n_tets, tet_err,
+                           tet_count, static_cast<cudaStream_t>(stream));
 }
 
 int rm_vertex_backward(const int32_t* indices, const float* vertices, int64_t n_tets, int64_t n_vertices,

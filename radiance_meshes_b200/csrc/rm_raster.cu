@@ -743,6 +743,161 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
   cp_async_wait<0>();
 }
 
+// ----------------------------------------------------------------------------
+// Densification statistics (slang/alphablend_shader_interp.slang:433-599,
+// internal/render_err.py:119-150): the forward walk again, from the pixel centres,
+// with the pixel state starting at log-transmittance 1 as the reference has it;
+// every hit adds T = exp(logT_before) * optical_depth times (1, err, err^2, ssim,
+// entry point, exit point, 1, mid point) to row g of tet_err[T,16] and updates
+// tet_count[T,2] (hit count, max of int(65535*T)).  The reference issues 14 float
+// and 2 integer atomics per (pixel, tet) hit; here the 16 pixels of a tile are
+// summed first (transposed butterfly) when at least four of them hit, else each
+// hit pixel issues four 128-bit reductions.
+// ----------------------------------------------------------------------------
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+k_tet_err(const int32_t* __restrict__ list, const int2* __restrict__ ranges, const float4* __restrict__ records,
+          RmCamera rcam, const float* __restrict__ pixel_err, const float* __restrict__ ssim_err,
+          float* __restrict__ tet_err, int32_t* __restrict__ tet_count, int subs, int64_t n_units) {
+  __shared__ __align__(16) float4 stage[kWarpsPerBlock][2][2][kChunk * 6];
+  __shared__ int stage_id[kWarpsPerBlock][2][2][kChunk];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int half = lane >> 4, lane16 = lane & 15;
+  const unsigned half_mask = 0xFFFFu << (16 * half);
+  const int64_t unit = ((int64_t)blockIdx.x * kWarpsPerBlock + warp) * 2 + half;
+  Unit u = make_unit(rcam, ranges, unit, n_units, subs, lane16);
+
+  f3 d = {0.f, 0.f, 1.f};
+  const int64_t pix = (int64_t)u.y * rcam.image_width + u.x;
+  const float sx = (float)u.x + 0.5f, sy = (float)u.y + 0.5f;
+  float perr = 0.f, serr = 0.f;
+  if (u.inside) {
+    d = ray_direction(rcam, sx, sy);
+    perr = __ldg(pixel_err + pix);
+    serr = __ldg(ssim_err + pix);
+  }
+  const float min_t = rcam.min_t;
+  const f3 cam = {__ldg(rcam.cam_pos), __ldg(rcam.cam_pos + 1), __ldg(rcam.cam_pos + 2)};
+  float X0, X1, Y0, Y1;
+  halfwarp_sample_box(u.inside, sx, sy, X0, X1, Y0, Y1);
+  const float qnan = __int_as_float(0x7fc00000);
+  float4 nq0 = make_float4(qnan, qnan, qnan, qnan), nq1 = nq0, nq2 = nq0;
+
+  float logT = 1.0f, T = 2.718281828f;  // the reference starts the walk at log-transmittance 1
+  bool active = u.inside;
+  const int nchunks = (u.len + kChunk - 1) / kChunk;
+  const int max_chunks = max(nchunks, __shfl_xor_sync(0xffffffffu, nchunks, 16));
+  bool fetching = __ballot_sync(0xffffffffu, active) & half_mask;
+
+  if (fetching && lane16 < u.len) {
+    int id = __ldg(list + u.start + lane16);
+    stage_id[warp][half][0][lane16] = id;
+    const float4* src = records + kRecStride * (int64_t)id;
+#pragma unroll
+    for (int k = 0; k < 6; ++k) cp_async16(stage[warp][half][0] + lane16 * 6 + k, src + k);
+    nq0 = __ldg(src + 6);
+    nq1 = __ldg(src + 7);
+    nq2 = __ldg(src + 8);
+  }
+  cp_async_commit();
+  int id_next = (fetching && kChunk + lane16 < u.len) ? __ldg(list + u.start + kChunk + lane16) : 0;
+
+  for (int c = 0; c < max_chunks; ++c) {
+    float4* cur = stage[warp][half][c & 1];
+    float4* nxt = stage[warp][half][(c & 1) ^ 1];
+    const int* cur_id = stage_id[warp][half][c & 1];
+    const float4 cq0 = nq0, cq1 = nq1, cq2 = nq2;
+    {
+      int e = (c + 1) * kChunk + lane16;
+      if (fetching && e < u.len) {
+        stage_id[warp][half][(c & 1) ^ 1][lane16] = id_next;
+        const float4* src = records + kRecStride * (int64_t)id_next;
+#pragma unroll
+        for (int k = 0; k < 6; ++k) cp_async16(nxt + lane16 * 6 + k, src + k);
+        nq0 = __ldg(src + 6);
+        nq1 = __ldg(src + 7);
+        nq2 = __ldg(src + 8);
+      }
+      cp_async_commit();
+      if (fetching && e + kChunk < u.len) id_next = __ldg(list + u.start + e + kChunk);
+    }
+    cp_async_wait<1>();
+    __syncwarp();
+    const bool nonzero = fetching && (c * kChunk + lane16 < u.len) && cur[lane16 * 6 + 5].w > 0.0f &&
+                         !hull_misses_box(cq0, cq1, cq2, X0, X1, Y0, Y1);
+    unsigned todo = (__ballot_sync(0xffffffffu, nonzero) >> (16 * half)) & 0xFFFFu;
+    const int steps = max(__popc(todo), __shfl_xor_sync(0xffffffffu, __popc(todo), 16));
+    for (int step = 0; step < steps; ++step) {
+      int j = 0;
+      bool in_range = false;
+      if (todo) {
+        j = __ffs(todo) - 1;
+        todo &= todo - 1;
+        in_range = true;
+      }
+      const float4* rec = cur + j * 6;
+      const float4 pl[4] = {rec[0], rec[1], rec[2], rec[3]};
+      bool hit = false;
+      Eval ev;
+      if (in_range && active) hit = slab_test<false>(pl, d, min_t, ev) && integrate(rec, d, min_t, ev);
+      const unsigned hits = __ballot_sync(0xffffffffu, hit);
+      if (hits == 0) continue;
+      float v[16];
+#pragma unroll
+      for (int q = 0; q < 16; ++q) v[q] = 0.0f;
+      int Ti = 0;
+      if (hit) {
+        const float Tw = T * ev.tau;
+        logT -= ev.tau;
+        T *= ev.alpha;
+        if (logT < -5.5f) active = false;
+        const float a1 = ev.enter + min_t, a2 = ev.exit + min_t, am = 0.5f * (ev.enter + ev.exit) + min_t;
+        v[0] = Tw;
+        v[1] = Tw * perr;
+        v[2] = Tw * perr * perr;
+        v[5] = Tw * serr;
+        v[6] = Tw * fmaf(a1, d.x, cam.x); v[7] = Tw * fmaf(a1, d.y, cam.y); v[8] = Tw * fmaf(a1, d.z, cam.z);
+        v[9] = Tw * fmaf(a2, d.x, cam.x); v[10] = Tw * fmaf(a2, d.y, cam.y); v[11] = Tw * fmaf(a2, d.z, cam.z);
+        v[12] = Tw;
+        v[13] = Tw * fmaf(am, d.x, cam.x); v[14] = Tw * fmaf(am, d.y, cam.y); v[15] = Tw * fmaf(am, d.z, cam.z);
+        Ti = (int)(65535.0f * Tw);
+      }
+      const unsigned my_hits = (hits >> (16 * half)) & 0xFFFFu;
+      int tmax = Ti;
+#pragma unroll
+      for (int o = 8; o >= 1; o >>= 1) tmax = max(tmax, __shfl_xor_sync(0xffffffffu, tmax, o));
+      const int g = cur_id[j];
+      if (my_hits && lane16 == __ffs(my_hits) - 1) {
+        atomicAdd(tet_count + 2 * (int64_t)g, __popc(my_hits));
+        atomicMax(tet_count + 2 * (int64_t)g + 1, tmax);
+      }
+      if (max(__popc(hits & 0xFFFFu), __popc(hits >> 16)) >= kButterflyMinHits) {
+#pragma unroll
+        for (int w = 8; w >= 1; w >>= 1) {
+          const bool up = lane16 & w;
+#pragma unroll
+          for (int i = 0; i < w; ++i) {
+            const float send = up ? v[i] : v[i + w];
+            const float keep = up ? v[i + w] : v[i];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, w);
+          }
+        }
+        if (my_hits && v[0] != 0.0f) atomicAdd(tet_err + 16 * (int64_t)g + lane16, v[0]);
+      } else if (hit) {
+        float4* row = reinterpret_cast<float4*>(tet_err + 16 * (int64_t)g);
+        atomicAdd(row + 0, make_float4(v[0], v[1], v[2], 0.0f));
+        atomicAdd(row + 1, make_float4(0.0f, v[5], v[6], v[7]));
+        atomicAdd(row + 2, make_float4(v[8], v[9], v[10], v[11]));
+        atomicAdd(row + 3, make_float4(v[12], v[13], v[14], v[15]));
+      }
+    }
+    __syncwarp();
+    unsigned act = __ballot_sync(0xffffffffu, active);
+    fetching = act & half_mask;
+    if (act == 0) break;
+  }
+  cp_async_wait<0>();
+}
+
 // Chain rule from record gradients to vertices and cell values; one thread per tet.
 __global__ void __launch_bounds__(256)
 k_backward_finish(const int32_t* __restrict__ indices, const float* __restrict__ vertices,
@@ -845,6 +1000,25 @@ int rm_launch_forward(const int32_t* list, const int32_t* ranges, const float* r
       list, reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam,
       reinterpret_cast<const float2*>(jitter), reinterpret_cast<float4*>(out_img), dist_img, n_contrib, subs,
       n_units);
+  RM_CUDA_CHECK(cudaPeekAtLastError());
+  return RM_OK;
+}
+
+int rm_launch_tet_err(const int32_t* list, const int32_t* ranges, const float* records, const RmCamera* cam,
+                      const float* pixel_err, const float* ssim_err, int64_t T, float* tet_err, int32_t* tet_count,
+                      cudaStream_t st) {
+  if (T == 0) return RM_OK;
+  RM_CUDA_CHECK(cudaMemsetAsync(tet_err, 0, sizeof(float) * 16 * (size_t)T, st));
+  RM_CUDA_CHECK(cudaMemsetAsync(tet_count, 0, sizeof(int32_t) * 2 * (size_t)T, st));
+  int subs;
+  int64_t n_units;
+  unsigned blocks;
+  unit_grid(cam, &subs, &n_units, &blocks);
+  if (n_units == 0) return RM_OK;
+  RmProfScope prof("k_tet_err", st);
+  rm::k_tet_err<<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
+      list, reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam, pixel_err,
+      ssim_err, tet_err, tet_count, subs, n_units);
   RM_CUDA_CHECK(cudaPeekAtLastError());
   return RM_OK;
 }

@@ -176,3 +176,15 @@ def vertex_backward(indices, vertices, cam, tiles_touched, grad_vs, grad_cc):
         _lib.check(lib.rm_vertex_backward(_ptr(indices), _ptr(vertices), T, V, cam.ref, _ptr(tiles_touched),
                                           _ptr(grad_vs), _ptr(grad_cc), _ptr(vertices_grad), _stream(dev)))
     return vertices_grad
+
+
+def tet_err(sorted_idx, tile_ranges, records, cam, pixel_err, ssim_err, n_tets):
+    """Densification statistics: (tet_err[T,16] f32, tet_count[T,2] i32)."""
+    lib = _lib.load()
+    dev = records.device
+    with torch.cuda.device(dev):
+        err = torch.empty((n_tets, 16), dtype=torch.float32, device=dev)
+        cnt = torch.empty((n_tets, 2), dtype=torch.int32, device=dev)
+        _lib.check(lib.rm_tet_err(_ptr(sorted_idx), _ptr(tile_ranges), _ptr(records), cam.ref, _ptr(pixel_err),
+                                  _ptr(ssim_err), n_tets, _ptr(err), _ptr(cnt), _stream(dev)))
+    return err, cnt

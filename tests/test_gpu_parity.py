@@ -270,3 +270,37 @@ def test_fisheye_camera(oracle, cuda_lib):
     if (diff == 0).all():
         np.testing.assert_array_equal(got["sorted_tetra_idx"], ref["sorted_idx"])
         assert rel_l2(got["image"], ref["output_img"]) <= IMG_TOL
+
+
+def test_densification_statistics(oracle, cuda_lib):
+    # calc_tet_err: per-tet error moments and hit counts against the oracle
+    from delaunay_rasterization.internal.render_err import tet_error_stats
+    from delaunay_rasterization.internal.render_grid import RenderGrid
+    from delaunay_rasterization.internal.tile_shader_slang import vertex_and_tile_shader
+    from radiance_meshes_b200.render import tcam_to_device
+    pts, tets, cell = scene_util.small_scene(600, seed=29, zero_frac=0.3)
+    H, W = 64, 72
+    tcam_np = scene_util.camera(H=H, W=W, tile=4)
+    rng = np.random.default_rng(3)
+    pixel_err = rng.normal(0, 0.1, (H, W)).astype(np.float32)
+    ssim_err = rng.uniform(0, 1, (H, W)).astype(np.float32)
+    ref = oracle.render(tets, pts, cell, tcam_np)
+    err_ref, cnt_ref = oracle.tet_err(ref["sorted_idx"], ref["tile_ranges"], tets, pts, cell, tcam_np, pixel_err,
+                                      ssim_err)
+    dev = torch.device("cuda:0")
+    tcam = tcam_to_device(tcam_np, dev)
+    idx_t, v, c = torch.tensor(tets, device=dev), torch.tensor(pts, device=dev), torch.tensor(cell, device=dev)
+    grid = RenderGrid(H, W, tile_width=4, tile_height=4)
+    sorted_idx, ranges, _, _, mask, _ = vertex_and_tile_shader(idx_t, v, tcam, grid)
+    np.testing.assert_array_equal(sorted_idx.cpu().numpy(), ref["sorted_idx"])
+    err, cnt = tet_error_stats(sorted_idx, ranges, idx_t, v, c, tcam, torch.tensor(pixel_err, device=dev),
+                               torch.tensor(ssim_err, device=dev), mask.to(torch.int32))
+    err, cnt = err.cpu().numpy(), cnt.cpu().numpy()
+    assert cnt_ref[:, 0].sum() > 10_000
+    assert not err[:, 3:5].any()
+    # sums of fp32 products in a different order, plus a handful of rounding-decided hits
+    assert rel_l2(err, err_ref) <= 1e-3
+    dcount = np.abs(cnt[:, 0] - cnt_ref[:, 0])
+    assert dcount.max() <= 2 and (dcount > 0).mean() <= 0.01
+    same = dcount == 0
+    assert np.abs(cnt[same, 1] - cnt_ref[same, 1]).max() <= 2 + 1e-4 * cnt_ref[:, 1].max()
