@@ -46,7 +46,8 @@ def render_err(gt_image, camera, model, tile_size=16, min_t=0.1, **kwargs):
         cam = raster.CameraArgs(tcam, dev)
         records = raster.pack_records(idx32, verts, cell_values.contiguous().float(), cam, mask.to(torch.int32))
         ray_jitter = 0.5 * torch.ones((camera.image_height, camera.image_width, 2), device=device)
-        output_img, _, _ = raster.forward(sorted_tetra_idx, tile_ranges, records, cam, ray_jitter)
+        output_img, _, _, _ = raster.forward(sorted_tetra_idx, tile_ranges, records, cam, ray_jitter,
+                                             want_hit_masks=False)
         render_img = output_img.permute(2, 0, 1)[:3, ...].clip(min=0, max=1)
         l1_err = (render_img - gt_image).mean(dim=0)
         ssim_err = (1 - ssim(render_img, gt_image).mean(dim=0)).clip(min=0, max=1)

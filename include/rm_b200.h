@@ -123,24 +123,31 @@ int rm_pack_records(const int32_t* indices, const float* vertices, const float* 
  * host side alphablend_tiled_slang_interp.py:11-52).
  *   ray_jitter[H,W,2] f32 -> output_img[H,W,4] (r,g,b,log-transmittance),
  *   distortion_img[H,W,5], n_contributors[H,W] i32.  Every pixel of the band is written.
+ *   hit_masks[N * S] u16 with S = ceil(tile_width*tile_height / 16) (optional, may be
+ *   NULL): for every list entry walked and every 16-pixel group of its tile, the pixels
+ *   (bit = pixel index inside the group) that hit the tet with positive
+ *   optical depth while still active; rm_backward needs it.  Entries beyond the largest
+ *   n_contributors of their tile are left unwritten.  No counterpart in the reference,
+ *   whose backward pass repeats every intersection test.
  */
 int rm_forward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, const float* records,
                const RmCamera* cam, const float* ray_jitter, float* output_img, float* distortion_img,
-               int32_t* n_contributors, void* stream);
+               int32_t* n_contributors, uint16_t* hit_masks, void* stream);
 
 /*
  * Backward integration.  Replaces splat_tiled.bwd / bwd_alpha_blend
  * (slang/alphablend_shader_interp.slang:273-369, host side
  * alphablend_tiled_slang_interp.py:70-112).
+ *   hit_masks[N * S] u16 is the array rm_forward wrote for the same lists and inputs;
  *   grad_records[T, RM_GRAD_RECORD_FLOATS] is caller-provided scratch (zeroed here);
  *   vertices_grad[V,3] and cell_values_grad[T,7] are fully written (zeroed here first).
  */
 int rm_backward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, const float* records,
                 const RmCamera* cam, const float* ray_jitter, const float* output_img,
-                const float* distortion_img, const int32_t* n_contributors, const float* grad_output_img,
-                const float* grad_distortion_img, const int32_t* indices, const float* vertices,
-                const float* cell_values, int64_t n_tets, int64_t n_vertices, float* grad_records,
-                float* vertices_grad, float* cell_values_grad, void* stream);
+                const float* distortion_img, const int32_t* n_contributors, const uint16_t* hit_masks,
+                const float* grad_output_img, const float* grad_distortion_img, const int32_t* indices,
+                const float* vertices, const float* cell_values, int64_t n_tets, int64_t n_vertices,
+                float* grad_records, float* vertices_grad, float* cell_values_grad, void* stream);
 
 /*
  * Densification statistics.  Replaces calc_tet_err (slang/alphablend_shader_interp.slang:433-599,
@@ -190,7 +197,8 @@ int rm_vertex_backward(const int32_t* indices, const float* vertices, int64_t n_
 int rm_backward_static_scratch(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, const float* records,
                                const RmCamera* cam, const float* ray_jitter, const float* output_img,
                                const float* distortion_img, const int32_t* n_contributors,
-                               const float* grad_output_img, const float* grad_distortion_img,
+                               const uint16_t* hit_masks, const float* grad_output_img,
+                               const float* grad_distortion_img,
                                const int32_t* indices, const float* vertices, const float* cell_values,
                                int64_t n_tets, int64_t n_vertices, float* vertices_grad, float* cell_values_grad,
                                void* stream);

@@ -911,7 +911,8 @@ int or_sensitive_pixels(const int32_t* sorted_idx, const int32_t* tile_ranges, c
 // hits with positive optical depth, and slab-test hits of zero-density tets.
 int or_walk_stats(const int32_t* sorted_idx, const int32_t* tile_ranges, const int32_t* indices,
                   const float* vertices, const float* cell, const OrCamera* ocam, const float* jitter,
-                  int32_t* walked, int32_t* hits, int32_t* empty_hits, int row0, int row1, int nthreads) {
+                  int32_t* walked, int32_t* hits, int32_t* empty_hits, int32_t* entry_hits, int row0, int row1,
+                  int nthreads) {
   Cam<float> cam = load_cam<float>(ocam);
   const int W = cam.Wd;
 #ifdef _OPENMP
@@ -933,6 +934,10 @@ int or_walk_stats(const int32_t* sorted_idx, const int32_t* tile_ranges, const i
       if (evaluate_tet(t, o, d, c)) {
         if (c.a > 0.f) {
           ++nh;
+          if (entry_hits) {
+#pragma omp atomic
+            entry_hits[j] += 1;
+          }
           update_state(s, c);
           if (s.logT < -5.5f) break;
         } else {

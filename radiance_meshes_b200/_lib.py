@@ -58,10 +58,11 @@ def load():
     lib.rm_list_scratch_bytes.argtypes = [i64, i64]
     lib.rm_build_tile_lists.argtypes = [vp, vp, i64, cam, i64, vp, vp, sz, vp, vp]
     lib.rm_pack_records.argtypes = [vp, vp, vp, i64, cam, vp, vp, vp]
-    lib.rm_forward.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, vp]
-    lib.rm_backward.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, vp, vp, vp, vp]
+    lib.rm_forward.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, vp, vp]
+    lib.rm_backward.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, vp, vp, vp, vp]
     lib.rm_vertex_backward.argtypes = [vp, vp, i64, i64, cam, vp, vp, vp, vp, vp]
-    lib.rm_backward_static_scratch.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, vp, vp, vp]
+    lib.rm_backward_static_scratch.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, vp, vp,
+                                               vp]
     lib.rm_tet_err.argtypes = [vp, vp, vp, cam, vp, vp, i64, vp, vp, vp]
     lib.rm_profile_enable.restype = None
     lib.rm_profile_enable.argtypes = [C.c_int]

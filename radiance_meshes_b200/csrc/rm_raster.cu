@@ -333,6 +333,7 @@ struct Unit {
   int x, y;       // pixel
   bool inside;    // pixel exists
   int start, len; // tile list
+  int sub, subs;  // which 16-pixel group of the tile this half-warp owns, out of how many
 };
 
 __device__ __forceinline__ Unit make_unit(const RmCamera& c, const int2* __restrict__ ranges, int64_t unit,
@@ -343,11 +344,14 @@ __device__ __forceinline__ Unit make_unit(const RmCamera& c, const int2* __restr
   u.len = 0;
   u.tile = 0;
   u.x = u.y = 0;
+  u.sub = 0;
+  u.subs = subs;
   if (unit >= n_units) return u;
   int64_t t = unit / subs;
   int sub = (int)(unit - t * subs);
   u.tile = c.tile_row_begin * c.grid_width + (int)t;
   int ty = u.tile / c.grid_width, tx = u.tile - ty * c.grid_width;
+  u.sub = sub;
   int p = sub * 16 + lane16;
   int ly = p / c.tile_width, lx = p - ly * c.tile_width;
   u.x = tx * c.tile_width + lx;
@@ -381,7 +385,8 @@ __device__ __forceinline__ void halfwarp_sample_box(bool inside, float sx, float
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, const float4* __restrict__ records,
           RmCamera rcam, const float2* __restrict__ jitter, float4* __restrict__ out_img,
-          float* __restrict__ dist_img, int32_t* __restrict__ n_contrib, int subs, int64_t n_units) {
+          float* __restrict__ dist_img, int32_t* __restrict__ n_contrib, uint16_t* __restrict__ hit_masks, int subs,
+          int64_t n_units) {
   __shared__ __align__(16) float4 stage[kWarpsPerBlock][2][2][kChunk * 6];  // [warp][half][buffer]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int half = lane >> 4, lane16 = lane & 15;
@@ -453,44 +458,53 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
     // Tets of zero density are walked (they count in n_contributors) but can never
     // contribute or terminate a pixel: only the entries flagged here are evaluated.
     // Neither are tets whose projection misses the box of this half-warp's samples.
-    const bool nonzero = (c * kChunk + lane16 < u.len) && cur[lane16 * 6 + 5].w > 0.0f &&
+    const bool nonzero = fetching && (c * kChunk + lane16 < u.len) && cur[lane16 * 6 + 5].w > 0.0f &&
                          !hull_misses_box(cq0, cq1, cq2, X0, X1, Y0, Y1);
     unsigned todo = (__ballot_sync(0xffffffffu, nonzero) >> (16 * half)) & 0xFFFFu;
-    if (active && todo) {
-      int j = __ffs(todo) - 1;
-      float4 pl[4] = {cur[j * 6], cur[j * 6 + 1], cur[j * 6 + 2], cur[j * 6 + 3]};
-      while (true) {
-        todo &= todo - 1;
-        // planes of the next record to evaluate, loaded while this one is tested
-        const int jn = todo ? __ffs(todo) - 1 : j;
-        const float4 nx[4] = {cur[jn * 6], cur[jn * 6 + 1], cur[jn * 6 + 2], cur[jn * 6 + 3]};
-        const float4* rec = cur + j * 6;
-        Eval e;
-        if (slab_test<false>(pl, d, min_t, e) && integrate(rec, d, min_t, e)) {
-          sr = fmaf(e.cr, T, sr);
-          sg = fmaf(e.cg, T, sg);
-          sb = fmaf(e.cb, T, sb);
-          logT -= e.tau;
-          T *= e.alpha;
-          float dens = rec[5].w;
-          float m1 = dens * (e.exit + e.enter) * 0.5f;
-          dx = fmaf(2.0f * m1, dz, dx);
-          dy = fmaf(2.0f * dens, dw, dy);
-          dz += dens;
-          dw += m1;
-          dv = fmaf(dens * dens, e.dt * (1.0f / 3.0f), dv);
-          if (logT < -5.5f) {
-            active = false;
-            contrib = c * kChunk + j + 1;  // entries walked, the terminating one included
-            break;
-          }
-        }
-        if (!todo) break;
-        j = jn;
+    // The two halves step through their own set bits in lock-step.  For every
+    // evaluated entry the pixels that hit it (while still active) are recorded in
+    // a 16-bit mask, kept by the lane whose index equals the entry's slot, so that
+    // the backward pass can go straight to the hits.
+    const int steps = max(__popc(todo), __shfl_xor_sync(0xffffffffu, __popc(todo), 16));
+    unsigned my_entry_hits = 0;
+    int jn = todo ? __ffs(todo) - 1 : 0;
+    float4 nx[4] = {cur[jn * 6], cur[jn * 6 + 1], cur[jn * 6 + 2], cur[jn * 6 + 3]};
+    for (int step = 0; step < steps; ++step) {
+      const int j = jn;
+      const bool in_range = todo != 0;
+      todo &= todo - 1;
+      const float4 pl[4] = {nx[0], nx[1], nx[2], nx[3]};
+      // planes of the next record to evaluate, loaded while this one is tested
+      jn = todo ? __ffs(todo) - 1 : j;
 #pragma unroll
-        for (int q = 0; q < 4; ++q) pl[q] = nx[q];
+      for (int q = 0; q < 4; ++q) nx[q] = cur[jn * 6 + q];
+      const float4* rec = cur + j * 6;
+      Eval e;
+      bool hit = false;
+      if (in_range && active) hit = slab_test<false>(pl, d, min_t, e) && integrate(rec, d, min_t, e);
+      if (hit) {
+        sr = fmaf(e.cr, T, sr);
+        sg = fmaf(e.cg, T, sg);
+        sb = fmaf(e.cb, T, sb);
+        logT -= e.tau;
+        T *= e.alpha;
+        float dens = rec[5].w;
+        float m1 = dens * (e.exit + e.enter) * 0.5f;
+        dx = fmaf(2.0f * m1, dz, dx);
+        dy = fmaf(2.0f * dens, dw, dy);
+        dz += dens;
+        dw += m1;
+        dv = fmaf(dens * dens, e.dt * (1.0f / 3.0f), dv);
+        if (logT < -5.5f) {
+          active = false;
+          contrib = c * kChunk + j + 1;  // entries walked, the terminating one included
+        }
       }
+      const unsigned hm = (__ballot_sync(0xffffffffu, hit) >> (16 * half)) & 0xFFFFu;
+      if (in_range && lane16 == j) my_entry_hits = hm;
     }
+    if (hit_masks && c * kChunk + lane16 < u.len)
+      hit_masks[(int64_t)(u.start + c * kChunk + lane16) * u.subs + u.sub] = (uint16_t)my_entry_hits;
     __syncwarp();
     unsigned act = __ballot_sync(0xffffffffu, active);
     fetching = act & half_mask;
@@ -514,10 +528,11 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, const float4* __restrict__ records,
            RmCamera rcam, const float2* __restrict__ jitter, const float4* __restrict__ out_img,
            const float* __restrict__ dist_img, const int32_t* __restrict__ n_contrib,
-           const float4* __restrict__ g_img, const float* __restrict__ g_dist, float* __restrict__ grec, int subs,
+           const uint16_t* __restrict__ hit_masks, const float4* __restrict__ g_img, const float* __restrict__ g_dist, float* __restrict__ grec, int subs,
            int64_t n_units) {
   __shared__ __align__(16) float4 stage[kWarpsPerBlock][2][2][kChunk * 6];
   __shared__ int stage_id[kWarpsPerBlock][2][2][kChunk];
+  __shared__ unsigned stage_mask[kWarpsPerBlock][2][2][kChunk];  // pixels of the tile that hit the entry (forward)
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int half = lane >> 4, lane16 = lane & 15;
   const int64_t unit = ((int64_t)blockIdx.x * kWarpsPerBlock + warp) * 2 + half;
@@ -528,12 +543,9 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
   float logT = 0.f, sz = 0.f, sw = 0.f;
   float gr = 0.f, gg = 0.f, gb = 0.f, glogT = 0.f, gx = 0.f, gy = 0.f, gz = 0.f, gw = 0.f, gv = 0.f;
   int nc = 0;
-  float sx = 0.f, sy = 0.f;
   if (u.inside) {
     float2 j = __ldg(jitter + pix);
-    sx = (float)u.x + j.x;
-    sy = (float)u.y + j.y;
-    d = ray_direction(rcam, sx, sy);
+    d = ray_direction(rcam, (float)u.x + j.x, (float)u.y + j.y);
     logT = __ldg(out_img + pix).w;
     sz = __ldg(dist_img + 5 * pix + 2);
     sw = __ldg(dist_img + 5 * pix + 3);
@@ -545,11 +557,6 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
   }
   const float min_t = rcam.min_t;
 
-  float X0, X1, Y0, Y1;
-  halfwarp_sample_box(u.inside, sx, sy, X0, X1, Y0, Y1);
-  const float qnan = __int_as_float(0x7fc00000);
-  float4 nq0 = make_float4(qnan, qnan, qnan, qnan), nq1 = nq0, nq2 = nq0;
-
   // entries at or beyond the largest n_contributors of the half are skipped by every pixel
   int nmax = nc;
 #pragma unroll
@@ -558,46 +565,52 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
   const int max_chunks = max(nchunks, __shfl_xor_sync(0xffffffffu, nchunks, 16));
 
   // chunk k of this half (k = 0 is the LAST chunk of its list) sits in buffer k&1
-  // list entry this lane stages for chunk k+1, loaded while chunk k is issued
+  // List entry and hit mask this lane stages for chunk k+1, loaded while chunk k is
+  // issued.  Only entries some pixel of the tile hit in the forward pass are staged
+  // and visited.
   int id_next = 0;
+  unsigned mask_next = 0;
   {
     const int e0 = (nchunks - 1) * kChunk + lane16;
-    if (nchunks >= 1 && e0 < nmax) id_next = __ldg(list + u.start + e0);
+    if (nchunks >= 1 && e0 < nmax) {
+      id_next = __ldg(list + u.start + e0);
+      mask_next = __ldg(hit_masks + (int64_t)(u.start + e0) * u.subs + u.sub);
+    }
   }
   auto issue = [&](int k) {
     int c = nchunks - 1 - k;
     if (c >= 0) {
       int e = c * kChunk + lane16;
       const int id = id_next;
-      if (c >= 1) id_next = __ldg(list + u.start + e - kChunk);  // always < nmax
-      if (e < nmax) {
-        stage_id[warp][half][k & 1][lane16] = id;
+      const unsigned m = e < nmax ? mask_next : 0u;
+      if (c >= 1) {  // entry e - kChunk is always below nmax
+        id_next = __ldg(list + u.start + e - kChunk);
+        mask_next = __ldg(hit_masks + (int64_t)(u.start + e - kChunk) * u.subs + u.sub);
+      }
+      stage_id[warp][half][k & 1][lane16] = id;
+      stage_mask[warp][half][k & 1][lane16] = m;
+      if (m) {
         const float4* src = records + kRecStride * (int64_t)id;
         float4* dst = stage[warp][half][k & 1] + lane16 * 6;
 #pragma unroll
         for (int q = 0; q < 6; ++q) cp_async16(dst + q, src + q);
-        nq0 = __ldg(src + 6);
-        nq1 = __ldg(src + 7);
-        nq2 = __ldg(src + 8);
       }
+    } else {
+      stage_mask[warp][half][k & 1][lane16] = 0u;
     }
     cp_async_commit();
   };
   issue(0);
   for (int k = 0; k < max_chunks; ++k) {
-    const float4 cq0 = nq0, cq1 = nq1, cq2 = nq2;
     issue(k + 1);
     cp_async_wait<1>();
     __syncwarp();
-    const int c = nchunks - 1 - k;
     const float4* cur = stage[warp][half][k & 1];
     const int* cur_id = stage_id[warp][half][k & 1];
-    // Staged entries with non-zero density, per half (zero-density tets never
-    // contribute).  Both halves step in lock-step through their own set bits,
-    // last entry first; a half that runs out idles.
-    const bool nonzero = c >= 0 && c * kChunk + lane16 < nmax && cur[lane16 * 6 + 5].w > 0.0f &&
-                         !hull_misses_box(cq0, cq1, cq2, X0, X1, Y0, Y1);
-    unsigned todo = (__ballot_sync(0xffffffffu, nonzero) >> (16 * half)) & 0xFFFFu;
+    const unsigned* cur_mask = stage_mask[warp][half][k & 1];
+    // Both halves step in lock-step through their own hit entries, last entry
+    // first; a half that runs out idles.
+    unsigned todo = (__ballot_sync(0xffffffffu, cur_mask[lane16] != 0u) >> (16 * half)) & 0xFFFFu;
     const int steps = max(__popc(todo), __shfl_xor_sync(0xffffffffu, __popc(todo), 16));
     for (int step = 0; step < steps; ++step) {
       int j = 0;
@@ -607,12 +620,13 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
         todo &= ~(1u << j);
         in_range = true;
       }
-      const int e = c * kChunk + j;
       const float4* rec = cur + j * 6;
-      const float4 pl[4] = {rec[0], rec[1], rec[2], rec[3]};
-      bool hit = false;
+      bool hit = in_range && ((cur_mask[j] >> lane16) & 1u);
       Eval ev;
-      if (in_range && u.inside && e < nc) hit = slab_test<true>(pl, d, min_t, ev) && integrate(rec, d, min_t, ev);
+      if (hit) {  // same arithmetic as the forward pass, so the test succeeds again
+        const float4 pl[4] = {rec[0], rec[1], rec[2], rec[3]};
+        hit = slab_test<true>(pl, d, min_t, ev) && integrate(rec, d, min_t, ev);
+      }
       const unsigned hits = __ballot_sync(0xffffffffu, hit);
       if (hits == 0) continue;
       // Per lane: gradient of the entering plane (v[0..3] -> row[4*pe..]), of the
@@ -989,7 +1003,8 @@ int rm_launch_pack(const int32_t* indices, const float* vertices, const float* c
 }
 
 int rm_launch_forward(const int32_t* list, const int32_t* ranges, const float* records, const RmCamera* cam,
-                      const float* jitter, float* out_img, float* dist_img, int32_t* n_contrib, cudaStream_t st) {
+                      const float* jitter, float* out_img, float* dist_img, int32_t* n_contrib, uint16_t* hit_masks,
+                      cudaStream_t st) {
   int subs;
   int64_t n_units;
   unsigned blocks;
@@ -998,8 +1013,8 @@ int rm_launch_forward(const int32_t* list, const int32_t* ranges, const float* r
   RmProfScope prof("k_forward", st);
   rm::k_forward<<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
       list, reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam,
-      reinterpret_cast<const float2*>(jitter), reinterpret_cast<float4*>(out_img), dist_img, n_contrib, subs,
-      n_units);
+      reinterpret_cast<const float2*>(jitter), reinterpret_cast<float4*>(out_img), dist_img, n_contrib, hit_masks,
+      subs, n_units);
   RM_CUDA_CHECK(cudaPeekAtLastError());
   return RM_OK;
 }
@@ -1025,7 +1040,8 @@ int rm_launch_tet_err(const int32_t* list, const int32_t* ranges, const float* r
 
 int rm_launch_backward(const int32_t* list, const int32_t* ranges, const float* records, const RmCamera* cam,
                        const float* jitter, const float* out_img, const float* dist_img, const int32_t* n_contrib,
-                       const float* g_img, const float* g_dist, const int32_t* indices, const float* vertices,
+                       const uint16_t* hit_masks, const float* g_img, const float* g_dist, const int32_t* indices,
+                       const float* vertices,
                        const float* cell, int64_t T, int64_t V, float* grec, float* vgrad, float* cgrad,
                        cudaStream_t st) {
   RM_CUDA_CHECK(cudaMemsetAsync(vgrad, 0, sizeof(float) * 3 * (size_t)V, st));
@@ -1040,7 +1056,7 @@ int rm_launch_backward(const int32_t* list, const int32_t* ranges, const float* 
     rm::k_backward<<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
         list, reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam,
         reinterpret_cast<const float2*>(jitter), reinterpret_cast<const float4*>(out_img), dist_img, n_contrib,
-        reinterpret_cast<const float4*>(g_img), g_dist, grec, subs, n_units);
+        hit_masks, reinterpret_cast<const float4*>(g_img), g_dist, grec, subs, n_units);
   }
   RmProfScope prof2("k_backward_finish", st);
   rm::k_backward_finish<<<(unsigned)((T + 255) / 256), 256, 0, st>>>(indices, vertices, cell, T, *cam,
@@ -1068,15 +1084,16 @@ float* g_static_addr[kMaxDevices] = {nullptr};
 extern "C" int rm_backward_static_scratch(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges,
                                           const float* records, const RmCamera* cam, const float* ray_jitter,
                                           const float* output_img, const float* distortion_img,
-                                          const int32_t* n_contributors, const float* grad_output_img,
+                                          const int32_t* n_contributors, const uint16_t* hit_masks,
+                                          const float* grad_output_img,
                                           const float* grad_distortion_img, const int32_t* indices,
                                           const float* vertices, const float* cell_values, int64_t n_tets,
                                           int64_t n_vertices, float* vertices_grad, float* cell_values_grad,
                                           void* stream) {
   if (n_tets < 0 || n_vertices < 0 || !cam) return RM_ERR_INVALID_ARG;
   if (n_tets > RM_STATIC_SCRATCH_MAX_TETS) return RM_ERR_STATIC_SCRATCH;
-  if (!tile_ranges || !ray_jitter || !output_img || !distortion_img || !n_contributors || !grad_output_img ||
-      !grad_distortion_img || !vertices_grad)
+  if (!tile_ranges || !ray_jitter || !output_img || !distortion_img || !n_contributors || !hit_masks ||
+      !grad_output_img || !grad_distortion_img || !vertices_grad)
     return RM_ERR_INVALID_ARG;
   if (n_tets > 0 && (!indices || !vertices || !cell_values || !cell_values_grad || !records))
     return RM_ERR_INVALID_ARG;
@@ -1116,8 +1133,8 @@ extern "C" int rm_backward_static_scratch(const int32_t* sorted_tetra_idx, const
     rm::k_backward<<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
         sorted_tetra_idx, reinterpret_cast<const int2*>(tile_ranges), reinterpret_cast<const float4*>(records), *cam,
         reinterpret_cast<const float2*>(ray_jitter), reinterpret_cast<const float4*>(output_img), distortion_img,
-        n_contributors, reinterpret_cast<const float4*>(grad_output_img), grad_distortion_img, scratch, subs,
-        n_units);
+        n_contributors, hit_masks, reinterpret_cast<const float4*>(grad_output_img), grad_distortion_img, scratch,
+        subs, n_units);
   }
   rm::k_backward_finish<<<(unsigned)((n_tets + 255) / 256), 256, 0, st>>>(
       indices, vertices, cell_values, n_tets, *cam, reinterpret_cast<const float4*>(scratch), vertices_grad,

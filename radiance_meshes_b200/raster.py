@@ -135,7 +135,9 @@ def pack_records(indices, vertices, cell_values, cam, tiles_touched=None):
     return records
 
 
-def forward(sorted_idx, tile_ranges, records, cam, ray_jitter):
+def forward(sorted_idx, tile_ranges, records, cam, ray_jitter, want_hit_masks=True):
+    """Returns (output_img, distortion_img, n_contributors, hit_masks); hit_masks (int16 view of the
+    per-entry 16-bit pixel masks) is what backward() needs and is None if not requested."""
     lib = _lib.load()
     dev = records.device
     H, W = cam.c.image_height, cam.c.image_width
@@ -145,13 +147,17 @@ def forward(sorted_idx, tile_ranges, records, cam, ray_jitter):
         output_img = alloc((H, W, 4), dtype=torch.float32, device=dev)
         distortion_img = alloc((H, W, 5), dtype=torch.float32, device=dev)
         n_contributors = alloc((H, W, 1), dtype=torch.int32, device=dev)
+        groups = (cam.c.tile_width * cam.c.tile_height + 15) // 16
+        hit_masks = torch.empty((max(int(sorted_idx.shape[0]) * groups, 1),), dtype=torch.int16, device=dev) \
+            if want_hit_masks else None
         _lib.check(lib.rm_forward(_ptr(sorted_idx), _ptr(tile_ranges), _ptr(records), cam.ref, _ptr(ray_jitter),
-                                  _ptr(output_img), _ptr(distortion_img), _ptr(n_contributors), _stream(dev)))
-    return output_img, distortion_img, n_contributors
+                                  _ptr(output_img), _ptr(distortion_img), _ptr(n_contributors), _ptr(hit_masks),
+                                  _stream(dev)))
+    return output_img, distortion_img, n_contributors, hit_masks
 
 
 def backward(sorted_idx, tile_ranges, records, cam, ray_jitter, output_img, distortion_img, n_contributors,
-             grad_output_img, grad_distortion_img, indices, vertices, cell_values):
+             hit_masks, grad_output_img, grad_distortion_img, indices, vertices, cell_values):
     lib = _lib.load()
     dev = records.device
     T, V = indices.shape[0], vertices.shape[0]
@@ -160,7 +166,7 @@ def backward(sorted_idx, tile_ranges, records, cam, ray_jitter, output_img, dist
         vertices_grad = torch.empty((V, 3), dtype=torch.float32, device=dev)
         cell_grad = torch.empty((T, 7), dtype=torch.float32, device=dev)
         _lib.check(lib.rm_backward(_ptr(sorted_idx), _ptr(tile_ranges), _ptr(records), cam.ref, _ptr(ray_jitter),
-                                   _ptr(output_img), _ptr(distortion_img), _ptr(n_contributors),
+                                   _ptr(output_img), _ptr(distortion_img), _ptr(n_contributors), _ptr(hit_masks),
                                    _ptr(grad_output_img), _ptr(grad_distortion_img), _ptr(indices), _ptr(vertices),
                                    _ptr(cell_values), T, V, _ptr(grad_records), _ptr(vertices_grad), _ptr(cell_grad),
                                    _stream(dev)))
