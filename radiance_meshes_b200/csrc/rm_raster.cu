@@ -388,11 +388,13 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
           float* __restrict__ dist_img, int32_t* __restrict__ n_contrib, uint16_t* __restrict__ hit_masks, int subs,
           int64_t n_units) {
   __shared__ __align__(16) float4 stage[kWarpsPerBlock][2][2][kChunk * 6];  // [warp][half][buffer]
+  __shared__ unsigned hit_bits[kWarpsPerBlock][2][kChunk];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int half = lane >> 4, lane16 = lane & 15;
   const unsigned half_mask = 0xFFFFu << (16 * half);
   const int64_t unit = ((int64_t)blockIdx.x * kWarpsPerBlock + warp) * 2 + half;
   Unit u = make_unit(rcam, ranges, unit, n_units, subs, lane16);
+  unsigned* hb = hit_bits[warp][half];
 
   f3 d = {0.f, 0.f, 1.f};
   const int64_t pix = (int64_t)u.y * rcam.image_width + u.x;
@@ -453,6 +455,7 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
       cp_async_commit();
       if (fetching && e + kChunk < u.len) id_next = __ldg(list + u.start + e + kChunk);
     }
+    hb[lane16] = 0u;  // slot of this lane's entry, read back after the chunk
     cp_async_wait<1>();
     __syncwarp();
     // Tets of zero density are walked (they count in n_contributors) but can never
@@ -461,50 +464,48 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
     const bool nonzero = fetching && (c * kChunk + lane16 < u.len) && cur[lane16 * 6 + 5].w > 0.0f &&
                          !hull_misses_box(cq0, cq1, cq2, X0, X1, Y0, Y1);
     unsigned todo = (__ballot_sync(0xffffffffu, nonzero) >> (16 * half)) & 0xFFFFu;
-    // The two halves step through their own set bits in lock-step.  For every
-    // evaluated entry the pixels that hit it (while still active) are recorded in
-    // a 16-bit mask, kept by the lane whose index equals the entry's slot, so that
-    // the backward pass can go straight to the hits.
-    const int steps = max(__popc(todo), __shfl_xor_sync(0xffffffffu, __popc(todo), 16));
-    unsigned my_entry_hits = 0;
-    int jn = todo ? __ffs(todo) - 1 : 0;
-    float4 nx[4] = {cur[jn * 6], cur[jn * 6 + 1], cur[jn * 6 + 2], cur[jn * 6 + 3]};
-    for (int step = 0; step < steps; ++step) {
-      const int j = jn;
-      const bool in_range = todo != 0;
-      todo &= todo - 1;
-      const float4 pl[4] = {nx[0], nx[1], nx[2], nx[3]};
-      // planes of the next record to evaluate, loaded while this one is tested
-      jn = todo ? __ffs(todo) - 1 : j;
-#pragma unroll
-      for (int q = 0; q < 4; ++q) nx[q] = cur[jn * 6 + q];
-      const float4* rec = cur + j * 6;
-      Eval e;
-      bool hit = false;
-      if (in_range && active) hit = slab_test<false>(pl, d, min_t, e) && integrate(rec, d, min_t, e);
-      if (hit) {
-        sr = fmaf(e.cr, T, sr);
-        sg = fmaf(e.cg, T, sg);
-        sb = fmaf(e.cb, T, sb);
-        logT -= e.tau;
-        T *= e.alpha;
-        float dens = rec[5].w;
-        float m1 = dens * (e.exit + e.enter) * 0.5f;
-        dx = fmaf(2.0f * m1, dz, dx);
-        dy = fmaf(2.0f * dens, dw, dy);
-        dz += dens;
-        dw += m1;
-        dv = fmaf(dens * dens, e.dt * (1.0f / 3.0f), dv);
-        if (logT < -5.5f) {
-          active = false;
-          contrib = c * kChunk + j + 1;  // entries walked, the terminating one included
+    // For every entry the pixels that hit it (while still active) are collected in a
+    // 16-bit mask in shared memory, so that the backward pass can go straight to the
+    // hits; slot j was cleared by lane j before the barrier above.
+    if (active && todo) {
+      int j = __ffs(todo) - 1;
+      float4 pl[4] = {cur[j * 6], cur[j * 6 + 1], cur[j * 6 + 2], cur[j * 6 + 3]};
+      while (true) {
+        todo &= todo - 1;
+        // planes of the next record to evaluate, loaded while this one is tested
+        const int jn = todo ? __ffs(todo) - 1 : j;
+        const float4 nx[4] = {cur[jn * 6], cur[jn * 6 + 1], cur[jn * 6 + 2], cur[jn * 6 + 3]};
+        const float4* rec = cur + j * 6;
+        Eval e;
+        if (slab_test<false>(pl, d, min_t, e) && integrate(rec, d, min_t, e)) {
+          atomicOr(&hb[j], 1u << lane16);
+          sr = fmaf(e.cr, T, sr);
+          sg = fmaf(e.cg, T, sg);
+          sb = fmaf(e.cb, T, sb);
+          logT -= e.tau;
+          T *= e.alpha;
+          float dens = rec[5].w;
+          float m1 = dens * (e.exit + e.enter) * 0.5f;
+          dx = fmaf(2.0f * m1, dz, dx);
+          dy = fmaf(2.0f * dens, dw, dy);
+          dz += dens;
+          dw += m1;
+          dv = fmaf(dens * dens, e.dt * (1.0f / 3.0f), dv);
+          if (logT < -5.5f) {
+            active = false;
+            contrib = c * kChunk + j + 1;  // entries walked, the terminating one included
+            break;
+          }
         }
+        if (!todo) break;
+        j = jn;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) pl[q] = nx[q];
       }
-      const unsigned hm = (__ballot_sync(0xffffffffu, hit) >> (16 * half)) & 0xFFFFu;
-      if (in_range && lane16 == j) my_entry_hits = hm;
     }
+    __syncwarp();
     if (hit_masks && c * kChunk + lane16 < u.len)
-      hit_masks[(int64_t)(u.start + c * kChunk + lane16) * u.subs + u.sub] = (uint16_t)my_entry_hits;
+      hit_masks[(int64_t)(u.start + c * kChunk + lane16) * u.subs + u.sub] = (uint16_t)hb[lane16];
     __syncwarp();
     unsigned act = __ballot_sync(0xffffffffu, active);
     fetching = act & half_mask;
