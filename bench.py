@@ -73,7 +73,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
                  "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -277,14 +277,18 @@ def run_gpu(args):
         return ms
 
     # ---- device-resident arm -------------------------------------------------------------------
-    for _ in range(args.warmup):
+    # The clock sampler is started before the warm-up so that nvidia-smi's own start-up
+    # (about a second of driver queries) does not fall into the timed region; it keeps
+    # sampling every 200 ms under load until the timed region ends.
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(1.0)
+    for _ in range(max(args.warmup, 20)):
         pkg, vg, cg = step(d)
     barrier()
     _lib.profile_read()
     _lib.profile_enable(True)
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
@@ -407,7 +411,7 @@ def run_gpu(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="config3", choices=sorted(WORKLOADS))

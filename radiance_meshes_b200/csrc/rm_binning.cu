@@ -181,12 +181,18 @@ k_radix_scatter(const uint32_t* __restrict__ keys_in, const uint32_t* __restrict
   // warp w owns keys [base + w*kWarpSpan, +kWarpSpan) in index order (stability)
   int64_t wbase = (int64_t)blockIdx.x * kSortTile + (int64_t)warp * kWarpSpan;
   uint32_t key[kSortItems], val[kSortItems], rnk[kSortItems];
+  // loads first (in flight together); the warp barriers of the ranking rounds would
+  // otherwise serialise them
 #pragma unroll
   for (int k = 0; k < kSortItems; ++k) {
     int64_t i = wbase + k * 32 + lane;
     bool valid = i < n;
     key[k] = valid ? keys_in[i] : 0xFFFFFFFFu;
     val[k] = valid ? vals_in[i] : 0u;
+  }
+#pragma unroll
+  for (int k = 0; k < kSortItems; ++k) {
+    const bool valid = wbase + k * 32 + lane < n;
     uint32_t d = (key[k] >> shift) & (kRadix - 1);
     uint32_t peers = __ballot_sync(0xffffffffu, valid);
 #pragma unroll
@@ -550,13 +556,18 @@ k_tile_scatter1(const uint32_t* __restrict__ cum, const uint32_t* __restrict__ s
   uint32_t* wc = cnt + (size_t)warp * bins;
   uint32_t tile[kBinItems], rank[kBinItems];
   uint32_t rnk[kBinItems / 2];  // two 16-bit ranks per word
+  // all gathers first (independent, in flight together), then the ranking rounds,
+  // whose warp barriers would otherwise serialise the loads
 #pragma unroll
   for (int k = 0; k < kBinItems; ++k) {
     const int jl = warp * kBinSpan + k * 32 + lane;
-    const bool valid = jl < cntItems;
     tile[k] = 0;
     rank[k] = 0;
-    if (valid) item_tile(jl, j0, r0, before, win, own, order, rect, grid_w, tile[k], rank[k]);
+    if (jl < cntItems) item_tile(jl, j0, r0, before, win, own, order, rect, grid_w, tile[k], rank[k]);
+  }
+#pragma unroll
+  for (int k = 0; k < kBinItems; ++k) {
+    const bool valid = warp * kBinSpan + k * 32 + lane < cntItems;
     const uint32_t r = rank_round(tile[k] & (bins - 1), valid, wc, 31 - __clz(bins));
     if (k & 1) rnk[k >> 1] |= r << 16; else rnk[k >> 1] = r;
   }
