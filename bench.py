@@ -283,8 +283,8 @@ def run_gpu(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-        time.sleep(1.0)
-    for _ in range(max(args.warmup, 20)):
+        time.sleep(1.5)
+    for _ in range(args.warmup):
         pkg, vg, cg = step(d)
     barrier()
     _lib.profile_read()
