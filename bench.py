@@ -358,6 +358,30 @@ def run_gpu(args):
         ms = [t for n, t in _lib.profile_read() if n == "k_tet_err"]
         tet_err_ms = float(np.mean(ms[1:])) if len(ms) > 1 else None
 
+    # ---- feature activation of a frozen model (the row before the rasterizer), timed separately ----
+    act_ms, act_bytes = None, None
+    if rank == 0:
+        from radiance_meshes_b200.activate import activate_output
+        gen = torch.Generator(device=dev).manual_seed(11)
+        sh = (torch.randn((T, 15, 3), device=dev, generator=gen) * 0.1).half()
+        rgb = torch.rand((T, 3), device=dev, generator=gen)
+        grd = torch.randn((T, 3), device=dev, generator=gen) * 0.1
+        dens = d["cell"][:, :1].contiguous()
+        cc = d["vertices"][d["indices"].long()].mean(1) + 0.01 * torch.randn((T, 3), device=dev, generator=gen)
+        _lib.profile_read()
+        _lib.profile_enable(True)
+        with torch.no_grad():
+            for _ in range(6):
+                activate_output(tcam["cam_pos"], dens, rgb, grd, sh, d["indices"], cc, d["vertices"], 3, 3)
+        torch.cuda.synchronize()
+        _lib.profile_enable(False)
+        ms = [t for n, t in _lib.profile_read() if n == "k_activate_output"]
+        act_ms = float(np.mean(ms[1:])) if len(ms) > 1 else None
+        # compulsory traffic: per tet density 4 + rgb 12 + grd 12 + sh 15*3*2 + indices 16 + circumcenter 12 +
+        # output 28, and the vertex table once (the four gathers per tet are served from L2)
+        act_bytes = T * (4 + 12 + 12 + 90 + 16 + 12 + 28) + V * 12
+        del sh, rgb, grd, cc
+
     if rank != 0:
         if world > 1:
             dist.barrier()
@@ -399,6 +423,11 @@ def run_gpu(args):
         densification_stats=dict(kernel="k_tet_err", ms=tet_err_ms,
                                  mpix_per_s=(H * W / (tet_err_ms * 1e-3) / 1e6) if tet_err_ms else None,
                                  note="calc_tet_err pass over the same lists; not part of `value`"),
+        feature_activation=dict(kernel="k_activate_output", ms=act_ms, algorithmic_bytes=act_bytes,
+                                achieved_gbs=(act_bytes / (act_ms * 1e-3) / 1e9) if act_ms else None,
+                                frac_of_hbm_peak=(act_bytes / (act_ms * 1e-3) / 1e9 / peak) if act_ms else None,
+                                note="activate_output, SH degree 3 with f16 coefficients, all tets; "
+                                     "not part of `value`"),
     )
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(sc, tcam_np)

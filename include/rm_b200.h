@@ -150,6 +150,21 @@ int rm_backward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, con
                 float* grad_records, float* vertices_grad, float* cell_values_grad, void* stream);
 
 /*
+ * Feature activation of a frozen model, the step before the rasterizer on the
+ * rendering path.  Replaces activate_output (utils/model_util.py:93-105, with
+ * offset_normalize :81-91 and eval_sh utils/eval_sh_py.py:121-179; callers
+ * tile_benchmark.py:62-67, models/frozen.py:216-223), forward only:
+ *   density[T], rgb[T,3], grd[T,3] f32, sh[T, n_sh_rest, 3] f32 or f16 (coefficients
+ *   beyond degree 0; (sh_degree+1)^2-1 <= n_sh_rest <= 24), indices[T,4] i32, circumcenters[T,3], vertices[V,3],
+ *   camera_center[3] (device) -> features[T,7] = (density, softplus_10(SH colour at
+ *   vertex 0), colour gradient scaled by min(rgb) / circumradius).
+ */
+int rm_activate_output(const float* camera_center, const float* density, const float* rgb, const float* grd,
+                       const void* sh, int sh_is_half, const int32_t* indices, const float* circumcenters,
+                       const float* vertices, int64_t n_tets, int sh_degree, int n_sh_rest, float* features,
+                       void* stream);
+
+/*
  * Densification statistics.  Replaces calc_tet_err (slang/alphablend_shader_interp.slang:433-599,
  * host side internal/render_err.py:119-150): every pixel walks its tile list from the
  * pixel centre and every hit adds its weight T (transmittance in front of the tet times

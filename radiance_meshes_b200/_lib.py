@@ -16,7 +16,8 @@ RM_STATUS_KEY_OVERFLOW = 2
 # every symbol include/rm_b200.h declares
 SYMBOLS = ["rm_strerror", "rm_version", "rm_bin_workspace_bytes", "rm_list_scratch_bytes", "rm_project_and_bin", "rm_build_tile_lists",
            "rm_pack_records", "rm_forward", "rm_backward", "rm_vertex_backward", "rm_profile_enable",
-           "rm_profile_read", "rm_backward_static_scratch", "rm_tet_err"]
+           "rm_profile_read", "rm_backward_static_scratch", "rm_tet_err",
+           "rm_activate_output"]
 RM_STATIC_SCRATCH_MAX_TETS = 131072
 RM_ERR_STATIC_SCRATCH = -5
 
@@ -64,6 +65,7 @@ def load():
     lib.rm_backward_static_scratch.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, vp, vp,
                                                vp]
     lib.rm_tet_err.argtypes = [vp, vp, vp, cam, vp, vp, i64, vp, vp, vp]
+    lib.rm_activate_output.argtypes = [vp, vp, vp, vp, vp, C.c_int, vp, vp, vp, i64, C.c_int, C.c_int, vp, vp]
     lib.rm_profile_enable.restype = None
     lib.rm_profile_enable.argtypes = [C.c_int]
     lib.rm_profile_read.argtypes = [C.c_char_p, sz, C.POINTER(C.c_float), C.c_int]

@@ -29,6 +29,9 @@ int rm_launch_backward(const int32_t*, const int32_t*, const float*, const RmCam
 int rm_launch_tet_err(const int32_t*, const int32_t*, const float*, const RmCamera*, const float*, const float*,
                       int64_t, float*, int32_t*, cudaStream_t);
 
+int rm_launch_activate(const float*, const float*, const float*, const float*, const void*, int, const int32_t*,
+                       const float*, const float*, int64_t, int, int, float*, cudaStream_t);
+
 static thread_local char g_last_error[256] = "";
 
 // ---- optional per-kernel timing ---------------------------------------------
@@ -255,6 +258,24 @@ int rm_backward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, con
                             n_contributors, hit_masks, grad_output_img, grad_distortion_img, indices, vertices, cell_values,
                             n_tets, n_vertices, grad_records, vertices_grad, cell_values_grad,
                             static_cast<cudaStream_t>(stream));
+}
+
+int rm_activate_output(const float* camera_center, const float* density, const float* rgb, const float* grd,
+                       const void* sh, int sh_is_half, const int32_t* indices, const float* circumcenters,
+                       const float* vertices, int64_t n_tets, int sh_degree, int n_sh_rest, float* features,
+                       void* stream) {
+  g_last_error[0] = 0;
+  if (n_tets < 0 || sh_degree < 0 || sh_degree > 4) return RM_ERR_INVALID_ARG;
+  if (n_tets == 0) return RM_OK;
+  if (n_sh_rest < (sh_degree + 1) * (sh_degree + 1) - 1 || n_sh_rest > 24) return RM_ERR_INVALID_ARG;
+  if (!camera_center || !density || !rgb || !grd || !indices || !circumcenters || !vertices || !features ||
+      (sh_degree > 0 && !sh))
+    return RM_ERR_INVALID_ARG;
+  if (!aligned16(indices)) return RM_ERR_WORKSPACE;
+  int rc = rm_bind_device(features);
+  if (rc) return rc;
+  return rm_launch_activate(camera_center, density, rgb, grd, sh, sh_is_half, indices, circumcenters, vertices,
+                            n_tets, sh_degree, n_sh_rest, features, static_cast<cudaStream_t>(stream));
 }
 
 int rm_tet_err(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, const float* records,
