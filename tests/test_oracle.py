@@ -206,3 +206,20 @@ def test_golden_fixture(oracle):
                              g["g_dist"])
     np.testing.assert_allclose(vg, g["vertices_grad"], rtol=1e-4, atol=1e-4 * np.abs(g["vertices_grad"]).max())
     np.testing.assert_allclose(cg, g["cell_grad"], rtol=1e-4, atol=1e-4 * np.abs(g["cell_grad"]).max())
+
+
+def test_circumspheres_against_reference_torch_geometry(oracle):
+    """Projection-stage circumcentres and the fp64 sort depth against values the reference's own
+    utils/topo_utils.py calculate_circumcenters_torch produced (tests/golden/make_topo_golden.py)."""
+    here = os.path.join(os.path.dirname(__file__), "golden")
+    g = np.load(os.path.join(here, "small_scene.npz"))
+    t = np.load(os.path.join(here, "topo_circumspheres.npz"))
+    vis = g["tiles_touched"] > 0
+    err = np.abs(g["circumcenter"].astype(np.float64) - t["circumcenter"]).max(1) / t["radius"]
+    assert err[vis].max() < 1e-6                      # the stage writes float32
+    tets = g["vertices"][g["indices"]]
+    for i in range(0, len(tets), 7):
+        p, c = oracle.power_f64(tets[i], g["eye"])
+        ref = ((g["eye"] - t["circumcenter"][i]) ** 2).sum() - t["radius"][i] ** 2
+        assert abs(p - ref) <= 1e-12 * max(1.0, abs(ref))
+        assert np.abs(c - t["circumcenter"][i]).max() <= 1e-12 * max(1.0, t["radius"][i])
