@@ -221,7 +221,7 @@ def run_gpu(args):
     import torch.distributed as dist
     from radiance_meshes_b200 import _lib, raster
     from radiance_meshes_b200 import dist as rmdist
-    from radiance_meshes_b200.render import render, tcam_to_device
+    from radiance_meshes_b200.render import HostFramePipeline, render, tcam_to_device
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -321,14 +321,11 @@ def run_gpu(args):
     h2d = sum(v.numel() * v.element_size() for v in host.values())
     d2h = sum(v.numel() * v.element_size() for v in out_host.values())
 
+    pipe = HostFramePipeline(dev)
+
     def e2e_step():
-        inp = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
-        pkg, vg, cg = step(inp)
-        out_host["image"].copy_(pkg["image"].detach(), non_blocking=True)
-        out_host["dist"].copy_(pkg["distortion_img"].detach(), non_blocking=True)
-        out_host["vg"].copy_(vg, non_blocking=True)
-        out_host["cg"].copy_(cg, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        # host buffers in, host buffers out; the copies overlap this frame's kernels on two copy streams
+        pipe.step(host, out_host, tcam, reduce_gradients=rmdist.allreduce_gradients)
 
     for _ in range(max(1, min(args.warmup, 3))):
         e2e_step()

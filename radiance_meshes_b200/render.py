@@ -19,8 +19,11 @@ def tcam_to_device(tcam, device):
     return out
 
 
-def render(indices, vertices, cell_values, tcam, ray_jitter=None):
-    """Returns dict(render[3,H,W], alpha[H,W] (log-transmittance), distortion_loss, mask, image, distortion_img)."""
+def render(indices, vertices, cell_values, tcam, ray_jitter=None, before_blend=None):
+    """Returns dict(render[3,H,W], alpha[H,W] (log-transmittance), distortion_loss, mask, image, distortion_img).
+
+    `before_blend`, if given, is called after the tile lists are built and before the first kernel that
+    reads `cell_values` and `ray_jitter` is launched (a pipeline waits there for their copies to land)."""
     H, W = int(tcam["image_height"]), int(tcam["image_width"])
     device = vertices.device
     if ray_jitter is None:
@@ -28,6 +31,8 @@ def render(indices, vertices, cell_values, tcam, ray_jitter=None):
     grid = RenderGrid(H, W, tile_height=int(tcam["tile_height"]), tile_width=int(tcam["tile_width"]))
     sorted_tetra_idx, tile_ranges, vs_tetra, circumcenter, mask, rect = vertex_and_tile_shader(
         indices, vertices, tcam, grid)
+    if before_blend is not None:
+        before_blend()
     image, distortion_img, tet_alive = AlphaBlendTiledRender.apply(
         sorted_tetra_idx, tile_ranges, indices, vertices, cell_values, grid, tcam, ray_jitter)
     total_density = (distortion_img[:, :, 2] ** 2).clip(min=1e-6)
@@ -36,3 +41,71 @@ def render(indices, vertices, cell_values, tcam, ray_jitter=None):
     return dict(render=image.permute(2, 0, 1)[:3], alpha=image[..., 3], distortion_loss=distortion_loss.mean(),
                 mask=mask, image=image, distortion_img=distortion_img, sorted_tetra_idx=sorted_tetra_idx,
                 tile_ranges=tile_ranges, vs_tetra=vs_tetra, circumcenter=circumcenter, rect=rect)
+
+
+class HostFramePipeline:
+    """Forward + backward of one frame whose inputs and results live in pinned host memory.
+
+    The host<->device copies run on two copy streams and overlap the kernels of the same
+    frame: projection and tile-list building start as soon as vertices and indices have
+    arrived, while the cell values (the largest input) are still in flight; the image and
+    the distortion moments go back to the host while the backward pass runs; only the two
+    gradient tensors are copied after the last kernel.  Device staging buffers for the
+    inputs are allocated once and reused by every frame.
+    """
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self.copy_in = torch.cuda.Stream(self.device)
+        self.copy_out = torch.cuda.Stream(self.device)
+        self.staging = {}
+
+    def _stage(self, name, host_tensor):
+        buf = self.staging.get(name)
+        if buf is None or buf.shape != host_tensor.shape or buf.dtype != host_tensor.dtype:
+            buf = torch.empty(host_tensor.shape, dtype=host_tensor.dtype, device=self.device)
+            self.staging[name] = buf
+        buf.copy_(host_tensor, non_blocking=True)
+        return buf
+
+    def step(self, host_in, host_out, tcam, reduce_gradients=None):
+        """host_in: indices, vertices, cell, jitter, g_img, g_dist (pinned).  host_out: image, dist, vg, cg
+        (pinned, filled on return).  `reduce_gradients([vertices_grad, cell_grad])`, if given, runs after the
+        backward pass and before the gradients are copied out (the sum over ranks of a multi-GPU job).
+        Returns the render package of the frame."""
+        cur = torch.cuda.current_stream(self.device)
+        ev_geometry, ev_cells, ev_grads = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
+        self.copy_in.wait_stream(cur)  # the previous frame's kernels are done with the staging buffers
+        with torch.cuda.stream(self.copy_in):
+            vertices = self._stage("vertices", host_in["vertices"])
+            indices = self._stage("indices", host_in["indices"])
+            ev_geometry.record(self.copy_in)
+            cell = self._stage("cell", host_in["cell"])
+            jitter = self._stage("jitter", host_in["jitter"])
+            ev_cells.record(self.copy_in)
+            g_img = self._stage("g_img", host_in["g_img"])
+            g_dist = self._stage("g_dist", host_in["g_dist"])
+            ev_grads.record(self.copy_in)
+        v = vertices.detach().requires_grad_(True)
+        c = cell.detach().requires_grad_(True)
+        cur.wait_event(ev_geometry)
+        pkg = render(indices, v, c, tcam, jitter, before_blend=lambda: cur.wait_event(ev_cells))
+        image, dimg = pkg["image"].detach(), pkg["distortion_img"].detach()
+        self.copy_out.wait_stream(cur)
+        with torch.cuda.stream(self.copy_out):
+            host_out["image"].copy_(image, non_blocking=True)
+            host_out["dist"].copy_(dimg, non_blocking=True)
+        image.record_stream(self.copy_out)
+        dimg.record_stream(self.copy_out)
+        cur.wait_event(ev_grads)
+        torch.autograd.backward([pkg["image"], pkg["distortion_img"]], [g_img, g_dist])
+        if reduce_gradients is not None:
+            reduce_gradients([v.grad, c.grad])
+        self.copy_out.wait_stream(cur)
+        with torch.cuda.stream(self.copy_out):
+            host_out["vg"].copy_(v.grad, non_blocking=True)
+            host_out["cg"].copy_(c.grad, non_blocking=True)
+        v.grad.record_stream(self.copy_out)
+        c.grad.record_stream(self.copy_out)
+        self.copy_out.synchronize()
+        return pkg

@@ -304,3 +304,40 @@ def test_densification_statistics(oracle, cuda_lib):
     assert dcount.max() <= 2 and (dcount > 0).mean() <= 0.01
     same = dcount == 0
     assert np.abs(cnt[same, 1] - cnt_ref[same, 1]).max() <= 2 + 1e-4 * cnt_ref[:, 1].max()
+
+
+def test_host_frame_pipeline_matches_direct_path():
+    """Host buffers in / host buffers out with overlapped copies gives the same frame and gradients."""
+    import torch
+    from radiance_meshes_b200.render import HostFramePipeline, render, tcam_to_device
+    pts, tets, cell = scene_util.small_scene(400, seed=21)
+    sc = dict(indices=np.ascontiguousarray(tets, np.int32), vertices=pts, cell_values=cell)
+    tcam_np = scene_util.camera(H=96, W=128, tile=4)
+    dev = torch.device("cuda:0")
+    tcam = tcam_to_device(tcam_np, dev)
+    rng = np.random.default_rng(5)
+    H, W = tcam_np["image_height"], tcam_np["image_width"]
+    host = dict(indices=torch.from_numpy(sc["indices"]).pin_memory(),
+                vertices=torch.from_numpy(sc["vertices"]).pin_memory(),
+                cell=torch.from_numpy(sc["cell_values"]).pin_memory(),
+                jitter=torch.from_numpy(rng.uniform(0, 1, (H, W, 2)).astype(np.float32)).pin_memory(),
+                g_img=torch.from_numpy(rng.normal(size=(H, W, 4)).astype(np.float32)).pin_memory(),
+                g_dist=torch.from_numpy((0.01 * rng.normal(size=(H, W, 5))).astype(np.float32)).pin_memory())
+    T, V = sc["indices"].shape[0], sc["vertices"].shape[0]
+    out = dict(image=torch.empty((H, W, 4)).pin_memory(), dist=torch.empty((H, W, 5)).pin_memory(),
+               vg=torch.empty((V, 3)).pin_memory(), cg=torch.empty((T, 7)).pin_memory())
+    pipe = HostFramePipeline(dev)
+    for _ in range(3):          # staging buffers are reused from the second frame on
+        for t in out.values():
+            t.fill_(float("nan"))
+        pipe.step(host, out, tcam)
+    d = {k: v.to(dev) for k, v in host.items()}
+    v = d["vertices"].requires_grad_(True)
+    c = d["cell"].requires_grad_(True)
+    pkg = render(d["indices"], v, c, tcam, d["jitter"])
+    torch.autograd.backward([pkg["image"], pkg["distortion_img"]], [d["g_img"], d["g_dist"]])
+    assert torch.equal(out["image"], pkg["image"].detach().cpu())
+    assert torch.equal(out["dist"], pkg["distortion_img"].detach().cpu())
+    for got, want in ((out["vg"], v.grad.cpu()), (out["cg"], c.grad.cpu())):   # float atomics: order varies
+        assert torch.isfinite(got).all()
+        assert float((got - want).norm() / want.norm().clamp_min(1e-20)) < 1e-5
