@@ -61,9 +61,10 @@ typedef struct RmCamera {
 
 /* Written by rm_project_and_bin at the start of the info buffer (device memory). */
 typedef struct RmBinInfo {
-  int64_t n_keys;      /* N = sum of tiles_touched */
-  int32_t n_visible;   /* tets with tiles_touched > 0 */
-  uint32_t status;     /* RM_STATUS_* bits */
+  int64_t n_keys;        /* N = sum of tiles_touched */
+  int64_t n_region_keys; /* sum over tets of the 8 x 4-tile regions their rectangle touches */
+  int32_t n_visible;     /* tets with tiles_touched > 0 */
+  uint32_t status;       /* RM_STATUS_* bits */
 } RmBinInfo;
 
 const char* rm_strerror(int code);
@@ -90,22 +91,24 @@ int rm_project_and_bin(const int32_t* indices, int64_t n_tets, const float* vert
                        float* circumcenter, int32_t* tile_ranges, RmBinInfo* info, void* workspace,
                        size_t workspace_bytes, void* stream);
 
-/* Bytes of scratch rm_build_tile_lists needs for n_keys (tile, tet) pairs on n_tiles tiles
- * (0 if the grid has more than 2^22 tiles, which is not supported). */
-size_t rm_list_scratch_bytes(int64_t n_keys, int64_t n_tiles);
+/* Bytes of scratch rm_build_tile_lists needs for n_region_keys (region, tet) pairs on a
+ * grid_height x grid_width tile grid (0 if the grid has more than 2^22 regions of 8 x 4
+ * tiles, which is not supported). */
+size_t rm_list_scratch_bytes(int64_t n_region_keys, int grid_height, int grid_width);
 
 /*
  * Stages 2-3: per-tile tet lists ordered by (sort depth bits, tet id).
  * Replaces generate_keys (slang/tile_shader.slang:49-97) + sort_by_keys
  * (sort_by_keys/sort_by_keys.cu:9-53): the result equals the value array of a
  * stable ascending sort of the keys (tile << 32 | sortable(depth)).
- *   n_keys must be RmBinInfo.n_keys read back by the caller;
- *   sorted_tetra_idx[N] i32 out; scratch: rm_list_scratch_bytes(N, G) bytes,
- *   256-byte aligned, caller-provided.
+ *   n_keys and n_region_keys must be RmBinInfo.n_keys and .n_region_keys read back
+ *   by the caller; sorted_tetra_idx[N] i32 out, 16-byte aligned; scratch:
+ *   rm_list_scratch_bytes(n_region_keys, grid_height, grid_width) bytes, 256-byte
+ *   aligned, caller-provided.
  */
 int rm_build_tile_lists(const int32_t* rect_tile_space, const int32_t* tile_ranges, int64_t n_tets,
-                        const RmCamera* cam, int64_t n_keys, void* workspace, void* scratch, size_t scratch_bytes,
-                        int32_t* sorted_tetra_idx, void* stream);
+                        const RmCamera* cam, int64_t n_keys, int64_t n_region_keys, void* workspace, void* scratch,
+                        size_t scratch_bytes, int32_t* sorted_tetra_idx, void* stream);
 
 /*
  * Per-frame packed tet records (4 outward face planes relative to the camera

@@ -31,7 +31,8 @@ class RmCamera(C.Structure):
 
 
 class RmBinInfo(C.Structure):
-    _fields_ = [("n_keys", C.c_int64), ("n_visible", C.c_int32), ("status", C.c_uint32)]
+    _fields_ = [("n_keys", C.c_int64), ("n_region_keys", C.c_int64), ("n_visible", C.c_int32),
+                ("status", C.c_uint32)]
 
 
 _lib = None
@@ -56,8 +57,8 @@ def load():
     lib.rm_bin_workspace_bytes.argtypes = [i64, i64]
     lib.rm_project_and_bin.argtypes = [vp, i64, vp, i64, cam, vp, vp, vp, vp, vp, vp, vp, sz, vp]
     lib.rm_list_scratch_bytes.restype = sz
-    lib.rm_list_scratch_bytes.argtypes = [i64, i64]
-    lib.rm_build_tile_lists.argtypes = [vp, vp, i64, cam, i64, vp, vp, sz, vp, vp]
+    lib.rm_list_scratch_bytes.argtypes = [i64, C.c_int, C.c_int]
+    lib.rm_build_tile_lists.argtypes = [vp, vp, i64, cam, i64, i64, vp, vp, sz, vp, vp]
     lib.rm_pack_records.argtypes = [vp, vp, vp, i64, cam, vp, vp, vp]
     lib.rm_forward.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, vp, vp]
     lib.rm_backward.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, vp, vp, vp, vp]

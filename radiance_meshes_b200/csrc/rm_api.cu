@@ -15,9 +15,9 @@ size_t rm_bin_layout_bytes(int64_t, int64_t);
 int rm_launch_bin_prepare(int64_t, const RmCamera*, void*, size_t, uint32_t**, uint32_t**, int32_t**, RmBinInfo*,
                           cudaStream_t);
 int rm_launch_bin_finish(int64_t, const RmCamera*, const int32_t*, int32_t*, RmBinInfo*, void*, cudaStream_t);
-int rm_launch_build_lists(const int32_t*, const int32_t*, int64_t, const RmCamera*, int64_t, void*, void*, size_t,
+int rm_launch_build_lists(const int32_t*, const int32_t*, int64_t, const RmCamera*, int64_t, int64_t, void*, void*, size_t,
                           int32_t*, cudaStream_t);
-size_t rm_list_plan_bytes(int64_t, int64_t);
+size_t rm_list_plan_bytes(int64_t, int, int);
 int rm_launch_pack(const int32_t*, const float*, const float*, int64_t, const RmCamera*, const int32_t*, float*,
                    cudaStream_t);
 int rm_launch_forward(const int32_t*, const int32_t*, const float*, const RmCamera*, const float*, float*, float*,
@@ -179,28 +179,29 @@ int rm_project_and_bin(const int32_t* indices, int64_t n_tets, const float* vert
   rc = rm_launch_project(indices, n_tets, vertices, n_vertices, cam, tiles_touched, rect_tile_space, vs_tetra,
                          circumcenter, depth_keys, order_in, tile_diff, info, st);
   if (rc) return rc;
-  return rm_launch_bin_finish(n_tets, cam, tiles_touched, tile_ranges, info, workspace, st);
+  return rm_launch_bin_finish(n_tets, cam, rect_tile_space, tile_ranges, info, workspace, st);
 }
 
-size_t rm_list_scratch_bytes(int64_t n_keys, int64_t n_tiles) {
-  if (n_keys < 0 || n_tiles < 1) return 0;
-  return rm_list_plan_bytes(n_keys, n_tiles);
+size_t rm_list_scratch_bytes(int64_t n_region_keys, int grid_height, int grid_width) {
+  if (n_region_keys < 0 || grid_height < 1 || grid_width < 1) return 0;
+  return rm_list_plan_bytes(n_region_keys, grid_height, grid_width);
 }
 
 int rm_build_tile_lists(const int32_t* rect_tile_space, const int32_t* tile_ranges, int64_t n_tets,
-                        const RmCamera* cam, int64_t n_keys, void* workspace, void* scratch, size_t scratch_bytes,
-                        int32_t* sorted_tetra_idx, void* stream) {
+                        const RmCamera* cam, int64_t n_keys, int64_t n_region_keys, void* workspace, void* scratch,
+                        size_t scratch_bytes, int32_t* sorted_tetra_idx, void* stream) {
   g_last_error[0] = 0;
   int rc = check_cam(cam);
   if (rc) return rc;
-  if (n_keys < 0 || n_tets < 0 || !workspace || !tile_ranges) return RM_ERR_INVALID_ARG;
+  if (n_keys < 0 || n_region_keys < 0 || n_tets < 0 || !workspace || !tile_ranges) return RM_ERR_INVALID_ARG;
   if (n_keys > 0x7fffffffll) return RM_ERR_TOO_MANY_KEYS;
   if (n_keys == 0) return RM_OK;
   if (!rect_tile_space || !scratch || !sorted_tetra_idx) return RM_ERR_INVALID_ARG;
+  if (!aligned16(rect_tile_space) || !aligned16(sorted_tetra_idx)) return RM_ERR_WORKSPACE;
   rc = rm_bind_device(workspace);
   if (rc) return rc;
-  return rm_launch_build_lists(rect_tile_space, tile_ranges, n_tets, cam, n_keys, workspace, scratch, scratch_bytes,
-                               sorted_tetra_idx, static_cast<cudaStream_t>(stream));
+  return rm_launch_build_lists(rect_tile_space, tile_ranges, n_tets, cam, n_keys, n_region_keys, workspace, scratch,
+                               scratch_bytes, sorted_tetra_idx, static_cast<cudaStream_t>(stream));
 }
 
 int rm_pack_records(const int32_t* indices, const float* vertices, const float* cell_values, int64_t n_tets,

@@ -24,9 +24,29 @@
 namespace rm {
 
 // ---------------------------------------------------------------------------
-// Device-wide exclusive scan of uint32 (three launches: block sums, scan of the
-// block sums, apply).  Optional gather: element i is in[gather[i]].
+// Regions: blocks of kRegW x kRegH tiles, one tile per lane of a warp.
 // ---------------------------------------------------------------------------
+constexpr int kRegShiftX = 3, kRegShiftY = 2;
+constexpr int kRegW = 1 << kRegShiftX, kRegH = 1 << kRegShiftY;  // 8 x 4 = 32 tiles
+
+// number of regions a tile rectangle (x0, y0, x1, y1), max exclusive, touches; 0 for an empty one
+__device__ __forceinline__ uint32_t regions_touched(int4 rc) {
+  if (rc.z <= rc.x || rc.w <= rc.y) return 0u;
+  return (uint32_t)((((rc.z - 1) >> kRegShiftX) - (rc.x >> kRegShiftX) + 1) *
+                    (((rc.w - 1) >> kRegShiftY) - (rc.y >> kRegShiftY) + 1));
+}
+
+// ---------------------------------------------------------------------------
+// Device-wide exclusive scan of uint32 (three launches: block sums, scan of the
+// block sums, apply).  Optional gather: element i is in[gather[i]].  With `rect`
+// the element is the number of regions rect[gather[i]] touches instead.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t scan_value(const uint32_t* __restrict__ in, const uint32_t* __restrict__ gather,
+                                               const int4* __restrict__ rect, int64_t i) {
+  if (rect) return regions_touched(__ldg(rect + gather[i]));
+  return gather ? in[gather[i]] : in[i];
+}
+
 constexpr int kScanThreads = 256;
 constexpr int kScanItems = 16;
 constexpr int kScanTile = kScanThreads * kScanItems;
@@ -61,15 +81,15 @@ __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* t
 }
 
 __global__ void __launch_bounds__(kScanThreads)
-k_scan_block_sums(const uint32_t* __restrict__ in, const uint32_t* __restrict__ gather, int64_t n,
-                  uint32_t* __restrict__ bsum) {
+k_scan_block_sums(const uint32_t* __restrict__ in, const uint32_t* __restrict__ gather,
+                  const int4* __restrict__ rect, int64_t n, uint32_t* __restrict__ bsum) {
   __shared__ uint32_t sm[kScanThreads / 32 + 1];
   int64_t base = (int64_t)blockIdx.x * kScanTile;
   uint32_t s = 0;
 #pragma unroll
   for (int k = 0; k < kScanItems; ++k) {
     int64_t i = base + k * kScanThreads + threadIdx.x;
-    if (i < n) s += gather ? in[gather[i]] : in[i];
+    if (i < n) s += scan_value(in, gather, rect, i);
   }
   uint32_t total;
   block_exclusive_scan<kScanThreads>(s, &total, sm);
@@ -93,8 +113,8 @@ __global__ void __launch_bounds__(1024) k_scan_sums(uint32_t* __restrict__ bsum,
 
 // inclusive = true writes the inclusive scan instead
 __global__ void __launch_bounds__(kScanThreads)
-k_scan_apply(const uint32_t* __restrict__ in, const uint32_t* __restrict__ gather, int64_t n,
-             const uint32_t* __restrict__ bsum, uint32_t* __restrict__ out, int inclusive) {
+k_scan_apply(const uint32_t* __restrict__ in, const uint32_t* __restrict__ gather, const int4* __restrict__ rect,
+             int64_t n, const uint32_t* __restrict__ bsum, uint32_t* __restrict__ out, int inclusive) {
   __shared__ uint32_t sm[kScanThreads / 32 + 1];
   // blocked arrangement: thread t owns items [t*kScanItems, (t+1)*kScanItems)
   int64_t base = (int64_t)blockIdx.x * kScanTile + (int64_t)threadIdx.x * kScanItems;
@@ -103,7 +123,7 @@ k_scan_apply(const uint32_t* __restrict__ in, const uint32_t* __restrict__ gathe
 #pragma unroll
   for (int k = 0; k < kScanItems; ++k) {
     int64_t i = base + k;
-    v[k] = i < n ? (gather ? in[gather[i]] : in[i]) : 0;
+    v[k] = i < n ? scan_value(in, gather, rect, i) : 0;
     s += v[k];
   }
   uint32_t total;
@@ -286,25 +306,40 @@ __global__ void k_write_ranges(const uint32_t* __restrict__ counts, const uint32
   ranges[g] = c ? make_int2((int)s, (int)(s + c)) : make_int2(0, 0);
 }
 
+// total_keys[0] = sum of the tile populations, total_keys[1] = sum of regions touched
 __global__ void k_finish_info(RmBinInfo* info, const unsigned long long* total_keys) {
-  unsigned long long n = *total_keys;
+  unsigned long long n = total_keys[0];
   info->n_keys = (int64_t)n;
+  info->n_region_keys = (int64_t)total_keys[1];
   if (n > 0x7fffffffull) info->status |= RM_STATUS_KEY_OVERFLOW;
 }
 
 // ---------------------------------------------------------------------------
-// Tile lists by a stable two-pass counting sort on the tile id.
+// Tile lists, built in two levels.
 //
-// Work items are the (tile, tet) pairs numbered in the reference's emission
-// order (tets by rank, then tile rows, then columns): item j belongs to the
-// rank r with cum[r-1] <= j < cum[r].  Because the items are generated in rank
-// order and both passes are stable, sorting them by tile id (low digit first,
-// then high digit) leaves every tile's segment ordered by rank, i.e. by
-// (depth bits, tet id): no per-tile sort, no atomics, deterministic.
-//   pass 1: generate items, stable split on the low  b1 bits of the tile id -> (rank, tile) pairs
-//   pass 2: stable split on the high b2 bits -> sorted_tetra_idx = order[rank]
+// Level 1 (regions).  Work items are the (region, tet) pairs numbered in rank
+// order (tets by rank, then region rows, then columns): item j belongs to the
+// rank r with cum[r-1] <= j < cum[r].  A stable two-pass counting sort on the
+// region id (low digit first, then high digit) leaves every region's segment
+// ordered by rank, i.e. by (depth bits, tet id): no per-region sort, no atomics
+// on the data path, deterministic.  A tet touches far fewer regions than tiles
+// (about 9 times fewer at 1080p with 4 x 4 pixel tiles), so this sort moves a
+// fraction of the pairs.  Every sorted entry carries the tet id and a 32-bit
+// mask of the region's tiles its rectangle covers.
+//   pass 1: generate items, stable split on the low  b1 bits of the region id -> (rank, region) pairs
+//   pass 2: stable split on the high b2 bits -> entries (tet id, tile mask)
 // Each pass is: per-block digit histogram, per-digit scan over the blocks,
 // stable scatter (warp-level match ranking, warps own consecutive item spans).
+//
+// Level 2 (tiles).  A region's segment is cut into chunks of kChunk entries, one
+// warp per chunk, lane l owning tile l of the region.  A lane's tile list is the
+// subsequence of entries whose mask has bit l: the count pass adds up the bits
+// per chunk and lane (a 32 x 32 bit transpose and a popcount per 32 entries), a
+// per-region scan over the chunks turns the counts into write cursors starting
+// at the tile's range, and the write pass walks the chunk again, every lane
+// appending the tet ids of its set bits to its own list through a four-entry
+// register buffer (16-byte stores).  Order inside a tile is the order of the
+// region's segment: rank order.
 // ---------------------------------------------------------------------------
 constexpr int kBinThreads = 256;
 constexpr int kBinItems = 16;
@@ -383,47 +418,72 @@ __device__ __forceinline__ void owners_of_items(const uint32_t* __restrict__ cum
   __syncthreads();
 }
 
-// tile id and rank of local item jl
-__device__ __forceinline__ void item_tile(int jl, int64_t j0, int r0, uint32_t before_r0, const uint32_t* win,
-                                          const uint16_t* own, const uint32_t* __restrict__ order,
-                                          const int4* __restrict__ rect, int grid_w, uint32_t& tile, uint32_t& rank) {
+// region id and rank of local item jl
+__device__ __forceinline__ void item_region(int jl, int64_t j0, int r0, uint32_t before_r0, const uint32_t* win,
+                                            const uint16_t* own, const uint32_t* __restrict__ order,
+                                            const int4* __restrict__ rect, int reg_w, uint32_t& region,
+                                            uint32_t& rank) {
   const int i = own[jl];
   rank = (uint32_t)(r0 + i);
   const uint32_t excl = i > 0 ? win[i - 1] : before_r0;
   const uint32_t local = (uint32_t)(j0 + jl - excl);
   const int4 rc = __ldg(rect + order[rank]);
-  const uint32_t w = (uint32_t)(rc.z - rc.x);
+  const uint32_t cx0 = (uint32_t)(rc.x >> kRegShiftX);
+  const uint32_t w = (uint32_t)((rc.z - 1) >> kRegShiftX) - cx0 + 1u;
   const uint32_t dy = local / w;
-  tile = (rc.y + dy) * grid_w + rc.x + (local - dy * w);
+  region = ((uint32_t)(rc.y >> kRegShiftY) + dy) * (uint32_t)reg_w + cx0 + (local - dy * w);
 }
 
+// Sorted entry of (rank, region): the tet id and the mask of the region's tiles (bit = 8 * row + column)
+// that the tet's rectangle covers.
+__device__ __forceinline__ uint2 region_entry(uint32_t rank, uint32_t region, const uint32_t* __restrict__ order,
+                                              const int4* __restrict__ rect, int reg_w) {
+  const uint32_t tet = order[rank];
+  const int4 rc = __ldg(rect + tet);
+  const int gy = (int)(region / (uint32_t)reg_w), gx = (int)(region - (uint32_t)gy * (uint32_t)reg_w);
+  const int lx0 = max(rc.x - gx * kRegW, 0), lx1 = min(rc.z - gx * kRegW, kRegW);
+  const int ly0 = max(rc.y - gy * kRegH, 0), ly1 = min(rc.w - gy * kRegH, kRegH);
+  const uint32_t row = (1u << lx1) - (1u << lx0);
+  const uint32_t rows = 0x01010101u & (uint32_t)((1ull << (8 * ly1)) - (1ull << (8 * ly0)));
+  return make_uint2(tet, row * rows);
+}
+
+// Pass-1 digit histogram of the block's items; also the population of every region
+// (region_count, zeroed by the caller), accumulated in shared memory when the
+// region table fits (n_regions_smem = n_regions) and with global atomics otherwise
+// (n_regions_smem = 0).
 __global__ void __launch_bounds__(kBinThreads)
-k_tile_hist1(const uint32_t* __restrict__ cum, const uint32_t* __restrict__ start_rank,
-             const uint32_t* __restrict__ order, int n_ranked,
-             const int4* __restrict__ rect, int grid_w, int64_t n_keys, uint32_t bins, uint32_t* __restrict__ hist,
-             int nblk) {
+k_region_hist1(const uint32_t* __restrict__ cum, const uint32_t* __restrict__ start_rank,
+               const uint32_t* __restrict__ order, int n_ranked, const int4* __restrict__ rect, int reg_w,
+               int64_t n_items, uint32_t bins, uint32_t* __restrict__ hist, int nblk, uint32_t n_regions_smem,
+               uint32_t* __restrict__ region_count) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   uint32_t* win = reinterpret_cast<uint32_t*>(smem_raw);
   uint32_t* s_misc = win + kBinTile + 4;
   uint16_t* own = reinterpret_cast<uint16_t*>(s_misc + 16);
   uint32_t* h = reinterpret_cast<uint32_t*>(own + kBinTile);
+  uint32_t* rh = h + bins;
   const int64_t j0 = (int64_t)blockIdx.x * kBinTile;
-  const int cnt = (int)min((int64_t)kBinTile, n_keys - j0);
-  for (uint32_t i = threadIdx.x; i < bins; i += kBinThreads) h[i] = 0;
+  const int cnt = (int)min((int64_t)kBinTile, n_items - j0);
+  for (uint32_t i = threadIdx.x; i < bins + n_regions_smem; i += kBinThreads) h[i] = 0;
   owners_of_items(cum, n_ranked, j0, start_rank, win, own, s_misc);
   const int r0 = (int)s_misc[8];
   const uint32_t before = s_misc[9];
   for (int jl = threadIdx.x; jl < cnt; jl += kBinThreads) {
-    uint32_t tile, rank;
-    item_tile(jl, j0, r0, before, win, own, order, rect, grid_w, tile, rank);
-    atomicAdd(&h[tile & (bins - 1)], 1u);
+    uint32_t region, rank;
+    item_region(jl, j0, r0, before, win, own, order, rect, reg_w, region, rank);
+    atomicAdd(&h[region & (bins - 1)], 1u);
+    if (n_regions_smem) atomicAdd(&rh[region], 1u);
+    else atomicAdd(region_count + region, 1u);
   }
   __syncthreads();
   for (uint32_t i = threadIdx.x; i < bins; i += kBinThreads) hist[(int64_t)i * nblk + blockIdx.x] = h[i];
+  for (uint32_t i = threadIdx.x; i < n_regions_smem; i += kBinThreads)
+    if (rh[i]) atomicAdd(region_count + i, rh[i]);
 }
 
 __global__ void __launch_bounds__(kBinThreads)
-k_tile_hist2(const uint2* __restrict__ pairs, int64_t n, int shift, uint32_t bins, uint32_t* __restrict__ hist,
+k_region_hist2(const uint2* __restrict__ pairs, int64_t n, int shift, uint32_t bins, uint32_t* __restrict__ hist,
              int nblk) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   uint32_t* h = reinterpret_cast<uint32_t*>(smem_raw);
@@ -526,15 +586,15 @@ __device__ __forceinline__ void local_layout(uint32_t bins, uint32_t* cnt, uint3
   __syncthreads();
 }
 
-// pass 1.  final != 0: the low digit is the whole tile id, write tet ids directly.
+// pass 1.  final != 0: the low digit is the whole region id, write the sorted entries directly.
 // Items are reordered by digit in shared memory first, so that the global
 // writes of one digit's run are contiguous.
 __global__ void __launch_bounds__(kBinThreads, 3)
-k_tile_scatter1(const uint32_t* __restrict__ cum, const uint32_t* __restrict__ start_rank,
-                const uint32_t* __restrict__ order, int n_ranked,
-                const int4* __restrict__ rect, int grid_w, int64_t n_keys, uint32_t bins,
-                const uint32_t* __restrict__ hist, const uint32_t* __restrict__ digit_total, int nblk, int final,
-                uint2* __restrict__ pairs_out, int32_t* __restrict__ sorted_idx) {
+k_region_scatter1(const uint32_t* __restrict__ cum, const uint32_t* __restrict__ start_rank,
+                  const uint32_t* __restrict__ order, int n_ranked,
+                  const int4* __restrict__ rect, int reg_w, int64_t n_items, uint32_t bins,
+                  const uint32_t* __restrict__ hist, const uint32_t* __restrict__ digit_total, int nblk, int final,
+                  uint2* __restrict__ pairs_out, uint2* __restrict__ entries) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   // [ sbuf (8 B x kBinTile), aliased by win + s_misc + own during generation | dbase | lstart | cnt ]
   uint2* sbuf = reinterpret_cast<uint2*>(smem_raw);
@@ -546,7 +606,7 @@ k_tile_scatter1(const uint32_t* __restrict__ cum, const uint32_t* __restrict__ s
   uint32_t* cnt = lstart + bins;
   uint32_t* s_scan = cnt + (size_t)kBinWarps * bins;  // 16 words
   const int64_t j0 = (int64_t)blockIdx.x * kBinTile;
-  const int cntItems = (int)min((int64_t)kBinTile, n_keys - j0);
+  const int cntItems = (int)min((int64_t)kBinTile, n_items - j0);
   for (uint32_t i = threadIdx.x; i < kBinWarps * bins; i += kBinThreads) cnt[i] = 0;
   owners_of_items(cum, n_ranked, j0, start_rank, win, own, s_misc);
   const int r0 = (int)s_misc[8];
@@ -563,7 +623,7 @@ k_tile_scatter1(const uint32_t* __restrict__ cum, const uint32_t* __restrict__ s
     const int jl = warp * kBinSpan + k * 32 + lane;
     tile[k] = 0;
     rank[k] = 0;
-    if (jl < cntItems) item_tile(jl, j0, r0, before, win, own, order, rect, grid_w, tile[k], rank[k]);
+    if (jl < cntItems) item_region(jl, j0, r0, before, win, own, order, rect, reg_w, tile[k], rank[k]);
   }
 #pragma unroll
   for (int k = 0; k < kBinItems; ++k) {
@@ -585,16 +645,17 @@ k_tile_scatter1(const uint32_t* __restrict__ cum, const uint32_t* __restrict__ s
   for (int lp = threadIdx.x; lp < cntItems; lp += kBinThreads) {
     const uint2 pr = sbuf[lp];
     const uint32_t g = dbase[pr.y & (bins - 1)] + (uint32_t)lp;
-    if (final) sorted_idx[g] = (int32_t)order[pr.x];
+    if (final) entries[g] = region_entry(pr.x, pr.y, order, rect, reg_w);
     else pairs_out[g] = pr;
   }
 }
 
-// pass 2: stable split on tile >> shift; writes the tet ids.
+// pass 2: stable split on region >> shift; writes the sorted entries.
 __global__ void __launch_bounds__(kBinThreads, 3)
-k_tile_scatter2(const uint2* __restrict__ pairs, int64_t n, int shift, uint32_t bins,
-                const uint32_t* __restrict__ hist, const uint32_t* __restrict__ digit_total, int nblk,
-                const uint32_t* __restrict__ order, int32_t* __restrict__ sorted_idx) {
+k_region_scatter2(const uint2* __restrict__ pairs, int64_t n, int shift, uint32_t bins,
+                  const uint32_t* __restrict__ hist, const uint32_t* __restrict__ digit_total, int nblk,
+                  const uint32_t* __restrict__ order, const int4* __restrict__ rect, int reg_w,
+                  uint2* __restrict__ entries) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   uint2* sbuf = reinterpret_cast<uint2*>(smem_raw);
   uint32_t* dbase = reinterpret_cast<uint32_t*>(smem_raw + 8 * kBinTile);
@@ -633,7 +694,155 @@ k_tile_scatter2(const uint2* __restrict__ pairs, int64_t n, int shift, uint32_t 
   __syncthreads();
   for (int lp = threadIdx.x; lp < cntItems; lp += kBinThreads) {
     const uint2 p2 = sbuf[lp];
-    sorted_idx[dbase[p2.y >> shift] + (uint32_t)lp] = (int32_t)order[p2.x];
+    entries[dbase[p2.y >> shift] + (uint32_t)lp] = region_entry(p2.x, p2.y, order, rect, reg_w);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Level 2: from the region segments to the tile lists.
+// ---------------------------------------------------------------------------
+constexpr int kChunk = 256;        // entries of a region segment handled by one warp
+constexpr int kFineThreads = 256;  // 8 warps = 8 chunks per block
+constexpr int kFineWarps = kFineThreads / 32;
+
+// Single block: region_start = exclusive scan of region_count, chunk_base = exclusive scan of
+// ceil(region_count / kChunk) (both with a closing total at index n_regions), and the region of
+// every chunk.
+__global__ void __launch_bounds__(1024)
+k_region_layout(const uint32_t* __restrict__ region_count, uint32_t n_regions, uint32_t* __restrict__ region_start,
+                uint32_t* __restrict__ chunk_base, uint32_t* __restrict__ chunk_region) {
+  __shared__ uint32_t sm[1024 / 32 + 1];
+  uint32_t carry_e = 0, carry_c = 0;
+  for (uint32_t base = 0; base < n_regions; base += 1024) {
+    const uint32_t r = base + threadIdx.x;
+    const uint32_t c = r < n_regions ? region_count[r] : 0u;
+    const uint32_t q = (c + kChunk - 1) / kChunk;
+    uint32_t total;
+    const uint32_t ex_e = block_exclusive_scan<1024>(c, &total, sm);
+    if (r < n_regions) region_start[r] = carry_e + ex_e;
+    carry_e += total;
+    const uint32_t ex_c = block_exclusive_scan<1024>(q, &total, sm);
+    if (r < n_regions) {
+      chunk_base[r] = carry_c + ex_c;
+      for (uint32_t k = 0; k < q; ++k) chunk_region[carry_c + ex_c + k] = r;
+    }
+    carry_c += total;
+  }
+  if (threadIdx.x == 0) {
+    region_start[n_regions] = carry_e;
+    chunk_base[n_regions] = carry_c;
+  }
+}
+
+// 32 x 32 bit transpose across the warp: lane l ends with bit i = bit l of lane i's word.
+__device__ __forceinline__ uint32_t warp_bit_transpose(uint32_t a) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int j = 16; j >= 1; j >>= 1) {
+    const uint32_t m = j == 16 ? 0x0000FFFFu : j == 8 ? 0x00FF00FFu : j == 4 ? 0x0F0F0F0Fu : j == 2 ? 0x33333333u
+                                                                                                    : 0x55555555u;
+    const uint32_t b = __shfl_xor_sync(0xffffffffu, a, j);
+    a = (lane & j) ? (((b >> j) & m) | (a & ~m)) : ((a & m) | ((b & m) << j));
+  }
+  return a;
+}
+
+struct ChunkSpan {
+  uint32_t begin, end;  // entries [begin, end) of the sorted entry array
+  uint32_t region;
+};
+__device__ __forceinline__ bool chunk_span(uint32_t chunk, const uint32_t* __restrict__ region_start,
+                                           const uint32_t* __restrict__ chunk_base,
+                                           const uint32_t* __restrict__ chunk_region, uint32_t n_regions,
+                                           ChunkSpan* sp) {
+  if (chunk >= chunk_base[n_regions]) return false;
+  const uint32_t r = chunk_region[chunk];
+  const uint32_t k = chunk - chunk_base[r];
+  sp->region = r;
+  sp->begin = region_start[r] + k * kChunk;
+  sp->end = min(sp->begin + (uint32_t)kChunk, region_start[r + 1]);
+  return true;
+}
+
+// count pass: chunk_cursor[chunk][lane] = number of the chunk's entries covering the lane's tile
+__global__ void __launch_bounds__(kFineThreads)
+k_fine_count(const uint2* __restrict__ entries, const uint32_t* __restrict__ region_start,
+             const uint32_t* __restrict__ chunk_base, const uint32_t* __restrict__ chunk_region, uint32_t n_regions,
+             uint32_t* __restrict__ chunk_cursor) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t chunk = blockIdx.x * kFineWarps + (threadIdx.x >> 5);
+  ChunkSpan sp;
+  if (!chunk_span(chunk, region_start, chunk_base, chunk_region, n_regions, &sp)) return;
+  uint32_t count = 0;
+  for (uint32_t e0 = sp.begin; e0 < sp.end; e0 += 32) {
+    const uint32_t e = e0 + lane;
+    const uint32_t mask = e < sp.end ? __ldg(&entries[e].y) : 0u;
+    count += __popc(warp_bit_transpose(mask));
+  }
+  chunk_cursor[(size_t)chunk * 32 + lane] = count;
+}
+
+// One warp per region: exclusive scan of the chunk counts along the region's chunks, starting
+// at the first list position of the lane's tile.
+__global__ void __launch_bounds__(kFineThreads)
+k_fine_cursors(const uint32_t* __restrict__ chunk_base, uint32_t n_regions, int reg_w, int grid_w, int grid_h,
+               const uint32_t* __restrict__ tile_start, uint32_t* __restrict__ chunk_cursor) {
+  const int lane = threadIdx.x & 31;
+  const uint32_t r = blockIdx.x * kFineWarps + (threadIdx.x >> 5);
+  if (r >= n_regions) return;
+  const int gy = (int)(r / (uint32_t)reg_w), gx = (int)(r - (uint32_t)gy * (uint32_t)reg_w);
+  const int tx = gx * kRegW + (lane & (kRegW - 1)), ty = gy * kRegH + (lane >> kRegShiftX);
+  uint32_t pos = (tx < grid_w && ty < grid_h) ? tile_start[(int64_t)ty * grid_w + tx] : 0u;
+  const uint32_t q1 = chunk_base[r + 1];
+  for (uint32_t q = chunk_base[r]; q < q1; ++q) {
+    const uint32_t c = chunk_cursor[(size_t)q * 32 + lane];
+    chunk_cursor[(size_t)q * 32 + lane] = pos;
+    pos += c;
+  }
+}
+
+// write pass: every lane appends the tet ids of the entries covering its tile to the tile's list
+__global__ void __launch_bounds__(kFineThreads)
+k_fine_write(const uint2* __restrict__ entries, const uint32_t* __restrict__ region_start,
+             const uint32_t* __restrict__ chunk_base, const uint32_t* __restrict__ chunk_region, uint32_t n_regions,
+             const uint32_t* __restrict__ chunk_cursor, uint32_t n_keys, int32_t* __restrict__ sorted_idx) {
+  __shared__ uint32_t s_tet[kFineWarps][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t chunk = blockIdx.x * kFineWarps + warp;
+  ChunkSpan sp;
+  if (!chunk_span(chunk, region_start, chunk_base, chunk_region, n_regions, &sp)) return;
+  uint32_t c = chunk_cursor[(size_t)chunk * 32 + lane];
+  const uint32_t aligned = (c + 3u) & ~3u;  // ids before this position go out one by one
+  uint32_t b0 = 0, b1 = 0, b2 = 0, b3 = 0;  // the last ids appended at or after `aligned`
+  for (uint32_t e0 = sp.begin; e0 < sp.end; e0 += 32) {
+    const uint32_t e = e0 + lane;
+    uint2 en = make_uint2(0u, 0u);
+    if (e < sp.end) en = __ldg(entries + e);
+    s_tet[warp][lane] = en.x;
+    uint32_t col = warp_bit_transpose(en.y);  // bit i: entry e0 + i covers this lane's tile
+    __syncwarp();
+    while (col) {
+      const int i = __ffs(col) - 1;
+      col &= col - 1;
+      const uint32_t tet = s_tet[warp][i];
+      // c < n_keys always holds when the masks agree with the tile populations; the test keeps a
+      // disagreement from writing outside the list array
+      if (c < aligned) {
+        if (c < n_keys) sorted_idx[c] = (int32_t)tet;
+      } else {
+        b0 = b1, b1 = b2, b2 = b3, b3 = tet;
+        if ((c & 3u) == 3u && c < n_keys)
+          *reinterpret_cast<uint4*>(sorted_idx + (c - 3u)) = make_uint4(b0, b1, b2, b3);
+      }
+      ++c;
+    }
+    __syncwarp();
+  }
+  if (c > aligned && c <= n_keys) {
+    const uint32_t left = (c - aligned) & 3u;
+    if (left >= 3) sorted_idx[c - 3] = (int32_t)b1;
+    if (left >= 2) sorted_idx[c - 2] = (int32_t)b2;
+    if (left >= 1) sorted_idx[c - 1] = (int32_t)b3;
   }
 }
 
@@ -702,23 +911,23 @@ int rm_launch_bin_prepare(int64_t T, const RmCamera* cam, void* ws, size_t ws_by
   return RM_OK;
 }
 
-static int launch_scan(const uint32_t* in, const uint32_t* gather, int64_t n, uint32_t* bsum, uint32_t* out,
-                       int inclusive, unsigned long long* total64, cudaStream_t st) {
+static int launch_scan(const uint32_t* in, const uint32_t* gather, const int4* rect, int64_t n, uint32_t* bsum,
+                       uint32_t* out, int inclusive, unsigned long long* total64, cudaStream_t st) {
   if (n <= 0) {
     if (total64) RM_CUDA_CHECK(cudaMemsetAsync(total64, 0, 8, st));
     return RM_OK;
   }
   int64_t nb = (n + rm::kScanTile - 1) / rm::kScanTile;
-  rm::k_scan_block_sums<<<(unsigned)nb, rm::kScanThreads, 0, st>>>(in, gather, n, bsum);
+  rm::k_scan_block_sums<<<(unsigned)nb, rm::kScanThreads, 0, st>>>(in, gather, rect, n, bsum);
   rm::k_scan_sums<<<1, 1024, 0, st>>>(bsum, nb, total64);
-  rm::k_scan_apply<<<(unsigned)nb, rm::kScanThreads, 0, st>>>(in, gather, n, bsum, out, inclusive);
+  rm::k_scan_apply<<<(unsigned)nb, rm::kScanThreads, 0, st>>>(in, gather, rect, n, bsum, out, inclusive);
   RM_CUDA_CHECK(cudaPeekAtLastError());
   return RM_OK;
 }
 
 // After k_project: rank the tets, build tile_ranges, the rank-ordered inclusive
 // scan of tiles_touched, and the info block.
-int rm_launch_bin_finish(int64_t T, const RmCamera* cam, const int32_t* tiles_touched, int32_t* tile_ranges,
+int rm_launch_bin_finish(int64_t T, const RmCamera* cam, const int32_t* rect, int32_t* tile_ranges,
                          RmBinInfo* info, void* ws, cudaStream_t st) {
   const int gh = cam->grid_height, gw = cam->grid_width;
   const int64_t G = (int64_t)gh * gw;
@@ -755,16 +964,17 @@ int rm_launch_bin_finish(int64_t T, const RmCamera* cam, const int32_t* tiles_to
     rm::k_diff_prefix_x<<<(gh + 1 + rows_per_block - 1) / rows_per_block, 32 * rows_per_block, 0, st>>>(diff, gh, gw);
     rm::k_diff_prefix_y<<<(gw + rows_per_block - 1) / rows_per_block, 32 * rows_per_block, 0, st>>>(diff, gh, gw,
                                                                                                   tcount);
-    int rc = launch_scan(tcount, nullptr, G, bsum, tstart, 0, nullptr, st);
+    int rc = launch_scan(tcount, nullptr, nullptr, G, bsum, tstart, 0, total_keys, st);
     if (rc) return rc;
     rm::k_write_ranges<<<(unsigned)((G + 255) / 256), 256, 0, st>>>(tcount, tstart, G,
                                                                     reinterpret_cast<int2*>(tile_ranges));
     RM_CUDA_CHECK(cudaPeekAtLastError());
   }
-  // 3. inclusive scan of tiles_touched in rank order (culled tets sort last with 0 tiles)
+  // 3. inclusive scan, in rank order, of the number of regions every tet touches (culled tets
+  //    have an empty rectangle and sort last)
   {
     RmProfScope prof("rank_order_scan(4 launches)", st);
-    int rc = launch_scan(reinterpret_cast<const uint32_t*>(tiles_touched), ord[0], T, bsum, cum, 1, total_keys, st);
+    int rc = launch_scan(nullptr, ord[0], reinterpret_cast<const int4*>(rect), T, bsum, cum, 1, total_keys + 1, st);
     if (rc) return rc;
     rm::k_finish_info<<<1, 1, 0, st>>>(info, total_keys);
     RM_CUDA_CHECK(cudaPeekAtLastError());
@@ -774,92 +984,135 @@ int rm_launch_bin_finish(int64_t T, const RmCamera* cam, const int32_t* tiles_to
 
 namespace {
 struct ListPlan {
-  int bits1, bits2, nblk;
-  size_t pairs, hist, dtot, starts, total;
+  int reg_w, reg_h, bits1, bits2, nblk;
+  uint32_t n_regions, n_regions_smem, max_chunks;
+  size_t pairs, entries, hist, dtot, starts, region_count, region_start, chunk_base, chunk_region, chunk_cursor,
+      total;
 };
-// split of the tile-id bits into the two digits and the scratch layout
-bool make_list_plan(int64_t n_keys, int64_t G, ListPlan* P) {
+constexpr uint32_t kMaxSmemRegions = 16384;  // 64 KB of per-block region counters
+// region grid, split of the region-id bits into the two digits, and the scratch layout
+bool make_list_plan(int64_t n_region_keys, int gh, int gw, ListPlan* P) {
+  P->reg_w = (gw + rm::kRegW - 1) / rm::kRegW;
+  P->reg_h = (gh + rm::kRegH - 1) / rm::kRegH;
+  const int64_t R = (int64_t)P->reg_w * P->reg_h;
   int bits = 1;
-  while (((int64_t)1 << bits) < G) ++bits;
-  if (bits > 22) return false;
+  while (((int64_t)1 << bits) < R) ++bits;
+  if (bits > 22 || n_region_keys > 0x7fffffffll) return false;
+  P->n_regions = (uint32_t)R;
+  P->n_regions_smem = P->n_regions <= kMaxSmemRegions ? P->n_regions : 0u;
   P->bits1 = bits <= 11 ? bits : (bits + 1) / 2;
   P->bits2 = bits - P->bits1;
-  P->nblk = (int)((n_keys + rm::kBinTile - 1) / rm::kBinTile);
+  P->nblk = (int)((n_region_keys + rm::kBinTile - 1) / rm::kBinTile);
+  P->max_chunks = (uint32_t)(n_region_keys / rm::kChunk + R + 1);
   size_t off = 0;
   auto take = [&](size_t bytes) {
     size_t o = off;
     off = align256(off + bytes);
     return o;
   };
-  P->pairs = take(P->bits2 ? 8 * (size_t)n_keys : 0);
+  P->pairs = take(P->bits2 ? 8 * (size_t)n_region_keys : 0);
+  P->entries = take(8 * (size_t)n_region_keys);
   P->hist = take(4 * ((size_t)1 << P->bits1) * (size_t)(P->nblk > 0 ? P->nblk : 1));
   P->dtot = take(4 * ((size_t)1 << P->bits1));
   P->starts = take(4 * (size_t)(P->nblk > 0 ? P->nblk : 1));
+  P->region_count = take(4 * (size_t)(R + 1));
+  P->region_start = take(4 * (size_t)(R + 1));
+  P->chunk_base = take(4 * (size_t)(R + 1));
+  P->chunk_region = take(4 * (size_t)P->max_chunks);
+  P->chunk_cursor = take(4 * 32 * (size_t)P->max_chunks);
   P->total = off;
   return true;
 }
 }  // namespace
 
-size_t rm_list_plan_bytes(int64_t n_keys, int64_t G) {
+size_t rm_list_plan_bytes(int64_t n_region_keys, int gh, int gw) {
   ListPlan P;
-  if (!make_list_plan(n_keys, G, &P)) return 0;
+  if (!make_list_plan(n_region_keys, gh, gw, &P)) return 0;
   return P.total;
 }
 
 int rm_launch_build_lists(const int32_t* rect, const int32_t* tile_ranges, int64_t T, const RmCamera* cam,
-                          int64_t n_keys, void* ws, void* scratch, size_t scratch_bytes, int32_t* sorted_idx,
-                          cudaStream_t st) {
+                          int64_t n_keys, int64_t n_region_keys, void* ws, void* scratch, size_t scratch_bytes,
+                          int32_t* sorted_idx, cudaStream_t st) {
   (void)tile_ranges;
   if (n_keys == 0) return RM_OK;
   const int gh = cam->grid_height, gw = cam->grid_width;
   const int64_t G = (int64_t)gh * gw;
   BinLayout L = make_layout(T, G, gh, gw);
   ListPlan P;
-  if (!make_list_plan(n_keys, G, &P)) return RM_ERR_INVALID_ARG;
+  if (n_region_keys < 1 || n_region_keys > n_keys || !make_list_plan(n_region_keys, gh, gw, &P))
+    return RM_ERR_INVALID_ARG;
   if (P.total > scratch_bytes || (reinterpret_cast<uintptr_t>(scratch) & 255)) return RM_ERR_WORKSPACE;
   char* b = static_cast<char*>(ws);
   const uint32_t* order = reinterpret_cast<uint32_t*>(b + L.ord_a);
   const uint32_t* cum = reinterpret_cast<uint32_t*>(b + L.cum);
+  const uint32_t* tile_start = reinterpret_cast<uint32_t*>(b + L.tile_start);
   char* sb = static_cast<char*>(scratch);
   uint2* pairs = reinterpret_cast<uint2*>(sb + P.pairs);
+  uint2* entries = reinterpret_cast<uint2*>(sb + P.entries);
   uint32_t* hist = reinterpret_cast<uint32_t*>(sb + P.hist);
   uint32_t* dtot = reinterpret_cast<uint32_t*>(sb + P.dtot);
   uint32_t* starts = reinterpret_cast<uint32_t*>(sb + P.starts);
+  uint32_t* region_count = reinterpret_cast<uint32_t*>(sb + P.region_count);
+  uint32_t* region_start = reinterpret_cast<uint32_t*>(sb + P.region_start);
+  uint32_t* chunk_base = reinterpret_cast<uint32_t*>(sb + P.chunk_base);
+  uint32_t* chunk_region = reinterpret_cast<uint32_t*>(sb + P.chunk_region);
+  uint32_t* chunk_cursor = reinterpret_cast<uint32_t*>(sb + P.chunk_cursor);
   const uint32_t bins1 = 1u << P.bits1, bins2 = 1u << P.bits2;
   const int4* rect4 = reinterpret_cast<const int4*>(rect);
   const size_t gen = 4 * (rm::kBinTile + 4 + 16) + 2 * rm::kBinTile;
-  const size_t smem_h1 = gen + 4 * bins1;
+  const size_t smem_h1 = gen + 4 * bins1 + 4 * (size_t)P.n_regions_smem;
   const size_t smem_s1 = 8 * rm::kBinTile + 4 * bins1 * (2 + rm::kBinWarps) + 64;
   const size_t smem_s2 = 8 * rm::kBinTile + 4 * bins2 * (2 + rm::kBinWarps) + 64;
-  RM_CUDA_CHECK(cudaFuncSetAttribute(rm::k_tile_hist1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_h1));
-  RM_CUDA_CHECK(cudaFuncSetAttribute(rm::k_tile_scatter1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_s1));
-  RM_CUDA_CHECK(cudaFuncSetAttribute(rm::k_tile_scatter2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_s2));
+  RM_CUDA_CHECK(cudaFuncSetAttribute(rm::k_region_hist1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_h1));
+  RM_CUDA_CHECK(
+      cudaFuncSetAttribute(rm::k_region_scatter1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_s1));
+  RM_CUDA_CHECK(
+      cudaFuncSetAttribute(rm::k_region_scatter2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_s2));
+  RM_CUDA_CHECK(cudaMemsetAsync(region_count, 0, 4 * (size_t)(P.n_regions + 1), st));
   {
-    RmProfScope prof("k_block_start_ranks+k_tile_hist1", st);
+    RmProfScope prof("k_block_start_ranks+k_region_hist1", st);
     rm::k_block_start_ranks<<<(P.nblk + 255) / 256, 256, 0, st>>>(cum, (int)T, P.nblk, starts);
-    rm::k_tile_hist1<<<P.nblk, rm::kBinThreads, smem_h1, st>>>(cum, starts, order, (int)T, rect4, gw, n_keys, bins1,
-                                                              hist, P.nblk);
+    rm::k_region_hist1<<<P.nblk, rm::kBinThreads, smem_h1, st>>>(cum, starts, order, (int)T, rect4, P.reg_w,
+                                                                n_region_keys, bins1, hist, P.nblk,
+                                                                P.n_regions_smem, region_count);
   }
   {
-    RmProfScope prof("k_radix_rowscan+k_tile_scatter1", st);
+    RmProfScope prof("k_radix_rowscan+k_region_scatter1", st);
     rm::k_radix_rowscan<<<bins1, 1024, 0, st>>>(hist, P.nblk, dtot);
-    rm::k_tile_scatter1<<<P.nblk, rm::kBinThreads, smem_s1, st>>>(cum, starts, order, (int)T, rect4, gw, n_keys,
-                                                                 bins1, hist, dtot, P.nblk, P.bits2 == 0, pairs,
-                                                                 sorted_idx);
+    rm::k_region_scatter1<<<P.nblk, rm::kBinThreads, smem_s1, st>>>(cum, starts, order, (int)T, rect4, P.reg_w,
+                                                                   n_region_keys, bins1, hist, dtot, P.nblk,
+                                                                   P.bits2 == 0, pairs, entries);
   }
   RM_CUDA_CHECK(cudaPeekAtLastError());
   if (P.bits2) {
     {
-      RmProfScope prof("k_tile_hist2", st);
-      rm::k_tile_hist2<<<P.nblk, rm::kBinThreads, 4 * bins2, st>>>(pairs, n_keys, P.bits1, bins2, hist, P.nblk);
+      RmProfScope prof("k_region_hist2", st);
+      rm::k_region_hist2<<<P.nblk, rm::kBinThreads, 4 * bins2, st>>>(pairs, n_region_keys, P.bits1, bins2, hist,
+                                                                    P.nblk);
     }
     {
-      RmProfScope prof("k_radix_rowscan+k_tile_scatter2", st);
+      RmProfScope prof("k_radix_rowscan+k_region_scatter2", st);
       rm::k_radix_rowscan<<<bins2, 1024, 0, st>>>(hist, P.nblk, dtot);
-      rm::k_tile_scatter2<<<P.nblk, rm::kBinThreads, smem_s2, st>>>(pairs, n_keys, P.bits1, bins2, hist, dtot,
-                                                                   P.nblk, order, sorted_idx);
+      rm::k_region_scatter2<<<P.nblk, rm::kBinThreads, smem_s2, st>>>(pairs, n_region_keys, P.bits1, bins2, hist,
+                                                                     dtot, P.nblk, order, rect4, P.reg_w, entries);
     }
     RM_CUDA_CHECK(cudaPeekAtLastError());
   }
+  const unsigned chunk_blocks = (P.max_chunks + rm::kFineWarps - 1) / rm::kFineWarps;
+  {
+    RmProfScope prof("k_region_layout+k_fine_count+k_fine_cursors", st);
+    rm::k_region_layout<<<1, 1024, 0, st>>>(region_count, P.n_regions, region_start, chunk_base, chunk_region);
+    rm::k_fine_count<<<chunk_blocks, rm::kFineThreads, 0, st>>>(entries, region_start, chunk_base, chunk_region,
+                                                               P.n_regions, chunk_cursor);
+    rm::k_fine_cursors<<<(P.n_regions + rm::kFineWarps - 1) / rm::kFineWarps, rm::kFineThreads, 0, st>>>(
+        chunk_base, P.n_regions, P.reg_w, gw, gh, tile_start, chunk_cursor);
+  }
+  {
+    RmProfScope prof("k_fine_write", st);
+    rm::k_fine_write<<<chunk_blocks, rm::kFineThreads, 0, st>>>(entries, region_start, chunk_base, chunk_region,
+                                                               P.n_regions, chunk_cursor, (uint32_t)n_keys, sorted_idx);
+  }
+  RM_CUDA_CHECK(cudaPeekAtLastError());
   return RM_OK;
 }

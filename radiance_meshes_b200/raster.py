@@ -11,7 +11,7 @@ from . import _lib
 
 # launches of this library's kernels (memsets not counted) per call, for bench accounting
 LAUNCHES_PROJECT_AND_BIN = 1 + 12 + 2 + 3 + 1 + 3 + 1
-LAUNCHES_BUILD_LISTS = 7
+LAUNCHES_BUILD_LISTS = 11
 LAUNCHES_FORWARD = 2
 LAUNCHES_BACKWARD = 2
 
@@ -83,7 +83,7 @@ def project_and_bin(indices, vertices, tcam, tile_rows=None):
         vs_tetra = torch.empty((T, 3), dtype=torch.float32, device=dev)
         circumcenter = torch.empty((T, 3), dtype=torch.float32, device=dev)
         tile_ranges = torch.empty((G, 2), dtype=torch.int32, device=dev)
-        info = torch.empty((2,), dtype=torch.int64, device=dev)
+        info = torch.empty((3,), dtype=torch.int64, device=dev)
         ws_bytes = lib.rm_bin_workspace_bytes(T, G)
         ws = torch.empty((ws_bytes,), dtype=torch.uint8, device=dev)
         _lib.check(lib.rm_project_and_bin(_ptr(indices), T, _ptr(verts), V, cam.ref, _ptr(tiles_touched), _ptr(rect),
@@ -97,7 +97,8 @@ def read_info(ctx):
     """The one host synchronisation of the binning stage: N, visible count, status."""
     host = ctx["info"].cpu()
     n_keys = int(host[0].item())
-    second = int(host[1].item())
+    ctx["n_region_keys"] = int(host[1].item())
+    second = int(host[2].item())
     n_visible = second & 0xFFFFFFFF
     status = (second >> 32) & 0xFFFFFFFF
     if status & _lib.RM_STATUS_NAN_VERTEX:
@@ -114,12 +115,16 @@ def build_tile_lists(ctx, n_keys):
     with torch.cuda.device(dev):
         sorted_idx = torch.empty((n_keys,), dtype=torch.int32, device=dev)
         if n_keys > 0:
-            nbytes = lib.rm_list_scratch_bytes(n_keys, ctx["G"])
+            if "n_region_keys" not in ctx:
+                raise RuntimeError("rm_b200: call read_info(ctx) before build_tile_lists")
+            n_region_keys = ctx["n_region_keys"]
+            gh, gw = ctx["cam"].c.grid_height, ctx["cam"].c.grid_width
+            nbytes = lib.rm_list_scratch_bytes(n_region_keys, gh, gw)
             if nbytes == 0:
-                raise RuntimeError("rm_b200: tile grids above 2^22 tiles are not supported")
+                raise RuntimeError("rm_b200: tile grids above 2^22 regions of 8 x 4 tiles are not supported")
             scratch = torch.empty((nbytes,), dtype=torch.uint8, device=dev)
             _lib.check(lib.rm_build_tile_lists(_ptr(ctx["rect"]), _ptr(ctx["tile_ranges"]), ctx["T"], ctx["cam"].ref,
-                                               n_keys, _ptr(ctx["workspace"]), _ptr(scratch), nbytes,
+                                               n_keys, n_region_keys, _ptr(ctx["workspace"]), _ptr(scratch), nbytes,
                                                _ptr(sorted_idx), _stream(dev)))
     return sorted_idx
 

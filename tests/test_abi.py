@@ -27,7 +27,7 @@ def test_header_symbols_exported(cuda_lib):
 def test_struct_layout_matches_header():
     import ctypes as C
     from radiance_meshes_b200 import _lib
-    assert C.sizeof(_lib.RmBinInfo) == 16
+    assert C.sizeof(_lib.RmBinInfo) == 24
     assert C.sizeof(_lib.RmCamera) == 4 * 8 + 12 * 4
     assert _lib.RM_RECORD_FLOATS == 36 and _lib.RM_GRAD_RECORD_FLOATS == 24
 
