@@ -102,7 +102,7 @@ size_t rm_list_scratch_bytes(int64_t n_region_keys, int grid_height, int grid_wi
  * (sort_by_keys/sort_by_keys.cu:9-53): the result equals the value array of a
  * stable ascending sort of the keys (tile << 32 | sortable(depth)).
  *   n_keys and n_region_keys must be RmBinInfo.n_keys and .n_region_keys read back
- *   by the caller; sorted_tetra_idx[N] i32 out, 16-byte aligned; scratch:
+ *   by the caller; sorted_tetra_idx[N] i32 out; scratch:
  *   rm_list_scratch_bytes(n_region_keys, grid_height, grid_width) bytes, 256-byte
  *   aligned, caller-provided.
  */

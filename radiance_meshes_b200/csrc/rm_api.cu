@@ -197,7 +197,7 @@ int rm_build_tile_lists(const int32_t* rect_tile_space, const int32_t* tile_rang
   if (n_keys > 0x7fffffffll) return RM_ERR_TOO_MANY_KEYS;
   if (n_keys == 0) return RM_OK;
   if (!rect_tile_space || !scratch || !sorted_tetra_idx) return RM_ERR_INVALID_ARG;
-  if (!aligned16(rect_tile_space) || !aligned16(sorted_tetra_idx)) return RM_ERR_WORKSPACE;
+  if (!aligned16(rect_tile_space)) return RM_ERR_WORKSPACE;
   rc = rm_bind_device(workspace);
   if (rc) return rc;
   return rm_launch_build_lists(rect_tile_space, tile_ranges, n_tets, cam, n_keys, n_region_keys, workspace, scratch,

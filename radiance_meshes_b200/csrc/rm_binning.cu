@@ -336,10 +336,10 @@ __global__ void k_finish_info(RmBinInfo* info, const unsigned long long* total_k
 // subsequence of entries whose mask has bit l: the count pass adds up the bits
 // per chunk and lane (a 32 x 32 bit transpose and a popcount per 32 entries), a
 // per-region scan over the chunks turns the counts into write cursors starting
-// at the tile's range, and the write pass walks the chunk again, every lane
-// appending the tet ids of its set bits to its own list through a four-entry
-// register buffer (16-byte stores).  Order inside a tile is the order of the
-// region's segment: rank order.
+// at the tile's range, and the write pass walks the chunk again: per round of 32
+// entries and per tile, the lanes whose entry covers the tile (one ballot) store
+// their tet ids behind the tile's cursor as one contiguous run.  Order inside a
+// tile is the order of the region's segment: rank order.
 // ---------------------------------------------------------------------------
 constexpr int kBinThreads = 256;
 constexpr int kBinItems = 16;
@@ -794,55 +794,52 @@ k_fine_cursors(const uint32_t* __restrict__ chunk_base, uint32_t n_regions, int 
   const int tx = gx * kRegW + (lane & (kRegW - 1)), ty = gy * kRegH + (lane >> kRegShiftX);
   uint32_t pos = (tx < grid_w && ty < grid_h) ? tile_start[(int64_t)ty * grid_w + tx] : 0u;
   const uint32_t q1 = chunk_base[r + 1];
-  for (uint32_t q = chunk_base[r]; q < q1; ++q) {
-    const uint32_t c = chunk_cursor[(size_t)q * 32 + lane];
-    chunk_cursor[(size_t)q * 32 + lane] = pos;
-    pos += c;
+  constexpr int kBatch = 8;  // independent loads in flight per step of the serial scan
+  for (uint32_t q = chunk_base[r]; q < q1; q += kBatch) {
+    uint32_t c[kBatch];
+#pragma unroll
+    for (int k = 0; k < kBatch; ++k) c[k] = q + k < q1 ? chunk_cursor[(size_t)(q + k) * 32 + lane] : 0u;
+#pragma unroll
+    for (int k = 0; k < kBatch; ++k) {
+      if (q + k < q1) chunk_cursor[(size_t)(q + k) * 32 + lane] = pos;
+      pos += c[k];
+    }
   }
 }
 
-// write pass: every lane appends the tet ids of the entries covering its tile to the tile's list
+// write pass: the warp appends, tile by tile, the tet ids of the round's 32 entries that cover
+// the tile.  For tile l the covering entries are the lanes whose mask has bit l (one ballot); they
+// store their tet id at the tile's cursor plus their position among the covering lanes, so the ids
+// of one tile leave as one contiguous store.
 __global__ void __launch_bounds__(kFineThreads)
 k_fine_write(const uint2* __restrict__ entries, const uint32_t* __restrict__ region_start,
              const uint32_t* __restrict__ chunk_base, const uint32_t* __restrict__ chunk_region, uint32_t n_regions,
              const uint32_t* __restrict__ chunk_cursor, uint32_t n_keys, int32_t* __restrict__ sorted_idx) {
-  __shared__ uint32_t s_tet[kFineWarps][32];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const uint32_t chunk = blockIdx.x * kFineWarps + warp;
+  const int lane = threadIdx.x & 31;
+  const uint32_t lt = (1u << lane) - 1u;
+  const uint32_t chunk = blockIdx.x * kFineWarps + (threadIdx.x >> 5);
   ChunkSpan sp;
   if (!chunk_span(chunk, region_start, chunk_base, chunk_region, n_regions, &sp)) return;
-  uint32_t c = chunk_cursor[(size_t)chunk * 32 + lane];
-  const uint32_t aligned = (c + 3u) & ~3u;  // ids before this position go out one by one
-  uint32_t b0 = 0, b1 = 0, b2 = 0, b3 = 0;  // the last ids appended at or after `aligned`
+  uint32_t c = chunk_cursor[(size_t)chunk * 32 + lane];  // next list position of this lane's tile
+  uint2 nxt = make_uint2(0u, 0u);
+  if (sp.begin + lane < sp.end) nxt = __ldg(entries + sp.begin + lane);
   for (uint32_t e0 = sp.begin; e0 < sp.end; e0 += 32) {
-    const uint32_t e = e0 + lane;
-    uint2 en = make_uint2(0u, 0u);
-    if (e < sp.end) en = __ldg(entries + e);
-    s_tet[warp][lane] = en.x;
-    uint32_t col = warp_bit_transpose(en.y);  // bit i: entry e0 + i covers this lane's tile
-    __syncwarp();
-    while (col) {
-      const int i = __ffs(col) - 1;
-      col &= col - 1;
-      const uint32_t tet = s_tet[warp][i];
-      // c < n_keys always holds when the masks agree with the tile populations; the test keeps a
+    const uint2 en = nxt;
+    const uint32_t e_next = e0 + 32 + lane;
+    nxt = make_uint2(0u, 0u);
+    if (e_next < sp.end) nxt = __ldg(entries + e_next);  // in flight while this round is written
+    uint32_t appended = 0;
+#pragma unroll
+    for (int l = 0; l < 32; ++l) {
+      const bool covers = (en.y >> l) & 1u;
+      const uint32_t col = __ballot_sync(0xffffffffu, covers);
+      const uint32_t pos = __shfl_sync(0xffffffffu, c, l) + __popc(col & lt);
+      // pos < n_keys always holds when the masks agree with the tile populations; the test keeps a
       // disagreement from writing outside the list array
-      if (c < aligned) {
-        if (c < n_keys) sorted_idx[c] = (int32_t)tet;
-      } else {
-        b0 = b1, b1 = b2, b2 = b3, b3 = tet;
-        if ((c & 3u) == 3u && c < n_keys)
-          *reinterpret_cast<uint4*>(sorted_idx + (c - 3u)) = make_uint4(b0, b1, b2, b3);
-      }
-      ++c;
+      if (covers && pos < n_keys) sorted_idx[pos] = (int32_t)en.x;
+      if (lane == l) appended = __popc(col);
     }
-    __syncwarp();
-  }
-  if (c > aligned && c <= n_keys) {
-    const uint32_t left = (c - aligned) & 3u;
-    if (left >= 3) sorted_idx[c - 3] = (int32_t)b1;
-    if (left >= 2) sorted_idx[c - 2] = (int32_t)b2;
-    if (left >= 1) sorted_idx[c - 1] = (int32_t)b3;
+    c += appended;
   }
 }
 
@@ -1101,10 +1098,16 @@ int rm_launch_build_lists(const int32_t* rect, const int32_t* tile_ranges, int64
   }
   const unsigned chunk_blocks = (P.max_chunks + rm::kFineWarps - 1) / rm::kFineWarps;
   {
-    RmProfScope prof("k_region_layout+k_fine_count+k_fine_cursors", st);
+    RmProfScope prof("k_region_layout", st);
     rm::k_region_layout<<<1, 1024, 0, st>>>(region_count, P.n_regions, region_start, chunk_base, chunk_region);
+  }
+  {
+    RmProfScope prof("k_fine_count", st);
     rm::k_fine_count<<<chunk_blocks, rm::kFineThreads, 0, st>>>(entries, region_start, chunk_base, chunk_region,
                                                                P.n_regions, chunk_cursor);
+  }
+  {
+    RmProfScope prof("k_fine_cursors", st);
     rm::k_fine_cursors<<<(P.n_regions + rm::kFineWarps - 1) / rm::kFineWarps, rm::kFineThreads, 0, st>>>(
         chunk_base, P.n_regions, P.reg_w, gw, gh, tile_start, chunk_cursor);
   }
