@@ -341,3 +341,68 @@ def test_host_frame_pipeline_matches_direct_path():
     for got, want in ((out["vg"], v.grad.cpu()), (out["cg"], c.grad.cpu())):   # float atomics: order varies
         assert torch.isfinite(got).all()
         assert float((got - want).norm() / want.norm().clamp_min(1e-20)) < 1e-5
+
+
+@pytest.mark.parametrize("H,W,tile,npts", [(1080, 1920, 4, 30_000),     # 4080 regions: two-pass region sort
+                                           (2160, 3840, 2, 4_000),      # 64800 regions: above the shared-memory table
+                                           (40, 2056, 4, 3_000)])       # one region row, ragged right edge
+def test_large_grid_tile_lists_bit_exact(oracle, cuda_lib, H, W, tile, npts):
+    """Tile lists on grids large enough for every region-sort configuration, against the oracle's
+    stable sort of (tile, depth) keys (projection + lists only: no pixels are rendered)."""
+    from delaunay_rasterization.internal.render_grid import RenderGrid
+    from delaunay_rasterization.internal.tile_shader_slang import vertex_and_tile_shader
+    from radiance_meshes_b200.render import tcam_to_device
+    pts = scenes.points_gaussians(npts, seed=11)
+    tets = scenes.delaunay(pts)
+    tcam = scenes.make_tcam(scenes.look_at((0.2, 0.1, 2.6)), H, W, 60.0, tile=tile, min_t=0.1)
+    pr = oracle.project(tets, pts, tcam)
+    ref_idx, ref_ranges = oracle.build_lists(pr["tiles_touched"], pr["rect"], pr["vs_tetra"],
+                                             tcam["grid_height"], tcam["grid_width"])
+    dev = torch.device("cuda:0")
+    grid = RenderGrid(H, W, tile_height=tile, tile_width=tile)
+    idx, ranges, vs, cc, mask, rect = vertex_and_tile_shader(
+        torch.tensor(tets, device=dev, dtype=torch.int32), torch.tensor(pts, device=dev), tcam_to_device(tcam, dev),
+        grid)
+    np.testing.assert_array_equal(rect.cpu().numpy(), pr["rect"])
+    np.testing.assert_array_equal(ranges.cpu().numpy(), ref_ranges)
+    np.testing.assert_array_equal(idx.cpu().numpy(), ref_idx)
+    assert len(ref_idx) > 10_000
+
+
+def test_full_size_lists_properties(cuda_lib):
+    """At the benchmark's size (1M points would take a minute to triangulate: 200k here, same 1080p grid)
+    the lists are checked through properties: every tile's segment is ascending in (depth bits, tet id),
+    holds exactly the tets whose rectangle covers the tile, and the segments tile the array."""
+    from delaunay_rasterization.internal.render_grid import RenderGrid
+    from delaunay_rasterization.internal.tile_shader_slang import vertex_and_tile_shader
+    from radiance_meshes_b200.render import tcam_to_device
+    pts = scenes.points_gaussians(200_000, seed=5)
+    tets = scenes.delaunay(pts)
+    H, W, tile = 1080, 1920, 4
+    tcam = scenes.make_tcam(scenes.look_at((0.0, 0.4, 2.8)), H, W, 60.0, tile=tile, min_t=0.1)
+    dev = torch.device("cuda:0")
+    grid = RenderGrid(H, W, tile_height=tile, tile_width=tile)
+    idx, ranges, vs, cc, mask, rect = vertex_and_tile_shader(
+        torch.tensor(tets, device=dev, dtype=torch.int32), torch.tensor(pts, device=dev), tcam_to_device(tcam, dev),
+        grid)
+    N = idx.shape[0]
+    gw = grid.grid_width
+    lens = (ranges[:, 1] - ranges[:, 0]).long()
+    assert int(lens.sum()) == N and N > 5_000_000
+    nonempty = lens > 0
+    starts = ranges[:, 0].long()[nonempty]
+    assert torch.equal(starts, (torch.cumsum(lens[nonempty], 0) - lens[nonempty]))        # segments tile the array
+    tile_of = torch.repeat_interleave(torch.arange(ranges.shape[0], device=dev), lens)   # tile of every entry
+    t = idx.long()
+    r = rect[t].long()
+    tx, ty = tile_of % gw, tile_of // gw
+    assert bool(((tx >= r[:, 0]) & (tx < r[:, 2]) & (ty >= r[:, 1]) & (ty < r[:, 3])).all())   # only covering tets
+    area = ((rect[:, 2] - rect[:, 0]) * (rect[:, 3] - rect[:, 1])).long()
+    assert int(area[mask].sum()) == N                                                          # and all of them
+    # ascending (sortable depth bits, tet id) inside every tile
+    bits = vs[:, 2].contiguous().view(torch.int32).long() & 0xFFFFFFFF
+    key = torch.where(bits >> 31 == 1, (~bits) & 0xFFFFFFFF, bits | 0x80000000)
+    k = key[t] * (1 << 23) + t                      # 32 key bits above 23 id bits (ids < 2^23 here)
+    assert tets.shape[0] < (1 << 23)
+    same_tile = tile_of[1:] == tile_of[:-1]
+    assert bool((k[1:][same_tile] > k[:-1][same_tile]).all())
