@@ -181,15 +181,22 @@ k_radix_rowscan(uint32_t* __restrict__ hist, int nblk, uint32_t* __restrict__ di
   if (threadIdx.x == 0) digit_total[blockIdx.x] = carry;
 }
 
-__global__ void __launch_bounds__(kSortThreads)
+__device__ __forceinline__ void local_layout(uint32_t bins, uint32_t* cnt, uint32_t* dbase, uint32_t* lstart,
+                                             uint32_t* s_scan);
+
+// Stable scatter of one pass.  The block's pairs are first reordered by digit in shared
+// memory, so that the global stores of one digit's run are contiguous.
+__global__ void __launch_bounds__(kSortThreads, 3)
 k_radix_scatter(const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in, int64_t n, int shift,
                 const uint32_t* __restrict__ hist, const uint32_t* __restrict__ digit_total, int nblk,
                 uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out) {
-  __shared__ uint32_t cnt[kSortWarps][kRadix];  // per-warp digit counts -> offsets
+  __shared__ uint2 sbuf[kSortTile];
+  __shared__ uint32_t cnt[kSortWarps * kRadix];  // per-warp digit counts -> offsets
   __shared__ uint32_t dbase[kRadix];
+  __shared__ uint32_t lstart[kRadix];
   __shared__ uint32_t sm[kSortThreads / 32 + 1];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int i = threadIdx.x; i < kSortWarps * kRadix; i += kSortThreads) (&cnt[0][0])[i] = 0;
+  for (int i = threadIdx.x; i < kSortWarps * kRadix; i += kSortThreads) cnt[i] = 0;
   // global base of each digit = exclusive scan of digit totals (256 values, one per thread)
   {
     uint32_t t = digit_total[threadIdx.x];
@@ -199,7 +206,9 @@ k_radix_scatter(const uint32_t* __restrict__ keys_in, const uint32_t* __restrict
   }
   __syncthreads();
   // warp w owns keys [base + w*kWarpSpan, +kWarpSpan) in index order (stability)
-  int64_t wbase = (int64_t)blockIdx.x * kSortTile + (int64_t)warp * kWarpSpan;
+  const int64_t bbase = (int64_t)blockIdx.x * kSortTile;
+  const int64_t wbase = bbase + (int64_t)warp * kWarpSpan;
+  uint32_t* wc = cnt + warp * kRadix;
   uint32_t key[kSortItems], val[kSortItems], rnk[kSortItems];
   // loads first (in flight together); the warp barriers of the ranking rounds would
   // otherwise serialise them
@@ -223,33 +232,28 @@ k_radix_scatter(const uint32_t* __restrict__ keys_in, const uint32_t* __restrict
     }
     uint32_t before = __popc(peers & ((1u << lane) - 1u));
     uint32_t prev = 0;
-    if (valid) prev = cnt[warp][d];
+    if (valid) prev = wc[d];
     __syncwarp();
-    if (valid && before == 0) cnt[warp][d] = prev + __popc(peers);
+    if (valid && before == 0) wc[d] = prev + __popc(peers);
     __syncwarp();
     rnk[k] = prev + before;
   }
   __syncthreads();
-  // per digit: exclusive scan over warps, plus the global base
-  {
-    uint32_t run = dbase[threadIdx.x];
+  local_layout(kRadix, cnt, dbase, lstart, sm);
 #pragma unroll
-    for (int w = 0; w < kSortWarps; ++w) {
-      uint32_t c = cnt[w][threadIdx.x];
-      cnt[w][threadIdx.x] = run;
-      run += c;
+  for (int k = 0; k < kSortItems; ++k) {
+    if (wbase + k * 32 + lane < n) {
+      const uint32_t d = (key[k] >> shift) & (kRadix - 1);
+      sbuf[lstart[d] + wc[d] + rnk[k]] = make_uint2(key[k], val[k]);
     }
   }
   __syncthreads();
-#pragma unroll
-  for (int k = 0; k < kSortItems; ++k) {
-    int64_t i = wbase + k * 32 + lane;
-    if (i < n) {
-      uint32_t d = (key[k] >> shift) & (kRadix - 1);
-      uint32_t pos = cnt[warp][d] + rnk[k];
-      keys_out[pos] = key[k];
-      vals_out[pos] = val[k];
-    }
+  const int n_block = (int)min((int64_t)kSortTile, n - bbase);
+  for (int lp = threadIdx.x; lp < n_block; lp += kSortThreads) {
+    const uint2 pr = sbuf[lp];
+    const uint32_t g = dbase[(pr.x >> shift) & (kRadix - 1)] + (uint32_t)lp;
+    keys_out[g] = pr.x;
+    vals_out[g] = pr.y;
   }
 }
 
@@ -345,6 +349,7 @@ constexpr int kBinThreads = 256;
 constexpr int kBinItems = 16;
 constexpr int kBinTile = kBinThreads * kBinItems;  // items per block
 constexpr int kBinWarps = kBinThreads / 32;
+static_assert(kBinThreads == kSortThreads, "local_layout is shared by the rank sort and the region sort");
 constexpr int kBinSpan = 32 * kBinItems;  // consecutive items owned by one warp
 
 template <int THREADS>
