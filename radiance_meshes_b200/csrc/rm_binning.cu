@@ -82,14 +82,19 @@ __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* t
 
 __global__ void __launch_bounds__(kScanThreads)
 k_scan_block_sums(const uint32_t* __restrict__ in, const uint32_t* __restrict__ gather,
-                  const int4* __restrict__ rect, int64_t n, uint32_t* __restrict__ bsum) {
+                  const int4* __restrict__ rect, int64_t n, uint32_t* __restrict__ bsum,
+                  uint32_t* __restrict__ values_out) {
   __shared__ uint32_t sm[kScanThreads / 32 + 1];
   int64_t base = (int64_t)blockIdx.x * kScanTile;
   uint32_t s = 0;
 #pragma unroll
   for (int k = 0; k < kScanItems; ++k) {
     int64_t i = base + k * kScanThreads + threadIdx.x;
-    if (i < n) s += scan_value(in, gather, rect, i);
+    if (i < n) {
+      const uint32_t v = scan_value(in, gather, rect, i);
+      if (values_out) values_out[i] = v;  // gathered once: the apply pass reads these in place
+      s += v;
+    }
   }
   uint32_t total;
   block_exclusive_scan<kScanThreads>(s, &total, sm);
@@ -113,8 +118,8 @@ __global__ void __launch_bounds__(1024) k_scan_sums(uint32_t* __restrict__ bsum,
 
 // inclusive = true writes the inclusive scan instead
 __global__ void __launch_bounds__(kScanThreads)
-k_scan_apply(const uint32_t* __restrict__ in, const uint32_t* __restrict__ gather, const int4* __restrict__ rect,
-             int64_t n, const uint32_t* __restrict__ bsum, uint32_t* __restrict__ out, int inclusive) {
+k_scan_apply(const uint32_t* in, const uint32_t* __restrict__ gather, const int4* __restrict__ rect,
+             int64_t n, const uint32_t* __restrict__ bsum, uint32_t* out /* may be `in` */, int inclusive) {
   __shared__ uint32_t sm[kScanThreads / 32 + 1];
   // blocked arrangement: thread t owns items [t*kScanItems, (t+1)*kScanItems)
   int64_t base = (int64_t)blockIdx.x * kScanTile + (int64_t)threadIdx.x * kScanItems;
@@ -920,9 +925,12 @@ static int launch_scan(const uint32_t* in, const uint32_t* gather, const int4* r
     return RM_OK;
   }
   int64_t nb = (n + rm::kScanTile - 1) / rm::kScanTile;
-  rm::k_scan_block_sums<<<(unsigned)nb, rm::kScanThreads, 0, st>>>(in, gather, rect, n, bsum);
+  // with a gather the values are fetched once, left in `out`, and scanned there in place
+  const bool stash = gather != nullptr;
+  rm::k_scan_block_sums<<<(unsigned)nb, rm::kScanThreads, 0, st>>>(in, gather, rect, n, bsum, stash ? out : nullptr);
   rm::k_scan_sums<<<1, 1024, 0, st>>>(bsum, nb, total64);
-  rm::k_scan_apply<<<(unsigned)nb, rm::kScanThreads, 0, st>>>(in, gather, rect, n, bsum, out, inclusive);
+  if (stash) rm::k_scan_apply<<<(unsigned)nb, rm::kScanThreads, 0, st>>>(out, nullptr, nullptr, n, bsum, out, inclusive);
+  else rm::k_scan_apply<<<(unsigned)nb, rm::kScanThreads, 0, st>>>(in, gather, rect, n, bsum, out, inclusive);
   RM_CUDA_CHECK(cudaPeekAtLastError());
   return RM_OK;
 }
