@@ -31,14 +31,14 @@ class AlphaBlendTiledRender(torch.autograd.Function):
         assert cam.c.grid_height == render_grid.grid_height and cam.c.grid_width == render_grid.grid_width
         records = raster.pack_records(indices, verts, cell, cam, lookup_tiles_touched(sorted_tetra_idx))
         need_grad = vertices.requires_grad or tet_density.requires_grad
-        output_img, distortion_img, n_contributors, hit_masks = raster.forward(
+        output_img, distortion_img, n_contributors, hits = raster.forward(
             sorted_tetra_idx, tile_ranges, records, cam, jitter, want_hit_masks=need_grad)
-        if hit_masks is None:
-            hit_masks = torch.empty((0,), dtype=torch.int16, device=dev)
+        if hits is None:  # nothing to differentiate: backward is never called
+            hits = tuple(torch.empty((0,), dtype=dt, device=dev) for dt in (torch.int32, torch.int32, torch.int16))
         # never written by the reference kernel either: always False
         tet_alive = torch.zeros((indices.shape[0],), dtype=torch.bool, device=dev)
         ctx.save_for_backward(sorted_tetra_idx, tile_ranges, indices, verts, cell, output_img, distortion_img,
-                              n_contributors, jitter, records, hit_masks)
+                              n_contributors, jitter, records, *hits)
         ctx.cam = cam
         ctx.mark_non_differentiable(tet_alive)
         return output_img, distortion_img, tet_alive
@@ -46,8 +46,9 @@ class AlphaBlendTiledRender(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output_img, grad_distortion_img, grad_vert_alive):
         (sorted_tetra_idx, tile_ranges, indices, verts, cell, output_img, distortion_img, n_contributors, jitter,
-         records, hit_masks) = ctx.saved_tensors
+         records, hit_counts, hit_ids, hit_masks) = ctx.saved_tensors
         vertices_grad, cell_grad = raster.backward(
             sorted_tetra_idx, tile_ranges, records, ctx.cam, jitter, output_img, distortion_img, n_contributors,
-            hit_masks, grad_output_img.contiguous().float(), grad_distortion_img.contiguous().float(), indices, verts, cell)
+            (hit_counts, hit_ids, hit_masks), grad_output_img.contiguous().float(),
+            grad_distortion_img.contiguous().float(), indices, verts, cell)
         return None, None, None, vertices_grad, cell_grad, None, None, None

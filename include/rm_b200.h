@@ -67,6 +67,24 @@ typedef struct RmBinInfo {
   uint32_t status;       /* RM_STATUS_* bits */
 } RmBinInfo;
 
+/*
+ * Hit lists, written by rm_forward and walked by rm_backward (device pointers).  No
+ * counterpart in the reference, whose backward pass walks every tile list again and
+ * repeats every intersection test.  A unit is one group of 16 pixels of a tile (tile t,
+ * group s of S = ceil(tile_width*tile_height / 16): unit t*S + s).  For every unit the
+ * forward pass appends, in list order, the entries that some pixel of the group hit with
+ * positive optical depth while still active:
+ *   counts[G*S] i32   number of such entries of the unit
+ *   ids[N*S] i32      their tet ids, unit (t, s) at [start(t)*S + s*len(t), ... + counts)
+ *   masks[N*S] u16    for each, the pixels of the group that hit it (bit = pixel index)
+ * with start/len from tile_ranges.  Slots beyond a unit's count are left unwritten.
+ */
+typedef struct RmHitList {
+  int32_t* counts;
+  int32_t* ids;
+  uint16_t* masks;
+} RmHitList;
+
 const char* rm_strerror(int code);
 int rm_version(void);
 
@@ -126,28 +144,24 @@ int rm_pack_records(const int32_t* indices, const float* vertices, const float* 
  * host side alphablend_tiled_slang_interp.py:11-52).
  *   ray_jitter[H,W,2] f32 -> output_img[H,W,4] (r,g,b,log-transmittance),
  *   distortion_img[H,W,5], n_contributors[H,W] i32.  Every pixel of the band is written.
- *   hit_masks[N * S] u16 with S = ceil(tile_width*tile_height / 16) (optional, may be
- *   NULL): for every list entry walked and every 16-pixel group of its tile, the pixels
- *   (bit = pixel index inside the group) that hit the tet with positive
- *   optical depth while still active; rm_backward needs it.  Entries beyond the largest
- *   n_contributors of their tile are left unwritten.  No counterpart in the reference,
- *   whose backward pass repeats every intersection test.
+ *   hits (optional, may be NULL): hit lists for rm_backward, see RmHitList.
  */
 int rm_forward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, const float* records,
                const RmCamera* cam, const float* ray_jitter, float* output_img, float* distortion_img,
-               int32_t* n_contributors, uint16_t* hit_masks, void* stream);
+               int32_t* n_contributors, const RmHitList* hits, void* stream);
 
 /*
  * Backward integration.  Replaces splat_tiled.bwd / bwd_alpha_blend
  * (slang/alphablend_shader_interp.slang:273-369, host side
  * alphablend_tiled_slang_interp.py:70-112).
- *   hit_masks[N * S] u16 is the array rm_forward wrote for the same lists and inputs;
+ *   hits are the hit lists rm_forward wrote for the same lists and inputs (sorted_tetra_idx and
+ *   n_contributors are accepted for symmetry with the reference's call and not read);
  *   grad_records[T, RM_GRAD_RECORD_FLOATS] is caller-provided scratch (zeroed here);
  *   vertices_grad[V,3] and cell_values_grad[T,7] are fully written (zeroed here first).
  */
 int rm_backward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, const float* records,
                 const RmCamera* cam, const float* ray_jitter, const float* output_img,
-                const float* distortion_img, const int32_t* n_contributors, const uint16_t* hit_masks,
+                const float* distortion_img, const int32_t* n_contributors, const RmHitList* hits,
                 const float* grad_output_img, const float* grad_distortion_img, const int32_t* indices,
                 const float* vertices, const float* cell_values, int64_t n_tets, int64_t n_vertices,
                 float* grad_records, float* vertices_grad, float* cell_values_grad, void* stream);
@@ -215,7 +229,7 @@ int rm_vertex_backward(const int32_t* indices, const float* vertices, int64_t n_
 int rm_backward_static_scratch(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, const float* records,
                                const RmCamera* cam, const float* ray_jitter, const float* output_img,
                                const float* distortion_img, const int32_t* n_contributors,
-                               const uint16_t* hit_masks, const float* grad_output_img,
+                               const RmHitList* hits, const float* grad_output_img,
                                const float* grad_distortion_img,
                                const int32_t* indices, const float* vertices, const float* cell_values,
                                int64_t n_tets, int64_t n_vertices, float* vertices_grad, float* cell_values_grad,

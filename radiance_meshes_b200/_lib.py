@@ -30,6 +30,10 @@ class RmCamera(C.Structure):
                 ("grid_width", C.c_int32), ("tile_row_begin", C.c_int32), ("tile_row_end", C.c_int32)]
 
 
+class RmHitList(C.Structure):
+    _fields_ = [("counts", C.c_void_p), ("ids", C.c_void_p), ("masks", C.c_void_p)]
+
+
 class RmBinInfo(C.Structure):
     _fields_ = [("n_keys", C.c_int64), ("n_region_keys", C.c_int64), ("n_visible", C.c_int32),
                 ("status", C.c_uint32)]
@@ -60,10 +64,11 @@ def load():
     lib.rm_list_scratch_bytes.argtypes = [i64, C.c_int, C.c_int]
     lib.rm_build_tile_lists.argtypes = [vp, vp, i64, cam, i64, i64, vp, vp, sz, vp, vp]
     lib.rm_pack_records.argtypes = [vp, vp, vp, i64, cam, vp, vp, vp]
-    lib.rm_forward.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, vp, vp]
-    lib.rm_backward.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, vp, vp, vp, vp]
+    hits = C.POINTER(RmHitList)
+    lib.rm_forward.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, hits, vp]
+    lib.rm_backward.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, hits, vp, vp, vp, vp, vp, i64, i64, vp, vp, vp, vp]
     lib.rm_vertex_backward.argtypes = [vp, vp, i64, i64, cam, vp, vp, vp, vp, vp]
-    lib.rm_backward_static_scratch.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, vp, vp,
+    lib.rm_backward_static_scratch.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, hits, vp, vp, vp, vp, vp, i64, i64, vp, vp,
                                                vp]
     lib.rm_tet_err.argtypes = [vp, vp, vp, cam, vp, vp, i64, vp, vp, vp]
     lib.rm_activate_output.argtypes = [vp, vp, vp, vp, vp, C.c_int, vp, vp, vp, i64, C.c_int, C.c_int, vp, vp]

@@ -21,9 +21,9 @@ size_t rm_list_plan_bytes(int64_t, int, int);
 int rm_launch_pack(const int32_t*, const float*, const float*, int64_t, const RmCamera*, const int32_t*, float*,
                    cudaStream_t);
 int rm_launch_forward(const int32_t*, const int32_t*, const float*, const RmCamera*, const float*, float*, float*,
-                      int32_t*, uint16_t*, cudaStream_t);
+                      int32_t*, const RmHitList*, cudaStream_t);
 int rm_launch_backward(const int32_t*, const int32_t*, const float*, const RmCamera*, const float*, const float*,
-                       const float*, const int32_t*, const uint16_t*, const float*, const float*, const int32_t*,
+                       const float*, const int32_t*, const RmHitList*, const float*, const float*, const int32_t*,
                        const float*, const float*, int64_t, int64_t, float*, float*, float*, cudaStream_t);
 
 int rm_launch_tet_err(const int32_t*, const int32_t*, const float*, const RmCamera*, const float*, const float*,
@@ -221,23 +221,24 @@ int rm_pack_records(const int32_t* indices, const float* vertices, const float* 
 
 int rm_forward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, const float* records,
                const RmCamera* cam, const float* ray_jitter, float* output_img, float* distortion_img,
-               int32_t* n_contributors, uint16_t* hit_masks, void* stream) {
+               int32_t* n_contributors, const RmHitList* hits, void* stream) {
   g_last_error[0] = 0;
   int rc = check_cam(cam);
   if (rc) return rc;
   if (!tile_ranges || !ray_jitter || !output_img || !distortion_img || !n_contributors) return RM_ERR_INVALID_ARG;
+  if (hits && (!hits->counts || !hits->ids || !hits->masks)) return RM_ERR_INVALID_ARG;
   if (!aligned16(output_img) || !aligned16(records) || (reinterpret_cast<uintptr_t>(ray_jitter) & 7) ||
       (reinterpret_cast<uintptr_t>(tile_ranges) & 7))
     return RM_ERR_WORKSPACE;
   rc = rm_bind_device(output_img);
   if (rc) return rc;
   return rm_launch_forward(sorted_tetra_idx, tile_ranges, records, cam, ray_jitter, output_img, distortion_img,
-                           n_contributors, hit_masks, static_cast<cudaStream_t>(stream));
+                           n_contributors, hits, static_cast<cudaStream_t>(stream));
 }
 
 int rm_backward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, const float* records,
                 const RmCamera* cam, const float* ray_jitter, const float* output_img,
-                const float* distortion_img, const int32_t* n_contributors, const uint16_t* hit_masks,
+                const float* distortion_img, const int32_t* n_contributors, const RmHitList* hits,
                 const float* grad_output_img, const float* grad_distortion_img, const int32_t* indices,
                 const float* vertices, const float* cell_values, int64_t n_tets, int64_t n_vertices,
                 float* grad_records, float* vertices_grad, float* cell_values_grad, void* stream) {
@@ -245,8 +246,8 @@ int rm_backward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, con
   int rc = check_cam(cam);
   if (rc) return rc;
   if (n_tets < 0 || n_vertices < 0) return RM_ERR_INVALID_ARG;
-  if (!tile_ranges || !ray_jitter || !output_img || !distortion_img || !n_contributors || !hit_masks ||
-      !grad_output_img || !grad_distortion_img || !vertices_grad)
+  if (!tile_ranges || !ray_jitter || !output_img || !distortion_img || !hits || !hits->counts || !hits->ids ||
+      !hits->masks || !grad_output_img || !grad_distortion_img || !vertices_grad)
     return RM_ERR_INVALID_ARG;
   if (n_tets > 0 && (!indices || !vertices || !cell_values || !grad_records || !cell_values_grad || !records))
     return RM_ERR_INVALID_ARG;
@@ -256,7 +257,7 @@ int rm_backward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, con
   rc = rm_bind_device(vertices_grad);
   if (rc) return rc;
   return rm_launch_backward(sorted_tetra_idx, tile_ranges, records, cam, ray_jitter, output_img, distortion_img,
-                            n_contributors, hit_masks, grad_output_img, grad_distortion_img, indices, vertices, cell_values,
+                            n_contributors, hits, grad_output_img, grad_distortion_img, indices, vertices, cell_values,
                             n_tets, n_vertices, grad_records, vertices_grad, cell_values_grad,
                             static_cast<cudaStream_t>(stream));
 }

@@ -385,8 +385,8 @@ __device__ __forceinline__ void halfwarp_sample_box(bool inside, float sx, float
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, const float4* __restrict__ records,
           RmCamera rcam, const float2* __restrict__ jitter, float4* __restrict__ out_img,
-          float* __restrict__ dist_img, int32_t* __restrict__ n_contrib, uint16_t* __restrict__ hit_masks, int subs,
-          int64_t n_units) {
+          float* __restrict__ dist_img, int32_t* __restrict__ n_contrib, int32_t* __restrict__ hit_counts,
+          int32_t* __restrict__ hit_ids, uint16_t* __restrict__ hit_masks, int subs, int64_t n_units) {
   __shared__ __align__(16) float4 stage[kWarpsPerBlock][2][2][kChunk * 6];  // [warp][half][buffer]
   __shared__ unsigned hit_bits[kWarpsPerBlock][2][kChunk];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -423,10 +423,16 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
 
   float4* buf0 = stage[warp][half][0];
   float4* buf1 = stage[warp][half][1];
+  // Hit list of this half-warp: the entries some pixel hit, in list order, each with its tet id and
+  // the 16-bit mask of the pixels that hit it; slots [hbase, hbase + n_hit).
+  const int64_t hbase = (int64_t)u.start * u.subs + (int64_t)u.sub * u.len;
+  int n_hit = 0;
+  int id_cur = 0;  // list entry this lane staged for the chunk being evaluated
   // prologue: stage chunk 0; the list entry of the chunk after next is always
   // loaded one iteration before it is needed
   if (fetching && lane16 < u.len) {
     int id = __ldg(list + u.start + lane16);
+    id_cur = id;
     const float4* src = records + kRecStride * (int64_t)id;
 #pragma unroll
     for (int k = 0; k < 6; ++k) cp_async16(buf0 + lane16 * 6 + k, src + k);
@@ -441,6 +447,8 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
     float4* cur = (c & 1) ? buf1 : buf0;
     float4* nxt = (c & 1) ? buf0 : buf1;
     const float4 cq0 = nq0, cq1 = nq1, cq2 = nq2;
+    const int id_here = id_cur;
+    id_cur = id_next;
     // issue the next chunk
     {
       int e = (c + 1) * kChunk + lane16;
@@ -465,8 +473,8 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
                          !hull_misses_box(cq0, cq1, cq2, X0, X1, Y0, Y1);
     unsigned todo = (__ballot_sync(0xffffffffu, nonzero) >> (16 * half)) & 0xFFFFu;
     // For every entry the pixels that hit it (while still active) are collected in a
-    // 16-bit mask in shared memory, so that the backward pass can go straight to the
-    // hits; slot j was cleared by lane j before the barrier above.
+    // 16-bit mask in shared memory; the entries with a non-zero mask go to the hit list
+    // the backward pass walks.  Slot j was cleared by lane j before the barrier above.
     if (active && todo) {
       int j = __ffs(todo) - 1;
       float4 pl[4] = {cur[j * 6], cur[j * 6 + 1], cur[j * 6 + 2], cur[j * 6 + 3]};
@@ -504,8 +512,16 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
       }
     }
     __syncwarp();
-    if (hit_masks && c * kChunk + lane16 < u.len)
-      hit_masks[(int64_t)(u.start + c * kChunk + lane16) * u.subs + u.sub] = (uint16_t)hb[lane16];
+    if (hit_ids) {  // append the chunk's entries that were hit, in list order
+      const unsigned m = hb[lane16];
+      const unsigned nzb = (__ballot_sync(0xffffffffu, m != 0u) >> (16 * half)) & 0xFFFFu;
+      if (m) {
+        const int64_t slot = hbase + n_hit + __popc(nzb & ((1u << lane16) - 1u));
+        hit_ids[slot] = id_here;
+        hit_masks[slot] = (uint16_t)m;
+      }
+      n_hit += __popc(nzb);
+    }
     __syncwarp();
     unsigned act = __ballot_sync(0xffffffffu, active);
     fetching = act & half_mask;
@@ -514,6 +530,7 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
   cp_async_wait<0>();
   if (active) contrib = u.len;  // walked the whole list
 
+  if (hit_counts && lane16 == 0 && unit < n_units) hit_counts[(int64_t)u.tile * u.subs + u.sub] = n_hit;
   if (u.inside) {
     out_img[pix] = make_float4(sr, sg, sb, logT);
     float* o = dist_img + 5 * pix;
@@ -526,11 +543,11 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
 // Backward
 // ----------------------------------------------------------------------------
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
-k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, const float4* __restrict__ records,
-           RmCamera rcam, const float2* __restrict__ jitter, const float4* __restrict__ out_img,
-           const float* __restrict__ dist_img, const int32_t* __restrict__ n_contrib,
-           const uint16_t* __restrict__ hit_masks, const float4* __restrict__ g_img, const float* __restrict__ g_dist, float* __restrict__ grec, int subs,
-           int64_t n_units) {
+k_backward(const int2* __restrict__ ranges, const float4* __restrict__ records, RmCamera rcam,
+           const float2* __restrict__ jitter, const float4* __restrict__ out_img, const float* __restrict__ dist_img,
+           const int32_t* __restrict__ hit_counts, const int32_t* __restrict__ hit_ids,
+           const uint16_t* __restrict__ hit_masks, const float4* __restrict__ g_img, const float* __restrict__ g_dist,
+           float* __restrict__ grec, int subs, int64_t n_units) {
   __shared__ __align__(16) float4 stage[kWarpsPerBlock][2][2][kChunk * 6];
   __shared__ int stage_id[kWarpsPerBlock][2][2][kChunk];
   __shared__ unsigned stage_mask[kWarpsPerBlock][2][2][kChunk];  // pixels of the tile that hit the entry (forward)
@@ -543,7 +560,6 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
   const int64_t pix = (int64_t)u.y * rcam.image_width + u.x;
   float logT = 0.f, sz = 0.f, sw = 0.f;
   float gr = 0.f, gg = 0.f, gb = 0.f, glogT = 0.f, gx = 0.f, gy = 0.f, gz = 0.f, gw = 0.f, gv = 0.f;
-  int nc = 0;
   if (u.inside) {
     float2 j = __ldg(jitter + pix);
     d = ray_direction(rcam, (float)u.x + j.x, (float)u.y + j.y);
@@ -554,28 +570,25 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
     gr = g4.x; gg = g4.y; gb = g4.z; glogT = g4.w;
     const float* gd = g_dist + 5 * pix;
     gx = __ldg(gd); gy = __ldg(gd + 1); gz = __ldg(gd + 2); gw = __ldg(gd + 3); gv = __ldg(gd + 4);
-    nc = min(__ldg(n_contrib + pix), u.len);
   }
   const float min_t = rcam.min_t;
 
-  // entries at or beyond the largest n_contributors of the half are skipped by every pixel
-  int nmax = nc;
-#pragma unroll
-  for (int o = 8; o >= 1; o >>= 1) nmax = max(nmax, __shfl_xor_sync(0xffffffffu, nmax, o));
+  // The half-warp walks its hit list (written by the forward pass: the entries some pixel of
+  // these 16 hit, in list order, with tet id and pixel mask) from the last entry to the first.
+  const int64_t hbase = (int64_t)u.start * u.subs + (int64_t)u.sub * u.len;
+  const int nmax = unit < n_units ? min(__ldg(hit_counts + (int64_t)u.tile * u.subs + u.sub), u.len) : 0;
   const int nchunks = (nmax + kChunk - 1) / kChunk;
   const int max_chunks = max(nchunks, __shfl_xor_sync(0xffffffffu, nchunks, 16));
 
-  // chunk k of this half (k = 0 is the LAST chunk of its list) sits in buffer k&1
-  // List entry and hit mask this lane stages for chunk k+1, loaded while chunk k is
-  // issued.  Only entries some pixel of the tile hit in the forward pass are staged
-  // and visited.
+  // chunk k of this half (k = 0 is the LAST chunk of its hit list) sits in buffer k&1
+  // Tet id and hit mask this lane stages for chunk k+1, loaded while chunk k is issued.
   int id_next = 0;
   unsigned mask_next = 0;
   {
     const int e0 = (nchunks - 1) * kChunk + lane16;
     if (nchunks >= 1 && e0 < nmax) {
-      id_next = __ldg(list + u.start + e0);
-      mask_next = __ldg(hit_masks + (int64_t)(u.start + e0) * u.subs + u.sub);
+      id_next = __ldg(hit_ids + hbase + e0);
+      mask_next = __ldg(hit_masks + hbase + e0);
     }
   }
   auto issue = [&](int k) {
@@ -585,8 +598,8 @@ k_backward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, co
       const int id = id_next;
       const unsigned m = e < nmax ? mask_next : 0u;
       if (c >= 1) {  // entry e - kChunk is always below nmax
-        id_next = __ldg(list + u.start + e - kChunk);
-        mask_next = __ldg(hit_masks + (int64_t)(u.start + e - kChunk) * u.subs + u.sub);
+        id_next = __ldg(hit_ids + hbase + e - kChunk);
+        mask_next = __ldg(hit_masks + hbase + e - kChunk);
       }
       stage_id[warp][half][k & 1][lane16] = id;
       stage_mask[warp][half][k & 1][lane16] = m;
@@ -1004,7 +1017,7 @@ int rm_launch_pack(const int32_t* indices, const float* vertices, const float* c
 }
 
 int rm_launch_forward(const int32_t* list, const int32_t* ranges, const float* records, const RmCamera* cam,
-                      const float* jitter, float* out_img, float* dist_img, int32_t* n_contrib, uint16_t* hit_masks,
+                      const float* jitter, float* out_img, float* dist_img, int32_t* n_contrib, const RmHitList* hits,
                       cudaStream_t st) {
   int subs;
   int64_t n_units;
@@ -1014,8 +1027,8 @@ int rm_launch_forward(const int32_t* list, const int32_t* ranges, const float* r
   RmProfScope prof("k_forward", st);
   rm::k_forward<<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
       list, reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam,
-      reinterpret_cast<const float2*>(jitter), reinterpret_cast<float4*>(out_img), dist_img, n_contrib, hit_masks,
-      subs, n_units);
+      reinterpret_cast<const float2*>(jitter), reinterpret_cast<float4*>(out_img), dist_img, n_contrib,
+      hits ? hits->counts : nullptr, hits ? hits->ids : nullptr, hits ? hits->masks : nullptr, subs, n_units);
   RM_CUDA_CHECK(cudaPeekAtLastError());
   return RM_OK;
 }
@@ -1041,10 +1054,11 @@ int rm_launch_tet_err(const int32_t* list, const int32_t* ranges, const float* r
 
 int rm_launch_backward(const int32_t* list, const int32_t* ranges, const float* records, const RmCamera* cam,
                        const float* jitter, const float* out_img, const float* dist_img, const int32_t* n_contrib,
-                       const uint16_t* hit_masks, const float* g_img, const float* g_dist, const int32_t* indices,
-                       const float* vertices,
-                       const float* cell, int64_t T, int64_t V, float* grec, float* vgrad, float* cgrad,
-                       cudaStream_t st) {
+                       const RmHitList* hits, const float* g_img, const float* g_dist, const int32_t* indices,
+                       const float* vertices, const float* cell, int64_t T, int64_t V, float* grec, float* vgrad,
+                       float* cgrad, cudaStream_t st) {
+  (void)list;
+  (void)n_contrib;  // the hit lists already stop at every pixel's last contributor
   RM_CUDA_CHECK(cudaMemsetAsync(vgrad, 0, sizeof(float) * 3 * (size_t)V, st));
   if (T == 0) return RM_OK;
   RM_CUDA_CHECK(cudaMemsetAsync(grec, 0, sizeof(float) * 24 * (size_t)T, st));
@@ -1055,9 +1069,9 @@ int rm_launch_backward(const int32_t* list, const int32_t* ranges, const float* 
   if (n_units > 0) {
     RmProfScope prof("k_backward", st);
     rm::k_backward<<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
-        list, reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam,
-        reinterpret_cast<const float2*>(jitter), reinterpret_cast<const float4*>(out_img), dist_img, n_contrib,
-        hit_masks, reinterpret_cast<const float4*>(g_img), g_dist, grec, subs, n_units);
+        reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam,
+        reinterpret_cast<const float2*>(jitter), reinterpret_cast<const float4*>(out_img), dist_img, hits->counts,
+        hits->ids, hits->masks, reinterpret_cast<const float4*>(g_img), g_dist, grec, subs, n_units);
   }
   RmProfScope prof2("k_backward_finish", st);
   rm::k_backward_finish<<<(unsigned)((T + 255) / 256), 256, 0, st>>>(indices, vertices, cell, T, *cam,
@@ -1085,7 +1099,7 @@ float* g_static_addr[kMaxDevices] = {nullptr};
 extern "C" int rm_backward_static_scratch(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges,
                                           const float* records, const RmCamera* cam, const float* ray_jitter,
                                           const float* output_img, const float* distortion_img,
-                                          const int32_t* n_contributors, const uint16_t* hit_masks,
+                                          const int32_t* n_contributors, const RmHitList* hits,
                                           const float* grad_output_img,
                                           const float* grad_distortion_img, const int32_t* indices,
                                           const float* vertices, const float* cell_values, int64_t n_tets,
@@ -1093,9 +1107,11 @@ extern "C" int rm_backward_static_scratch(const int32_t* sorted_tetra_idx, const
                                           void* stream) {
   if (n_tets < 0 || n_vertices < 0 || !cam) return RM_ERR_INVALID_ARG;
   if (n_tets > RM_STATIC_SCRATCH_MAX_TETS) return RM_ERR_STATIC_SCRATCH;
-  if (!tile_ranges || !ray_jitter || !output_img || !distortion_img || !n_contributors || !hit_masks ||
-      !grad_output_img || !grad_distortion_img || !vertices_grad)
+  if (!tile_ranges || !ray_jitter || !output_img || !distortion_img || !hits || !hits->counts || !hits->ids ||
+      !hits->masks || !grad_output_img || !grad_distortion_img || !vertices_grad)
     return RM_ERR_INVALID_ARG;
+  (void)sorted_tetra_idx;
+  (void)n_contributors;
   if (n_tets > 0 && (!indices || !vertices || !cell_values || !cell_values_grad || !records))
     return RM_ERR_INVALID_ARG;
   if (cam->image_height <= 0 || cam->image_width <= 0 || cam->tile_height <= 0 || cam->tile_width <= 0 ||
@@ -1132,10 +1148,10 @@ extern "C" int rm_backward_static_scratch(const int32_t* sorted_tetra_idx, const
   unit_grid(cam, &subs, &n_units, &blocks);
   if (n_units > 0) {
     rm::k_backward<<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
-        sorted_tetra_idx, reinterpret_cast<const int2*>(tile_ranges), reinterpret_cast<const float4*>(records), *cam,
+        reinterpret_cast<const int2*>(tile_ranges), reinterpret_cast<const float4*>(records), *cam,
         reinterpret_cast<const float2*>(ray_jitter), reinterpret_cast<const float4*>(output_img), distortion_img,
-        n_contributors, hit_masks, reinterpret_cast<const float4*>(grad_output_img), grad_distortion_img, scratch,
-        subs, n_units);
+        hits->counts, hits->ids, hits->masks, reinterpret_cast<const float4*>(grad_output_img), grad_distortion_img,
+        scratch, subs, n_units);
   }
   rm::k_backward_finish<<<(unsigned)((n_tets + 255) / 256), 256, 0, st>>>(
       indices, vertices, cell_values, n_tets, *cam, reinterpret_cast<const float4*>(scratch), vertices_grad,

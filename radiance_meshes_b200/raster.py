@@ -140,9 +140,17 @@ def pack_records(indices, vertices, cell_values, cam, tiles_touched=None):
     return records
 
 
+def hit_list_ref(hits):
+    """ctypes argument for a hit list given as the (counts, ids, masks) tensors forward() returns."""
+    if hits is None:
+        return None
+    counts, ids, masks = hits
+    return C.byref(_lib.RmHitList(_ptr(counts), _ptr(ids), _ptr(masks)))
+
+
 def forward(sorted_idx, tile_ranges, records, cam, ray_jitter, want_hit_masks=True):
-    """Returns (output_img, distortion_img, n_contributors, hit_masks); hit_masks (int16 view of the
-    per-entry 16-bit pixel masks) is what backward() needs and is None if not requested."""
+    """Returns (output_img, distortion_img, n_contributors, hits); hits = (counts int32 [G*S], ids int32 [N*S],
+    masks int16 [N*S]) are the hit lists backward() walks, None if not requested."""
     lib = _lib.load()
     dev = records.device
     H, W = cam.c.image_height, cam.c.image_width
@@ -152,17 +160,22 @@ def forward(sorted_idx, tile_ranges, records, cam, ray_jitter, want_hit_masks=Tr
         output_img = alloc((H, W, 4), dtype=torch.float32, device=dev)
         distortion_img = alloc((H, W, 5), dtype=torch.float32, device=dev)
         n_contributors = alloc((H, W, 1), dtype=torch.int32, device=dev)
-        groups = (cam.c.tile_width * cam.c.tile_height + 15) // 16
-        hit_masks = torch.empty((max(int(sorted_idx.shape[0]) * groups, 1),), dtype=torch.int16, device=dev) \
-            if want_hit_masks else None
+        hits = None
+        if want_hit_masks:
+            groups = (cam.c.tile_width * cam.c.tile_height + 15) // 16
+            slots = max(int(sorted_idx.shape[0]) * groups, 1)
+            units = cam.c.grid_height * cam.c.grid_width * groups
+            hits = (alloc((units,), dtype=torch.int32, device=dev),
+                    torch.empty((slots,), dtype=torch.int32, device=dev),
+                    torch.empty((slots,), dtype=torch.int16, device=dev))
         _lib.check(lib.rm_forward(_ptr(sorted_idx), _ptr(tile_ranges), _ptr(records), cam.ref, _ptr(ray_jitter),
-                                  _ptr(output_img), _ptr(distortion_img), _ptr(n_contributors), _ptr(hit_masks),
+                                  _ptr(output_img), _ptr(distortion_img), _ptr(n_contributors), hit_list_ref(hits),
                                   _stream(dev)))
-    return output_img, distortion_img, n_contributors, hit_masks
+    return output_img, distortion_img, n_contributors, hits
 
 
 def backward(sorted_idx, tile_ranges, records, cam, ray_jitter, output_img, distortion_img, n_contributors,
-             hit_masks, grad_output_img, grad_distortion_img, indices, vertices, cell_values):
+             hits, grad_output_img, grad_distortion_img, indices, vertices, cell_values):
     lib = _lib.load()
     dev = records.device
     T, V = indices.shape[0], vertices.shape[0]
@@ -171,7 +184,7 @@ def backward(sorted_idx, tile_ranges, records, cam, ray_jitter, output_img, dist
         vertices_grad = torch.empty((V, 3), dtype=torch.float32, device=dev)
         cell_grad = torch.empty((T, 7), dtype=torch.float32, device=dev)
         _lib.check(lib.rm_backward(_ptr(sorted_idx), _ptr(tile_ranges), _ptr(records), cam.ref, _ptr(ray_jitter),
-                                   _ptr(output_img), _ptr(distortion_img), _ptr(n_contributors), _ptr(hit_masks),
+                                   _ptr(output_img), _ptr(distortion_img), _ptr(n_contributors), hit_list_ref(hits),
                                    _ptr(grad_output_img), _ptr(grad_distortion_img), _ptr(indices), _ptr(vertices),
                                    _ptr(cell_values), T, V, _ptr(grad_records), _ptr(vertices_grad), _ptr(cell_grad),
                                    _stream(dev)))

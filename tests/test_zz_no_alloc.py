@@ -63,14 +63,15 @@ def test_static_scratch_backward_matches_rm_backward(cuda_lib):
         vg_ref = torch.empty((V, 3), device=dev)
         cg_ref = torch.empty((T, 7), device=dev)
         _lib.check(cuda_lib.rm_backward(_p(sorted_idx), _p(bctx["tile_ranges"]), _p(records), cam.ref, _p(jitter),
-                                        _p(out), _p(dist), _p(nc), _p(hm), _p(g_img), _p(g_dist), _p(indices), _p(vertices),
+                                        _p(out), _p(dist), _p(nc), raster.hit_list_ref(hm), _p(g_img), _p(g_dist), _p(indices), _p(vertices),
                                         _p(cells), T, V, _p(scratch), _p(vg_ref), _p(cg_ref), stream))
         # new entry point: outputs pre-filled with garbage, no scratch argument
         vg = torch.full((V, 3), 123.0, device=dev)
         cg = torch.full((T, 7), -7.0, device=dev)
         _lib.check(cuda_lib.rm_backward_static_scratch(
             _p(sorted_idx), _p(bctx["tile_ranges"]), _p(records), cam.ref, _p(jitter), _p(out), _p(dist), _p(nc),
-            _p(hm), _p(g_img), _p(g_dist), _p(indices), _p(vertices), _p(cells), T, V, _p(vg), _p(cg), stream))
+            raster.hit_list_ref(hm), _p(g_img), _p(g_dist), _p(indices), _p(vertices), _p(cells), T, V, _p(vg), _p(cg),
+            stream))
         torch.cuda.synchronize()
         assert vg_ref.abs().max() > 0 and cg_ref.abs().max() > 0
         assert _rel(vg, vg_ref) <= GRAD_TOL, f"call {call}: vertex gradients differ"
@@ -87,7 +88,8 @@ def test_static_scratch_rejects_oversized_mesh(cuda_lib):
     cam.grid_height = cam.grid_width = 4
     cam.tile_row_end = 4
     rc = cuda_lib.rm_backward_static_scratch(
-        _p(dummy), _p(dummy), _p(dummy), C.byref(cam), _p(dummy), _p(dummy), _p(dummy), _p(dummy), _p(dummy),
+        _p(dummy), _p(dummy), _p(dummy), C.byref(cam), _p(dummy), _p(dummy), _p(dummy), _p(dummy),
+        C.byref(_lib.RmHitList(_p(dummy), _p(dummy), _p(dummy))),
         _p(dummy), _p(dummy), _p(dummy), _p(dummy), _p(dummy), _lib.RM_STATIC_SCRATCH_MAX_TETS + 1, 4, _p(dummy),
         _p(dummy), None)
     assert rc == _lib.RM_ERR_STATIC_SCRATCH
