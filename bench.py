@@ -356,7 +356,7 @@ def run_gpu(args):
         tet_err_ms = float(np.mean(ms[1:])) if len(ms) > 1 else None
 
     # ---- feature activation of a frozen model (the row before the rasterizer), timed separately ----
-    act_ms, act_bytes = None, None
+    act_ms, act_bytes, inference_ms = None, None, None
     if rank == 0:
         from radiance_meshes_b200.activate import activate_output
         gen = torch.Generator(device=dev).manual_seed(11)
@@ -377,7 +377,19 @@ def run_gpu(args):
         # compulsory traffic: per tet density 4 + rgb 12 + grd 12 + sh 15*3*2 + indices 16 + circumcenter 12 +
         # output 28, and the vertex table once (the four gathers per tet are served from L2)
         act_bytes = T * (4 + 12 + 12 + 90 + 16 + 12 + 28) + V * 12
-        del sh, rgb, grd, cc
+        # ---- forward-only frame, the protocol of the reference's published FPS (tile_benchmark.py:59-94:
+        # activate_output + render under no_grad), here timed with CUDA events on the device
+        inf0, inf1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.no_grad():
+            for it in range(3 + 10):
+                if it == 3:
+                    inf0.record()
+                feats = activate_output(tcam["cam_pos"], dens, rgb, grd, sh, d["indices"], cc, d["vertices"], 3, 3)
+                render(d["indices"], d["vertices"], feats, tcam, d["jitter"])
+            inf1.record()
+        torch.cuda.synchronize()
+        inference_ms = inf0.elapsed_time(inf1) / 10
+        del sh, rgb, grd, cc, feats
 
     if rank != 0:
         if world > 1:
@@ -425,6 +437,11 @@ def run_gpu(args):
                                 frac_of_hbm_peak=(act_bytes / (act_ms * 1e-3) / 1e9 / peak) if act_ms else None,
                                 note="activate_output, SH degree 3 with f16 coefficients, all tets; "
                                      "not part of `value`"),
+        forward_only=dict(ms_per_frame=inference_ms, fps=(1e3 / inference_ms) if inference_ms else None,
+                          mpix_per_s=(H * W / (inference_ms * 1e-3) / 1e6) if inference_ms else None,
+                          note="activate_output + projection + lists + forward under no_grad, the protocol of the "
+                               "reference's published FPS table (synthetic SH-activated features); not part of "
+                               "`value`"),
     )
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(sc, tcam_np)
