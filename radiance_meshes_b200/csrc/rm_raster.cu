@@ -147,6 +147,9 @@ k_pack_records(const int32_t* __restrict__ indices, const float* __restrict__ ve
 #pragma unroll
       for (int k = 0; k < 4; ++k) la[k] = lb[k] = lc[k] = qnan;
     }
+    // A tet of zero density can neither contribute nor terminate a pixel: its first line separates
+    // every sample box, so the examination of the integration kernels drops it without reading more.
+    if (!(density > 0.0f)) { la[0] = 0.0f; lb[0] = 0.0f; lc[0] = -1.0f; }
     r[6] = make_float4(la[0], lb[0], lc[0], la[1]);
     r[7] = make_float4(lb[1], lc[1], la[2], lb[2]);
     r[8] = make_float4(lc[2], la[3], lb[3], lc[3]);
@@ -382,19 +385,34 @@ __device__ __forceinline__ void halfwarp_sample_box(bool inside, float sx, float
 // ----------------------------------------------------------------------------
 // Forward
 // ----------------------------------------------------------------------------
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+// Examination and evaluation are decoupled.  A half-warp examines its list 16 entries at a
+// time: every lane reads the hull lines of one entry (48 bytes, prefetched one chunk ahead) and
+// decides whether the tet can touch the half-warp's samples at all (zero density is encoded as
+// an always-separating line by k_pack_records); the candidates go, in list order and with their
+// list position, to a queue in shared memory.  Whenever both half-warps of the warp have 16
+// candidates (or nothing left to examine), the next 16 records are staged with cp.async
+// while the previously staged 16 are evaluated.  Only candidates are staged, and the two
+// half-warps, which execute in lock-step, evaluate equally long batches.
+constexpr int kQueue = 2 * kChunk;
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, 5)
 k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, const float4* __restrict__ records,
           RmCamera rcam, const float2* __restrict__ jitter, float4* __restrict__ out_img,
           float* __restrict__ dist_img, int32_t* __restrict__ n_contrib, int32_t* __restrict__ hit_counts,
           int32_t* __restrict__ hit_ids, uint16_t* __restrict__ hit_masks, int subs, int64_t n_units) {
   __shared__ __align__(16) float4 stage[kWarpsPerBlock][2][2][kChunk * 6];  // [warp][half][buffer]
   __shared__ unsigned hit_bits[kWarpsPerBlock][2][kChunk];
+  __shared__ int queue_id[kWarpsPerBlock][2][kQueue], queue_pos[kWarpsPerBlock][2][kQueue];
+  __shared__ int batch_id[kWarpsPerBlock][2][2][kChunk], batch_pos[kWarpsPerBlock][2][2][kChunk];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int half = lane >> 4, lane16 = lane & 15;
   const unsigned half_mask = 0xFFFFu << (16 * half);
+  const unsigned below = (1u << lane16) - 1u;
   const int64_t unit = ((int64_t)blockIdx.x * kWarpsPerBlock + warp) * 2 + half;
   Unit u = make_unit(rcam, ranges, unit, n_units, subs, lane16);
   unsigned* hb = hit_bits[warp][half];
+  int* q_id = queue_id[warp][half];
+  int* q_pos = queue_pos[warp][half];
 
   f3 d = {0.f, 0.f, 1.f};
   const int64_t pix = (int64_t)u.y * rcam.image_width + u.x;
@@ -408,80 +426,106 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
   const float min_t = rcam.min_t;
   float X0, X1, Y0, Y1;
   halfwarp_sample_box(u.inside, sx, sy, X0, X1, Y0, Y1);
-  const float qnan = __int_as_float(0x7fc00000);
-  float4 nq0 = make_float4(qnan, qnan, qnan, qnan), nq1 = nq0, nq2 = nq0;  // hull lines of the record this lane stages
 
   float sr = 0.f, sg = 0.f, sb = 0.f, logT = 0.f, T = 1.f;
   float dx = 0.f, dy = 0.f, dz = 0.f, dw = 0.f, dv = 0.f;
   int contrib = 0;
   bool active = u.inside;
-
-  const int nchunks = (u.len + kChunk - 1) / kChunk;
-  // all lanes of the warp iterate up to the longer of the two lists
-  const int max_chunks = max(nchunks, __shfl_xor_sync(0xffffffffu, nchunks, 16));
   bool fetching = __ballot_sync(0xffffffffu, active) & half_mask;
 
-  float4* buf0 = stage[warp][half][0];
-  float4* buf1 = stage[warp][half][1];
   // Hit list of this half-warp: the entries some pixel hit, in list order, each with its tet id and
   // the 16-bit mask of the pixels that hit it; slots [hbase, hbase + n_hit).
   const int64_t hbase = (int64_t)u.start * u.subs + (int64_t)u.sub * u.len;
   int n_hit = 0;
-  int id_cur = 0;  // list entry this lane staged for the chunk being evaluated
-  // prologue: stage chunk 0; the list entry of the chunk after next is always
-  // loaded one iteration before it is needed
-  if (fetching && lane16 < u.len) {
-    int id = __ldg(list + u.start + lane16);
-    id_cur = id;
-    const float4* src = records + kRecStride * (int64_t)id;
-#pragma unroll
-    for (int k = 0; k < 6; ++k) cp_async16(buf0 + lane16 * 6 + k, src + k);
-    nq0 = __ldg(src + 6);
-    nq1 = __ldg(src + 7);
-    nq2 = __ldg(src + 8);
-  }
-  cp_async_commit();
-  int id_next = (fetching && kChunk + lane16 < u.len) ? __ldg(list + u.start + kChunk + lane16) : 0;
 
-  for (int c = 0; c < max_chunks; ++c) {
-    float4* cur = (c & 1) ? buf1 : buf0;
-    float4* nxt = (c & 1) ? buf0 : buf1;
-    const float4 cq0 = nq0, cq1 = nq1, cq2 = nq2;
-    const int id_here = id_cur;
-    id_cur = id_next;
-    // issue the next chunk
+  // examination state: entry src + lane16 is the one this lane examines next; its tet id and hull
+  // lines are already in registers, the id of the entry after it is in flight
+  int src = 0;
+  int qn = 0;  // candidates waiting in the queue (same value in all lanes of the half)
+  int id_e = (fetching && lane16 < u.len) ? __ldg(list + u.start + lane16) : -1;
+  int id_n = (fetching && kChunk + lane16 < u.len) ? __ldg(list + u.start + kChunk + lane16) : -1;
+  const float qnan = __int_as_float(0x7fc00000);
+  float4 hq0 = make_float4(qnan, qnan, qnan, qnan), hq1 = hq0, hq2 = hq0;
+  if (id_e >= 0) {
+    const float4* src_rec = records + kRecStride * (int64_t)id_e;
+    hq0 = __ldg(src_rec + 6);
+    hq1 = __ldg(src_rec + 7);
+    hq2 = __ldg(src_rec + 8);
+  }
+
+  int buf = 0;    // buffer holding the batch to evaluate
+  int n_cur = 0;  // its number of entries
+  for (;;) {
     {
-      int e = (c + 1) * kChunk + lane16;
-      if (fetching && e < u.len) {
-        const float4* src = records + kRecStride * (int64_t)id_next;
-#pragma unroll
-        for (int k = 0; k < 6; ++k) cp_async16(nxt + lane16 * 6 + k, src + k);
-        nq0 = __ldg(src + 6);
-        nq1 = __ldg(src + 7);
-        nq2 = __ldg(src + 8);
-      }
-      cp_async_commit();
-      if (fetching && e + kChunk < u.len) id_next = __ldg(list + u.start + e + kChunk);
+      const bool done = !fetching || (n_cur == 0 && qn == 0 && src >= u.len);
+      if (__all_sync(0xffffffffu, done)) break;
     }
-    hb[lane16] = 0u;  // slot of this lane's entry, read back after the chunk
+    // ---- examine until both halves have a full batch queued or nothing left to examine
+    for (;;) {
+      const bool need = fetching && qn < kChunk && src < u.len;
+      if (!__any_sync(0xffffffffu, need)) break;
+      const bool cand = need && id_e >= 0 && !hull_misses_box(hq0, hq1, hq2, X0, X1, Y0, Y1);
+      const unsigned cb = (__ballot_sync(0xffffffffu, cand) >> (16 * half)) & 0xFFFFu;
+      if (cand) {
+        const int slot = qn + __popc(cb & below);
+        q_id[slot] = id_e;
+        q_pos[slot] = src + lane16;
+      }
+      if (need) {
+        qn += __popc(cb);
+        src += kChunk;
+        id_e = id_n;
+        if (id_e >= 0) {
+          const float4* src_rec = records + kRecStride * (int64_t)id_e;
+          hq0 = __ldg(src_rec + 6);
+          hq1 = __ldg(src_rec + 7);
+          hq2 = __ldg(src_rec + 8);
+        }
+        id_n = (src + kChunk + lane16 < u.len) ? __ldg(list + u.start + src + kChunk + lane16) : -1;
+      }
+    }
+    __syncwarp();
+    // ---- stage the next batch: the first min(qn, 16) queued candidates
+    const int nb = buf ^ 1;
+    const int take = fetching ? min(qn, kChunk) : 0;
+    int keep_id = 0, keep_pos = 0;
+    if (lane16 < take) {
+      const int id = q_id[lane16];
+      batch_id[warp][half][nb][lane16] = id;
+      batch_pos[warp][half][nb][lane16] = q_pos[lane16];
+      const float4* src_rec = records + kRecStride * (int64_t)id;
+      float4* dst = stage[warp][half][nb] + lane16 * 6;
+#pragma unroll
+      for (int k = 0; k < 6; ++k) cp_async16(dst + k, src_rec + k);
+    }
+    cp_async_commit();
+    if (take + lane16 < qn) {  // the rest of the queue moves to its front
+      keep_id = q_id[take + lane16];
+      keep_pos = q_pos[take + lane16];
+    }
+    __syncwarp();
+    if (take + lane16 < qn) {
+      q_id[lane16] = keep_id;
+      q_pos[lane16] = keep_pos;
+    }
+    qn -= take;
+    hb[lane16] = 0u;  // slot of entry lane16 of the batch evaluated now, read back after it
     cp_async_wait<1>();
     __syncwarp();
-    // Tets of zero density are walked (they count in n_contributors) but can never
-    // contribute or terminate a pixel: only the entries flagged here are evaluated.
-    // Neither are tets whose projection misses the box of this half-warp's samples.
-    const bool nonzero = fetching && (c * kChunk + lane16 < u.len) && cur[lane16 * 6 + 5].w > 0.0f &&
-                         !hull_misses_box(cq0, cq1, cq2, X0, X1, Y0, Y1);
-    unsigned todo = (__ballot_sync(0xffffffffu, nonzero) >> (16 * half)) & 0xFFFFu;
+    // ---- evaluate the batch staged one iteration ago
+    const float4* cur = stage[warp][half][buf];
+    const int* cur_pos = batch_pos[warp][half][buf];
+    unsigned todo = n_cur >= kChunk ? 0xFFFFu : ((1u << n_cur) - 1u);
     // For every entry the pixels that hit it (while still active) are collected in a
     // 16-bit mask in shared memory; the entries with a non-zero mask go to the hit list
-    // the backward pass walks.  Slot j was cleared by lane j before the barrier above.
+    // the backward pass walks.
     if (active && todo) {
-      int j = __ffs(todo) - 1;
-      float4 pl[4] = {cur[j * 6], cur[j * 6 + 1], cur[j * 6 + 2], cur[j * 6 + 3]};
+      int j = 0;
+      float4 pl[4] = {cur[0], cur[1], cur[2], cur[3]};
       while (true) {
         todo &= todo - 1;
         // planes of the next record to evaluate, loaded while this one is tested
-        const int jn = todo ? __ffs(todo) - 1 : j;
+        const int jn = todo ? j + 1 : j;
         const float4 nx[4] = {cur[jn * 6], cur[jn * 6 + 1], cur[jn * 6 + 2], cur[jn * 6 + 3]};
         const float4* rec = cur + j * 6;
         Eval e;
@@ -501,7 +545,7 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
           dv = fmaf(dens * dens, e.dt * (1.0f / 3.0f), dv);
           if (logT < -5.5f) {
             active = false;
-            contrib = c * kChunk + j + 1;  // entries walked, the terminating one included
+            contrib = cur_pos[j] + 1;  // entries walked, the terminating one included
             break;
           }
         }
@@ -512,20 +556,20 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
       }
     }
     __syncwarp();
-    if (hit_ids) {  // append the chunk's entries that were hit, in list order
-      const unsigned m = hb[lane16];
+    if (hit_ids) {  // append the batch's entries that were hit, in list order
+      const unsigned m = lane16 < n_cur ? hb[lane16] : 0u;
       const unsigned nzb = (__ballot_sync(0xffffffffu, m != 0u) >> (16 * half)) & 0xFFFFu;
       if (m) {
-        const int64_t slot = hbase + n_hit + __popc(nzb & ((1u << lane16) - 1u));
-        hit_ids[slot] = id_here;
+        const int64_t slot = hbase + n_hit + __popc(nzb & below);
+        hit_ids[slot] = batch_id[warp][half][buf][lane16];
         hit_masks[slot] = (uint16_t)m;
       }
       n_hit += __popc(nzb);
     }
     __syncwarp();
-    unsigned act = __ballot_sync(0xffffffffu, active);
-    fetching = act & half_mask;
-    if (act == 0) break;
+    fetching = __ballot_sync(0xffffffffu, active) & half_mask;
+    buf = nb;
+    n_cur = take;
   }
   cp_async_wait<0>();
   if (active) contrib = u.len;  // walked the whole list
