@@ -406,3 +406,25 @@ def test_full_size_lists_properties(cuda_lib):
     assert tets.shape[0] < (1 << 23)
     same_tile = tile_of[1:] == tile_of[:-1]
     assert bool((k[1:][same_tile] > k[:-1][same_tile]).all())
+
+
+def test_config2_forward_only_case(oracle, cuda_lib):
+    # 100,000 points from 8 Gaussians -> ~673k tets, 800x800, fov 50, forward only: every stage against
+    # the oracle at the full size of the configuration
+    sc = scenes.make_scene(2)
+    tcam = scenes.config_camera(2)
+    H, W = tcam["image_height"], tcam["image_width"]
+    assert (H, W) == (800, 800) and sc["indices"].shape[0] > 600_000
+    ref, got = check_against_oracle(oracle, sc["vertices"], sc["indices"], sc["cell_values"], tcam,
+                                    scene_util.jitter(H, W, 2), check_grad=False)
+    assert ref["sorted_idx"].shape[0] > 5_000_000
+
+
+def test_config3_shaped_scene_fwd_bwd(oracle, cuda_lib):
+    # the benchmark's scene law (clusters + far shell, 40 % empty tets) and ring camera at a size the
+    # oracle renders in seconds: 60,000 points, 480x270
+    sc = scenes.make_scene(3, n_points=60_000)
+    tcam = scenes.config_camera(3, view=5, height=270, width=480)
+    ref, got = check_against_oracle(oracle, sc["vertices"], sc["indices"], sc["cell_values"], tcam,
+                                    scene_util.jitter(270, 480, 9), check_grad=True)
+    assert ref["sorted_idx"].shape[0] > 1_000_000
