@@ -151,6 +151,19 @@ int rm_forward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, cons
                int32_t* n_contributors, const RmHitList* hits, void* stream);
 
 /*
+ * Forward pass of the constant-colour debug renderer.  Replaces splat_tiled of
+ * slang/alphablend_shader.slang:279-330 (alpha_blend :100-182, evaluate_tetra
+ * utils.slang:160-186; host side alphablend_tiled_slang.py:83-128), forward only.
+ *   records: rm_pack_records of cell values (density, r, g, b, 0, 0, 0);
+ *   samples at the pixel centres; output_img[H,W,4] = (r, g, b, transmittance),
+ *   distortion_img[H,W,4], n_contributors[H,W]; a pixel stops once its transmittance
+ *   is below 1/255.  ladder_p must not be 0.
+ */
+int rm_forward_constant_color(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, const float* records,
+                              const RmCamera* cam, float pre_multi, float ladder_p, float* output_img,
+                              float* distortion_img, int32_t* n_contributors, void* stream);
+
+/*
  * Backward integration.  Replaces splat_tiled.bwd / bwd_alpha_blend
  * (slang/alphablend_shader_interp.slang:273-369, host side
  * alphablend_tiled_slang_interp.py:70-112).

@@ -134,6 +134,27 @@ def forward(sorted_idx, tile_ranges, indices, vertices, cell_values, tcam, jitte
     return out, dist, nc
 
 
+def forward_constant_color(sorted_idx, tile_ranges, indices, vertices, rgbs, tcam, pre_multi=100.0, ladder_p=-0.1,
+                           nthreads=0):
+    """Constant-colour debug renderer, forward. rgbs[T,4] = (r, g, b, density).
+    Returns (output_img[H,W,4] = (r,g,b,transmittance), distortion_img[H,W,4], n_contributors[H,W])."""
+    sorted_idx = np.ascontiguousarray(_np(sorted_idx), np.int32)
+    tile_ranges = np.ascontiguousarray(_np(tile_ranges), np.int32)
+    indices = np.ascontiguousarray(_np(indices), np.int32)
+    vertices = np.ascontiguousarray(_np(vertices), np.float32)
+    rgbs = np.ascontiguousarray(_np(rgbs), np.float32)
+    cam = make_camera(tcam)
+    H, W = cam.image_height, cam.image_width
+    out = np.zeros((H, W, 4), np.float32)
+    dist = np.zeros((H, W, 4), np.float32)
+    nc = np.zeros((H, W), np.int32)
+    rc = lib().or_forward_constant_color(_p(sorted_idx), _p(tile_ranges), _p(indices), _p(vertices), _p(rgbs),
+                                         C.byref(cam), C.c_float(pre_multi), C.c_float(ladder_p), _p(out), _p(dist),
+                                         _p(nc), C.c_int(nthreads))
+    assert rc == 0
+    return out, dist, nc
+
+
 def backward(sorted_idx, tile_ranges, indices, vertices, cell_values, tcam, jitter, out_img, dist_img, n_contrib,
              g_img, g_dist, rows=None, nthreads=0, dtype=np.float32):
     """Stage 6. Returns (vertices_grad[V,3], cell_values_grad[T,7])."""

@@ -857,6 +857,72 @@ int or_backward_f64(const int32_t* sorted_idx, const int32_t* tile_ranges, const
                                n_contrib, g_img, g_dist, vgrad, cgrad, row0, row1, nthreads);
 }
 
+// ---------------------------------------------------------------------------
+// Constant-colour debug renderer, forward: slang/alphablend_shader.slang:26-182
+// (tukey_power_ladder, update_distortion_state, update_pixel_state, alpha_blend)
+// with evaluate_tetra of slang/utils.slang:160-186 and the host side
+// alphablend_tiled_slang.py:83-128.  rgbs[T,4] = (r, g, b, density); samples at the
+// pixel centres; alpha = clip(1 - exp(-density * dt), 0, 1) with dt = |t_exit - t_enter|;
+// a miss leaves the pixel unchanged (the reference passes it through the update with
+// alpha 0 and an unwritten distance; its weight is 0).  out_img = (r, g, b,
+// transmittance), dist_img has 4 channels.
+// ---------------------------------------------------------------------------
+static inline float tukey_power_ladder(float x, float p) {
+  float xp = std::fabs(x);
+  float xs = xp / std::fmax(1.0754944e-20f, std::fabs(p - 1.0f));
+  float sgn = x > 0.0f ? 1.0f : (x < 0.0f ? -1.0f : 0.0f);
+  return sgn * std::fabs(p - 1.0f) / p * (std::pow(xs + 1.0f, p) - 1.0f);
+}
+int or_forward_constant_color(const int32_t* sorted_idx, const int32_t* tile_ranges, const int32_t* indices,
+                              const float* vertices, const float* rgbs, const OrCamera* ocam, float pre_multi,
+                              float ladder_p, float* out_img, float* dist_img, int32_t* n_contrib, int nthreads) {
+  Cam<float> cam = load_cam<float>(ocam);
+  const int H = cam.H, W = cam.Wd;
+#ifdef _OPENMP
+  if (nthreads > 0) omp_set_num_threads(nthreads);
+#endif
+#pragma omp parallel for schedule(dynamic, 16)
+  for (int64_t p = 0; p < (int64_t)H * W; ++p) {
+    int y = int(p / W), x = int(p % W);
+    int tile = (y / cam.tile_h) * cam.grid_w + (x / cam.tile_w);
+    int64_t s0 = tile_ranges[2 * tile], s1 = tile_ranges[2 * tile + 1];
+    V3<float> o, d;
+    get_ray(cam, float(x) + 0.5f, float(y) + 0.5f, o, d);
+    float r = 0.f, g = 0.f, b = 0.f, T = 1.f;
+    float dx = 0.f, dy = 0.f, dz = 0.f, dw = 0.f;
+    int contrib = 0;
+    for (int64_t j = s0; j < s1; ++j) {
+      ++contrib;
+      const int64_t id = sorted_idx[j];
+      V3<float> v[4];
+      for (int k = 0; k < 4; ++k) v[k] = load_v(vertices, indices[4 * id + k]);
+      Planes<float> pl;
+      make_planes(v, o, pl);
+      float te, tx;
+      int ie, ix;
+      if (!intersect(pl, d, te, tx, ie, ix)) continue;
+      const float enter = std::fmax(te, 0.0f);
+      const float dt = std::fmax(std::fabs(tx - enter), 0.0f);
+      const float alpha = safe_clip(1.0f - safe_exp(-rgbs[4 * id + 3] * dt), 0.0f, 1.0f);
+      const float weight = T * alpha;
+      const float m = tukey_power_ladder(enter * pre_multi, ladder_p);
+      dx = dx + 2.0f * weight * m * dz;
+      dy = dy + 2.0f * weight * dw;
+      dz = dz + weight;
+      dw = dw + weight * m;
+      r += alpha * rgbs[4 * id + 0] * T;
+      g += alpha * rgbs[4 * id + 1] * T;
+      b += alpha * rgbs[4 * id + 2] * T;
+      T = T * (1.0f - alpha);
+      if (T < 1.0f / 255.0f) break;
+    }
+    out_img[4 * p + 0] = r; out_img[4 * p + 1] = g; out_img[4 * p + 2] = b; out_img[4 * p + 3] = T;
+    dist_img[4 * p + 0] = dx; dist_img[4 * p + 1] = dy; dist_img[4 * p + 2] = dz; dist_img[4 * p + 3] = dw;
+    n_contrib[p] = contrib;
+  }
+  return 0;
+}
+
 // Pixels whose result is decided by floating-point rounding in the reference
 // algorithm itself: a ray that grazes a tet (chord length within `tol` relative
 // of zero, counted either as a hit or as a miss) adds that tet's full density

@@ -17,7 +17,7 @@ RM_STATUS_KEY_OVERFLOW = 2
 SYMBOLS = ["rm_strerror", "rm_version", "rm_bin_workspace_bytes", "rm_list_scratch_bytes", "rm_project_and_bin", "rm_build_tile_lists",
            "rm_pack_records", "rm_forward", "rm_backward", "rm_vertex_backward", "rm_profile_enable",
            "rm_profile_read", "rm_backward_static_scratch", "rm_tet_err",
-           "rm_activate_output"]
+           "rm_activate_output", "rm_forward_constant_color"]
 RM_STATIC_SCRATCH_MAX_TETS = 131072
 RM_ERR_STATIC_SCRATCH = -5
 
@@ -72,6 +72,7 @@ def load():
                                                vp]
     lib.rm_tet_err.argtypes = [vp, vp, vp, cam, vp, vp, i64, vp, vp, vp]
     lib.rm_activate_output.argtypes = [vp, vp, vp, vp, vp, C.c_int, vp, vp, vp, i64, C.c_int, C.c_int, vp, vp]
+    lib.rm_forward_constant_color.argtypes = [vp, vp, vp, cam, C.c_float, C.c_float, vp, vp, vp, vp]
     lib.rm_profile_enable.restype = None
     lib.rm_profile_enable.argtypes = [C.c_int]
     lib.rm_profile_read.argtypes = [C.c_char_p, sz, C.POINTER(C.c_float), C.c_int]

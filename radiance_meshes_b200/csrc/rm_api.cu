@@ -22,6 +22,8 @@ int rm_launch_pack(const int32_t*, const float*, const float*, int64_t, const Rm
                    cudaStream_t);
 int rm_launch_forward(const int32_t*, const int32_t*, const float*, const RmCamera*, const float*, float*, float*,
                       int32_t*, const RmHitList*, cudaStream_t);
+int rm_launch_forward_constant_color(const int32_t*, const int32_t*, const float*, const RmCamera*, float, float,
+                                     float*, float*, int32_t*, cudaStream_t);
 int rm_launch_backward(const int32_t*, const int32_t*, const float*, const RmCamera*, const float*, const float*,
                        const float*, const int32_t*, const RmHitList*, const float*, const float*, const int32_t*,
                        const float*, const float*, int64_t, int64_t, float*, float*, float*, cudaStream_t);
@@ -234,6 +236,24 @@ int rm_forward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, cons
   if (rc) return rc;
   return rm_launch_forward(sorted_tetra_idx, tile_ranges, records, cam, ray_jitter, output_img, distortion_img,
                            n_contributors, hits, static_cast<cudaStream_t>(stream));
+}
+
+int rm_forward_constant_color(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, const float* records,
+                              const RmCamera* cam, float pre_multi, float ladder_p, float* output_img,
+                              float* distortion_img, int32_t* n_contributors, void* stream) {
+  g_last_error[0] = 0;
+  int rc = check_cam(cam);
+  if (rc) return rc;
+  if (!tile_ranges || !output_img || !distortion_img || !n_contributors || ladder_p == 0.0f)
+    return RM_ERR_INVALID_ARG;
+  if (!aligned16(output_img) || !aligned16(distortion_img) || !aligned16(records) ||
+      (reinterpret_cast<uintptr_t>(tile_ranges) & 7))
+    return RM_ERR_WORKSPACE;
+  rc = rm_bind_device(output_img);
+  if (rc) return rc;
+  return rm_launch_forward_constant_color(sorted_tetra_idx, tile_ranges, records, cam, pre_multi, ladder_p,
+                                          output_img, distortion_img, n_contributors,
+                                          static_cast<cudaStream_t>(stream));
 }
 
 int rm_backward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, const float* records,

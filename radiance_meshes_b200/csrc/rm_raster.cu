@@ -395,11 +395,28 @@ __device__ __forceinline__ void halfwarp_sample_box(bool inside, float sx, float
 // half-warps, which execute in lock-step, evaluate equally long batches.
 constexpr int kQueue = 2 * kChunk;
 
+// The Tukey power ladder of the constant-colour variant (slang/alphablend_shader.slang:26-33):
+// sign(x) |p-1|/p ((|x|/|p-1| + 1)^p - 1).
+__device__ __forceinline__ float tukey_power_ladder(float x, float p) {
+  const float q = fmaxf(fabsf(p - 1.0f), 1.0754944e-20f);
+  const float y = fabsf(p - 1.0f) / p * (__powf(fabsf(x) / q + 1.0f, p) - 1.0f);
+  return x > 0.0f ? y : (x < 0.0f ? -y : 0.0f);
+}
+
+// CONST_COLOR = false: the interpolated-colour renderer (slang/alphablend_shader_interp.slang).
+// CONST_COLOR = true: the constant-colour debug renderer (slang/alphablend_shader.slang:100-182,
+// utils.slang:160-186): records packed with a zero colour gradient, samples at the pixel centres
+// (jitter == nullptr), pixel state (rgb, transmittance) with alpha = 1 - exp(-density * dt), four
+// distortion moments weighted by transmittance * alpha with the power ladder of the entry distance,
+// termination when the transmittance falls below 1/255; out_img = (r, g, b, transmittance) and
+// dist_img has four channels.
+template <bool CONST_COLOR>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32, 5)
 k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, const float4* __restrict__ records,
           RmCamera rcam, const float2* __restrict__ jitter, float4* __restrict__ out_img,
           float* __restrict__ dist_img, int32_t* __restrict__ n_contrib, int32_t* __restrict__ hit_counts,
-          int32_t* __restrict__ hit_ids, uint16_t* __restrict__ hit_masks, int subs, int64_t n_units) {
+          int32_t* __restrict__ hit_ids, uint16_t* __restrict__ hit_masks, int subs, int64_t n_units,
+          float pre_multi, float ladder_p) {
   __shared__ __align__(16) float4 stage[kWarpsPerBlock][2][2][kChunk * 6];  // [warp][half][buffer]
   __shared__ unsigned hit_bits[kWarpsPerBlock][2][kChunk];
   __shared__ int queue_id[kWarpsPerBlock][2][kQueue], queue_pos[kWarpsPerBlock][2][kQueue];
@@ -418,7 +435,7 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
   const int64_t pix = (int64_t)u.y * rcam.image_width + u.x;
   float sx = 0.f, sy = 0.f;
   if (u.inside) {
-    float2 j = __ldg(jitter + pix);
+    float2 j = jitter ? __ldg(jitter + pix) : make_float2(0.5f, 0.5f);
     sx = (float)u.x + j.x;
     sy = (float)u.y + j.y;
     d = ray_direction(rcam, sx, sy);
@@ -534,16 +551,29 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
           sr = fmaf(e.cr, T, sr);
           sg = fmaf(e.cg, T, sg);
           sb = fmaf(e.cb, T, sb);
-          logT -= e.tau;
-          T *= e.alpha;
-          float dens = rec[5].w;
-          float m1 = dens * (e.exit + e.enter) * 0.5f;
-          dx = fmaf(2.0f * m1, dz, dx);
-          dy = fmaf(2.0f * dens, dw, dy);
-          dz += dens;
-          dw += m1;
-          dv = fmaf(dens * dens, e.dt * (1.0f / 3.0f), dv);
-          if (logT < -5.5f) {
+          bool finished;
+          if (CONST_COLOR) {
+            const float weight = T * (1.0f - e.alpha);
+            const float m = tukey_power_ladder(e.enter * pre_multi, ladder_p);
+            dx = fmaf(2.0f * weight * m, dz, dx);
+            dy = fmaf(2.0f * weight, dw, dy);
+            dz += weight;
+            dw = fmaf(weight, m, dw);
+            T *= e.alpha;
+            finished = T < 1.0f / 255.0f;
+          } else {
+            logT -= e.tau;
+            T *= e.alpha;
+            float dens = rec[5].w;
+            float m1 = dens * (e.exit + e.enter) * 0.5f;
+            dx = fmaf(2.0f * m1, dz, dx);
+            dy = fmaf(2.0f * dens, dw, dy);
+            dz += dens;
+            dw += m1;
+            dv = fmaf(dens * dens, e.dt * (1.0f / 3.0f), dv);
+            finished = logT < -5.5f;
+          }
+          if (finished) {
             active = false;
             contrib = cur_pos[j] + 1;  // entries walked, the terminating one included
             break;
@@ -576,9 +606,14 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
 
   if (hit_counts && lane16 == 0 && unit < n_units) hit_counts[(int64_t)u.tile * u.subs + u.sub] = n_hit;
   if (u.inside) {
-    out_img[pix] = make_float4(sr, sg, sb, logT);
-    float* o = dist_img + 5 * pix;
-    o[0] = dx; o[1] = dy; o[2] = dz; o[3] = dw; o[4] = dv;
+    if (CONST_COLOR) {
+      out_img[pix] = make_float4(sr, sg, sb, T);
+      reinterpret_cast<float4*>(dist_img)[pix] = make_float4(dx, dy, dz, dw);
+    } else {
+      out_img[pix] = make_float4(sr, sg, sb, logT);
+      float* o = dist_img + 5 * pix;
+      o[0] = dx; o[1] = dy; o[2] = dz; o[3] = dw; o[4] = dv;
+    }
     n_contrib[pix] = contrib;
   }
 }
@@ -1069,10 +1104,28 @@ int rm_launch_forward(const int32_t* list, const int32_t* ranges, const float* r
   unit_grid(cam, &subs, &n_units, &blocks);
   if (n_units == 0) return RM_OK;
   RmProfScope prof("k_forward", st);
-  rm::k_forward<<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
+  rm::k_forward<false><<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
       list, reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam,
       reinterpret_cast<const float2*>(jitter), reinterpret_cast<float4*>(out_img), dist_img, n_contrib,
-      hits ? hits->counts : nullptr, hits ? hits->ids : nullptr, hits ? hits->masks : nullptr, subs, n_units);
+      hits ? hits->counts : nullptr, hits ? hits->ids : nullptr, hits ? hits->masks : nullptr, subs, n_units, 0.0f,
+      0.0f);
+  RM_CUDA_CHECK(cudaPeekAtLastError());
+  return RM_OK;
+}
+
+int rm_launch_forward_constant_color(const int32_t* list, const int32_t* ranges, const float* records,
+                                     const RmCamera* cam, float pre_multi, float ladder_p, float* out_img,
+                                     float* dist_img, int32_t* n_contrib, cudaStream_t st) {
+  int subs;
+  int64_t n_units;
+  unsigned blocks;
+  unit_grid(cam, &subs, &n_units, &blocks);
+  if (n_units == 0) return RM_OK;
+  RmProfScope prof("k_forward<constant colour>", st);
+  rm::k_forward<true><<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
+      list, reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam, nullptr,
+      reinterpret_cast<float4*>(out_img), dist_img, n_contrib, nullptr, nullptr, nullptr, subs, n_units, pre_multi,
+      ladder_p);
   RM_CUDA_CHECK(cudaPeekAtLastError());
   return RM_OK;
 }
