@@ -243,15 +243,17 @@ struct Eval {
   float cr, cg, cb;           // colour contribution
 };
 
-// TRACK = false (forward): only the distances are needed, so the entering and exit
-// distances are plain max/min chains; TRACK = true (backward) also records which
-// plane produced each of them.
+// The entering and exit distances are plain max/min chains over the four planes.
+// TRACK = true (backward) also reports which plane produced each of them: the first
+// plane, in index order, whose distance equals the chain's result (what a running
+// "strictly greater / strictly smaller" update would have kept).
 template <bool TRACK>
 __device__ __forceinline__ bool slab_test(const float4 (&rec)[4], f3 d, float min_t, Eval& e) {
   // Distances are first taken from the camera position (u = -D/den) and shifted
   // by min_t afterwards: t = -(D + min_t*den)/den = u - min_t.
   float ue = -1e30f, ux = 1e30f;
-  int ie = -1, ix = -1;
+  float us[4];
+  bool ent[4], ext[4];
   bool miss = false;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -261,21 +263,22 @@ __device__ __forceinline__ bool slab_test(const float4 (&rec)[4], f3 d, float mi
     const bool par = fabsf(den) < 1e-10f;  // ray parallel to the plane: ignored unless outside
     miss = miss || (par && fmaf(min_t, den, p.w) > 0.0f);
     const bool entering = den < 0.0f;
-    if (TRACK) {
-      if (!par) {
-        if (entering) {
-          if (u > ue) { ue = u; ie = i; }
-        } else {
-          if (u < ux) { ux = u; ix = i; }
-        }
-      }
-    } else {
-      ue = fmaxf(ue, (entering && !par) ? u : -1e30f);
-      ux = fminf(ux, (entering || par) ? 1e30f : u);
-    }
+    us[i] = u;
+    ent[i] = entering && !par;
+    ext[i] = !(entering || par);
+    ue = fmaxf(ue, ent[i] ? u : -1e30f);
+    ux = fminf(ux, ext[i] ? u : 1e30f);
   }
   const float te = ue - min_t, tx = ux - min_t;
   if (miss || te > tx || tx <= 0.0f) return false;
+  int ie = -1, ix = -1;
+  if (TRACK) {
+#pragma unroll
+    for (int i = 3; i >= 0; --i) {
+      if (ent[i] && us[i] == ue) ie = i;
+      if (ext[i] && us[i] == ux) ix = i;
+    }
+  }
   e.te = te; e.tx = tx; e.ie = ie; e.ix = ix;
   e.enter = fmaxf(te, 0.0f);
   e.exit = fmaxf(tx, e.enter);
@@ -329,7 +332,8 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 
 constexpr int kWarpsPerBlock = 4;
 constexpr int kChunk = 16;  // records staged per half-warp per round
-constexpr int kButterflyMinHits = 4;  // fewer hit pixels in a tile: direct atomics instead of the shuffle reduction
+constexpr int kButterflyMinHits = 4;
+constexpr bool kSmemReduce = true;  // per-tile sums by a shared-memory transpose instead of the shuffle butterfly  // fewer hit pixels in a tile: direct atomics instead of the shuffle reduction
 
 struct Unit {
   int tile;       // linear tile index
@@ -630,6 +634,7 @@ k_backward(const int2* __restrict__ ranges, const float4* __restrict__ records, 
   __shared__ __align__(16) float4 stage[kWarpsPerBlock][2][2][kChunk * 6];
   __shared__ int stage_id[kWarpsPerBlock][2][2][kChunk];
   __shared__ unsigned stage_mask[kWarpsPerBlock][2][2][kChunk];  // pixels of the tile that hit the entry (forward)
+  __shared__ __align__(16) float reduce_buf[kWarpsPerBlock][2 * (kChunk * 20 + 16)];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int half = lane >> 4, lane16 = lane & 15;
   const int64_t unit = ((int64_t)blockIdx.x * kWarpsPerBlock + warp) * 2 + half;
@@ -819,15 +824,33 @@ k_backward(const int2* __restrict__ ranges, const float4* __restrict__ records, 
       const bool use_butterfly =
           __ballot_sync(0xffffffffu, odd || (my_hits != 0 && __popc(my_hits) < kButterflyMinHits)) == 0;
       if (use_butterfly) {
-        // 16 -> 8 -> 4 -> 2 -> 1; lane l of a half ends with the total of field l
+        if (kSmemReduce) {
+          // transpose through shared memory: every lane stores its 16 values as a row (stride 20
+          // floats keeps the 128-bit stores aligned and the column reads free of bank conflicts),
+          // then lane l adds up column l
+          float* rb = reduce_buf[warp] + half * (kChunk * 20 + 16);
+          float4* row4 = reinterpret_cast<float4*>(rb + lane16 * 20);
+          row4[0] = make_float4(v[0], v[1], v[2], v[3]);
+          row4[1] = make_float4(v[4], v[5], v[6], v[7]);
+          row4[2] = make_float4(v[8], v[9], v[10], v[11]);
+          row4[3] = make_float4(v[12], v[13], v[14], v[15]);
+          __syncwarp();
+          float sum = 0.0f;
 #pragma unroll
-        for (int w = 8; w >= 1; w >>= 1) {
-          const bool up = lane16 & w;
+          for (int r = 0; r < kChunk; ++r) sum += rb[r * 20 + lane16];
+          __syncwarp();
+          v[0] = sum;
+        } else {
+          // 16 -> 8 -> 4 -> 2 -> 1; lane l of a half ends with the total of field l
 #pragma unroll
-          for (int i = 0; i < w; ++i) {
-            const float send = up ? v[i] : v[i + w];
-            const float keep = up ? v[i + w] : v[i];
-            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, w);
+          for (int w = 8; w >= 1; w >>= 1) {
+            const bool up = lane16 & w;
+#pragma unroll
+            for (int i = 0; i < w; ++i) {
+              const float send = up ? v[i] : v[i + w];
+              const float keep = up ? v[i + w] : v[i];
+              v[i] = keep + __shfl_xor_sync(0xffffffffu, send, w);
+            }
           }
         }
         if (my_hits && v[0] != 0.0f) {
