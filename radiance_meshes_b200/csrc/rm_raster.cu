@@ -243,8 +243,15 @@ struct Eval {
   float cr, cg, cb;           // colour contribution
 };
 
-// The entering and exit distances are plain max/min chains over the four planes.
-// TRACK = true (backward) also reports which plane produced each of them: the first
+// The entering and exit distances are plain max/min chains over the four planes:
+// a plane the ray crosses inwards (den < 0) bounds the entry, one it crosses outwards
+// (den > 0) the exit.  The reference ignores a plane with |den| < 1e-10 unless the
+// origin lies outside it, which is a miss (slang/intersect.slang:478-607).  The chains
+// give the same answers without the special case: such a plane's distance -D/den is
+// huge, positive when the origin is outside (the entry passes the exit: a miss) and
+// negative when it is inside (no effect on the maximum), and symmetrically for the
+// exit; den = 0 gives +-inf, which behaves the same, or NaN, which fmaxf/fminf drop.
+// TRACK = true (backward) also reports which plane produced each distance: the first
 // plane, in index order, whose distance equals the chain's result (what a running
 // "strictly greater / strictly smaller" update would have kept).
 template <bool TRACK>
@@ -253,30 +260,25 @@ __device__ __forceinline__ bool slab_test(const float4 (&rec)[4], f3 d, float mi
   // by min_t afterwards: t = -(D + min_t*den)/den = u - min_t.
   float ue = -1e30f, ux = 1e30f;
   float us[4];
-  bool ent[4], ext[4];
-  bool miss = false;
+  bool ent[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const float4 p = rec[i];
     const float den = p.x * d.x + p.y * d.y + p.z * d.z;
     const float u = __fdividef(-p.w, den);
-    const bool par = fabsf(den) < 1e-10f;  // ray parallel to the plane: ignored unless outside
-    miss = miss || (par && fmaf(min_t, den, p.w) > 0.0f);
-    const bool entering = den < 0.0f;
+    ent[i] = den < 0.0f;
     us[i] = u;
-    ent[i] = entering && !par;
-    ext[i] = !(entering || par);
     ue = fmaxf(ue, ent[i] ? u : -1e30f);
-    ux = fminf(ux, ext[i] ? u : 1e30f);
+    ux = fminf(ux, ent[i] ? 1e30f : u);
   }
   const float te = ue - min_t, tx = ux - min_t;
-  if (miss || te > tx || tx <= 0.0f) return false;
+  if (!(te <= tx) || tx <= 0.0f) return false;
   int ie = -1, ix = -1;
   if (TRACK) {
 #pragma unroll
     for (int i = 3; i >= 0; --i) {
       if (ent[i] && us[i] == ue) ie = i;
-      if (ext[i] && us[i] == ux) ix = i;
+      if (!ent[i] && us[i] == ux) ix = i;
     }
   }
   e.te = te; e.tx = tx; e.ie = ie; e.ix = ix;
