@@ -538,19 +538,13 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
     // ---- evaluate the batch staged one iteration ago
     const float4* cur = stage[warp][half][buf];
     const int* cur_pos = batch_pos[warp][half][buf];
-    unsigned todo = n_cur >= kChunk ? 0xFFFFu : ((1u << n_cur) - 1u);
     // For every entry the pixels that hit it (while still active) are collected in a
     // 16-bit mask in shared memory; the entries with a non-zero mask go to the hit list
     // the backward pass walks.
-    if (active && todo) {
-      int j = 0;
-      float4 pl[4] = {cur[0], cur[1], cur[2], cur[3]};
-      while (true) {
-        todo &= todo - 1;
-        // planes of the next record to evaluate, loaded while this one is tested
-        const int jn = todo ? j + 1 : j;
-        const float4 nx[4] = {cur[jn * 6], cur[jn * 6 + 1], cur[jn * 6 + 2], cur[jn * 6 + 3]};
+    if (active) {
+      for (int j = 0; j < n_cur; ++j) {
         const float4* rec = cur + j * 6;
+        const float4 pl[4] = {rec[0], rec[1], rec[2], rec[3]};
         Eval e;
         if (slab_test<false>(pl, d, min_t, e) && integrate(rec, d, min_t, e)) {
           atomicOr(&hb[j], 1u << lane16);
@@ -585,10 +579,6 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
             break;
           }
         }
-        if (!todo) break;
-        j = jn;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) pl[q] = nx[q];
       }
     }
     __syncwarp();
