@@ -331,6 +331,21 @@ def test_host_frame_pipeline_matches_direct_path():
         for t in out.values():
             t.fill_(float("nan"))
         pipe.step(host, out, tcam)
+    # two frames in flight, each with its own result buffers
+    outs = [out, {k: torch.empty_like(t).pin_memory() for k, t in out.items()}]
+    pipe2 = HostFramePipeline(dev, frames_in_flight=2)
+    tickets = []
+    for i in range(5):
+        if i >= 2:
+            pipe2.wait(tickets[i - 2])
+        for t in outs[i % 2].values():
+            t.fill_(float("nan"))
+        tickets.append(pipe2.submit(host, outs[i % 2], tcam))
+    pipe2.wait(tickets[-2])
+    pipe2.wait(tickets[-1])
+    torch.cuda.synchronize()
+    for k in ("image", "dist"):
+        assert torch.equal(outs[0][k], outs[1][k])
     d = {k: v.to(dev) for k, v in host.items()}
     v = d["vertices"].requires_grad_(True)
     c = d["cell"].requires_grad_(True)
@@ -338,7 +353,8 @@ def test_host_frame_pipeline_matches_direct_path():
     torch.autograd.backward([pkg["image"], pkg["distortion_img"]], [d["g_img"], d["g_dist"]])
     assert torch.equal(out["image"], pkg["image"].detach().cpu())
     assert torch.equal(out["dist"], pkg["distortion_img"].detach().cpu())
-    for got, want in ((out["vg"], v.grad.cpu()), (out["cg"], c.grad.cpu())):   # float atomics: order varies
+    for got, want in ((out["vg"], v.grad.cpu()), (out["cg"], c.grad.cpu()), (outs[1]["vg"], v.grad.cpu()),
+                      (outs[1]["cg"], c.grad.cpu())):   # float atomics: order varies
         assert torch.isfinite(got).all()
         assert float((got - want).norm() / want.norm().clamp_min(1e-20)) < 1e-5
 
