@@ -134,7 +134,8 @@ int rm_build_tile_lists(const int32_t* rect_tile_space, const int32_t* tile_rang
  * coordinates): the staged form of load_tet_alphablend_interp
  * (slang/interp_version.slang:100-153).
  * tiles_touched may be NULL (pack every tet) or [T] (skip culled tets).
- * records[T, RM_RECORD_FLOATS] f32 out, 16-byte aligned.
+ * records[T, RM_RECORD_FLOATS] f32 out, 16-byte aligned; with tiles_touched given, the rows of
+ * culled tets (which appear in no tile list) are left unwritten.
  */
 int rm_pack_records(const int32_t* indices, const float* vertices, const float* cell_values, int64_t n_tets,
                     const RmCamera* cam, const int32_t* tiles_touched, float* records, void* stream);

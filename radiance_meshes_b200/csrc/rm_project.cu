@@ -138,13 +138,20 @@ __device__ __forceinline__ void find_extent_unclipped(const f3 cs[4], f3& mn, f3
     mn = {fminf(mn.x, px), fminf(mn.y, py), fminf(mn.z, p.z)};
     mx = {fmaxf(mx.x, px), fmaxf(mx.y, py), fmaxf(mx.z, p.z)};
   };
-#pragma unroll
-  for (int k = 0; k < 4; ++k) add(cs[k]);
-  // directed edges of the faces (0,1,2) (0,2,3) (0,3,1) (1,3,2)
-  const int ea[12] = {0, 1, 2, 0, 2, 3, 0, 3, 1, 1, 3, 2};
-  const int eb[12] = {1, 2, 0, 2, 3, 0, 3, 1, 0, 3, 2, 1};
-#pragma unroll
-  for (int e = 0; e < 12; ++e) add(lerp3(cs[ea[e]], cs[eb[e]], 1.0f));
+  // One pass per face (a, b, c) = (0,1,2) (0,2,3) (0,3,1) (1,3,2): vertex number `face` and the end
+  // samples of the directed edges a->b, b->c, c->a.  The loop is kept rolled (the vertices are picked
+  // with selects, not indexed) so that the kernel stays small enough for the instruction cache.
+#pragma unroll 1
+  for (int face = 0; face < 4; ++face) {
+    const f3 a = face == 3 ? cs[1] : cs[0];
+    const f3 b = face == 0 ? cs[1] : (face == 1 ? cs[2] : cs[3]);
+    const f3 cc = face == 0 ? cs[2] : (face == 1 ? cs[3] : (face == 2 ? cs[1] : cs[2]));
+    const f3 own = face == 0 ? cs[0] : (face == 1 ? cs[1] : (face == 2 ? cs[2] : cs[3]));
+    add(own);
+    add(lerp3(a, b, 1.0f));
+    add(lerp3(b, cc, 1.0f));
+    add(lerp3(cc, a, 1.0f));
+  }
 }
 
 __device__ __forceinline__ bool is_planar(const f3 v[4]) {

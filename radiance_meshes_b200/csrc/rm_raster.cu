@@ -69,12 +69,15 @@ k_pack_records(const int32_t* __restrict__ indices, const float* __restrict__ ve
                const float* __restrict__ cell, int64_t T, RmCamera rcam, const int32_t* __restrict__ tiles_touched,
                float4* __restrict__ records) {
   __shared__ __align__(16) float4 sm[kPackThreads * kRecStride];
+  __shared__ bool packed[kPackThreads];  // culled tets appear in no list: their rows are not written
   const int64_t g0 = (int64_t)blockIdx.x * kPackThreads;
   const int64_t g = g0 + threadIdx.x;
   float4 r[kRecStride];
 #pragma unroll
   for (int k = 0; k < kRecStride; ++k) r[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (g < T && !(tiles_touched && tiles_touched[g] == 0)) {
+  const bool live = g < T && !(tiles_touched && tiles_touched[g] == 0);
+  packed[threadIdx.x] = live;
+  if (live) {
     f3 cam = {__ldg(rcam.cam_pos), __ldg(rcam.cam_pos + 1), __ldg(rcam.cam_pos + 2)};
     int4 id = __ldg(reinterpret_cast<const int4*>(indices) + g);
     f3 v[4] = {load3(vertices, id.x), load3(vertices, id.y), load3(vertices, id.z), load3(vertices, id.w)};
@@ -159,7 +162,8 @@ k_pack_records(const int32_t* __restrict__ indices, const float* __restrict__ ve
   __syncthreads();
   const int64_t n_rec = min((int64_t)kPackThreads, T - g0);
   float4* out = records + g0 * kRecStride;
-  for (int i = threadIdx.x; i < n_rec * kRecStride; i += kPackThreads) out[i] = sm[i];
+  for (int i = threadIdx.x; i < n_rec * kRecStride; i += kPackThreads)
+    if (packed[i / kRecStride]) out[i] = sm[i];
 }
 
 // True if one of the four hull edge lines of a tet's projection (l0, l1, l2) has the
