@@ -1025,25 +1025,31 @@ k_tet_err(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
 }
 
 // Chain rule from record gradients to vertices and cell values; one thread per tet.
-__global__ void __launch_bounds__(256)
+constexpr int kFinishThreads = 256;
+
+__global__ void __launch_bounds__(kFinishThreads)
 k_backward_finish(const int32_t* __restrict__ indices, const float* __restrict__ vertices,
                   const float* __restrict__ cell, int64_t T, RmCamera rcam, const float4* __restrict__ grec,
                   float* __restrict__ vgrad, float* __restrict__ cgrad) {
-  int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (g >= T) return;
+  // the block's cell-value gradient rows (7 floats per tet) leave through shared memory as
+  // contiguous 16-byte stores
+  __shared__ __align__(16) float rows[kFinishThreads * 7];
+  const int64_t g0 = (int64_t)blockIdx.x * kFinishThreads;
+  const int64_t g = g0 + threadIdx.x;
+  float* co = rows + 7 * threadIdx.x;
   float4 q[6];
   bool any = false;
+  if (g < T) {
 #pragma unroll
-  for (int k = 0; k < 6; ++k) {
-    q[k] = __ldg(grec + 6 * g + k);
-    any = any || q[k].x != 0.f || q[k].y != 0.f || q[k].z != 0.f || q[k].w != 0.f;
+    for (int k = 0; k < 6; ++k) {
+      q[k] = __ldg(grec + 6 * g + k);
+      any = any || q[k].x != 0.f || q[k].y != 0.f || q[k].z != 0.f || q[k].w != 0.f;
+    }
   }
-  float* co = cgrad + 7 * g;
   if (!any) {
 #pragma unroll
     for (int k = 0; k < 7; ++k) co[k] = 0.0f;
-    return;
-  }
+  } else {
   f3 cam = {__ldg(rcam.cam_pos), __ldg(rcam.cam_pos + 1), __ldg(rcam.cam_pos + 2)};
   int4 id = __ldg(reinterpret_cast<const int4*>(indices) + g);
   const int vid[4] = {id.x, id.y, id.z, id.w};
@@ -1088,6 +1094,16 @@ k_backward_finish(const int32_t* __restrict__ indices, const float* __restrict__
   co[4] = g_grd.x;
   co[5] = g_grd.y;
   co[6] = g_grd.z;
+  }
+  __syncthreads();
+  const int n_rows = (int)min((int64_t)kFinishThreads, T - g0);
+  float* dst = cgrad + 7 * g0;  // 7 * 256 floats per block: 16-byte aligned whenever cgrad is
+  if (n_rows == kFinishThreads && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+    for (int i = threadIdx.x; i < kFinishThreads * 7 / 4; i += kFinishThreads)
+      reinterpret_cast<float4*>(dst)[i] = reinterpret_cast<const float4*>(rows)[i];
+  } else {
+    for (int i = threadIdx.x; i < n_rows * 7; i += kFinishThreads) dst[i] = rows[i];
+  }
 }
 
 }  // namespace rm
@@ -1190,7 +1206,7 @@ int rm_launch_backward(const int32_t* list, const int32_t* ranges, const float* 
         hits->ids, hits->masks, reinterpret_cast<const float4*>(g_img), g_dist, grec, subs, n_units);
   }
   RmProfScope prof2("k_backward_finish", st);
-  rm::k_backward_finish<<<(unsigned)((T + 255) / 256), 256, 0, st>>>(indices, vertices, cell, T, *cam,
+  rm::k_backward_finish<<<(unsigned)((T + rm::kFinishThreads - 1) / rm::kFinishThreads), rm::kFinishThreads, 0, st>>>(indices, vertices, cell, T, *cam,
                                                                      reinterpret_cast<const float4*>(grec), vgrad,
                                                                      cgrad);
   RM_CUDA_CHECK(cudaPeekAtLastError());
@@ -1269,7 +1285,7 @@ extern "C" int rm_backward_static_scratch(const int32_t* sorted_tetra_idx, const
         hits->counts, hits->ids, hits->masks, reinterpret_cast<const float4*>(grad_output_img), grad_distortion_img,
         scratch, subs, n_units);
   }
-  rm::k_backward_finish<<<(unsigned)((n_tets + 255) / 256), 256, 0, st>>>(
+  rm::k_backward_finish<<<(unsigned)((n_tets + rm::kFinishThreads - 1) / rm::kFinishThreads), rm::kFinishThreads, 0, st>>>(
       indices, vertices, cell_values, n_tets, *cam, reinterpret_cast<const float4*>(scratch), vertices_grad,
       cell_values_grad);
   RM_CUDA_CHECK(cudaPeekAtLastError());
