@@ -621,7 +621,7 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
 // ----------------------------------------------------------------------------
 // Backward
 // ----------------------------------------------------------------------------
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, 4)
 k_backward(const int2* __restrict__ ranges, const float4* __restrict__ records, RmCamera rcam,
            const float2* __restrict__ jitter, const float4* __restrict__ out_img, const float* __restrict__ dist_img,
            const int32_t* __restrict__ hit_counts, const int32_t* __restrict__ hit_ids,
