@@ -129,8 +129,6 @@ KERNEL_STAGE = {
     "k_project": ("project", 1.0),
     "k_forward": ("forward", 1.0),
     "k_backward": ("backward", 1.0),
-    "k_radix_rowscan+k_tile_scatter1": ("scan_emit", 1.0),
-    "k_radix_rowscan+k_tile_scatter2": ("sort", 1.0),
 }
 
 

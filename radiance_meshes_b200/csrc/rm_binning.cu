@@ -335,7 +335,8 @@ __global__ void k_finish_info(RmBinInfo* info, const unsigned long long* total_k
 // (about 9 times fewer at 1080p with 4 x 4 pixel tiles), so this sort moves a
 // fraction of the pairs.  Every sorted entry carries the tet id and a 32-bit
 // mask of the region's tiles its rectangle covers.
-//   pass 1: generate items, stable split on the low  b1 bits of the region id -> (rank, region) pairs
+//   generate: the (rank, region) pairs, their low-digit histogram and the region populations
+//   pass 1: stable split on the low  b1 bits of the region id
 //   pass 2: stable split on the high b2 bits -> entries (tet id, tile mask)
 // Each pass is: per-block digit histogram, per-digit scan over the blocks,
 // stable scatter (warp-level match ranking, warps own consecutive item spans).
@@ -458,7 +459,8 @@ __device__ __forceinline__ uint2 region_entry(uint32_t rank, uint32_t region, co
   return make_uint2(tet, row * rows);
 }
 
-// Pass-1 digit histogram of the block's items; also the population of every region
+// Generates the block's (rank, region) pairs, writes them out, and forms their pass-1 digit
+// histogram; also the population of every region
 // (region_count, zeroed by the caller), accumulated in shared memory when the
 // region table fits (n_regions_smem = n_regions) and with global atomics otherwise
 // (n_regions_smem = 0).
@@ -466,7 +468,7 @@ __global__ void __launch_bounds__(kBinThreads)
 k_region_hist1(const uint32_t* __restrict__ cum, const uint32_t* __restrict__ start_rank,
                const uint32_t* __restrict__ order, int n_ranked, const int4* __restrict__ rect, int reg_w,
                int64_t n_items, uint32_t bins, uint32_t* __restrict__ hist, int nblk, uint32_t n_regions_smem,
-               uint32_t* __restrict__ region_count) {
+               uint32_t* __restrict__ region_count, uint2* __restrict__ pairs_out) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   uint32_t* win = reinterpret_cast<uint32_t*>(smem_raw);
   uint32_t* s_misc = win + kBinTile + 4;
@@ -482,6 +484,7 @@ k_region_hist1(const uint32_t* __restrict__ cum, const uint32_t* __restrict__ st
   for (int jl = threadIdx.x; jl < cnt; jl += kBinThreads) {
     uint32_t region, rank;
     item_region(jl, j0, r0, before, win, own, order, rect, reg_w, region, rank);
+    pairs_out[j0 + jl] = make_uint2(rank, region);  // generated once; the scatter passes read them back
     atomicAdd(&h[region & (bins - 1)], 1u);
     if (n_regions_smem) atomicAdd(&rh[region], 1u);
     else atomicAdd(region_count + region, 1u);
@@ -503,7 +506,7 @@ k_region_hist2(const uint2* __restrict__ pairs, int64_t n, int shift, uint32_t b
 #pragma unroll
   for (int k = 0; k < kBinItems; ++k) {
     int64_t i = base + k * kBinThreads + threadIdx.x;
-    if (i < n) atomicAdd(&h[pairs[i].y >> shift], 1u);
+    if (i < n) atomicAdd(&h[(pairs[i].y >> shift) & (bins - 1)], 1u);
   }
   __syncthreads();
   for (uint32_t i = threadIdx.x; i < bins; i += kBinThreads) hist[(int64_t)i * nblk + blockIdx.x] = h[i];
@@ -596,76 +599,15 @@ __device__ __forceinline__ void local_layout(uint32_t bins, uint32_t* cnt, uint3
   __syncthreads();
 }
 
-// pass 1.  final != 0: the low digit is the whole region id, write the sorted entries directly.
-// Items are reordered by digit in shared memory first, so that the global
-// writes of one digit's run are contiguous.
+// One stable counting pass on the digit (region >> shift) & (bins - 1).  final == 0: the reordered
+// pairs go to pairs_out; final != 0: the sorted entries (tet id, tile mask) are written instead.
+// Items are reordered by digit in shared memory first, so that the global writes of one digit's
+// run are contiguous.
 __global__ void __launch_bounds__(kBinThreads, 3)
-k_region_scatter1(const uint32_t* __restrict__ cum, const uint32_t* __restrict__ start_rank,
-                  const uint32_t* __restrict__ order, int n_ranked,
-                  const int4* __restrict__ rect, int reg_w, int64_t n_items, uint32_t bins,
-                  const uint32_t* __restrict__ hist, const uint32_t* __restrict__ digit_total, int nblk, int final,
-                  uint2* __restrict__ pairs_out, uint2* __restrict__ entries) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  // [ sbuf (8 B x kBinTile), aliased by win + s_misc + own during generation | dbase | lstart | cnt ]
-  uint2* sbuf = reinterpret_cast<uint2*>(smem_raw);
-  uint32_t* win = reinterpret_cast<uint32_t*>(smem_raw);
-  uint32_t* s_misc = win + kBinTile + 4;
-  uint16_t* own = reinterpret_cast<uint16_t*>(s_misc + 16);
-  uint32_t* dbase = reinterpret_cast<uint32_t*>(smem_raw + 8 * kBinTile);
-  uint32_t* lstart = dbase + bins;
-  uint32_t* cnt = lstart + bins;
-  uint32_t* s_scan = cnt + (size_t)kBinWarps * bins;  // 16 words
-  const int64_t j0 = (int64_t)blockIdx.x * kBinTile;
-  const int cntItems = (int)min((int64_t)kBinTile, n_items - j0);
-  for (uint32_t i = threadIdx.x; i < kBinWarps * bins; i += kBinThreads) cnt[i] = 0;
-  owners_of_items(cum, n_ranked, j0, start_rank, win, own, s_misc);
-  const int r0 = (int)s_misc[8];
-  const uint32_t before = s_misc[9];
-  digit_bases(bins, hist, digit_total, nblk, dbase, s_scan);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  uint32_t* wc = cnt + (size_t)warp * bins;
-  uint32_t tile[kBinItems], rank[kBinItems];
-  uint32_t rnk[kBinItems / 2];  // two 16-bit ranks per word
-  // all gathers first (independent, in flight together), then the ranking rounds,
-  // whose warp barriers would otherwise serialise the loads
-#pragma unroll
-  for (int k = 0; k < kBinItems; ++k) {
-    const int jl = warp * kBinSpan + k * 32 + lane;
-    tile[k] = 0;
-    rank[k] = 0;
-    if (jl < cntItems) item_region(jl, j0, r0, before, win, own, order, rect, reg_w, tile[k], rank[k]);
-  }
-#pragma unroll
-  for (int k = 0; k < kBinItems; ++k) {
-    const bool valid = warp * kBinSpan + k * 32 + lane < cntItems;
-    const uint32_t r = rank_round(tile[k] & (bins - 1), valid, wc, 31 - __clz(bins));
-    if (k & 1) rnk[k >> 1] |= r << 16; else rnk[k >> 1] = r;
-  }
-  __syncthreads();  // win / own are dead from here on: sbuf may overwrite them
-  local_layout(bins, cnt, dbase, lstart, s_scan);
-#pragma unroll
-  for (int k = 0; k < kBinItems; ++k) {
-    const int jl = warp * kBinSpan + k * 32 + lane;
-    if (jl >= cntItems) continue;
-    const uint32_t dgt = tile[k] & (bins - 1);
-    const uint32_t lp = lstart[dgt] + wc[dgt] + ((rnk[k >> 1] >> (16 * (k & 1))) & 0xFFFFu);
-    sbuf[lp] = make_uint2(rank[k], tile[k]);
-  }
-  __syncthreads();
-  for (int lp = threadIdx.x; lp < cntItems; lp += kBinThreads) {
-    const uint2 pr = sbuf[lp];
-    const uint32_t g = dbase[pr.y & (bins - 1)] + (uint32_t)lp;
-    if (final) entries[g] = region_entry(pr.x, pr.y, order, rect, reg_w);
-    else pairs_out[g] = pr;
-  }
-}
-
-// pass 2: stable split on region >> shift; writes the sorted entries.
-__global__ void __launch_bounds__(kBinThreads, 3)
-k_region_scatter2(const uint2* __restrict__ pairs, int64_t n, int shift, uint32_t bins,
-                  const uint32_t* __restrict__ hist, const uint32_t* __restrict__ digit_total, int nblk,
-                  const uint32_t* __restrict__ order, const int4* __restrict__ rect, int reg_w,
-                  uint2* __restrict__ entries) {
+k_region_scatter(const uint2* __restrict__ pairs, int64_t n, int shift, uint32_t bins,
+                 const uint32_t* __restrict__ hist, const uint32_t* __restrict__ digit_total, int nblk, int final,
+                 const uint32_t* __restrict__ order, const int4* __restrict__ rect, int reg_w,
+                 uint2* __restrict__ pairs_out, uint2* __restrict__ entries) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   uint2* sbuf = reinterpret_cast<uint2*>(smem_raw);
   uint32_t* dbase = reinterpret_cast<uint32_t*>(smem_raw + 8 * kBinTile);
@@ -689,7 +631,7 @@ k_region_scatter2(const uint2* __restrict__ pairs, int64_t n, int shift, uint32_
 #pragma unroll
   for (int k = 0; k < kBinItems; ++k) {
     const bool valid = warp * kBinSpan + k * 32 + lane < cntItems;
-    const uint32_t r = rank_round(pr[k].y >> shift, valid, wc, 31 - __clz(bins));
+    const uint32_t r = rank_round((pr[k].y >> shift) & (bins - 1), valid, wc, 31 - __clz(bins));
     if (k & 1) rnk[k >> 1] |= r << 16; else rnk[k >> 1] = r;
   }
   __syncthreads();
@@ -697,14 +639,16 @@ k_region_scatter2(const uint2* __restrict__ pairs, int64_t n, int shift, uint32_
 #pragma unroll
   for (int k = 0; k < kBinItems; ++k) {
     if (warp * kBinSpan + k * 32 + lane >= cntItems) continue;
-    const uint32_t dgt = pr[k].y >> shift;
+    const uint32_t dgt = (pr[k].y >> shift) & (bins - 1);
     const uint32_t lp = lstart[dgt] + wc[dgt] + ((rnk[k >> 1] >> (16 * (k & 1))) & 0xFFFFu);
     sbuf[lp] = pr[k];
   }
   __syncthreads();
   for (int lp = threadIdx.x; lp < cntItems; lp += kBinThreads) {
     const uint2 p2 = sbuf[lp];
-    entries[dbase[p2.y >> shift] + (uint32_t)lp] = region_entry(p2.x, p2.y, order, rect, reg_w);
+    const uint32_t g = dbase[(p2.y >> shift) & (bins - 1)] + (uint32_t)lp;
+    if (final) entries[g] = region_entry(p2.x, p2.y, order, rect, reg_w);
+    else pairs_out[g] = p2;
   }
 }
 
@@ -996,7 +940,7 @@ namespace {
 struct ListPlan {
   int reg_w, reg_h, bits1, bits2, nblk;
   uint32_t n_regions, n_regions_smem, max_chunks;
-  size_t pairs, entries, hist, dtot, starts, region_count, region_start, chunk_base, chunk_region, chunk_cursor,
+  size_t pairs_a, pairs_b, entries, hist, dtot, starts, region_count, region_start, chunk_base, chunk_region, chunk_cursor,
       total;
 };
 constexpr uint32_t kMaxSmemRegions = 16384;  // 64 KB of per-block region counters
@@ -1020,7 +964,8 @@ bool make_list_plan(int64_t n_region_keys, int gh, int gw, ListPlan* P) {
     off = align256(off + bytes);
     return o;
   };
-  P->pairs = take(P->bits2 ? 8 * (size_t)n_region_keys : 0);
+  P->pairs_a = take(8 * (size_t)n_region_keys);
+  P->pairs_b = take(P->bits2 ? 8 * (size_t)n_region_keys : 0);
   P->entries = take(8 * (size_t)n_region_keys);
   P->hist = take(4 * ((size_t)1 << P->bits1) * (size_t)(P->nblk > 0 ? P->nblk : 1));
   P->dtot = take(4 * ((size_t)1 << P->bits1));
@@ -1058,7 +1003,8 @@ int rm_launch_build_lists(const int32_t* rect, const int32_t* tile_ranges, int64
   const uint32_t* cum = reinterpret_cast<uint32_t*>(b + L.cum);
   const uint32_t* tile_start = reinterpret_cast<uint32_t*>(b + L.tile_start);
   char* sb = static_cast<char*>(scratch);
-  uint2* pairs = reinterpret_cast<uint2*>(sb + P.pairs);
+  uint2* pairs_a = reinterpret_cast<uint2*>(sb + P.pairs_a);
+  uint2* pairs_b = reinterpret_cast<uint2*>(sb + P.pairs_b);
   uint2* entries = reinterpret_cast<uint2*>(sb + P.entries);
   uint32_t* hist = reinterpret_cast<uint32_t*>(sb + P.hist);
   uint32_t* dtot = reinterpret_cast<uint32_t*>(sb + P.dtot);
@@ -1075,37 +1021,36 @@ int rm_launch_build_lists(const int32_t* rect, const int32_t* tile_ranges, int64
   const size_t smem_s1 = 8 * rm::kBinTile + 4 * bins1 * (2 + rm::kBinWarps) + 64;
   const size_t smem_s2 = 8 * rm::kBinTile + 4 * bins2 * (2 + rm::kBinWarps) + 64;
   RM_CUDA_CHECK(cudaFuncSetAttribute(rm::k_region_hist1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_h1));
-  RM_CUDA_CHECK(
-      cudaFuncSetAttribute(rm::k_region_scatter1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_s1));
-  RM_CUDA_CHECK(
-      cudaFuncSetAttribute(rm::k_region_scatter2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_s2));
+  RM_CUDA_CHECK(cudaFuncSetAttribute(rm::k_region_scatter, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)(smem_s1 > smem_s2 ? smem_s1 : smem_s2)));
   RM_CUDA_CHECK(cudaMemsetAsync(region_count, 0, 4 * (size_t)(P.n_regions + 1), st));
   {
     RmProfScope prof("k_block_start_ranks+k_region_hist1", st);
     rm::k_block_start_ranks<<<(P.nblk + 255) / 256, 256, 0, st>>>(cum, (int)T, P.nblk, starts);
     rm::k_region_hist1<<<P.nblk, rm::kBinThreads, smem_h1, st>>>(cum, starts, order, (int)T, rect4, P.reg_w,
                                                                 n_region_keys, bins1, hist, P.nblk,
-                                                                P.n_regions_smem, region_count);
+                                                                P.n_regions_smem, region_count, pairs_a);
   }
   {
-    RmProfScope prof("k_radix_rowscan+k_region_scatter1", st);
+    RmProfScope prof("k_radix_rowscan+k_region_scatter(pass 1)", st);
     rm::k_radix_rowscan<<<bins1, 1024, 0, st>>>(hist, P.nblk, dtot);
-    rm::k_region_scatter1<<<P.nblk, rm::kBinThreads, smem_s1, st>>>(cum, starts, order, (int)T, rect4, P.reg_w,
-                                                                   n_region_keys, bins1, hist, dtot, P.nblk,
-                                                                   P.bits2 == 0, pairs, entries);
+    rm::k_region_scatter<<<P.nblk, rm::kBinThreads, smem_s1, st>>>(pairs_a, n_region_keys, 0, bins1, hist, dtot,
+                                                                  P.nblk, P.bits2 == 0, order, rect4, P.reg_w,
+                                                                  pairs_b, entries);
   }
   RM_CUDA_CHECK(cudaPeekAtLastError());
   if (P.bits2) {
     {
       RmProfScope prof("k_region_hist2", st);
-      rm::k_region_hist2<<<P.nblk, rm::kBinThreads, 4 * bins2, st>>>(pairs, n_region_keys, P.bits1, bins2, hist,
+      rm::k_region_hist2<<<P.nblk, rm::kBinThreads, 4 * bins2, st>>>(pairs_b, n_region_keys, P.bits1, bins2, hist,
                                                                     P.nblk);
     }
     {
-      RmProfScope prof("k_radix_rowscan+k_region_scatter2", st);
+      RmProfScope prof("k_radix_rowscan+k_region_scatter(pass 2)", st);
       rm::k_radix_rowscan<<<bins2, 1024, 0, st>>>(hist, P.nblk, dtot);
-      rm::k_region_scatter2<<<P.nblk, rm::kBinThreads, smem_s2, st>>>(pairs, n_region_keys, P.bits1, bins2, hist,
-                                                                     dtot, P.nblk, order, rect4, P.reg_w, entries);
+      rm::k_region_scatter<<<P.nblk, rm::kBinThreads, smem_s2, st>>>(pairs_b, n_region_keys, P.bits1, bins2, hist,
+                                                                    dtot, P.nblk, 1, order, rect4, P.reg_w, nullptr,
+                                                                    entries);
     }
     RM_CUDA_CHECK(cudaPeekAtLastError());
   }
