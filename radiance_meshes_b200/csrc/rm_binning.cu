@@ -335,7 +335,7 @@ __global__ void k_finish_info(RmBinInfo* info, const unsigned long long* total_k
 // (about 9 times fewer at 1080p with 4 x 4 pixel tiles), so this sort moves a
 // fraction of the pairs.  Every sorted entry carries the tet id and a 32-bit
 // mask of the region's tiles its rectangle covers.
-//   generate: the (rank, region) pairs, their low-digit histogram and the region populations
+//   generate: the (tet, region) pairs, their low-digit histogram and the region populations
 //   pass 1: stable split on the low  b1 bits of the region id
 //   pass 2: stable split on the high b2 bits -> entries (tet id, tile mask)
 // Each pass is: per-block digit histogram, per-digit scan over the blocks,
@@ -429,27 +429,27 @@ __device__ __forceinline__ void owners_of_items(const uint32_t* __restrict__ cum
   __syncthreads();
 }
 
-// region id and rank of local item jl
+// region id and tet id of local item jl
 __device__ __forceinline__ void item_region(int jl, int64_t j0, int r0, uint32_t before_r0, const uint32_t* win,
                                             const uint16_t* own, const uint32_t* __restrict__ order,
                                             const int4* __restrict__ rect, int reg_w, uint32_t& region,
-                                            uint32_t& rank) {
+                                            uint32_t& tet) {
   const int i = own[jl];
-  rank = (uint32_t)(r0 + i);
+  const uint32_t rank = (uint32_t)(r0 + i);
   const uint32_t excl = i > 0 ? win[i - 1] : before_r0;
   const uint32_t local = (uint32_t)(j0 + jl - excl);
-  const int4 rc = __ldg(rect + order[rank]);
+  tet = order[rank];
+  const int4 rc = __ldg(rect + tet);
   const uint32_t cx0 = (uint32_t)(rc.x >> kRegShiftX);
   const uint32_t w = (uint32_t)((rc.z - 1) >> kRegShiftX) - cx0 + 1u;
   const uint32_t dy = local / w;
   region = ((uint32_t)(rc.y >> kRegShiftY) + dy) * (uint32_t)reg_w + cx0 + (local - dy * w);
 }
 
-// Sorted entry of (rank, region): the tet id and the mask of the region's tiles (bit = 8 * row + column)
+// Sorted entry of (tet, region): the tet id and the mask of the region's tiles (bit = 8 * row + column)
 // that the tet's rectangle covers.
-__device__ __forceinline__ uint2 region_entry(uint32_t rank, uint32_t region, const uint32_t* __restrict__ order,
-                                              const int4* __restrict__ rect, int reg_w) {
-  const uint32_t tet = order[rank];
+__device__ __forceinline__ uint2 region_entry(uint32_t tet, uint32_t region, const int4* __restrict__ rect,
+                                              int reg_w) {
   const int4 rc = __ldg(rect + tet);
   const int gy = (int)(region / (uint32_t)reg_w), gx = (int)(region - (uint32_t)gy * (uint32_t)reg_w);
   const int lx0 = max(rc.x - gx * kRegW, 0), lx1 = min(rc.z - gx * kRegW, kRegW);
@@ -459,7 +459,7 @@ __device__ __forceinline__ uint2 region_entry(uint32_t rank, uint32_t region, co
   return make_uint2(tet, row * rows);
 }
 
-// Generates the block's (rank, region) pairs, writes them out, and forms their pass-1 digit
+// Generates the block's (tet, region) pairs, writes them out, and forms their pass-1 digit
 // histogram; also the population of every region
 // (region_count, zeroed by the caller), accumulated in shared memory when the
 // region table fits (n_regions_smem = n_regions) and with global atomics otherwise
@@ -482,9 +482,9 @@ k_region_hist1(const uint32_t* __restrict__ cum, const uint32_t* __restrict__ st
   const int r0 = (int)s_misc[8];
   const uint32_t before = s_misc[9];
   for (int jl = threadIdx.x; jl < cnt; jl += kBinThreads) {
-    uint32_t region, rank;
-    item_region(jl, j0, r0, before, win, own, order, rect, reg_w, region, rank);
-    pairs_out[j0 + jl] = make_uint2(rank, region);  // generated once; the scatter passes read them back
+    uint32_t region, tet;
+    item_region(jl, j0, r0, before, win, own, order, rect, reg_w, region, tet);
+    pairs_out[j0 + jl] = make_uint2(tet, region);  // generated once; the scatter passes read them back
     atomicAdd(&h[region & (bins - 1)], 1u);
     if (n_regions_smem) atomicAdd(&rh[region], 1u);
     else atomicAdd(region_count + region, 1u);
@@ -606,8 +606,8 @@ __device__ __forceinline__ void local_layout(uint32_t bins, uint32_t* cnt, uint3
 __global__ void __launch_bounds__(kBinThreads, 3)
 k_region_scatter(const uint2* __restrict__ pairs, int64_t n, int shift, uint32_t bins,
                  const uint32_t* __restrict__ hist, const uint32_t* __restrict__ digit_total, int nblk, int final,
-                 const uint32_t* __restrict__ order, const int4* __restrict__ rect, int reg_w,
-                 uint2* __restrict__ pairs_out, uint2* __restrict__ entries) {
+                 const int4* __restrict__ rect, int reg_w, uint2* __restrict__ pairs_out,
+                 uint2* __restrict__ entries) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   uint2* sbuf = reinterpret_cast<uint2*>(smem_raw);
   uint32_t* dbase = reinterpret_cast<uint32_t*>(smem_raw + 8 * kBinTile);
@@ -647,7 +647,7 @@ k_region_scatter(const uint2* __restrict__ pairs, int64_t n, int shift, uint32_t
   for (int lp = threadIdx.x; lp < cntItems; lp += kBinThreads) {
     const uint2 p2 = sbuf[lp];
     const uint32_t g = dbase[(p2.y >> shift) & (bins - 1)] + (uint32_t)lp;
-    if (final) entries[g] = region_entry(p2.x, p2.y, order, rect, reg_w);
+    if (final) entries[g] = region_entry(p2.x, p2.y, rect, reg_w);
     else pairs_out[g] = p2;
   }
 }
@@ -1035,8 +1035,8 @@ int rm_launch_build_lists(const int32_t* rect, const int32_t* tile_ranges, int64
     RmProfScope prof("k_radix_rowscan+k_region_scatter(pass 1)", st);
     rm::k_radix_rowscan<<<bins1, 1024, 0, st>>>(hist, P.nblk, dtot);
     rm::k_region_scatter<<<P.nblk, rm::kBinThreads, smem_s1, st>>>(pairs_a, n_region_keys, 0, bins1, hist, dtot,
-                                                                  P.nblk, P.bits2 == 0, order, rect4, P.reg_w,
-                                                                  pairs_b, entries);
+                                                                  P.nblk, P.bits2 == 0, rect4, P.reg_w, pairs_b,
+                                                                  entries);
   }
   RM_CUDA_CHECK(cudaPeekAtLastError());
   if (P.bits2) {
@@ -1049,8 +1049,7 @@ int rm_launch_build_lists(const int32_t* rect, const int32_t* tile_ranges, int64
       RmProfScope prof("k_radix_rowscan+k_region_scatter(pass 2)", st);
       rm::k_radix_rowscan<<<bins2, 1024, 0, st>>>(hist, P.nblk, dtot);
       rm::k_region_scatter<<<P.nblk, rm::kBinThreads, smem_s2, st>>>(pairs_b, n_region_keys, P.bits1, bins2, hist,
-                                                                    dtot, P.nblk, 1, order, rect4, P.reg_w, nullptr,
-                                                                    entries);
+                                                                    dtot, P.nblk, 1, rect4, P.reg_w, nullptr, entries);
     }
     RM_CUDA_CHECK(cudaPeekAtLastError());
   }
