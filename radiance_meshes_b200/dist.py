@@ -19,11 +19,32 @@ import torch
 import torch.distributed as dist
 
 
+def _covering_view(grads):
+    """If the tensors are contiguous views of one storage, a flat view of that storage from the first to the
+    last of them (the gaps between them are padding); else None."""
+    if len(grads) < 2 or any(not g.is_contiguous() or g.dtype != grads[0].dtype for g in grads):
+        return None
+    base = grads[0].untyped_storage().data_ptr()
+    if any(g.untyped_storage().data_ptr() != base for g in grads):
+        return None
+    lo = min(g.storage_offset() for g in grads)
+    hi = max(g.storage_offset() + g.numel() for g in grads)
+    if hi - lo > 2 * sum(g.numel() for g in grads):
+        return None
+    return torch.empty(0, dtype=grads[0].dtype, device=grads[0].device).set_(
+        grads[0].untyped_storage(), lo, (hi - lo,))
+
+
 def allreduce_gradients(grads, group=None):
-    """Sum each gradient tensor over the ranks, in place. Returns the list."""
+    """Sum each gradient tensor over the ranks, in place. Returns the list.  Tensors that share one
+    allocation (as the two gradients of the rasterizer's backward pass do) are summed with one call."""
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
-        for g in grads:
-            dist.all_reduce(g, op=dist.ReduceOp.SUM, group=group)
+        flat = _covering_view(grads)
+        if flat is not None:
+            dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
+        else:
+            for g in grads:
+                dist.all_reduce(g, op=dist.ReduceOp.SUM, group=group)
     return grads
 
 

@@ -181,8 +181,14 @@ def backward(sorted_idx, tile_ranges, records, cam, ray_jitter, output_img, dist
     T, V = indices.shape[0], vertices.shape[0]
     with torch.cuda.device(dev):
         grad_records = torch.empty((T, _lib.RM_GRAD_RECORD_FLOATS), dtype=torch.float32, device=dev)
-        vertices_grad = torch.empty((V, 3), dtype=torch.float32, device=dev)
-        cell_grad = torch.empty((T, 7), dtype=torch.float32, device=dev)
+        # both gradients live in one allocation (the second one 16-byte aligned), so that a multi-GPU
+        # job can sum them over the ranks with a single all-reduce (dist.allreduce_gradients)
+        off = (3 * V + 3) // 4 * 4
+        flat = torch.empty((off + 7 * T,), dtype=torch.float32, device=dev)
+        vertices_grad = flat[:3 * V].view(V, 3)
+        cell_grad = flat[off:].view(T, 7)
+        if off > 3 * V:
+            flat[3 * V:off].zero_()
         _lib.check(lib.rm_backward(_ptr(sorted_idx), _ptr(tile_ranges), _ptr(records), cam.ref, _ptr(ray_jitter),
                                    _ptr(output_img), _ptr(distortion_img), _ptr(n_contributors), hit_list_ref(hits),
                                    _ptr(grad_output_img), _ptr(grad_distortion_img), _ptr(indices), _ptr(vertices),

@@ -74,8 +74,15 @@ def _worker(rank, world, port, results):
             return torch.from_numpy(out)
         full, band = rmdist.render_band_split(band_fn, tcam["grid_height"], tcam["tile_height"], rank, world,
                                               row_weights=weights.numpy())
+        # --- gradients that share one allocation are summed with a single collective, padding included
+        flat = torch.arange(20, dtype=torch.float32) * (rank + 1)
+        a, b = flat[:6].view(2, 3), flat[8:15].view(1, 7)
+        separate = [torch.full((3,), float(rank + 1)), torch.full((2, 2), 10.0 * (rank + 1))]
+        rmdist.allreduce_gradients([a, b])
+        rmdist.allreduce_gradients(separate)
         results[rank] = dict(vg=vg.numpy(), cg=cg.numpy(), n_images=len(images), full=full.numpy(), band=band,
-                             weights=weights.numpy())
+                             weights=weights.numpy(), flat=flat.numpy(), covering=rmdist._covering_view([a, b]).numel(),
+                             separate=[t.numpy() for t in separate])
     finally:
         dist.destroy_process_group()
 
@@ -106,6 +113,13 @@ def test_two_rank_view_parallel_and_band_split(oracle):
     # weights are the per-row key counts
     lens = (ranges_full[:, 1] - ranges_full[:, 0]).reshape(_view(0)["grid_height"], -1).sum(1)
     np.testing.assert_array_equal(results[0]["weights"], lens)
+    # shared-allocation gradients: one collective over the covering view (ranks hold 1x and 2x the ramp)
+    for r in range(2):
+        assert results[r]["covering"] == 15
+        np.testing.assert_array_equal(results[r]["flat"][:15], 3.0 * np.arange(15, dtype=np.float32))
+        np.testing.assert_array_equal(results[r]["flat"][15:], (r + 1.0) * np.arange(15, 20, dtype=np.float32))
+        np.testing.assert_array_equal(results[r]["separate"][0], np.full((3,), 3.0, np.float32))
+        np.testing.assert_array_equal(results[r]["separate"][1], np.full((2, 2), 30.0, np.float32))
 
 
 def test_band_lists_are_subsets_of_full_lists(oracle):
