@@ -3,7 +3,7 @@
 
 python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload config3|config2|small]
 
-One JSON line on stdout (rank 0).  See DESIGN.md for the definition of every field.
+One JSON line on stdout (rank 0).
 """
 import argparse
 import json
@@ -435,7 +435,8 @@ def run_gpu(args):
         roofline = dict(bound="hbm", kernel=dominant, achieved=achieved, peak=peak, peak_source=peak_src,
                         unit="GB/s", frac=(achieved / peak) if achieved else None, traffic=None,
                         kernel_ms=kernel_ms[dominant], algorithmic_bytes=bytes_alg,
-                        note="issue-bound kernel: ~16 pixel evaluations per staged record; see DESIGN.md")
+                        note="issue-bound kernel (about 16 pixel evaluations per staged record): the HBM fraction is low by "
+                             "construction")
     frame_bytes = sum(alg.values())
     line = dict(
         metric="fwd+bwd Mpix/s at 1080p, 6.5M tets", value=value, unit="Mpix/s", n_gpus=world, steps=args.steps,
