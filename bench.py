@@ -432,8 +432,16 @@ def run_gpu(args):
         stage, share = KERNEL_STAGE.get(dominant, (None, 1.0))
         bytes_alg = alg[stage] * share if stage else None
         achieved = bytes_alg / (kernel_ms[dominant] * 1e-3) / 1e9 if bytes_alg else None
+        # DRAM traffic per launch: dram__bytes_read + write of one ncu capture on the 300k-point scene
+        # (a --set full capture of the full-size launch is too large), scaled by the ratio of the stage's
+        # algorithmic bytes; None for kernels that were not captured
+        captured = {"k_backward": (486.7e6, 572.2e6), "k_forward": (520.4e6, 437.3e6)}
+        traffic = None
+        if dominant in captured and bytes_alg:
+            traffic = captured[dominant][0] * bytes_alg / captured[dominant][1]
         roofline = dict(bound="hbm", kernel=dominant, achieved=achieved, peak=peak, peak_source=peak_src,
-                        unit="GB/s", frac=(achieved / peak) if achieved else None, traffic=None,
+                        unit="GB/s", frac=(achieved / peak) if achieved else None, traffic=traffic,
+                        traffic_source="ncu capture on the 300k-point scene scaled by algorithmic bytes",
                         kernel_ms=kernel_ms[dominant], algorithmic_bytes=bytes_alg,
                         note="issue-bound kernel (about 16 pixel evaluations per staged record): the HBM fraction is low by "
                              "construction")
