@@ -102,7 +102,9 @@ def look_at(eye, target=(0.0, 0.0, 0.0), up=(0.0, 1.0, 0.0)):
 
 
 def make_tcam(viewmat, height, width, fov_deg, tile=4, min_t=0.1, camera_type=0, distortion=None):
-    """tcam dictionary with NumPy values (the caller converts the arrays to device tensors)."""
+    """tcam dictionary with NumPy values (the caller converts the arrays to device tensors).
+    `tile` is the tile edge in pixels, or (tile_height, tile_width)."""
+    tile_h, tile_w = (tile, tile) if isinstance(tile, int) else (int(tile[0]), int(tile[1]))
     fovy = math.radians(fov_deg)
     fy = height / (2 * math.tan(fovy / 2))
     fx = fy
@@ -116,8 +118,8 @@ def make_tcam(viewmat, height, width, fov_deg, tile=4, min_t=0.1, camera_type=0,
         image_height=int(height), image_width=int(width), fovy=float(fovy), fovx=float(fovx),
         distortion_params=np.zeros(4, np.float32) if distortion is None else np.asarray(distortion, np.float32),
         camera_type=int(camera_type),
-        tile_height=int(tile), tile_width=int(tile),
-        grid_height=(height + tile - 1) // tile, grid_width=(width + tile - 1) // tile,
+        tile_height=tile_h, tile_width=tile_w,
+        grid_height=(height + tile_h - 1) // tile_h, grid_width=(width + tile_w - 1) // tile_w,
         min_t=float(min_t),
     )
 

@@ -444,3 +444,23 @@ def test_config3_shaped_scene_fwd_bwd(oracle, cuda_lib):
     ref, got = check_against_oracle(oracle, sc["vertices"], sc["indices"], sc["cell_values"], tcam,
                                     scene_util.jitter(270, 480, 9), check_grad=True)
     assert ref["sorted_idx"].shape[0] > 1_000_000
+
+
+@pytest.mark.parametrize("seed", list(range(8)))
+def test_random_configurations(oracle, cuda_lib, seed):
+    """Seeded sweep over image sizes, tile shapes, camera placements and densities: every stage against the
+    oracle.  Exercises ragged tiles, non-square tiles, several 16-pixel groups per tile, regions cut by the
+    image border and cameras inside the mesh."""
+    rng = np.random.default_rng(1000 + seed)
+    H, W = int(rng.integers(17, 140)), int(rng.integers(17, 180))
+    th, tw = [(2, 2), (4, 4), (8, 8), (16, 16), (4, 8), (8, 4), (2, 16), (5, 3)][seed]
+    n_points = int(rng.integers(80, 700))
+    pts, tets, cell = scene_util.small_scene(n_points, seed=50 + seed, zero_frac=float(rng.uniform(0.0, 0.6)),
+                                             sigma=float(rng.uniform(0.5, 2.0)))
+    r = float(rng.uniform(0.2, 3.0))                       # below ~1: the camera sits inside the point cloud
+    ang = rng.uniform(0, 2 * np.pi, 2)
+    eye = (r * np.cos(ang[0]) * np.cos(ang[1]), r * np.sin(ang[1]), r * np.sin(ang[0]) * np.cos(ang[1]))
+    tcam = scenes.make_tcam(scenes.look_at(eye), H, W, float(rng.uniform(35, 100)), tile=(th, tw),
+                            min_t=float(rng.uniform(0.01, 0.3)))
+    check_against_oracle(oracle, pts, tets, cell, tcam, scene_util.jitter(H, W, seed), seed=seed, check_grad=True,
+                         max_flips=0.02)
