@@ -1,7 +1,7 @@
 """Benchmark of the rasterizer hot path: forward+backward Mpix/s at 1920x1080 over a
 ~6.5M-tet synthetic unbounded-scene mesh (one view per GPU).
 
-python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload config3|config2|small]
+python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload config3|config2|config4|small|medium]
 
 One JSON line on stdout (rank 0).
 """
@@ -27,6 +27,7 @@ WORKLOADS = {
     "config2": (2, None, 2),
     "small": (3, 60_000, 3),
     "medium": (3, 300_000, 3),
+    "config4": (4, None, 4),   # 3M points -> ~20M tets; the triangulation alone takes minutes
 }
 CACHE_DIR = os.environ.get("RM_BENCH_CACHE", "/tmp/rm_b200_cache")
 

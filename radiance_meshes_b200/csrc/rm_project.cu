@@ -36,6 +36,9 @@ __device__ __forceinline__ f3 point2camspace(f3 p, const DevCam& c) {
 #pragma unroll
   for (int i = 0; i < 4; ++i)
     h[i] = c.W[4 * i + 0] * p.x + c.W[4 * i + 1] * p.y + c.W[4 * i + 2] * p.z + c.W[4 * i + 3] * 1.0f;
+  // A rigid world-to-camera transform has the last row (0, 0, 0, 1): w is exactly 1 and x / 1 is x, so
+  // the three guarded divisions reduce to the clip (same bits, far fewer instructions).
+  if (h[3] == 1.0f) return {safe_clipf(h[0], -1e20f, 1e20f), safe_clipf(h[1], -1e20f, 1e20f), safe_clipf(h[2], -1e20f, 1e20f)};
   return {safe_divf(h[0], h[3]), safe_divf(h[1], h[3]), safe_divf(h[2], h[3])};
 }
 
