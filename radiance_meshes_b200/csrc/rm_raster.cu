@@ -9,21 +9,28 @@
 // test), slang/camera.slang:241-346 (ray generation).
 //
 // Design (not the reference's structure):
-//   * Tets are packed once per frame into 96-byte records holding the four
-//     outward face planes relative to the CAMERA POSITION (n_i, D_i) and the
-//     colour field folded to (grd, s0 = grd.(cam - v0), base, density).  The
-//     per-pixel origin offset o = cam + min_t*d only shifts each plane distance
-//     by min_t*(n_i.d), so the per-(pixel,tet) work drops from four cross
-//     products to four dot products.
+//   * Tets are packed once per frame into 144-byte records: the four outward
+//     face planes relative to the CAMERA POSITION (n_i, D_i), the colour field
+//     folded to (grd, s0 = grd.(cam - v0), base, density) - 96 bytes that are
+//     staged in shared memory - and the edge lines of the tet's projected hull
+//     (48 bytes, read only to decide whether a tet can touch a tile's samples).
+//     The per-pixel origin offset o = cam + min_t*d only shifts each plane
+//     distance by min_t*(n_i.d), so the per-(pixel,tet) work drops from four
+//     cross products to four dot products.
 //   * A half-warp owns 16 pixels of one tile; a warp therefore walks two tile
-//     lists in lock-step.  Records are staged 16 at a time per half-warp into
-//     shared memory with 128-bit cp.async copies, double buffered, and a
-//     half-warp stops fetching as soon as all of its pixels have terminated.
-//   * Backward accumulates gradients with respect to the 24 record fields:
-//     a transposed butterfly reduction over the 16 pixels (23 shuffles) leaves
-//     each lane with at most two sums, added to a per-tet row with one atomic
-//     each; a per-tet kernel then applies the chain rule to vertices and cell
-//     values (12 vertex atomics per tet instead of 19 atomics per pixel hit).
+//     lists in lock-step.  Forward: the list is examined 16 entries at a time
+//     (hull lines against the box of the half-warp's samples); candidates queue
+//     up in shared memory and are staged 16 at a time with 128-bit cp.async
+//     copies, double buffered, so both half-warps evaluate equally long batches.
+//     A half-warp stops as soon as all of its pixels have terminated.  Every
+//     entry that some pixel hit is appended, with the mask of those pixels, to
+//     the half-warp's hit list.
+//   * Backward walks the hit lists back to front and accumulates gradients with
+//     respect to 16 of the 24 record fields per hit (entering plane, exit plane,
+//     colour fields): the 16 pixels' values are summed through a shared-memory
+//     transpose when they share both faces, else added with 128-bit atomics, into
+//     a per-tet row; a per-tet kernel then applies the chain rule to vertices and
+//     cell values (12 vertex atomics per tet instead of 19 atomics per pixel hit).
 
 #include "rm_common.cuh"
 
@@ -338,8 +345,7 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 
 constexpr int kWarpsPerBlock = 4;
 constexpr int kChunk = 16;  // records staged per half-warp per round
-constexpr int kButterflyMinHits = 4;
-constexpr bool kSmemReduce = true;  // per-tile sums by a shared-memory transpose instead of the shuffle butterfly  // fewer hit pixels in a tile: direct atomics instead of the shuffle reduction
+constexpr int kTileSumMinHits = 4;  // fewer hit pixels in a tile: every pixel adds its own values with atomics
 
 struct Unit {
   int tile;       // linear tile index
@@ -807,8 +813,8 @@ k_backward(const int2* __restrict__ ranges, const float4* __restrict__ records, 
       }
       // Reduction over the pixels of a tile.  If every contributing lane of a half
       // enters through the same face and leaves through the same face, and enough
-      // lanes hit, the 16 sums are formed with a transposed butterfly (15 shuffles,
-      // one atomic per lane); otherwise each hit lane adds its own 16 values.
+      // lanes hit, the 16 sums are formed first (shared-memory transpose, one atomic
+      // per lane); otherwise each hit lane adds its own 16 values.
       const unsigned my_hits = (hits >> (16 * half)) & 0xFFFFu;
       const unsigned e_lanes = (__ballot_sync(0xffffffffu, pe >= 0) >> (16 * half)) & 0xFFFFu;
       const unsigned x_lanes = (__ballot_sync(0xffffffffu, px >= 0) >> (16 * half)) & 0xFFFFu;
@@ -817,43 +823,28 @@ k_backward(const int2* __restrict__ ranges, const float4* __restrict__ records, 
       const int pe_ref = __shfl_sync(0xffffffffu, pe, src_e);
       const int px_ref = __shfl_sync(0xffffffffu, px, src_x);
       const bool odd = (pe >= 0 && pe != pe_ref) || (px >= 0 && px != px_ref);
-      const bool use_butterfly =
-          __ballot_sync(0xffffffffu, odd || (my_hits != 0 && __popc(my_hits) < kButterflyMinHits)) == 0;
-      if (use_butterfly) {
-        if (kSmemReduce) {
-          // transpose through shared memory: every lane stores its 16 values as a row (stride 20
-          // floats keeps the 128-bit stores aligned and the column reads free of bank conflicts),
-          // then lane l adds up column l
-          float* rb = reduce_buf[warp] + half * (kChunk * 20 + 16);
-          float4* row4 = reinterpret_cast<float4*>(rb + lane16 * 20);
-          row4[0] = make_float4(v[0], v[1], v[2], v[3]);
-          row4[1] = make_float4(v[4], v[5], v[6], v[7]);
-          row4[2] = make_float4(v[8], v[9], v[10], v[11]);
-          row4[3] = make_float4(v[12], v[13], v[14], v[15]);
-          __syncwarp();
-          float sum = 0.0f;
+      const bool sum_over_tile =
+          __ballot_sync(0xffffffffu, odd || (my_hits != 0 && __popc(my_hits) < kTileSumMinHits)) == 0;
+      if (sum_over_tile) {
+        // transpose through shared memory: every lane stores its 16 values as a row (stride 20
+        // floats keeps the 128-bit stores aligned and the column reads free of bank conflicts),
+        // then lane l adds up column l
+        float* rb = reduce_buf[warp] + half * (kChunk * 20 + 16);
+        float4* row4 = reinterpret_cast<float4*>(rb + lane16 * 20);
+        row4[0] = make_float4(v[0], v[1], v[2], v[3]);
+        row4[1] = make_float4(v[4], v[5], v[6], v[7]);
+        row4[2] = make_float4(v[8], v[9], v[10], v[11]);
+        row4[3] = make_float4(v[12], v[13], v[14], v[15]);
+        __syncwarp();
+        float sum = 0.0f;
 #pragma unroll
-          for (int r = 0; r < kChunk; ++r) sum += rb[r * 20 + lane16];
-          __syncwarp();
-          v[0] = sum;
-        } else {
-          // 16 -> 8 -> 4 -> 2 -> 1; lane l of a half ends with the total of field l
-#pragma unroll
-          for (int w = 8; w >= 1; w >>= 1) {
-            const bool up = lane16 & w;
-#pragma unroll
-            for (int i = 0; i < w; ++i) {
-              const float send = up ? v[i] : v[i + w];
-              const float keep = up ? v[i + w] : v[i];
-              v[i] = keep + __shfl_xor_sync(0xffffffffu, send, w);
-            }
-          }
-        }
-        if (my_hits && v[0] != 0.0f) {
+        for (int r = 0; r < kChunk; ++r) sum += rb[r * 20 + lane16];
+        __syncwarp();
+        if (my_hits && sum != 0.0f) {
           float* row = grec + (int64_t)cur_id[j] * 24;
           const int f = lane16;
           const int dst = f < 4 ? 4 * pe_ref + f : (f < 8 ? 4 * px_ref + (f - 4) : f + 8);
-          if (dst >= 0) atomicAdd(row + dst, v[0]);
+          if (dst >= 0) atomicAdd(row + dst, sum);
         }
       } else if (hit) {
         // 128-bit reductions: a plane's four sums and the colour sums are 16-byte aligned
@@ -996,7 +987,7 @@ k_tet_err(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
         atomicAdd(tet_count + 2 * (int64_t)g, __popc(my_hits));
         atomicMax(tet_count + 2 * (int64_t)g + 1, tmax);
       }
-      if (max(__popc(hits & 0xFFFFu), __popc(hits >> 16)) >= kButterflyMinHits) {
+      if (max(__popc(hits & 0xFFFFu), __popc(hits >> 16)) >= kTileSumMinHits) {
 #pragma unroll
         for (int w = 8; w >= 1; w >>= 1) {
           const bool up = lane16 & w;
