@@ -34,7 +34,8 @@ class AlphaBlendTiledRender(torch.autograd.Function):
         output_img, distortion_img, n_contributors, hits = raster.forward(
             sorted_tetra_idx, tile_ranges, records, cam, jitter, want_hit_masks=need_grad)
         if hits is None:  # nothing to differentiate: backward is never called
-            hits = tuple(torch.empty((0,), dtype=dt, device=dev) for dt in (torch.int32, torch.int32, torch.int16))
+            hits = tuple(torch.empty((0,), dtype=dt, device=dev)
+                         for dt in (torch.int32, torch.int32, torch.int16, torch.uint8))
         # never written by the reference kernel either: always False
         tet_alive = torch.zeros((indices.shape[0],), dtype=torch.bool, device=dev)
         ctx.save_for_backward(sorted_tetra_idx, tile_ranges, indices, verts, cell, output_img, distortion_img,
@@ -46,9 +47,9 @@ class AlphaBlendTiledRender(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output_img, grad_distortion_img, grad_vert_alive):
         (sorted_tetra_idx, tile_ranges, indices, verts, cell, output_img, distortion_img, n_contributors, jitter,
-         records, hit_counts, hit_ids, hit_masks) = ctx.saved_tensors
+         records, hit_counts, hit_ids, hit_masks, tet_flags) = ctx.saved_tensors
         vertices_grad, cell_grad = raster.backward(
             sorted_tetra_idx, tile_ranges, records, ctx.cam, jitter, output_img, distortion_img, n_contributors,
-            (hit_counts, hit_ids, hit_masks), grad_output_img.contiguous().float(),
+            (hit_counts, hit_ids, hit_masks, tet_flags), grad_output_img.contiguous().float(),
             grad_distortion_img.contiguous().float(), indices, verts, cell)
         return None, None, None, vertices_grad, cell_grad, None, None, None

@@ -77,12 +77,16 @@ typedef struct RmBinInfo {
  *   counts[G*S] i32   number of such entries of the unit
  *   ids[N*S] i32      their tet ids, unit (t, s) at [start(t)*S + s*len(t), ... + counts)
  *   masks[N*S] u16    for each, the pixels of the group that hit it (bit = pixel index)
+ *   tet_flags[T] u8   set to 1 for every tet that appears in some hit list; the caller
+ *                     zero-fills it before rm_forward.  The backward pass clears and reads
+ *                     the record-gradient rows of flagged tets only.
  * with start/len from tile_ranges.  Slots beyond a unit's count are left unwritten.
  */
 typedef struct RmHitList {
   int32_t* counts;
   int32_t* ids;
   uint16_t* masks;
+  uint8_t* tet_flags;
 } RmHitList;
 
 const char* rm_strerror(int code);
@@ -170,7 +174,8 @@ int rm_forward_constant_color(const int32_t* sorted_tetra_idx, const int32_t* ti
  * alphablend_tiled_slang_interp.py:70-112).
  *   hits are the hit lists rm_forward wrote for the same lists and inputs (sorted_tetra_idx and
  *   n_contributors are accepted for symmetry with the reference's call and not read);
- *   grad_records[T, RM_GRAD_RECORD_FLOATS] is caller-provided scratch (zeroed here);
+ *   grad_records[T, RM_GRAD_RECORD_FLOATS] is caller-provided scratch (the rows of flagged tets are
+ *   zeroed here; the others are neither written nor read);
  *   vertices_grad[V,3] and cell_values_grad[T,7] are fully written (zeroed here first).
  */
 int rm_backward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, const float* records,

@@ -31,7 +31,7 @@ class RmCamera(C.Structure):
 
 
 class RmHitList(C.Structure):
-    _fields_ = [("counts", C.c_void_p), ("ids", C.c_void_p), ("masks", C.c_void_p)]
+    _fields_ = [("counts", C.c_void_p), ("ids", C.c_void_p), ("masks", C.c_void_p), ("tet_flags", C.c_void_p)]
 
 
 class RmBinInfo(C.Structure):

@@ -228,7 +228,7 @@ int rm_forward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, cons
   int rc = check_cam(cam);
   if (rc) return rc;
   if (!tile_ranges || !ray_jitter || !output_img || !distortion_img || !n_contributors) return RM_ERR_INVALID_ARG;
-  if (hits && (!hits->counts || !hits->ids || !hits->masks)) return RM_ERR_INVALID_ARG;
+  if (hits && (!hits->counts || !hits->ids || !hits->masks || !hits->tet_flags)) return RM_ERR_INVALID_ARG;
   if (!aligned16(output_img) || !aligned16(records) || (reinterpret_cast<uintptr_t>(ray_jitter) & 7) ||
       (reinterpret_cast<uintptr_t>(tile_ranges) & 7))
     return RM_ERR_WORKSPACE;
@@ -267,7 +267,7 @@ int rm_backward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, con
   if (rc) return rc;
   if (n_tets < 0 || n_vertices < 0) return RM_ERR_INVALID_ARG;
   if (!tile_ranges || !ray_jitter || !output_img || !distortion_img || !hits || !hits->counts || !hits->ids ||
-      !hits->masks || !grad_output_img || !grad_distortion_img || !vertices_grad)
+      !hits->masks || !hits->tet_flags || !grad_output_img || !grad_distortion_img || !vertices_grad)
     return RM_ERR_INVALID_ARG;
   if (n_tets > 0 && (!indices || !vertices || !cell_values || !grad_records || !cell_values_grad || !records))
     return RM_ERR_INVALID_ARG;

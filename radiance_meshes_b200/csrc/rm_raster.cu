@@ -431,8 +431,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32, 5)
 k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, const float4* __restrict__ records,
           RmCamera rcam, const float2* __restrict__ jitter, float4* __restrict__ out_img,
           float* __restrict__ dist_img, int32_t* __restrict__ n_contrib, int32_t* __restrict__ hit_counts,
-          int32_t* __restrict__ hit_ids, uint16_t* __restrict__ hit_masks, int subs, int64_t n_units,
-          float pre_multi, float ladder_p) {
+          int32_t* __restrict__ hit_ids, uint16_t* __restrict__ hit_masks, uint8_t* __restrict__ tet_flags,
+          int subs, int64_t n_units, float pre_multi, float ladder_p) {
   __shared__ __align__(16) float4 stage[kWarpsPerBlock][2][2][kChunk * 6];  // [warp][half][buffer]
   __shared__ unsigned hit_bits[kWarpsPerBlock][2][kChunk];
   __shared__ int queue_id[kWarpsPerBlock][2][kQueue], queue_pos[kWarpsPerBlock][2][kQueue];
@@ -597,8 +597,10 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
       const unsigned nzb = (__ballot_sync(0xffffffffu, m != 0u) >> (16 * half)) & 0xFFFFu;
       if (m) {
         const int64_t slot = hbase + n_hit + __popc(nzb & below);
-        hit_ids[slot] = batch_id[warp][half][buf][lane16];
+        const int id = batch_id[warp][half][buf][lane16];
+        hit_ids[slot] = id;
         hit_masks[slot] = (uint16_t)m;
+        tet_flags[id] = 1;  // this tet receives a gradient
       }
       n_hit += __popc(nzb);
     }
@@ -1015,13 +1017,21 @@ k_tet_err(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
   cp_async_wait<0>();
 }
 
+// Clears the record-gradient rows (6 float4 each) of the tets flagged by the forward pass.
+__global__ void __launch_bounds__(256)
+k_clear_flagged_rows(const uint8_t* __restrict__ tet_flags, int64_t T, float4* __restrict__ grec) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= 6 * T) return;
+  if (tet_flags[i / 6]) grec[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
 // Chain rule from record gradients to vertices and cell values; one thread per tet.
 constexpr int kFinishThreads = 256;
 
 __global__ void __launch_bounds__(kFinishThreads)
 k_backward_finish(const int32_t* __restrict__ indices, const float* __restrict__ vertices,
                   const float* __restrict__ cell, int64_t T, RmCamera rcam, const float4* __restrict__ grec,
-                  float* __restrict__ vgrad, float* __restrict__ cgrad) {
+                  const uint8_t* __restrict__ tet_flags, float* __restrict__ vgrad, float* __restrict__ cgrad) {
   // the block's cell-value gradient rows (7 floats per tet) leave through shared memory as
   // contiguous 16-byte stores
   __shared__ __align__(16) float rows[kFinishThreads * 7];
@@ -1030,7 +1040,7 @@ k_backward_finish(const int32_t* __restrict__ indices, const float* __restrict__
   float* co = rows + 7 * threadIdx.x;
   float4 q[6];
   bool any = false;
-  if (g < T) {
+  if (g < T && tet_flags[g]) {  // rows of tets without a hit were neither cleared nor written
 #pragma unroll
     for (int k = 0; k < 6; ++k) {
       q[k] = __ldg(grec + 6 * g + k);
@@ -1133,8 +1143,8 @@ int rm_launch_forward(const int32_t* list, const int32_t* ranges, const float* r
   rm::k_forward<false><<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
       list, reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam,
       reinterpret_cast<const float2*>(jitter), reinterpret_cast<float4*>(out_img), dist_img, n_contrib,
-      hits ? hits->counts : nullptr, hits ? hits->ids : nullptr, hits ? hits->masks : nullptr, subs, n_units, 0.0f,
-      0.0f);
+      hits ? hits->counts : nullptr, hits ? hits->ids : nullptr, hits ? hits->masks : nullptr,
+      hits ? hits->tet_flags : nullptr, subs, n_units, 0.0f, 0.0f);
   RM_CUDA_CHECK(cudaPeekAtLastError());
   return RM_OK;
 }
@@ -1150,8 +1160,8 @@ int rm_launch_forward_constant_color(const int32_t* list, const int32_t* ranges,
   RmProfScope prof("k_forward<constant colour>", st);
   rm::k_forward<true><<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
       list, reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam, nullptr,
-      reinterpret_cast<float4*>(out_img), dist_img, n_contrib, nullptr, nullptr, nullptr, subs, n_units, pre_multi,
-      ladder_p);
+      reinterpret_cast<float4*>(out_img), dist_img, n_contrib, nullptr, nullptr, nullptr, nullptr, subs, n_units,
+      pre_multi, ladder_p);
   RM_CUDA_CHECK(cudaPeekAtLastError());
   return RM_OK;
 }
@@ -1184,7 +1194,8 @@ int rm_launch_backward(const int32_t* list, const int32_t* ranges, const float* 
   (void)n_contrib;  // the hit lists already stop at every pixel's last contributor
   RM_CUDA_CHECK(cudaMemsetAsync(vgrad, 0, sizeof(float) * 3 * (size_t)V, st));
   if (T == 0) return RM_OK;
-  RM_CUDA_CHECK(cudaMemsetAsync(grec, 0, sizeof(float) * 24 * (size_t)T, st));
+  rm::k_clear_flagged_rows<<<(unsigned)((6 * T + 255) / 256), 256, 0, st>>>(hits->tet_flags, T,
+                                                                            reinterpret_cast<float4*>(grec));
   int subs;
   int64_t n_units;
   unsigned blocks;
@@ -1198,8 +1209,8 @@ int rm_launch_backward(const int32_t* list, const int32_t* ranges, const float* 
   }
   RmProfScope prof2("k_backward_finish", st);
   rm::k_backward_finish<<<(unsigned)((T + rm::kFinishThreads - 1) / rm::kFinishThreads), rm::kFinishThreads, 0, st>>>(indices, vertices, cell, T, *cam,
-                                                                     reinterpret_cast<const float4*>(grec), vgrad,
-                                                                     cgrad);
+                                                                     reinterpret_cast<const float4*>(grec),
+                                                                     hits->tet_flags, vgrad, cgrad);
   RM_CUDA_CHECK(cudaPeekAtLastError());
   return RM_OK;
 }
@@ -1231,7 +1242,7 @@ extern "C" int rm_backward_static_scratch(const int32_t* sorted_tetra_idx, const
   if (n_tets < 0 || n_vertices < 0 || !cam) return RM_ERR_INVALID_ARG;
   if (n_tets > RM_STATIC_SCRATCH_MAX_TETS) return RM_ERR_STATIC_SCRATCH;
   if (!tile_ranges || !ray_jitter || !output_img || !distortion_img || !hits || !hits->counts || !hits->ids ||
-      !hits->masks || !grad_output_img || !grad_distortion_img || !vertices_grad)
+      !hits->masks || !hits->tet_flags || !grad_output_img || !grad_distortion_img || !vertices_grad)
     return RM_ERR_INVALID_ARG;
   (void)sorted_tetra_idx;
   (void)n_contributors;
@@ -1264,7 +1275,8 @@ extern "C" int rm_backward_static_scratch(const int32_t* sorted_tetra_idx, const
   // The array keeps the previous call's sums: clear the rows this call accumulates into.
   RM_CUDA_CHECK(cudaMemsetAsync(vertices_grad, 0, sizeof(float) * 3 * (size_t)n_vertices, st));
   if (n_tets == 0) return RM_OK;
-  RM_CUDA_CHECK(cudaMemsetAsync(scratch, 0, sizeof(float) * RM_GRAD_RECORD_FLOATS * (size_t)n_tets, st));
+  rm::k_clear_flagged_rows<<<(unsigned)((6 * n_tets + 255) / 256), 256, 0, st>>>(hits->tet_flags, n_tets,
+                                                                                 reinterpret_cast<float4*>(scratch));
   int subs;
   int64_t n_units;
   unsigned blocks;
@@ -1277,8 +1289,8 @@ extern "C" int rm_backward_static_scratch(const int32_t* sorted_tetra_idx, const
         scratch, subs, n_units);
   }
   rm::k_backward_finish<<<(unsigned)((n_tets + rm::kFinishThreads - 1) / rm::kFinishThreads), rm::kFinishThreads, 0, st>>>(
-      indices, vertices, cell_values, n_tets, *cam, reinterpret_cast<const float4*>(scratch), vertices_grad,
-      cell_values_grad);
+      indices, vertices, cell_values, n_tets, *cam, reinterpret_cast<const float4*>(scratch), hits->tet_flags,
+      vertices_grad, cell_values_grad);
   RM_CUDA_CHECK(cudaPeekAtLastError());
   return RM_OK;
 }

@@ -13,7 +13,7 @@ from . import _lib
 LAUNCHES_PROJECT_AND_BIN = 1 + 12 + 2 + 3 + 1 + 3 + 1
 LAUNCHES_BUILD_LISTS = 11
 LAUNCHES_FORWARD = 2
-LAUNCHES_BACKWARD = 2
+LAUNCHES_BACKWARD = 3
 
 
 def _ptr(t):
@@ -144,13 +144,13 @@ def hit_list_ref(hits):
     """ctypes argument for a hit list given as the (counts, ids, masks) tensors forward() returns."""
     if hits is None:
         return None
-    counts, ids, masks = hits
-    return C.byref(_lib.RmHitList(_ptr(counts), _ptr(ids), _ptr(masks)))
+    counts, ids, masks, tet_flags = hits
+    return C.byref(_lib.RmHitList(_ptr(counts), _ptr(ids), _ptr(masks), _ptr(tet_flags)))
 
 
 def forward(sorted_idx, tile_ranges, records, cam, ray_jitter, want_hit_masks=True):
     """Returns (output_img, distortion_img, n_contributors, hits); hits = (counts int32 [G*S], ids int32 [N*S],
-    masks int16 [N*S]) are the hit lists backward() walks, None if not requested."""
+    masks int16 [N*S], tet_flags uint8 [T]) are the hit lists backward() walks, None if not requested."""
     lib = _lib.load()
     dev = records.device
     H, W = cam.c.image_height, cam.c.image_width
@@ -167,7 +167,8 @@ def forward(sorted_idx, tile_ranges, records, cam, ray_jitter, want_hit_masks=Tr
             units = cam.c.grid_height * cam.c.grid_width * groups
             hits = (alloc((units,), dtype=torch.int32, device=dev),
                     torch.empty((slots,), dtype=torch.int32, device=dev),
-                    torch.empty((slots,), dtype=torch.int16, device=dev))
+                    torch.empty((slots,), dtype=torch.int16, device=dev),
+                    torch.zeros((max(int(records.shape[0]), 1),), dtype=torch.uint8, device=dev))
         _lib.check(lib.rm_forward(_ptr(sorted_idx), _ptr(tile_ranges), _ptr(records), cam.ref, _ptr(ray_jitter),
                                   _ptr(output_img), _ptr(distortion_img), _ptr(n_contributors), hit_list_ref(hits),
                                   _stream(dev)))

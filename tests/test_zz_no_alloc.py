@@ -89,7 +89,7 @@ def test_static_scratch_rejects_oversized_mesh(cuda_lib):
     cam.tile_row_end = 4
     rc = cuda_lib.rm_backward_static_scratch(
         _p(dummy), _p(dummy), _p(dummy), C.byref(cam), _p(dummy), _p(dummy), _p(dummy), _p(dummy),
-        C.byref(_lib.RmHitList(_p(dummy), _p(dummy), _p(dummy))),
+        C.byref(_lib.RmHitList(_p(dummy), _p(dummy), _p(dummy), _p(dummy))),
         _p(dummy), _p(dummy), _p(dummy), _p(dummy), _p(dummy), _lib.RM_STATIC_SCRATCH_MAX_TETS + 1, 4, _p(dummy),
         _p(dummy), None)
     assert rc == _lib.RM_ERR_STATIC_SCRATCH
