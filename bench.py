@@ -490,6 +490,98 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+def run_bands(args):
+    """One large frame split over the ranks by tile-row bands (forward only, strong scaling): the mesh of
+    the workload seen by a 3840x2160, 90 degree camera on the ring.  Every rank projects all tets with the
+    rectangles clamped to its band, builds the band's lists, renders it, and the bands are combined with one
+    all-reduce.  The bands are balanced by the per-row pair counts of the same view (known from the
+    previous frame in a moving sequence), computed before the timed region."""
+    import torch
+    import torch.distributed as dist
+    from delaunay_rasterization.internal.render_grid import RenderGrid
+    from delaunay_rasterization.internal.tile_shader_slang import vertex_and_tile_shader
+    from radiance_meshes_b200 import _lib
+    from radiance_meshes_b200 import dist as rmdist
+    from radiance_meshes_b200.render import render, tcam_to_device
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.load()
+    if rank == 0:
+        sc = load_scene(args.workload, 0, world)
+    if world > 1:
+        dist.barrier()
+    if rank != 0:
+        sc = load_scene(args.workload, rank, world)
+    H, W, tile = 2160, 3840, 4
+    tcam_np = scenes.ring_camera(0, 8, H, W, 90.0, tile=tile)
+    tcam = tcam_to_device(tcam_np, dev)
+    ind = torch.from_numpy(sc["indices"]).to(dev)
+    ver = torch.from_numpy(sc["vertices"]).to(dev)
+    cell = torch.from_numpy(sc["cell_values"]).to(dev)
+    jit = torch.rand((H, W, 2), device=dev, generator=torch.Generator(device=dev).manual_seed(5))
+    grid = RenderGrid(H, W, tile_height=tile, tile_width=tile)
+    with torch.no_grad():
+        sidx, ranges, _, _, mask, rect = vertex_and_tile_shader(ind, ver, tcam, grid)
+        weights = rmdist.row_weights_from_rects(rect, mask.to(torch.int32), grid.grid_height).cpu().numpy()
+        n_pairs = int(sidx.shape[0])
+        del sidx, ranges, rect
+    band = rmdist.tile_row_bands(grid.grid_height, world, weights)[rank]
+
+    def band_fn(b):
+        t = dict(tcam)
+        t["tile_rows"] = b
+        return render(ind, ver, cell, t, jit)["image"]
+
+    def step():
+        with torch.no_grad():
+            full, _ = rmdist.render_band_split(band_fn, grid.grid_height, tile, rank, world, row_weights=weights)
+        return full
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(1.5)
+    for _ in range(args.warmup):
+        step()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        line = dict(metric="fwd Mpix/s, one 3840x2160 frame split in tile-row bands", value=H * W / (ms * 1e-3) / 1e6,
+                    unit="Mpix/s", n_gpus=world, steps=args.steps, warmup=args.warmup, ms_per_step=ms,
+                    higher_is_better=True, scaling="strong", vs_baseline=None, dtype="f32", data="synthetic",
+                    config=dict(workload=f"{args.workload} mesh ({sc['indices'].shape[0]} tets), 3840x2160, fov 90, "
+                                         f"tile 4, forward only, {world} tile-row band(s)",
+                                tile_tet_pairs=n_pairs, band_rows_rank0=list(band),
+                                l2_policy="inputs larger than L2"),
+                    clocks=clocks)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -498,12 +590,18 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="config3", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--mode", default="views", choices=["views", "bands"],
+                    help="views: one view per GPU, fwd+bwd, gradients all-reduced (the headline metric); "
+                         "bands: one 4K frame split by tile-row bands, forward only")
     args = ap.parse_args()
     if args.impl == "reference":
         if args.steps > 4:
             args.steps = 4
         args.warmup = min(args.warmup, 1)
         run_reference(args)
+    elif args.mode == "bands":
+        args.warmup = max(args.warmup, 3)
+        run_bands(args)
     else:
         args.warmup = max(args.warmup, 3)
         run_gpu(args)
