@@ -86,18 +86,32 @@ def row_weights_from_rects(rect_tile_space, tiles_touched, grid_height):
     return torch.cumsum(diff, 0)[:grid_height]
 
 
-def combine_band_images(local_image, band, tile_height, group=None):
+def combine_band_images(local_image, band, tile_height, group=None, bands=None):
     """Full image from per-rank band images.
 
     local_image is full-size [H, W, C] with valid rows only inside the rank's band
-    (other rows are ignored). Returns the full image on every rank.
+    (other rows are ignored). Returns the full image on every rank.  With `bands` (the
+    bands of all ranks, as tile_row_bands returns them) only the band rows travel, in one
+    all-gather of equally sized, padded blocks; without it the images are summed.
     """
     H = local_image.shape[0]
     r0, r1 = band
     y0, y1 = min(r0 * tile_height, H), min(r1 * tile_height, H)
+    multi = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+    if multi and bands is not None:
+        rows = [(min(b0 * tile_height, H), min(b1 * tile_height, H)) for b0, b1 in bands]
+        m = max(1, max(b - a for a, b in rows))
+        send = torch.zeros((m,) + tuple(local_image.shape[1:]), dtype=local_image.dtype, device=local_image.device)
+        send[:y1 - y0] = local_image[y0:y1]
+        recv = [torch.empty_like(send) for _ in rows]
+        dist.all_gather(recv, send, group=group)
+        out = torch.zeros_like(local_image)
+        for (a, b), block in zip(rows, recv):
+            out[a:b] = block[:b - a]
+        return out
     out = torch.zeros_like(local_image)
     out[y0:y1] = local_image[y0:y1]
-    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+    if multi:
         dist.all_reduce(out, op=dist.ReduceOp.SUM, group=group)
     return out
 
@@ -134,4 +148,4 @@ def render_band_split(render_band_fn, grid_height, tile_height, rank, world_size
     if local is None:
         # a rank without rows still has to join the collective with the right shape
         local = render_band_fn((0, 0))
-    return combine_band_images(local, band, tile_height, group), band
+    return combine_band_images(local, band, tile_height, group, bands=bands), band
