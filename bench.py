@@ -133,8 +133,10 @@ KERNEL_STAGE = {
 }
 
 
-def cpu_baseline(sc, tcam, tile_rows=8):
-    """Shader-math CPU oracle (OpenMP, all cores) on a band of tile rows of the same frame."""
+def cpu_baseline(sc, tcam, jitter, g_img, g_dist, tile_rows=8):
+    """Shader-math CPU oracle (OpenMP, all cores) on a band of tile rows of the same frame, with the
+    frame's own jitter and upstream gradients.  Returns the timing entry and the oracle's results on
+    the band, which `band_parity` compares with the GPU frame."""
     from oracle import oracle as O
     H, W = tcam["image_height"], tcam["image_width"]
     th = tcam["tile_height"]
@@ -149,23 +151,65 @@ def cpu_baseline(sc, tcam, tile_rows=8):
     tt, rect = O.restrict_to_tile_rows(pr["tiles_touched"], pr["rect"], r0, r1)
     idx, ranges = O.build_lists(tt, rect, pr["vs_tetra"], tcam["grid_height"], tcam["grid_width"])
     t_lists = time.time() - t0
-    jit = np.full((H, W, 2), 0.5, np.float32)
     t0 = time.time()
-    out, dist, nc = O.forward(idx, ranges, sc["indices"], sc["vertices"], sc["cell_values"], tcam, jit, rows=rows)
+    out, dist, nc = O.forward(idx, ranges, sc["indices"], sc["vertices"], sc["cell_values"], tcam, jitter, rows=rows)
     t_fwd = time.time() - t0
-    rng = np.random.default_rng(0)
-    g_img = rng.normal(size=(H, W, 4)).astype(np.float32)
-    g_dist = (0.01 * rng.normal(size=(H, W, 5))).astype(np.float32)
+    # pixels the reference algorithm itself decides by rounding carry no upstream gradient on either side
+    keep = ~O.sensitive_pixels(idx, ranges, sc["indices"], sc["vertices"], sc["cell_values"], tcam, jitter, tol=2e-5)
+    band = np.zeros((H, W), bool)
+    band[rows[0]:rows[1]] = True
+    gm = (keep & band)[..., None]
+    g_img_b, g_dist_b = (g_img * gm).astype(np.float32), (g_dist * gm).astype(np.float32)
     t0 = time.time()
-    O.backward(idx, ranges, sc["indices"], sc["vertices"], sc["cell_values"], tcam, jit, out, dist, nc, g_img, g_dist,
-               rows=rows)
+    vg, cg = O.backward(idx, ranges, sc["indices"], sc["vertices"], sc["cell_values"], tcam, jitter, out, dist, nc,
+                        g_img_b, g_dist_b, rows=rows)
     t_bwd = time.time() - t0
     npx = (rows[1] - rows[0]) * W
     total = t_proj * npx / (H * W) + t_lists + t_fwd + t_bwd
-    return dict(value=npx / total / 1e6, unit="Mpix/s", cores=cores, kind="port",
-                sample=(f"shader-math CPU oracle (C++/OpenMP) on pixel rows {rows[0]}..{rows[1]} of the same frame: "
-                        f"project(all tets) {t_proj:.2f}s scaled by the band's share, lists {t_lists:.2f}s, "
-                        f"forward {t_fwd:.2f}s, backward {t_bwd:.2f}s"))
+    entry = dict(value=npx / total / 1e6, unit="Mpix/s", cores=cores, kind="port",
+                 sample=(f"shader-math CPU oracle (C++/OpenMP) on pixel rows {rows[0]}..{rows[1]} of the same frame: "
+                         f"project(all tets) {t_proj:.2f}s scaled by the band's share, lists {t_lists:.2f}s, "
+                         f"forward {t_fwd:.2f}s, backward {t_bwd:.2f}s"))
+    ref = dict(rows=rows, tile_rows=(r0, r1), project=pr, idx=idx, ranges=ranges, out=out, dist=dist, keep=keep,
+               g_img=g_img_b, g_dist=g_dist_b, vg=vg, cg=cg)
+    return entry, ref
+
+
+def rel_l2(a, b):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
+
+
+def band_parity(ref, tcam_np, render_frame):
+    """The benchmarked frame against the oracle on the oracle's band (outside the timed region).
+    `render_frame(g_img, g_dist)` renders the full frame on the GPU with the given upstream gradients and
+    returns the package plus both gradients as NumPy arrays."""
+    gw = tcam_np["grid_width"]
+    r0, r1 = ref["tile_rows"]
+    y0, y1 = ref["rows"]
+    got = render_frame(ref["g_img"], ref["g_dist"])
+    pr = ref["project"]
+    rect_ok = bool(np.array_equal(got["rect"], pr["rect"]) and
+                   np.array_equal(got["vs_tetra"].view(np.uint32), pr["vs_tetra"].view(np.uint32)))
+    g_rng, o_rng = got["tile_ranges"][r0 * gw:r1 * gw], ref["ranges"][r0 * gw:r1 * gw]
+    g_len, o_len = g_rng[:, 1] - g_rng[:, 0], o_rng[:, 1] - o_rng[:, 0]
+    lists_ok = bool(np.array_equal(g_len, o_len))
+    if lists_ok and o_len.sum() > 0:
+        nz = np.nonzero(g_len)[0]
+        g_seg = got["sorted_tetra_idx"][g_rng[nz[0], 0]:g_rng[nz[-1], 1]]
+        o_seg = ref["idx"][o_rng[nz[0], 0]:o_rng[nz[-1], 1]]
+        lists_ok = bool(np.array_equal(g_seg, o_seg))
+    keep = ref["keep"][y0:y1]
+    return dict(rows=[int(y0), int(y1)], band_list_entries=int(o_len.sum()),
+                rect_and_depth_bit_exact_all_tets=rect_ok, tile_lists_bit_exact=lists_ok,
+                image_rel_l2=rel_l2(got["image"][y0:y1], ref["out"][y0:y1]),
+                distortion_rel_l2=rel_l2(got["distortion_img"][y0:y1][keep], ref["dist"][y0:y1][keep]),
+                vertices_grad_rel_l2=rel_l2(got["vertices_grad"], ref["vg"]),
+                cell_grad_rel_l2=rel_l2(got["cell_grad"], ref["cg"]),
+                rounding_decided_pixels=float(1.0 - keep.mean()),
+                tolerances=dict(image=1e-4, gradients=1e-3),
+                note="GPU full frame vs CPU oracle on the band; upstream gradients zero outside the band and on "
+                     "pixels the reference algorithm decides by rounding")
 
 
 def run_reference(args):
@@ -179,7 +223,9 @@ def run_reference(args):
     sc = load_scene(args.workload)
     tcam = camera_for(args.workload, 0)
     H, W = tcam["image_height"], tcam["image_width"]
-    cores = O.num_threads()
+    # all host cores this process may run on (a launcher such as torchrun exports OMP_NUM_THREADS=1, which
+    # the OpenMP runtime would otherwise inherit)
+    cores = len(os.sched_getaffinity(0))
     # 64 samples per ray keep a 30-step run within a few minutes (each sample tests every tet); the
     # reference's own tests use 5 000-10 000 samples, so this flatters its CPU path by two orders of magnitude
     n_samples = 64
@@ -190,7 +236,7 @@ def run_reference(args):
     def step(i):
         p0 = center + i * cores
         O.quad_render(sc["vertices"], sc["indices"], vc, td, H, W, tcam["world_view_transform"], fx, fy,
-                      tcam["min_t"], n_samples, pixels=(p0, p0 + cores), want_grad=True)
+                      tcam["min_t"], n_samples, pixels=(p0, p0 + cores), want_grad=True, nthreads=cores)
 
     for i in range(args.warmup):
         step(-1 - i)
@@ -204,7 +250,8 @@ def run_reference(args):
     line = dict(impl="reference", metric="fwd+bwd Mpix/s at 1080p, 6.5M tets", value=value, unit="Mpix/s",
                 n_gpus=args.gpus, steps=args.steps, warmup=args.warmup, ms_per_step=1e3 * dt / args.steps,
                 higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f64", data="synthetic",
-                config=dict(workload=workload_name(args.workload, sc, tcam)),
+                config=dict(workload=workload_name(args.workload, sc, tcam), tets=int(sc["indices"].shape[0]),
+                            vertices=int(sc["vertices"].shape[0])),
                 cpu_baseline=dict(value=value, unit="Mpix/s", cores=cores, kind="port", sample=sample),
                 e2e=dict(value=value, unit="Mpix/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
                 gpu_launches=0)
@@ -255,14 +302,23 @@ def run_gpu(args):
     tcam = tcam_to_device(tcam_np, dev)
     T, V = sc["indices"].shape[0], sc["vertices"].shape[0]
 
-    def step(inp):
+    ar_events = []
+
+    def step(inp, reduce=True, time_allreduce=False):
         v = inp["vertices"].requires_grad_(True)
         c = inp["cell"].requires_grad_(True)
         v.grad = None
         c.grad = None
         pkg = render(inp["indices"], v, c, tcam, inp["jitter"])
         torch.autograd.backward([pkg["image"], pkg["distortion_img"]], [inp["g_img"], inp["g_dist"]])
-        rmdist.allreduce_gradients([v.grad, c.grad])
+        if reduce and world > 1:
+            if time_allreduce:
+                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a0.record()
+            rmdist.allreduce_gradients([v.grad, c.grad])
+            if time_allreduce:
+                a1.record()
+                ar_events.append((a0, a1))
         return pkg, v.grad, c.grad
 
     def barrier():
@@ -280,7 +336,8 @@ def run_gpu(args):
     # ---- device-resident arm -------------------------------------------------------------------
     # The clock sampler is started before the warm-up so that nvidia-smi's own start-up
     # (about a second of driver queries) does not fall into the timed region; it keeps
-    # sampling every 200 ms under load until the timed region ends.
+    # sampling every 200 ms under load until the timed region ends.  Per-kernel event
+    # profiling stays off here; it runs in a separate short loop afterwards.
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -288,20 +345,47 @@ def run_gpu(args):
     for _ in range(args.warmup):
         pkg, vg, cg = step(d)
     barrier()
-    _lib.profile_read()
-    _lib.profile_enable(True)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    launches0 = _lib.launch_count()
     barrier()
-    e0.record()
-    for _ in range(args.steps):
-        pkg, vg, cg = step(d)
-    e1.record()
+    evs[0].record()
+    for i in range(args.steps):
+        pkg, vg, cg = step(d, time_allreduce=True)
+        evs[i + 1].record()
     barrier()
     clocks = sampler.stop() if rank == 0 else None
+    launches = _lib.launch_count() - launches0
+    per_step = [evs[i].elapsed_time(evs[i + 1]) for i in range(args.steps)]
+    ms_local = evs[0].elapsed_time(evs[-1]) / args.steps
+    ms_step = max_over_ranks(ms_local)
+    ms_median = max_over_ranks(float(np.median(per_step)))
+    value = H * W * world / (ms_step * 1e-3) / 1e6
+    allreduce = None
+    rank_ms = [ms_local]
+    if world > 1:
+        ar_ms = float(np.mean([a.elapsed_time(b) for a, b in ar_events]))
+        ar_bytes = (vg.numel() + cg.numel()) * 4
+        t = torch.tensor([ms_local, ar_ms], device=dev, dtype=torch.float64)
+        allr = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(allr, t)
+        rank_ms = [float(x[0].item()) for x in allr]
+        ar_all = [float(x[1].item()) for x in allr]
+        # the collective's own duration is what the rank that arrives LAST waits; earlier ranks also wait for it
+        ar_min = min(ar_all)
+        allreduce = dict(bytes=ar_bytes, ms_min_over_ranks=ar_min, ms_max_over_ranks=max(ar_all),
+                         bus_gbs=2 * (world - 1) / world * ar_bytes / (ar_min * 1e-3) / 1e9,
+                         note="CUDA events around the NCCL all-reduce of both gradients inside every timed step; the "
+                              "minimum over ranks is the collective itself, the rest is waiting for the slowest view")
+
+    # ---- per-kernel times: a separate short loop with the library's event profiling on ----
+    _lib.profile_read()
+    _lib.profile_enable(True)
+    for _ in range(3):
+        step(d, reduce=False)
+    torch.cuda.synchronize()
     _lib.profile_enable(False)
     prof = _lib.profile_read()
-    ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
-    value = H * W * world / (ms_step * 1e-3) / 1e6
+    barrier()
 
     N = int(pkg["sorted_tetra_idx"].shape[0])
     Tv = int(pkg["mask"].sum().item())
@@ -315,6 +399,39 @@ def run_gpu(args):
     kernel_ms = {k: v[1] / v[0] for k, v in per_kernel.items()}
     total_kernel_ms = sum(kernel_ms.values())
     dominant = max(kernel_ms, key=kernel_ms.get) if kernel_ms else None
+
+    # ---- multi-GPU parity (outside the timed region): the all-reduced gradients against the sum of the
+    # N per-view gradients rendered serially on rank 0
+    parity_multi = None
+    if world > 1:
+        _, vg_ar, cg_ar = step(d)
+        vg_ar, cg_ar = vg_ar.clone(), cg_ar.clone()
+        if rank == 0:
+            vs, cs = torch.zeros_like(vg_ar, dtype=torch.float64), torch.zeros_like(cg_ar, dtype=torch.float64)
+            for r in range(world):
+                rr = np.random.default_rng(1234 + r)
+                inp = dict(d)
+                inp["jitter"] = torch.from_numpy(rr.uniform(0, 1, (H, W, 2)).astype(np.float32)).to(dev)
+                inp["g_img"] = torch.from_numpy(rr.normal(size=(H, W, 4)).astype(np.float32)).to(dev)
+                inp["g_dist"] = torch.from_numpy((0.01 * rr.normal(size=(H, W, 5))).astype(np.float32)).to(dev)
+                tc = tcam_to_device(camera_for(args.workload, r % 8), dev)
+                v = inp["vertices"].requires_grad_(True)
+                c = inp["cell"].requires_grad_(True)
+                v.grad = None
+                c.grad = None
+                pk = render(inp["indices"], v, c, tc, inp["jitter"])
+                torch.autograd.backward([pk["image"], pk["distortion_img"]], [inp["g_img"], inp["g_dist"]])
+                vs += v.grad.double()
+                cs += c.grad.double()
+                del pk
+            ev = float(((vg_ar.double() - vs).norm() / vs.norm().clamp_min(1e-30)).item())
+            ec = float(((cg_ar.double() - cs).norm() / cs.norm().clamp_min(1e-30)).item())
+            parity_multi = dict(views=world, vertices_grad_rel_l2=ev, cell_grad_rel_l2=ec, tolerance=1e-5,
+                                ok=bool(ev <= 1e-5 and ec <= 1e-5),
+                                note="NCCL all-reduced gradients vs the float64 sum of the per-view gradients "
+                                     "rendered one after the other on rank 0 (differences: order of float atomics)")
+            del vs, cs
+        barrier()
 
     # ---- end-to-end arm: host buffers in, host buffers out, copies inside the timed region -----
     out_host = dict(image=torch.empty((H, W, 4)).pin_memory(), dist=torch.empty((H, W, 5)).pin_memory(),
@@ -417,6 +534,58 @@ def run_gpu(args):
         inference_ms = inf0.elapsed_time(inf1) / 10
         del sh, rgb, grd, cc, feats
 
+    # ---- how much of the walk is useful work: list entries walked, entries recorded in the hit lists,
+    # (pixel, tet) hits; from one frame rendered through the stage-level calls, outside the timed region
+    hit_stats = None
+    if rank == 0:
+        with torch.no_grad():
+            bctx = raster.project_and_bin(d["indices"], d["vertices"], tcam)
+            nk, _ = raster.read_info(bctx)
+            sidx = raster.build_tile_lists(bctx, nk)
+            recs = raster.pack_records(bctx["indices"], bctx["vertices"], d["cell"], bctx["cam"], bctx["tiles_touched"])
+            _, _, ncontrib, hits = raster.forward(sidx, bctx["tile_ranges"], recs, bctx["cam"], d["jitter"])
+            counts, _, masks, flags = hits
+            counts64 = counts.to(torch.int64)
+            nbatch = (counts64 + 15) // 16
+            start = bctx["tile_ranges"][:, 0].to(torch.int64)
+            mbase = start + 16 * torch.arange(counts.shape[0], device=dev, dtype=torch.int64)  # 4x4 tiles: one unit per tile
+            first = torch.cumsum(nbatch, 0) - nbatch
+            total_b = int(nbatch.sum().item())
+            owner = torch.repeat_interleave(torch.arange(counts.shape[0], device=dev), nbatch)
+            within = torch.arange(total_b, device=dev, dtype=torch.int64) - first[owner]
+            slots = (mbase[owner] + 16 * within)[:, None] + torch.arange(16, device=dev, dtype=torch.int64)[None, :]
+            bits = masks[slots.reshape(-1)].to(torch.int32) & 0xFFFF
+            pop16 = torch.tensor([bin(i).count("1") for i in range(65536)], device=dev, dtype=torch.int32)
+            pixel_hits = int(pop16[bits.long()].to(torch.int64).sum().item())
+            hit_stats = dict(list_entries=nk, walked_pixel_entries=int(ncontrib.to(torch.int64).sum().item()),
+                             recorded_entries=int(counts64.sum().item()), pixel_hits=pixel_hits,
+                             tets_with_gradient=int(flags.to(torch.int64).sum().item()),
+                             pixels_per_recorded_entry=pixel_hits / max(int(counts64.sum().item()), 1),
+                             hits_per_pixel=pixel_hits / (H * W),
+                             note="walked_pixel_entries = sum of n_contributors (the reference's pair evaluations, "
+                                  "forward); pixel_hits = (pixel, tet) pairs with a contribution (the pair evaluations "
+                                  "of this implementation, forward and backward)")
+            del bctx, sidx, recs, hits, counts, masks, flags, slots, bits, owner, within, ncontrib
+
+    # ---- parity of the benchmarked frame itself against the CPU oracle, on the oracle's band of rows
+    cpu_entry, parity = None, None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu_entry, ref = cpu_baseline(sc, tcam_np, host["jitter"].numpy(), host["g_img"].numpy(),
+                                      host["g_dist"].numpy())
+
+        def render_frame(g_img, g_dist):
+            inp = dict(d)
+            inp["g_img"] = torch.from_numpy(g_img).to(dev)
+            inp["g_dist"] = torch.from_numpy(g_dist).to(dev)
+            pk, gv_, gc_ = step(inp, reduce=False)
+            out = {k: pk[k].detach().cpu().numpy() for k in ("image", "distortion_img", "sorted_tetra_idx",
+                                                             "tile_ranges", "rect", "vs_tetra")}
+            out["vertices_grad"], out["cell_grad"] = gv_.cpu().numpy(), gc_.cpu().numpy()
+            return out
+
+        parity = band_parity(ref, tcam_np, render_frame)
+        del ref
+
     if rank != 0:
         if world > 1:
             dist.barrier()
@@ -435,18 +604,38 @@ def run_gpu(args):
         achieved = bytes_alg / (kernel_ms[dominant] * 1e-3) / 1e9 if bytes_alg else None
         # DRAM traffic per launch: dram__bytes_read + write of one ncu capture on the 300k-point scene
         # (a --set full capture of the full-size launch is too large), scaled by the ratio of the stage's
-        # algorithmic bytes; None for kernels that were not captured
-        captured = {"k_backward": (486.7e6, 572.2e6), "k_forward": (520.4e6, 437.3e6)}
-        traffic = None
-        if dominant in captured and bytes_alg:
-            traffic = captured[dominant][0] * bytes_alg / captured[dominant][1]
+        # algorithmic bytes; the captured figures live beside the summary that documents the capture
+        traffic, traffic_src = None, None
+        cap_path = os.path.join(ROOT, "profiles", "dram_traffic_medium_scene.json")
+        if os.path.exists(cap_path) and bytes_alg:
+            cap = json.load(open(cap_path))
+            ent = cap.get("kernels", {}).get(dominant)
+            if ent:
+                traffic = ent["dram_bytes"] * bytes_alg / ent["algorithmic_bytes"]
+                traffic_src = cap.get("source")
         roofline = dict(bound="hbm", kernel=dominant, achieved=achieved, peak=peak, peak_source=peak_src,
                         unit="GB/s", frac=(achieved / peak) if achieved else None, traffic=traffic,
-                        traffic_source="ncu capture on the 300k-point scene scaled by algorithmic bytes",
+                        traffic_source=traffic_src,
                         kernel_ms=kernel_ms[dominant], algorithmic_bytes=bytes_alg,
                         note="issue-bound kernel (about 16 pixel evaluations per staged record): the HBM fraction is low by "
                              "construction")
     frame_bytes = sum(alg.values())
+    # Second roofline: the integration kernels are bound by the fp32 pipes, not by HBM.  Pair evaluations x
+    # 170 flop (slab test + segment integral) against 148 SMs x 128 lanes x 2 flop at the sampled SM clock.
+    fp32_pipe = None
+    if hit_stats and clocks and clocks.get("sm_mhz"):
+        peak_tf = 148 * 128 * 2 * clocks["sm_mhz"] * 1e6 / 1e12
+        fwd_ms, bwd_ms = kernel_ms.get("k_forward"), kernel_ms.get("k_backward")
+        fp32_pipe = dict(flop_per_pair=170, peak_tflops=peak_tf,
+                         forward=dict(pairs_reference_algorithm=hit_stats["walked_pixel_entries"],
+                                      pairs_evaluated=hit_stats["pixel_hits"],
+                                      frac=(hit_stats["walked_pixel_entries"] * 170 / (fwd_ms * 1e-3) / 1e12 / peak_tf)
+                                      if fwd_ms else None),
+                         backward=dict(pairs=hit_stats["pixel_hits"],
+                                       frac=(hit_stats["pixel_hits"] * 2 * 170 / (bwd_ms * 1e-3) / 1e12 / peak_tf)
+                                       if bwd_ms else None),
+                         note="forward: the reference algorithm's pair evaluations (sum of n_contributors) per second of "
+                              "k_forward; backward: hits x (re-evaluation + reverse, counted as 2 x 170 flop)")
     line = dict(
         metric="fwd+bwd Mpix/s at 1080p, 6.5M tets", value=value, unit="Mpix/s", n_gpus=world, steps=args.steps,
         warmup=args.warmup, ms_per_step=ms_step, higher_is_better=True, scaling="weak", vs_baseline=None,
@@ -460,8 +649,10 @@ def run_gpu(args):
         e2e_streaming=dict(value=H * W * world / (e2e_stream_ms * 1e-3) / 1e6, unit="Mpix/s",
                            ms_per_step=e2e_stream_ms, h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h,
                            mode="two independent frames in flight (HostFramePipeline.submit/wait)"),
-        gpu_launches=args.steps * (raster.LAUNCHES_PROJECT_AND_BIN + raster.LAUNCHES_BUILD_LISTS +
-                                   raster.LAUNCHES_FORWARD + raster.LAUNCHES_BACKWARD),
+        gpu_launches=int(launches), ms_per_step_median=ms_median,
+        rank_step_ms=dict(min=min(rank_ms), median=float(np.median(rank_ms)), max=max(rank_ms)),
+        allreduce=allreduce, parity=parity, parity_multi=parity_multi, hit_stats=hit_stats,
+        fp32_pipe=fp32_pipe,
         roofline=roofline,
         frame_roofline=dict(algorithmic_bytes=frame_bytes, achieved=frame_bytes / (ms_step * 1e-3) / 1e9,
                             peak=peak, unit="GB/s", frac=frame_bytes / (ms_step * 1e-3) / 1e9 / peak,
@@ -482,8 +673,8 @@ def run_gpu(args):
                                "reference's published FPS table (synthetic SH-activated features); not part of "
                                "`value`"),
     )
-    if world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline(sc, tcam_np)
+    if cpu_entry is not None:
+        line["cpu_baseline"] = cpu_entry
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -595,9 +786,6 @@ def main():
                          "bands: one 4K frame split by tile-row bands, forward only")
     args = ap.parse_args()
     if args.impl == "reference":
-        if args.steps > 4:
-            args.steps = 4
-        args.warmup = min(args.warmup, 1)
         run_reference(args)
     elif args.mode == "bands":
         args.warmup = max(args.warmup, 3)

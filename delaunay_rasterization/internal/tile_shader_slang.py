@@ -7,17 +7,9 @@ mask[T] bool, rect_tile_space[T,4] i32), with autograd from vs_tetra and
 circumcenter to the vertices.  One host synchronisation (to learn N) instead of
 the reference's four.
 """
-import weakref
-
 import torch
 
 from radiance_meshes_b200 import raster
-
-# binning context of the VertexShader call that produced a given tiles_touched tensor
-_pending = {}
-# (weakref to sorted_tetra_idx, tiles_touched) of recent calls, so that the
-# integration stage can skip culled tets when packing records
-_recent_lists = []
 
 
 def ceil_div(x, y):
@@ -25,21 +17,28 @@ def ceil_div(x, y):
 
 
 def lookup_tiles_touched(sorted_tetra_idx):
-    for ref, tiles_touched in _recent_lists:
-        if ref() is sorted_tetra_idx:
-            return tiles_touched
-    return None
+    """tiles_touched of the call that produced this list tensor (None for any other tensor): the
+    integration stage skips the records of culled tets with it."""
+    return getattr(sorted_tetra_idx, "_rm_tiles_touched", None)
 
 
 class VertexShader(torch.autograd.Function):
-    """Per-tet projection, culling, sort depth, circumcentre and tile count."""
+    """Per-tet projection, culling, sort depth, circumcentre and tile count.
+
+    `holder`, if given, receives the binning context (workspace, tile ranges, counters) that
+    `vertex_and_tile_shader` needs to finish the tile lists; a bare `VertexShader.apply(indices,
+    vertices, tcam, render_grid)` keeps nothing beyond its four outputs."""
 
     @staticmethod
-    def forward(ctx, indices, vertices, tcam, render_grid, device="cuda"):
+    def forward(ctx, indices, vertices, tcam, render_grid, *extra):
+        # extra: the reference's optional `device` argument, then the optional holder
+        holder = extra[1] if len(extra) > 1 else None
+        ctx.n_extra = len(extra)
         bctx = raster.project_and_bin(indices, vertices, tcam)
         ctx.bctx_small = (bctx["indices"], bctx["vertices"], bctx["cam"], bctx["tiles_touched"])
         ctx.mark_non_differentiable(bctx["tiles_touched"], bctx["rect"])
-        _pending[bctx["tiles_touched"].data_ptr()] = bctx
+        if holder is not None:
+            holder["bctx"] = bctx
         return bctx["tiles_touched"], bctx["rect"], bctx["vs_tetra"], bctx["circumcenter"]
 
     @staticmethod
@@ -48,17 +47,18 @@ class VertexShader(torch.autograd.Function):
         grad_vertices = raster.vertex_backward(indices, vertices, cam, tiles_touched,
                                                grad_vs_tetra.contiguous().float(),
                                                grad_circumcenter.contiguous().float())
-        return None, grad_vertices, None, None
+        return (None, grad_vertices, None, None) + (None,) * ctx.n_extra
 
 
 def vertex_and_tile_shader(indices, vertices, cam, render_grid):
-    tiles_touched, rect_tile_space, vs_tetra, circumcenter = VertexShader.apply(indices, vertices, cam, render_grid)
-    bctx = _pending.pop(tiles_touched.data_ptr())
+    holder = {}
+    tiles_touched, rect_tile_space, vs_tetra, circumcenter = VertexShader.apply(indices, vertices, cam, render_grid,
+                                                                                "cuda", holder)
+    bctx = holder.pop("bctx")
     with torch.no_grad():
         n_keys, _ = raster.read_info(bctx)
         sorted_tetra_idx = raster.build_tile_lists(bctx, n_keys)
         tile_ranges = bctx["tile_ranges"]
         mask = tiles_touched > 0
-    _recent_lists.append((weakref.ref(sorted_tetra_idx), tiles_touched))
-    del _recent_lists[:-4]
+    sorted_tetra_idx._rm_tiles_touched = tiles_touched
     return sorted_tetra_idx, tile_ranges, vs_tetra, circumcenter, mask, rect_tile_space

@@ -32,6 +32,8 @@ extern "C" {
 /* bits of RmBinInfo.status */
 #define RM_STATUS_NAN_VERTEX 1u   /* a vertex coordinate is NaN (tile_shader_slang.py:78 asserts on this) */
 #define RM_STATUS_KEY_OVERFLOW 2u /* more than 2^31-1 (tile, tet) pairs (int32 cumsum, tile_shader_slang.py:36) */
+#define RM_STATUS_BAD_INDEX 4u    /* a tet names a vertex outside [0, n_vertices): the tet is treated as culled
+                                     (the reference would read out of bounds) */
 
 /* Floats per packed tet record (24 used by the integration + 12 for the hull edge
  * lines of the projected tet, used to cull whole tiles) and per record-gradient row. */
@@ -71,15 +73,18 @@ typedef struct RmBinInfo {
  * Hit lists, written by rm_forward and walked by rm_backward (device pointers).  No
  * counterpart in the reference, whose backward pass walks every tile list again and
  * repeats every intersection test.  A unit is one group of 16 pixels of a tile (tile t,
- * group s of S = ceil(tile_width*tile_height / 16): unit t*S + s).  For every unit the
- * forward pass appends, in list order, the entries that some pixel of the group hit with
- * positive optical depth while still active:
- *   counts[G*S] i32   number of such entries of the unit
- *   ids[N*S] i32      their tet ids, unit (t, s) at [start(t)*S + s*len(t), ... + counts)
- *   masks[N*S] u16    for each, the pixels of the group that hit it (bit = pixel index)
- *   tet_flags[T] u8   set to 1 for every tet that appears in some hit list; the caller
- *                     zero-fills it before rm_forward.  The backward pass clears and reads
- *                     the record-gradient rows of flagged tets only.
+ * group s of S = ceil(tile_width*tile_height / 16): unit t*S + s).  The forward pass
+ * evaluates a unit's list in batches of 16 entries that can cover one of its pixels (the
+ * last batch may hold fewer) and records every batch, in list order:
+ *   counts[G*S] i32        number of recorded entries of the unit
+ *   ids[N*S] i32           their tet ids, unit (t, s) at [start(t)*S + s*len(t), ... + counts)
+ *   masks[N*S + 16*G*S] u16  for batch b of unit q = t*S + s, at [start(t)*S + s*len(t) + 16*q + 16*b, + 16):
+ *                          per pixel of the group, the bit set of the batch entries the pixel
+ *                          hit with positive optical depth while still active (bit = entry
+ *                          index inside the batch)
+ *   tet_flags[T] u8        set to 1 for every tet that appears in some hit list; the caller
+ *                          zero-fills it before rm_forward.  The backward pass clears and reads
+ *                          the record-gradient rows of flagged tets only.
  * with start/len from tile_ranges.  Slots beyond a unit's count are left unwritten.
  */
 typedef struct RmHitList {
@@ -139,10 +144,12 @@ int rm_build_tile_lists(const int32_t* rect_tile_space, const int32_t* tile_rang
  * (slang/interp_version.slang:100-153).
  * tiles_touched may be NULL (pack every tet) or [T] (skip culled tets).
  * records[T, RM_RECORD_FLOATS] f32 out, 16-byte aligned; with tiles_touched given, the rows of
- * culled tets (which appear in no tile list) are left unwritten.
+ * culled tets (which appear in no tile list) are left unwritten.  A tet that names a vertex
+ * outside [0, n_vertices) gets a record that no pixel can hit.
  */
 int rm_pack_records(const int32_t* indices, const float* vertices, const float* cell_values, int64_t n_tets,
-                    const RmCamera* cam, const int32_t* tiles_touched, float* records, void* stream);
+                    int64_t n_vertices, const RmCamera* cam, const int32_t* tiles_touched, float* records,
+                    void* stream);
 
 /*
  * Forward integration.  Replaces splat_tiled (slang/alphablend_shader_interp.slang:371-431,
@@ -266,6 +273,12 @@ int rm_backward_static_scratch(const int32_t* sorted_tetra_idx, const int32_t* t
  */
 void rm_profile_enable(int on);
 int rm_profile_read(char* names, size_t names_bytes, float* ms, int max_records);
+
+/* Number of kernels this library has launched in this process so far (all entry points, all
+ * threads; memsets and copies are not kernels and are not counted).  A measurement aid with no
+ * counterpart in the reference: the difference across a timed region is the number of this
+ * library's launches inside it. */
+int64_t rm_launch_count(void);
 
 #ifdef __cplusplus
 }

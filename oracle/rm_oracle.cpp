@@ -194,6 +194,40 @@ inline void undistort(F& px, F& py, const Cam<F>& c) {
   py = y;
 }
 
+// The reference's acos/sin are the CUDA library's, whose last bit no other implementation
+// reproduces.  The fp32 oracle therefore fixes them as series evaluated in IEEE double in a
+// stated order and rounded to float once (error far below half a float ulp except on exact
+// rounding ties), which an independent implementation can match bit for bit:
+//   asin(s) = sum_n c_n s^(2n+1), c_0 = 1, c_{n+1} = c_n (2n+1)^2 / ((2n+2)(2n+3)), 21 terms, |s| <= 0.5
+//   acos(x) = pi/2 - asin(x) for x < 0.5, else 2 asin(sqrt((1 - x)/2))
+//   sin(t)  = sum_n (-1)^n t^(2n+1)/(2n+1)!, 13 terms
+inline double asin_series(double s) {
+  const double s2 = s * s;
+  double term = s, sum = s;
+  for (int n = 0; n < 20; ++n) {
+    const double a = double(2 * n + 1);
+    term = term * s2 * (a * a / (double(2 * n + 2) * double(2 * n + 3)));
+    sum += term;
+  }
+  return sum;
+}
+inline float fisheye_acos(float x) {
+  const double xd = double(x);
+  if (xd < 0.5) return float(1.5707963267948966 - asin_series(xd));
+  return float(2.0 * asin_series(std::sqrt((1.0 - xd) * 0.5)));
+}
+inline float fisheye_sin(float t) {
+  const double td = double(t), t2 = td * td;
+  double term = td, sum = td;
+  for (int n = 1; n < 13; ++n) {
+    term = -(term * t2) / (double(2 * n) * double(2 * n + 1));
+    sum += term;
+  }
+  return float(sum);
+}
+inline double fisheye_acos(double x) { return std::acos(x); }  // fp64 instantiation: finite-difference checks only
+inline double fisheye_sin(double t) { return std::sin(t); }
+
 // slang/camera.slang:380-414 (camspace_to_image)
 template <class F>
 inline V3<F> camspace_to_image(V3<F> p, const Cam<F>& c) {
@@ -201,8 +235,8 @@ inline V3<F> camspace_to_image(V3<F> p, const Cam<F>& c) {
   if (c.type == 1) {
     V3<F> dir = normalize(p);
     F sat = std::fmin(std::fmax(dir.z, F(0)), F(1));
-    F theta = std::acos(sat);
-    F st = std::sin(theta);
+    F theta = fisheye_acos(sat);
+    F st = fisheye_sin(theta);
     F k = (st < F(1e-6f)) ? F(1) : theta / st;
     ux = dir.x * k;
     uy = dir.y * k;

@@ -12,14 +12,16 @@ RM_RECORD_FLOATS = 36
 RM_GRAD_RECORD_FLOATS = 24
 RM_STATUS_NAN_VERTEX = 1
 RM_STATUS_KEY_OVERFLOW = 2
+RM_STATUS_BAD_INDEX = 4
 
 # every symbol include/rm_b200.h declares
 SYMBOLS = ["rm_strerror", "rm_version", "rm_bin_workspace_bytes", "rm_list_scratch_bytes", "rm_project_and_bin", "rm_build_tile_lists",
            "rm_pack_records", "rm_forward", "rm_backward", "rm_vertex_backward", "rm_profile_enable",
            "rm_profile_read", "rm_backward_static_scratch", "rm_tet_err",
-           "rm_activate_output", "rm_forward_constant_color"]
+           "rm_activate_output", "rm_forward_constant_color", "rm_launch_count"]
 RM_STATIC_SCRATCH_MAX_TETS = 131072
 RM_ERR_STATIC_SCRATCH = -5
+RM_ERR_INVALID_ARG = -1
 
 
 class RmCamera(C.Structure):
@@ -63,7 +65,7 @@ def load():
     lib.rm_list_scratch_bytes.restype = sz
     lib.rm_list_scratch_bytes.argtypes = [i64, C.c_int, C.c_int]
     lib.rm_build_tile_lists.argtypes = [vp, vp, i64, cam, i64, i64, vp, vp, sz, vp, vp]
-    lib.rm_pack_records.argtypes = [vp, vp, vp, i64, cam, vp, vp, vp]
+    lib.rm_pack_records.argtypes = [vp, vp, vp, i64, i64, cam, vp, vp, vp]
     hits = C.POINTER(RmHitList)
     lib.rm_forward.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, hits, vp]
     lib.rm_backward.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, hits, vp, vp, vp, vp, vp, i64, i64, vp, vp, vp, vp]
@@ -76,6 +78,7 @@ def load():
     lib.rm_profile_enable.restype = None
     lib.rm_profile_enable.argtypes = [C.c_int]
     lib.rm_profile_read.argtypes = [C.c_char_p, sz, C.POINTER(C.c_float), C.c_int]
+    lib.rm_launch_count.restype = C.c_int64
     for name in SYMBOLS:
         getattr(lib, name)
     _lib = lib
@@ -85,6 +88,11 @@ def load():
 def check(rc):
     if rc != 0:
         raise RuntimeError(f"rm_b200: {load().rm_strerror(rc).decode()} (code {rc})")
+
+
+def launch_count():
+    """Kernels this library has launched in this process so far."""
+    return int(load().rm_launch_count())
 
 
 def profile_enable(on=True):

@@ -163,11 +163,11 @@ int rm_launch_activate(const float* camera_center, const float* density, const f
   const size_t smem = (size_t)rm::kActThreads * n_rest * 3 * (sh_is_half ? 2 : 4) + rm::kActThreads * 7 * sizeof(float);
   RmProfScope prof("k_activate_output", st);
   if (sh_is_half)
-    rm::k_activate_output<__half><<<blocks, rm::kActThreads, smem, st>>>(
+    rm_count_launch(), rm::k_activate_output<__half><<<blocks, rm::kActThreads, smem, st>>>(
         camera_center, density, rgb, grd, static_cast<const __half*>(sh), indices, circumcenters, vertices, T, deg,
         n_rest, features);
   else
-    rm::k_activate_output<float><<<blocks, rm::kActThreads, smem, st>>>(
+    rm_count_launch(), rm::k_activate_output<float><<<blocks, rm::kActThreads, smem, st>>>(
         camera_center, density, rgb, grd, static_cast<const float*>(sh), indices, circumcenters, vertices, T, deg,
         n_rest, features);
   RM_CUDA_CHECK(cudaPeekAtLastError());

@@ -18,8 +18,8 @@ int rm_launch_bin_finish(int64_t, const RmCamera*, const int32_t*, int32_t*, RmB
 int rm_launch_build_lists(const int32_t*, const int32_t*, int64_t, const RmCamera*, int64_t, int64_t, void*, void*, size_t,
                           int32_t*, cudaStream_t);
 size_t rm_list_plan_bytes(int64_t, int, int);
-int rm_launch_pack(const int32_t*, const float*, const float*, int64_t, const RmCamera*, const int32_t*, float*,
-                   cudaStream_t);
+int rm_launch_pack(const int32_t*, const float*, const float*, int64_t, int64_t, const RmCamera*, const int32_t*,
+                   float*, cudaStream_t);
 int rm_launch_forward(const int32_t*, const int32_t*, const float*, const RmCamera*, const float*, float*, float*,
                       int32_t*, const RmHitList*, cudaStream_t);
 int rm_launch_forward_constant_color(const int32_t*, const int32_t*, const float*, const RmCamera*, float, float,
@@ -66,6 +66,10 @@ void rm_prof_end(cudaStream_t st) {
   g_prof_open = -1;
 }
 
+#include <atomic>
+static std::atomic<long long> g_launches{0};
+void rm_count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
 void rm_set_last_cuda_error(cudaError_t e, const char* file, int line) {
   snprintf(g_last_error, sizeof(g_last_error), "CUDA error %d (%s) at %s:%d", (int)e, cudaGetErrorString(e), file,
            line);
@@ -91,7 +95,7 @@ int rm_bind_device(const void* device_ptr) {
   return RM_OK;
 }
 
-static int check_cam(const RmCamera* c) {
+int rm_check_cam(const RmCamera* c) {
   if (!c || !c->world_view_transform || !c->K || !c->cam_pos || !c->distortion_params) return RM_ERR_INVALID_ARG;
   if (c->image_height <= 0 || c->image_width <= 0 || c->tile_height <= 0 || c->tile_width <= 0)
     return RM_ERR_INVALID_ARG;
@@ -103,7 +107,7 @@ static int check_cam(const RmCamera* c) {
   if ((int64_t)c->grid_height * c->grid_width > 0x7fffffffll) return RM_ERR_INVALID_ARG;
   return RM_OK;
 }
-static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+void rm_clear_last_error() { g_last_error[0] = 0; }
 
 extern "C" {
 
@@ -120,7 +124,9 @@ const char* rm_strerror(int code) {
   }
 }
 
-int rm_version(void) { return 100; }
+int rm_version(void) { return 101; }
+
+int64_t rm_launch_count(void) { return (int64_t)g_launches.load(std::memory_order_relaxed); }
 
 void rm_profile_enable(int on) {
   std::lock_guard<std::mutex> lk(g_prof_mu);
@@ -163,13 +169,13 @@ int rm_project_and_bin(const int32_t* indices, int64_t n_tets, const float* vert
                        float* circumcenter, int32_t* tile_ranges, RmBinInfo* info, void* workspace,
                        size_t workspace_bytes, void* stream) {
   g_last_error[0] = 0;
-  int rc = check_cam(cam);
+  int rc = rm_check_cam(cam);
   if (rc) return rc;
   if (n_tets < 0 || n_vertices < 0 || n_tets > 0x7fffffffll || !info || !tile_ranges || !workspace)
     return RM_ERR_INVALID_ARG;
   if (n_tets > 0 && (!indices || !vertices || !tiles_touched || !rect_tile_space || !vs_tetra || !circumcenter))
     return RM_ERR_INVALID_ARG;
-  if (!aligned16(indices) || !aligned16(rect_tile_space) || (reinterpret_cast<uintptr_t>(workspace) & 255))
+  if (!rm_aligned16(indices) || !rm_aligned16(rect_tile_space) || (reinterpret_cast<uintptr_t>(workspace) & 255))
     return RM_ERR_WORKSPACE;
   rc = rm_bind_device(workspace);
   if (rc) return rc;
@@ -193,13 +199,13 @@ int rm_build_tile_lists(const int32_t* rect_tile_space, const int32_t* tile_rang
                         const RmCamera* cam, int64_t n_keys, int64_t n_region_keys, void* workspace, void* scratch,
                         size_t scratch_bytes, int32_t* sorted_tetra_idx, void* stream) {
   g_last_error[0] = 0;
-  int rc = check_cam(cam);
+  int rc = rm_check_cam(cam);
   if (rc) return rc;
   if (n_keys < 0 || n_region_keys < 0 || n_tets < 0 || !workspace || !tile_ranges) return RM_ERR_INVALID_ARG;
   if (n_keys > 0x7fffffffll) return RM_ERR_TOO_MANY_KEYS;
   if (n_keys == 0) return RM_OK;
   if (!rect_tile_space || !scratch || !sorted_tetra_idx) return RM_ERR_INVALID_ARG;
-  if (!aligned16(rect_tile_space)) return RM_ERR_WORKSPACE;
+  if (!rm_aligned16(rect_tile_space)) return RM_ERR_WORKSPACE;
   rc = rm_bind_device(workspace);
   if (rc) return rc;
   return rm_launch_build_lists(rect_tile_space, tile_ranges, n_tets, cam, n_keys, n_region_keys, workspace, scratch,
@@ -207,17 +213,18 @@ int rm_build_tile_lists(const int32_t* rect_tile_space, const int32_t* tile_rang
 }
 
 int rm_pack_records(const int32_t* indices, const float* vertices, const float* cell_values, int64_t n_tets,
-                    const RmCamera* cam, const int32_t* tiles_touched, float* records, void* stream) {
+                    int64_t n_vertices, const RmCamera* cam, const int32_t* tiles_touched, float* records,
+                    void* stream) {
   g_last_error[0] = 0;
-  int rc = check_cam(cam);
+  int rc = rm_check_cam(cam);
   if (rc) return rc;
-  if (n_tets < 0) return RM_ERR_INVALID_ARG;
+  if (n_tets < 0 || n_vertices < 0) return RM_ERR_INVALID_ARG;
   if (n_tets == 0) return RM_OK;
   if (!indices || !vertices || !cell_values || !records) return RM_ERR_INVALID_ARG;
-  if (!aligned16(indices) || !aligned16(records)) return RM_ERR_WORKSPACE;
+  if (!rm_aligned16(indices) || !rm_aligned16(records)) return RM_ERR_WORKSPACE;
   rc = rm_bind_device(records);
   if (rc) return rc;
-  return rm_launch_pack(indices, vertices, cell_values, n_tets, cam, tiles_touched, records,
+  return rm_launch_pack(indices, vertices, cell_values, n_tets, n_vertices, cam, tiles_touched, records,
                         static_cast<cudaStream_t>(stream));
 }
 
@@ -225,11 +232,11 @@ int rm_forward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, cons
                const RmCamera* cam, const float* ray_jitter, float* output_img, float* distortion_img,
                int32_t* n_contributors, const RmHitList* hits, void* stream) {
   g_last_error[0] = 0;
-  int rc = check_cam(cam);
+  int rc = rm_check_cam(cam);
   if (rc) return rc;
   if (!tile_ranges || !ray_jitter || !output_img || !distortion_img || !n_contributors) return RM_ERR_INVALID_ARG;
   if (hits && (!hits->counts || !hits->ids || !hits->masks || !hits->tet_flags)) return RM_ERR_INVALID_ARG;
-  if (!aligned16(output_img) || !aligned16(records) || (reinterpret_cast<uintptr_t>(ray_jitter) & 7) ||
+  if (!rm_aligned16(output_img) || !rm_aligned16(records) || (reinterpret_cast<uintptr_t>(ray_jitter) & 7) ||
       (reinterpret_cast<uintptr_t>(tile_ranges) & 7))
     return RM_ERR_WORKSPACE;
   rc = rm_bind_device(output_img);
@@ -242,11 +249,11 @@ int rm_forward_constant_color(const int32_t* sorted_tetra_idx, const int32_t* ti
                               const RmCamera* cam, float pre_multi, float ladder_p, float* output_img,
                               float* distortion_img, int32_t* n_contributors, void* stream) {
   g_last_error[0] = 0;
-  int rc = check_cam(cam);
+  int rc = rm_check_cam(cam);
   if (rc) return rc;
   if (!tile_ranges || !output_img || !distortion_img || !n_contributors || ladder_p == 0.0f)
     return RM_ERR_INVALID_ARG;
-  if (!aligned16(output_img) || !aligned16(distortion_img) || !aligned16(records) ||
+  if (!rm_aligned16(output_img) || !rm_aligned16(distortion_img) || !rm_aligned16(records) ||
       (reinterpret_cast<uintptr_t>(tile_ranges) & 7))
     return RM_ERR_WORKSPACE;
   rc = rm_bind_device(output_img);
@@ -263,7 +270,7 @@ int rm_backward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, con
                 const float* vertices, const float* cell_values, int64_t n_tets, int64_t n_vertices,
                 float* grad_records, float* vertices_grad, float* cell_values_grad, void* stream) {
   g_last_error[0] = 0;
-  int rc = check_cam(cam);
+  int rc = rm_check_cam(cam);
   if (rc) return rc;
   if (n_tets < 0 || n_vertices < 0) return RM_ERR_INVALID_ARG;
   if (!tile_ranges || !ray_jitter || !output_img || !distortion_img || !hits || !hits->counts || !hits->ids ||
@@ -271,8 +278,8 @@ int rm_backward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, con
     return RM_ERR_INVALID_ARG;
   if (n_tets > 0 && (!indices || !vertices || !cell_values || !grad_records || !cell_values_grad || !records))
     return RM_ERR_INVALID_ARG;
-  if (!aligned16(output_img) || !aligned16(grad_output_img) || !aligned16(records) || !aligned16(grad_records) ||
-      !aligned16(indices))
+  if (!rm_aligned16(output_img) || !rm_aligned16(grad_output_img) || !rm_aligned16(records) || !rm_aligned16(grad_records) ||
+      !rm_aligned16(indices))
     return RM_ERR_WORKSPACE;
   rc = rm_bind_device(vertices_grad);
   if (rc) return rc;
@@ -293,7 +300,7 @@ int rm_activate_output(const float* camera_center, const float* density, const f
   if (!camera_center || !density || !rgb || !grd || !indices || !circumcenters || !vertices || !features ||
       (sh_degree > 0 && !sh))
     return RM_ERR_INVALID_ARG;
-  if (!aligned16(indices)) return RM_ERR_WORKSPACE;
+  if (!rm_aligned16(indices)) return RM_ERR_WORKSPACE;
   int rc = rm_bind_device(features);
   if (rc) return rc;
   return rm_launch_activate(camera_center, density, rgb, grd, sh, sh_is_half, indices, circumcenters, vertices,
@@ -304,12 +311,12 @@ int rm_tet_err(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, cons
                const RmCamera* cam, const float* pixel_err, const float* ssim_err, int64_t n_tets, float* tet_err,
                int32_t* tet_count, void* stream) {
   g_last_error[0] = 0;
-  int rc = check_cam(cam);
+  int rc = rm_check_cam(cam);
   if (rc) return rc;
   if (n_tets < 0 || !tile_ranges || !pixel_err || !ssim_err) return RM_ERR_INVALID_ARG;
   if (n_tets == 0) return RM_OK;
   if (!records || !tet_err || !tet_count) return RM_ERR_INVALID_ARG;
-  if (!aligned16(records) || !aligned16(tet_err) || (reinterpret_cast<uintptr_t>(tile_ranges) & 7))
+  if (!rm_aligned16(records) || !rm_aligned16(tet_err) || (reinterpret_cast<uintptr_t>(tile_ranges) & 7))
     return RM_ERR_WORKSPACE;
   rc = rm_bind_device(tet_err);
   if (rc) return rc;
@@ -321,12 +328,12 @@ int rm_vertex_backward(const int32_t* indices, const float* vertices, int64_t n_
                        const RmCamera* cam, const int32_t* tiles_touched, const float* grad_vs_tetra,
                        const float* grad_circumcenter, float* vertices_grad, void* stream) {
   g_last_error[0] = 0;
-  int rc = check_cam(cam);
+  int rc = rm_check_cam(cam);
   if (rc) return rc;
   if (n_tets < 0 || n_vertices < 0 || !vertices_grad) return RM_ERR_INVALID_ARG;
   if (n_tets > 0 && (!indices || !vertices || !tiles_touched || !grad_vs_tetra || !grad_circumcenter))
     return RM_ERR_INVALID_ARG;
-  if (!aligned16(indices)) return RM_ERR_WORKSPACE;
+  if (!rm_aligned16(indices)) return RM_ERR_WORKSPACE;
   rc = rm_bind_device(vertices_grad);
   if (rc) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);

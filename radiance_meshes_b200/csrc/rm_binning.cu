@@ -871,10 +871,10 @@ static int launch_scan(const uint32_t* in, const uint32_t* gather, const int4* r
   int64_t nb = (n + rm::kScanTile - 1) / rm::kScanTile;
   // with a gather the values are fetched once, left in `out`, and scanned there in place
   const bool stash = gather != nullptr;
-  rm::k_scan_block_sums<<<(unsigned)nb, rm::kScanThreads, 0, st>>>(in, gather, rect, n, bsum, stash ? out : nullptr);
-  rm::k_scan_sums<<<1, 1024, 0, st>>>(bsum, nb, total64);
-  if (stash) rm::k_scan_apply<<<(unsigned)nb, rm::kScanThreads, 0, st>>>(out, nullptr, nullptr, n, bsum, out, inclusive);
-  else rm::k_scan_apply<<<(unsigned)nb, rm::kScanThreads, 0, st>>>(in, gather, rect, n, bsum, out, inclusive);
+  rm_count_launch(), rm::k_scan_block_sums<<<(unsigned)nb, rm::kScanThreads, 0, st>>>(in, gather, rect, n, bsum, stash ? out : nullptr);
+  rm_count_launch(), rm::k_scan_sums<<<1, 1024, 0, st>>>(bsum, nb, total64);
+  if (stash) rm_count_launch(), rm::k_scan_apply<<<(unsigned)nb, rm::kScanThreads, 0, st>>>(out, nullptr, nullptr, n, bsum, out, inclusive);
+  else rm_count_launch(), rm::k_scan_apply<<<(unsigned)nb, rm::kScanThreads, 0, st>>>(in, gather, rect, n, bsum, out, inclusive);
   RM_CUDA_CHECK(cudaPeekAtLastError());
   return RM_OK;
 }
@@ -904,9 +904,9 @@ int rm_launch_bin_finish(int64_t T, const RmCamera* cam, const int32_t* rect, in
     for (int pass = 0; pass < 4; ++pass) {
       int src = pass & 1, dst = src ^ 1;
       int shift = pass * rm::kRadixBits;
-      rm::k_radix_hist<<<L.nblk_sort, rm::kSortThreads, 0, st>>>(keys[src], T, shift, hist, L.nblk_sort);
-      rm::k_radix_rowscan<<<rm::kRadix, 1024, 0, st>>>(hist, L.nblk_sort, dtot);
-      rm::k_radix_scatter<<<L.nblk_sort, rm::kSortThreads, 0, st>>>(keys[src], ord[src], T, shift, hist, dtot,
+      rm_count_launch(), rm::k_radix_hist<<<L.nblk_sort, rm::kSortThreads, 0, st>>>(keys[src], T, shift, hist, L.nblk_sort);
+      rm_count_launch(), rm::k_radix_rowscan<<<rm::kRadix, 1024, 0, st>>>(hist, L.nblk_sort, dtot);
+      rm_count_launch(), rm::k_radix_scatter<<<L.nblk_sort, rm::kSortThreads, 0, st>>>(keys[src], ord[src], T, shift, hist, dtot,
                                                                    L.nblk_sort, keys[dst], ord[dst]);
     }
     RM_CUDA_CHECK(cudaPeekAtLastError());
@@ -915,12 +915,12 @@ int rm_launch_bin_finish(int64_t T, const RmCamera* cam, const int32_t* rect, in
   {
     RmProfScope prof("tile_ranges(6 launches)", st);
     int rows_per_block = 4;  // 128 threads
-    rm::k_diff_prefix_x<<<(gh + 1 + rows_per_block - 1) / rows_per_block, 32 * rows_per_block, 0, st>>>(diff, gh, gw);
-    rm::k_diff_prefix_y<<<(gw + rows_per_block - 1) / rows_per_block, 32 * rows_per_block, 0, st>>>(diff, gh, gw,
+    rm_count_launch(), rm::k_diff_prefix_x<<<(gh + 1 + rows_per_block - 1) / rows_per_block, 32 * rows_per_block, 0, st>>>(diff, gh, gw);
+    rm_count_launch(), rm::k_diff_prefix_y<<<(gw + rows_per_block - 1) / rows_per_block, 32 * rows_per_block, 0, st>>>(diff, gh, gw,
                                                                                                   tcount);
     int rc = launch_scan(tcount, nullptr, nullptr, G, bsum, tstart, 0, total_keys, st);
     if (rc) return rc;
-    rm::k_write_ranges<<<(unsigned)((G + 255) / 256), 256, 0, st>>>(tcount, tstart, G,
+    rm_count_launch(), rm::k_write_ranges<<<(unsigned)((G + 255) / 256), 256, 0, st>>>(tcount, tstart, G,
                                                                     reinterpret_cast<int2*>(tile_ranges));
     RM_CUDA_CHECK(cudaPeekAtLastError());
   }
@@ -930,7 +930,7 @@ int rm_launch_bin_finish(int64_t T, const RmCamera* cam, const int32_t* rect, in
     RmProfScope prof("rank_order_scan(4 launches)", st);
     int rc = launch_scan(nullptr, ord[0], reinterpret_cast<const int4*>(rect), T, bsum, cum, 1, total_keys + 1, st);
     if (rc) return rc;
-    rm::k_finish_info<<<1, 1, 0, st>>>(info, total_keys);
+    rm_count_launch(), rm::k_finish_info<<<1, 1, 0, st>>>(info, total_keys);
     RM_CUDA_CHECK(cudaPeekAtLastError());
   }
   return RM_OK;
@@ -1026,15 +1026,15 @@ int rm_launch_build_lists(const int32_t* rect, const int32_t* tile_ranges, int64
   RM_CUDA_CHECK(cudaMemsetAsync(region_count, 0, 4 * (size_t)(P.n_regions + 1), st));
   {
     RmProfScope prof("k_block_start_ranks+k_region_hist1", st);
-    rm::k_block_start_ranks<<<(P.nblk + 255) / 256, 256, 0, st>>>(cum, (int)T, P.nblk, starts);
-    rm::k_region_hist1<<<P.nblk, rm::kBinThreads, smem_h1, st>>>(cum, starts, order, (int)T, rect4, P.reg_w,
+    rm_count_launch(), rm::k_block_start_ranks<<<(P.nblk + 255) / 256, 256, 0, st>>>(cum, (int)T, P.nblk, starts);
+    rm_count_launch(), rm::k_region_hist1<<<P.nblk, rm::kBinThreads, smem_h1, st>>>(cum, starts, order, (int)T, rect4, P.reg_w,
                                                                 n_region_keys, bins1, hist, P.nblk,
                                                                 P.n_regions_smem, region_count, pairs_a);
   }
   {
     RmProfScope prof("k_radix_rowscan+k_region_scatter(pass 1)", st);
-    rm::k_radix_rowscan<<<bins1, 1024, 0, st>>>(hist, P.nblk, dtot);
-    rm::k_region_scatter<<<P.nblk, rm::kBinThreads, smem_s1, st>>>(pairs_a, n_region_keys, 0, bins1, hist, dtot,
+    rm_count_launch(), rm::k_radix_rowscan<<<bins1, 1024, 0, st>>>(hist, P.nblk, dtot);
+    rm_count_launch(), rm::k_region_scatter<<<P.nblk, rm::kBinThreads, smem_s1, st>>>(pairs_a, n_region_keys, 0, bins1, hist, dtot,
                                                                   P.nblk, P.bits2 == 0, rect4, P.reg_w, pairs_b,
                                                                   entries);
   }
@@ -1042,13 +1042,13 @@ int rm_launch_build_lists(const int32_t* rect, const int32_t* tile_ranges, int64
   if (P.bits2) {
     {
       RmProfScope prof("k_region_hist2", st);
-      rm::k_region_hist2<<<P.nblk, rm::kBinThreads, 4 * bins2, st>>>(pairs_b, n_region_keys, P.bits1, bins2, hist,
+      rm_count_launch(), rm::k_region_hist2<<<P.nblk, rm::kBinThreads, 4 * bins2, st>>>(pairs_b, n_region_keys, P.bits1, bins2, hist,
                                                                     P.nblk);
     }
     {
       RmProfScope prof("k_radix_rowscan+k_region_scatter(pass 2)", st);
-      rm::k_radix_rowscan<<<bins2, 1024, 0, st>>>(hist, P.nblk, dtot);
-      rm::k_region_scatter<<<P.nblk, rm::kBinThreads, smem_s2, st>>>(pairs_b, n_region_keys, P.bits1, bins2, hist,
+      rm_count_launch(), rm::k_radix_rowscan<<<bins2, 1024, 0, st>>>(hist, P.nblk, dtot);
+      rm_count_launch(), rm::k_region_scatter<<<P.nblk, rm::kBinThreads, smem_s2, st>>>(pairs_b, n_region_keys, P.bits1, bins2, hist,
                                                                     dtot, P.nblk, 1, rect4, P.reg_w, nullptr, entries);
     }
     RM_CUDA_CHECK(cudaPeekAtLastError());
@@ -1056,21 +1056,21 @@ int rm_launch_build_lists(const int32_t* rect, const int32_t* tile_ranges, int64
   const unsigned chunk_blocks = (P.max_chunks + rm::kFineWarps - 1) / rm::kFineWarps;
   {
     RmProfScope prof("k_region_layout", st);
-    rm::k_region_layout<<<1, 1024, 0, st>>>(region_count, P.n_regions, region_start, chunk_base, chunk_region);
+    rm_count_launch(), rm::k_region_layout<<<1, 1024, 0, st>>>(region_count, P.n_regions, region_start, chunk_base, chunk_region);
   }
   {
     RmProfScope prof("k_fine_count", st);
-    rm::k_fine_count<<<chunk_blocks, rm::kFineThreads, 0, st>>>(entries, region_start, chunk_base, chunk_region,
+    rm_count_launch(), rm::k_fine_count<<<chunk_blocks, rm::kFineThreads, 0, st>>>(entries, region_start, chunk_base, chunk_region,
                                                                P.n_regions, chunk_cursor);
   }
   {
     RmProfScope prof("k_fine_cursors", st);
-    rm::k_fine_cursors<<<(P.n_regions + rm::kFineWarps - 1) / rm::kFineWarps, rm::kFineThreads, 0, st>>>(
+    rm_count_launch(), rm::k_fine_cursors<<<(P.n_regions + rm::kFineWarps - 1) / rm::kFineWarps, rm::kFineThreads, 0, st>>>(
         chunk_base, P.n_regions, P.reg_w, gw, gh, tile_start, chunk_cursor);
   }
   {
     RmProfScope prof("k_fine_write", st);
-    rm::k_fine_write<<<chunk_blocks, rm::kFineThreads, 0, st>>>(entries, region_start, chunk_base, chunk_region,
+    rm_count_launch(), rm::k_fine_write<<<chunk_blocks, rm::kFineThreads, 0, st>>>(entries, region_start, chunk_base, chunk_region,
                                                                P.n_regions, chunk_cursor, (uint32_t)n_keys, sorted_idx);
   }
   RM_CUDA_CHECK(cudaPeekAtLastError());

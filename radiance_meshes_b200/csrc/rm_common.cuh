@@ -16,7 +16,16 @@
   } while (0)
 
 void rm_set_last_cuda_error(cudaError_t e, const char* file, int line);
+void rm_clear_last_error();
 int rm_bind_device(const void* device_ptr);
+// Host-side checks every entry point applies to its camera and to pointers it accesses with
+// 128-bit loads or stores.
+int rm_check_cam(const RmCamera* c);
+static inline bool rm_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// Every kernel launch of the library is counted (rm_launch_count), so that a caller can state how
+// many of this library's kernels ran inside a timed region.
+void rm_count_launch();
 
 // Optional per-kernel timing (rm_profile_enable): a scope records a CUDA event
 // pair on the launch stream around the launches it encloses.

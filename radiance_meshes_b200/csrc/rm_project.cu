@@ -55,13 +55,45 @@ __device__ __forceinline__ void distort(float& x, float& y, const DevCam& c) {
   y = ny;
 }
 
+// Fisheye angle functions with a fixed operation sequence (IEEE double, no contraction), so
+// that tile rectangles of fisheye cameras are reproducible bit for bit by any implementation
+// that evaluates the same series; the result is rounded to float once.  Library acosf/sinf
+// differ between vendors in the last bit.
+//   asin(s) = sum_n c_n s^(2n+1), c_0 = 1, c_{n+1} = c_n (2n+1)^2 / ((2n+2)(2n+3)), |s| <= 0.5
+//   acos(x) = pi/2 - asin(x) for x < 0.5, 2 asin(sqrt((1 - x)/2)) otherwise        (0 <= x <= 1)
+//   sin(t)  = sum_n (-1)^n t^(2n+1)/(2n+1)!,                                        0 <= t <= pi/2
+__device__ __forceinline__ double asin_series(double s) {
+  const double s2 = s * s;
+  double term = s, sum = s;
+  for (int n = 0; n < 20; ++n) {
+    const double a = double(2 * n + 1);
+    term = term * s2 * (a * a / (double(2 * n + 2) * double(2 * n + 3)));
+    sum += term;
+  }
+  return sum;
+}
+__device__ __forceinline__ float fisheye_acos(float x) {
+  const double xd = double(x);
+  if (xd < 0.5) return float(1.5707963267948966 - asin_series(xd));
+  return float(2.0 * asin_series(sqrt((1.0 - xd) * 0.5)));
+}
+__device__ __forceinline__ float fisheye_sin(float t) {
+  const double td = double(t), t2 = td * td;
+  double term = td, sum = td;
+  for (int n = 1; n < 13; ++n) {
+    term = -(term * t2) / (double(2 * n) * double(2 * n + 1));
+    sum += term;
+  }
+  return float(sum);
+}
+
 __device__ __forceinline__ f3 camspace_to_image(f3 p, const DevCam& c) {
   float ux, uy;
   if (c.type == 1) {
     f3 dir = normalize3(p);
     float sat = fminf(fmaxf(dir.z, 0.0f), 1.0f);
-    float theta = acosf(sat);
-    float st = sinf(theta);
+    float theta = fisheye_acos(sat);
+    float st = fisheye_sin(theta);
     float k = (st < 1e-6f) ? 1.0f : theta / st;
     ux = dir.x * k;
     uy = dir.y * k;
@@ -222,8 +254,23 @@ k_project(const int32_t* __restrict__ indices, int64_t T, const float* __restric
   float ccx = 0.0f, ccy = 0.0f, ccz = 0.0f;
 
   int4 id = __ldg(reinterpret_cast<const int4*>(indices) + g);
-  f3 v[4] = {load3(vertices, id.x), load3(vertices, id.y), load3(vertices, id.z), load3(vertices, id.w)};
+  // A vertex id outside [0, V) would read out of bounds here and in every later stage: the tet is
+  // culled (later stages skip culled tets) and the host is told through the status word.
+  const bool ids_ok = (uint32_t)id.x < (uint64_t)V && (uint32_t)id.y < (uint64_t)V && (uint32_t)id.z < (uint64_t)V &&
+                      (uint32_t)id.w < (uint64_t)V;
+  if (!ids_ok) {
+    atomicOr(&info->status, RM_STATUS_BAD_INDEX);
+    id = make_int4(0, 0, 0, 0);
+  }
+  f3 v[4] = {{0.f, 0.f, 0.f}, {0.f, 0.f, 0.f}, {0.f, 0.f, 0.f}, {0.f, 0.f, 0.f}};
+  if (ids_ok) {
+    v[0] = load3(vertices, id.x);
+    v[1] = load3(vertices, id.y);
+    v[2] = load3(vertices, id.z);
+    v[3] = load3(vertices, id.w);
+  }
   do {
+    if (!ids_ok) break;
     if (is_planar(v)) break;
     f3 cs[4];
 #pragma unroll
@@ -371,7 +418,7 @@ int rm_launch_project(const int32_t* indices, int64_t T, const float* vertices, 
   if (n == 0) return RM_OK;
   unsigned blocks = (unsigned)((n + 255) / 256);
   RmProfScope prof("k_project", st);
-  rm::k_project<<<blocks, 256, 0, st>>>(indices, T, vertices, V, *cam, tiles_touched, reinterpret_cast<int4*>(rect),
+  rm_count_launch(), rm::k_project<<<blocks, 256, 0, st>>>(indices, T, vertices, V, *cam, tiles_touched, reinterpret_cast<int4*>(rect),
                                         vs_tetra, circumcenter, depth_keys, order_in, tile_diff, info);
   RM_CUDA_CHECK(cudaPeekAtLastError());
   return RM_OK;
@@ -383,7 +430,7 @@ int rm_launch_vertex_backward(const int32_t* indices, const float* vertices, int
   if (T == 0) return RM_OK;
   unsigned blocks = (unsigned)((T + 255) / 256);
   RmProfScope prof("k_vertex_backward", st);
-  rm::k_vertex_backward<<<blocks, 256, 0, st>>>(indices, vertices, T, *cam, tiles_touched, g_vs, g_cc, vgrad);
+  rm_count_launch(), rm::k_vertex_backward<<<blocks, 256, 0, st>>>(indices, vertices, T, *cam, tiles_touched, g_vs, g_cc, vgrad);
   RM_CUDA_CHECK(cudaPeekAtLastError());
   return RM_OK;
 }

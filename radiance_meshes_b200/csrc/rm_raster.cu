@@ -32,6 +32,8 @@
 //     a per-tet row; a per-tet kernel then applies the chain rule to vertices and
 //     cell values (12 vertex atomics per tet instead of 19 atomics per pixel hit).
 
+#include <stdlib.h>
+
 #include "rm_common.cuh"
 
 namespace rm {
@@ -73,8 +75,8 @@ constexpr int kPackThreads = 128;
 // records through shared memory so that the global stores are contiguous.
 __global__ void __launch_bounds__(kPackThreads)
 k_pack_records(const int32_t* __restrict__ indices, const float* __restrict__ vertices,
-               const float* __restrict__ cell, int64_t T, RmCamera rcam, const int32_t* __restrict__ tiles_touched,
-               float4* __restrict__ records) {
+               const float* __restrict__ cell, int64_t T, int64_t V, RmCamera rcam,
+               const int32_t* __restrict__ tiles_touched, float4* __restrict__ records) {
   __shared__ __align__(16) float4 sm[kPackThreads * kRecStride];
   __shared__ bool packed[kPackThreads];  // culled tets appear in no list: their rows are not written
   const int64_t g0 = (int64_t)blockIdx.x * kPackThreads;
@@ -84,9 +86,18 @@ k_pack_records(const int32_t* __restrict__ indices, const float* __restrict__ ve
   for (int k = 0; k < kRecStride; ++k) r[k] = make_float4(0.f, 0.f, 0.f, 0.f);
   const bool live = g < T && !(tiles_touched && tiles_touched[g] == 0);
   packed[threadIdx.x] = live;
+  int4 id = make_int4(0, 0, 0, 0);
+  bool ids_ok = false;
   if (live) {
+    id = __ldg(reinterpret_cast<const int4*>(indices) + g);
+    ids_ok = (uint32_t)id.x < (uint64_t)V && (uint32_t)id.y < (uint64_t)V && (uint32_t)id.z < (uint64_t)V &&
+             (uint32_t)id.w < (uint64_t)V;
+    // A tet that names a vertex outside the table (the projection stage culls it and reports it) keeps the
+    // all-zero planes and gets the always-separating line below: no pixel can hit it.
+    if (!ids_ok) r[6] = make_float4(0.0f, 0.0f, -1.0f, 0.0f);
+  }
+  if (live && ids_ok) {
     f3 cam = {__ldg(rcam.cam_pos), __ldg(rcam.cam_pos + 1), __ldg(rcam.cam_pos + 2)};
-    int4 id = __ldg(reinterpret_cast<const int4*>(indices) + g);
     f3 v[4] = {load3(vertices, id.x), load3(vertices, id.y), load3(vertices, id.z), load3(vertices, id.w)};
     PlaneSetup p;
     make_planes(v, cam, p);
@@ -117,6 +128,9 @@ k_pack_records(const int32_t* __restrict__ indices, const float* __restrict__ ve
       ok = ok && Z > 1e-3f;
       px[k] = fx * (X / Z) + cx;
       py[k] = fy * (Y / Z) + cy;
+      // A vertex just in front of the camera projects to coordinates whose fp32 rounding (and that of
+      // the line offsets built from them) exceeds the 0.01 pixel margin of the tests: no cull then.
+      ok = ok && fabsf(px[k]) <= 1e4f && fabsf(py[k]) <= 1e4f;
     }
     // Edge lines of the convex hull of the four projected vertices, a*x + b*y + c >= 0
     // inside, (a, b) of unit length.  A vertex pair is a hull edge iff the other two
@@ -261,7 +275,11 @@ struct Eval {
 // give the same answers without the special case: such a plane's distance -D/den is
 // huge, positive when the origin is outside (the entry passes the exit: a miss) and
 // negative when it is inside (no effect on the maximum), and symmetrically for the
-// exit; den = 0 gives +-inf, which behaves the same, or NaN, which fmaxf/fminf drop.
+// exit.  A denominator of exactly zero gives +-inf with the sign that rejects the ray
+// when the origin is outside and changes nothing when it is inside, provided -0 counts
+// as "crossing inwards": the direction of a plane is therefore read from the sign bit
+// of den, not from den < 0.  0/0 is NaN, which fmaxf/fminf drop (the reference ignores
+// that plane too).
 // TRACK = true (backward) also reports which plane produced each distance: the first
 // plane, in index order, whose distance equals the chain's result (what a running
 // "strictly greater / strictly smaller" update would have kept).
@@ -277,7 +295,7 @@ __device__ __forceinline__ bool slab_test(const float4 (&rec)[4], f3 d, float mi
     const float4 p = rec[i];
     const float den = p.x * d.x + p.y * d.y + p.z * d.z;
     const float u = __fdividef(-p.w, den);
-    ent[i] = den < 0.0f;
+    ent[i] = __float_as_int(den) < 0;  // sign bit: -0 bounds the entry, +0 the exit
     us[i] = u;
     ue = fmaxf(ue, ent[i] ? u : -1e30f);
     ux = fminf(ux, ent[i] ? 1e30f : u);
@@ -401,15 +419,29 @@ __device__ __forceinline__ void halfwarp_sample_box(bool inside, float sx, float
 // ----------------------------------------------------------------------------
 // Forward
 // ----------------------------------------------------------------------------
-// Examination and evaluation are decoupled.  A half-warp examines its list 16 entries at a
-// time: every lane reads the hull lines of one entry (48 bytes, prefetched one chunk ahead) and
-// decides whether the tet can touch the half-warp's samples at all (zero density is encoded as
-// an always-separating line by k_pack_records); the candidates go, in list order and with their
-// list position, to a queue in shared memory.  Whenever both half-warps of the warp have 16
-// candidates (or nothing left to examine), the next 16 records are staged with cp.async
-// while the previously staged 16 are evaluated.  Only candidates are staged, and the two
-// half-warps, which execute in lock-step, evaluate equally long batches.
-constexpr int kQueue = 2 * kChunk;
+// A half-warp owns 16 pixels of one tile and walks the tile's list in three stages that
+// are decoupled by two small queues in shared memory (ring buffers of 32 slots):
+//   1. examination, 16 entries at a time: every lane reads the hull lines of one entry
+//      (48 bytes, prefetched one chunk ahead) and tests them against the bounding box of
+//      the half-warp's sample positions (zero density is encoded as an always-separating
+//      line by k_pack_records); survivors go to queue A in list order with their position;
+//   2. when both half-warps hold 16 entries in queue A (or have nothing left to examine),
+//      every lane takes one of them and tests the hull lines against each of the 16 sample
+//      positions, which gives the mask of the pixels whose ray can touch the tet; entries
+//      with an empty mask are dropped, the others go to queue B with their mask;
+//   3. when both half-warps hold 16 entries in queue B (or have run dry), their records
+//      (96 bytes each) are staged with 128-bit cp.async, double buffered, and the batch
+//      staged one round earlier is evaluated: the masks are transposed so that every
+//      lane (= pixel) holds the bit set of the batch entries that cover it, and every
+//      lane walks its own bits in list order.  Lanes therefore work on different entries
+//      at the same time and no lane runs a slab test for a tet that cannot cover its
+//      pixel.  A pixel stops at its termination threshold; a half-warp stops examining
+//      once all of its pixels have stopped.
+// For the backward pass every evaluated batch is appended to the half-warp's hit list:
+// the tet ids of the batch and, per pixel, the bit set of the batch entries it hit.
+constexpr int kBatch = 16;       // entries staged and evaluated per half-warp and round
+constexpr int kRing = 32;        // slots of each candidate queue
+constexpr int kStageStride = 7;  // float4 per staged record: 6 used; the odd stride spreads the records over the banks
 
 // The Tukey power ladder of the constant-colour variant (slang/alphablend_shader.slang:26-33):
 // sign(x) |p-1|/p ((|x|/|p-1| + 1)^p - 1).
@@ -417,6 +449,41 @@ __device__ __forceinline__ float tukey_power_ladder(float x, float p) {
   const float q = fmaxf(fabsf(p - 1.0f), 1.0754944e-20f);
   const float y = fabsf(p - 1.0f) / p * (__powf(fabsf(x) / q + 1.0f, p) - 1.0f);
   return x > 0.0f ? y : (x < 0.0f ? -y : 0.0f);
+}
+
+// Mask of the sample positions sp[0..15] that lie inside (or within 0.01 pixel of) the convex hull
+// given by four edge lines; NaN lines (cull disabled for the tet) give the full mask.
+__device__ __forceinline__ uint32_t hull_pixel_mask(float4 l0, float4 l1, float4 l2, const float2* __restrict__ sp) {
+  const float a0 = l0.x, b0 = l0.y, c0 = l0.z + 0.01f;
+  const float a1 = l0.w, b1 = l1.x, c1 = l1.y + 0.01f;
+  const float a2 = l1.z, b2 = l1.w, c2 = l2.x + 0.01f;
+  const float a3 = l2.y, b3 = l2.z, c3 = l2.w + 0.01f;
+  uint32_t m = 0;
+#pragma unroll
+  for (int i = 0; i < 16; i += 2) {
+    const float4 s = *reinterpret_cast<const float4*>(sp + i);  // two sample positions
+    const float e0 = fminf(fminf(fmaf(a0, s.x, fmaf(b0, s.y, c0)), fmaf(a1, s.x, fmaf(b1, s.y, c1))),
+                           fminf(fmaf(a2, s.x, fmaf(b2, s.y, c2)), fmaf(a3, s.x, fmaf(b3, s.y, c3))));
+    const float e1 = fminf(fminf(fmaf(a0, s.z, fmaf(b0, s.w, c0)), fmaf(a1, s.z, fmaf(b1, s.w, c1))),
+                           fminf(fmaf(a2, s.z, fmaf(b2, s.w, c2)), fmaf(a3, s.z, fmaf(b3, s.w, c3))));
+    if (!(e0 < 0.0f)) m |= 1u << i;
+    if (!(e1 < 0.0f)) m |= 2u << i;
+  }
+  return m;
+}
+
+// Bit j of the result = bit `lane16` of word j of the 16 masks at `masks` (16-byte aligned).
+__device__ __forceinline__ uint32_t transpose_masks(const uint32_t* __restrict__ masks, int lane16) {
+  uint32_t bits = 0;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const uint4 w = reinterpret_cast<const uint4*>(masks)[q];
+    bits |= ((w.x >> lane16) & 1u) << (4 * q);
+    bits |= ((w.y >> lane16) & 1u) << (4 * q + 1);
+    bits |= ((w.z >> lane16) & 1u) << (4 * q + 2);
+    bits |= ((w.w >> lane16) & 1u) << (4 * q + 3);
+  }
+  return bits;
 }
 
 // CONST_COLOR = false: the interpolated-colour renderer (slang/alphablend_shader_interp.slang).
@@ -427,25 +494,30 @@ __device__ __forceinline__ float tukey_power_ladder(float x, float p) {
 // termination when the transmittance falls below 1/255; out_img = (r, g, b, transmittance) and
 // dist_img has four channels.
 template <bool CONST_COLOR>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32, 5)
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, 4)
 k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, const float4* __restrict__ records,
           RmCamera rcam, const float2* __restrict__ jitter, float4* __restrict__ out_img,
           float* __restrict__ dist_img, int32_t* __restrict__ n_contrib, int32_t* __restrict__ hit_counts,
           int32_t* __restrict__ hit_ids, uint16_t* __restrict__ hit_masks, uint8_t* __restrict__ tet_flags,
           int subs, int64_t n_units, float pre_multi, float ladder_p) {
-  __shared__ __align__(16) float4 stage[kWarpsPerBlock][2][2][kChunk * 6];  // [warp][half][buffer]
-  __shared__ unsigned hit_bits[kWarpsPerBlock][2][kChunk];
-  __shared__ int queue_id[kWarpsPerBlock][2][kQueue], queue_pos[kWarpsPerBlock][2][kQueue];
-  __shared__ int batch_id[kWarpsPerBlock][2][2][kChunk], batch_pos[kWarpsPerBlock][2][2][kChunk];
+  __shared__ __align__(16) float4 stage[kWarpsPerBlock][2][2][kBatch * kStageStride];  // [warp][half][buffer]
+  __shared__ __align__(16) float2 samples[kWarpsPerBlock][2][16];
+  __shared__ int qa_id[kWarpsPerBlock][2][kRing], qa_pos[kWarpsPerBlock][2][kRing];
+  __shared__ int qb_id[kWarpsPerBlock][2][kRing], qb_pos[kWarpsPerBlock][2][kRing];
+  __shared__ uint32_t qb_mask[kWarpsPerBlock][2][kRing];
+  __shared__ int batch_id[kWarpsPerBlock][2][2][kBatch], batch_pos[kWarpsPerBlock][2][2][kBatch];
+  __shared__ __align__(16) uint32_t batch_mask[kWarpsPerBlock][2][2][kBatch];
+  constexpr unsigned FULL = 0xffffffffu;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int half = lane >> 4, lane16 = lane & 15;
-  const unsigned half_mask = 0xFFFFu << (16 * half);
   const unsigned below = (1u << lane16) - 1u;
   const int64_t unit = ((int64_t)blockIdx.x * kWarpsPerBlock + warp) * 2 + half;
   Unit u = make_unit(rcam, ranges, unit, n_units, subs, lane16);
-  unsigned* hb = hit_bits[warp][half];
-  int* q_id = queue_id[warp][half];
-  int* q_pos = queue_pos[warp][half];
+  int* a_id = qa_id[warp][half];
+  int* a_pos = qa_pos[warp][half];
+  int* b_id = qb_id[warp][half];
+  int* b_pos = qb_pos[warp][half];
+  uint32_t* b_mask = qb_mask[warp][half];
 
   f3 d = {0.f, 0.f, 1.f};
   const int64_t pix = (int64_t)u.y * rcam.image_width + u.x;
@@ -456,6 +528,7 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
     sy = (float)u.y + j.y;
     d = ray_direction(rcam, sx, sy);
   }
+  samples[warp][half][lane16] = make_float2(sx, sy);
   const float min_t = rcam.min_t;
   float X0, X1, Y0, Y1;
   halfwarp_sample_box(u.inside, sx, sy, X0, X1, Y0, Y1);
@@ -464,19 +537,21 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
   float dx = 0.f, dy = 0.f, dz = 0.f, dw = 0.f, dv = 0.f;
   int contrib = 0;
   bool active = u.inside;
-  bool fetching = __ballot_sync(0xffffffffu, active) & half_mask;
+  unsigned act16 = (__ballot_sync(FULL, active) >> (16 * half)) & 0xFFFFu;  // pixels of this half still walking
+  bool fetching = act16 != 0;
 
-  // Hit list of this half-warp: the entries some pixel hit, in list order, each with its tet id and
-  // the 16-bit mask of the pixels that hit it; slots [hbase, hbase + n_hit).
+  // Hit list of this half-warp: the tet ids of every evaluated batch at [hbase, hbase + n_ent), and for
+  // batch b the 16 per-pixel bit sets at [mbase + 16 b, + 16).  Every batch but the last holds 16 entries.
   const int64_t hbase = (int64_t)u.start * u.subs + (int64_t)u.sub * u.len;
-  int n_hit = 0;
+  const int64_t mbase = hbase + 16 * ((int64_t)u.tile * u.subs + u.sub);
+  int n_ent = 0;
 
   // examination state: entry src + lane16 is the one this lane examines next; its tet id and hull
   // lines are already in registers, the id of the entry after it is in flight
   int src = 0;
-  int qn = 0;  // candidates waiting in the queue (same value in all lanes of the half)
+  int qa_h = 0, qa_n = 0, qb_h = 0, qb_n = 0;  // ring heads and fill levels (the same in all lanes of the half)
   int id_e = (fetching && lane16 < u.len) ? __ldg(list + u.start + lane16) : -1;
-  int id_n = (fetching && kChunk + lane16 < u.len) ? __ldg(list + u.start + kChunk + lane16) : -1;
+  int id_n = (fetching && kBatch + lane16 < u.len) ? __ldg(list + u.start + kBatch + lane16) : -1;
   const float qnan = __int_as_float(0x7fc00000);
   float4 hq0 = make_float4(qnan, qnan, qnan, qnan), hq1 = hq0, hq2 = hq0;
   if (id_e >= 0) {
@@ -488,131 +563,149 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
 
   int buf = 0;    // buffer holding the batch to evaluate
   int n_cur = 0;  // its number of entries
+  __syncwarp();
   for (;;) {
     {
-      const bool done = !fetching || (n_cur == 0 && qn == 0 && src >= u.len);
-      if (__all_sync(0xffffffffu, done)) break;
+      const bool done = !fetching || (n_cur == 0 && qb_n == 0 && qa_n == 0 && src >= u.len);
+      if (__all_sync(FULL, done)) break;
     }
-    // ---- examine until both halves have a full batch queued or nothing left to examine
+    // ---- stages 1 and 2: until both halves hold a full batch in queue B or have run dry
     for (;;) {
-      const bool need = fetching && qn < kChunk && src < u.len;
-      if (!__any_sync(0xffffffffu, need)) break;
-      const bool cand = need && id_e >= 0 && !hull_misses_box(hq0, hq1, hq2, X0, X1, Y0, Y1);
-      const unsigned cb = (__ballot_sync(0xffffffffu, cand) >> (16 * half)) & 0xFFFFu;
-      if (cand) {
-        const int slot = qn + __popc(cb & below);
-        q_id[slot] = id_e;
-        q_pos[slot] = src + lane16;
-      }
-      if (need) {
-        qn += __popc(cb);
-        src += kChunk;
-        id_e = id_n;
-        if (id_e >= 0) {
-          const float4* src_rec = records + kRecStride * (int64_t)id_e;
-          hq0 = __ldg(src_rec + 6);
-          hq1 = __ldg(src_rec + 7);
-          hq2 = __ldg(src_rec + 8);
+      const bool need_b = fetching && qb_n < kBatch && (qa_n > 0 || src < u.len);
+      if (!__any_sync(FULL, need_b)) break;
+      const bool ready_a = !need_b || qa_n >= kBatch || src >= u.len;
+      if (!__all_sync(FULL, ready_a)) {
+        const bool ex = need_b && !ready_a;
+        const bool cand = ex && id_e >= 0 && !hull_misses_box(hq0, hq1, hq2, X0, X1, Y0, Y1);
+        const unsigned cb = (__ballot_sync(FULL, cand) >> (16 * half)) & 0xFFFFu;
+        if (cand) {
+          const int slot = (qa_h + qa_n + __popc(cb & below)) & (kRing - 1);
+          a_id[slot] = id_e;
+          a_pos[slot] = src + lane16;
         }
-        id_n = (src + kChunk + lane16 < u.len) ? __ldg(list + u.start + src + kChunk + lane16) : -1;
+        if (ex) {
+          qa_n += __popc(cb);
+          src += kBatch;
+          id_e = id_n;
+          if (id_e >= 0) {
+            const float4* src_rec = records + kRecStride * (int64_t)id_e;
+            hq0 = __ldg(src_rec + 6);
+            hq1 = __ldg(src_rec + 7);
+            hq2 = __ldg(src_rec + 8);
+          }
+          id_n = (src + kBatch + lane16 < u.len) ? __ldg(list + u.start + src + kBatch + lane16) : -1;
+        }
+        continue;
       }
+      __syncwarp();
+      const int take_a = need_b ? min(qa_n, kBatch) : 0;
+      uint32_t m = 0;
+      int cid = 0, cpos = 0;
+      if (lane16 < take_a) {
+        const int slot = (qa_h + lane16) & (kRing - 1);
+        cid = a_id[slot];
+        cpos = a_pos[slot];
+        const float4* src_rec = records + kRecStride * (int64_t)cid;
+        m = hull_pixel_mask(__ldg(src_rec + 6), __ldg(src_rec + 7), __ldg(src_rec + 8), samples[warp][half]) & act16;
+      }
+      const unsigned lb = (__ballot_sync(FULL, m != 0u) >> (16 * half)) & 0xFFFFu;
+      if (m) {
+        const int slot = (qb_h + qb_n + __popc(lb & below)) & (kRing - 1);
+        b_id[slot] = cid;
+        b_pos[slot] = cpos;
+        b_mask[slot] = m;
+      }
+      qa_h = (qa_h + take_a) & (kRing - 1);
+      qa_n -= take_a;
+      qb_n += __popc(lb);
+      __syncwarp();
     }
     __syncwarp();
-    // ---- stage the next batch: the first min(qn, 16) queued candidates
+    // ---- stage 3a: stage the next batch, the first min(qb_n, 16) entries of queue B
     const int nb = buf ^ 1;
-    const int take = fetching ? min(qn, kChunk) : 0;
-    int keep_id = 0, keep_pos = 0;
+    const int take = fetching ? min(qb_n, kBatch) : 0;
     if (lane16 < take) {
-      const int id = q_id[lane16];
+      const int slot = (qb_h + lane16) & (kRing - 1);
+      const int id = b_id[slot];
       batch_id[warp][half][nb][lane16] = id;
-      batch_pos[warp][half][nb][lane16] = q_pos[lane16];
+      batch_pos[warp][half][nb][lane16] = b_pos[slot];
+      batch_mask[warp][half][nb][lane16] = b_mask[slot];
       const float4* src_rec = records + kRecStride * (int64_t)id;
-      float4* dst = stage[warp][half][nb] + lane16 * 6;
+      float4* dst = stage[warp][half][nb] + lane16 * kStageStride;
 #pragma unroll
       for (int k = 0; k < 6; ++k) cp_async16(dst + k, src_rec + k);
+    } else {
+      batch_mask[warp][half][nb][lane16] = 0u;
     }
     cp_async_commit();
-    if (take + lane16 < qn) {  // the rest of the queue moves to its front
-      keep_id = q_id[take + lane16];
-      keep_pos = q_pos[take + lane16];
-    }
-    __syncwarp();
-    if (take + lane16 < qn) {
-      q_id[lane16] = keep_id;
-      q_pos[lane16] = keep_pos;
-    }
-    qn -= take;
-    hb[lane16] = 0u;  // slot of entry lane16 of the batch evaluated now, read back after it
+    qb_h = (qb_h + take) & (kRing - 1);
+    qb_n -= take;
     cp_async_wait<1>();
     __syncwarp();
-    // ---- evaluate the batch staged one iteration ago
+    // ---- stage 3b: evaluate the batch staged one round ago; every lane walks the entries covering its pixel
     const float4* cur = stage[warp][half][buf];
     const int* cur_pos = batch_pos[warp][half][buf];
-    // For every entry the pixels that hit it (while still active) are collected in a
-    // 16-bit mask in shared memory; the entries with a non-zero mask go to the hit list
-    // the backward pass walks.
-    if (active) {
-      for (int j = 0; j < n_cur; ++j) {
-        const float4* rec = cur + j * 6;
-        const float4 pl[4] = {rec[0], rec[1], rec[2], rec[3]};
-        Eval e;
-        if (slab_test<false>(pl, d, min_t, e) && integrate(rec, d, min_t, e)) {
-          atomicOr(&hb[j], 1u << lane16);
-          sr = fmaf(e.cr, T, sr);
-          sg = fmaf(e.cg, T, sg);
-          sb = fmaf(e.cb, T, sb);
-          bool finished;
-          if (CONST_COLOR) {
-            const float weight = T * (1.0f - e.alpha);
-            const float m = tukey_power_ladder(e.enter * pre_multi, ladder_p);
-            dx = fmaf(2.0f * weight * m, dz, dx);
-            dy = fmaf(2.0f * weight, dw, dy);
-            dz += weight;
-            dw = fmaf(weight, m, dw);
-            T *= e.alpha;
-            finished = T < 1.0f / 255.0f;
-          } else {
-            logT -= e.tau;
-            T *= e.alpha;
-            float dens = rec[5].w;
-            float m1 = dens * (e.exit + e.enter) * 0.5f;
-            dx = fmaf(2.0f * m1, dz, dx);
-            dy = fmaf(2.0f * dens, dw, dy);
-            dz += dens;
-            dw += m1;
-            dv = fmaf(dens * dens, e.dt * (1.0f / 3.0f), dv);
-            finished = logT < -5.5f;
-          }
-          if (finished) {
-            active = false;
-            contrib = cur_pos[j] + 1;  // entries walked, the terminating one included
-            break;
-          }
+    uint32_t bits = (active && n_cur > 0) ? transpose_masks(batch_mask[warp][half][buf], lane16) : 0u;
+    uint32_t hitbits = 0;
+    while (bits) {
+      const int j = __ffs(bits) - 1;
+      bits &= bits - 1;
+      const float4* rec = cur + j * kStageStride;
+      const float4 pl[4] = {rec[0], rec[1], rec[2], rec[3]};
+      Eval e;
+      if (slab_test<false>(pl, d, min_t, e) && integrate(rec, d, min_t, e)) {
+        hitbits |= 1u << j;
+        sr = fmaf(e.cr, T, sr);
+        sg = fmaf(e.cg, T, sg);
+        sb = fmaf(e.cb, T, sb);
+        bool finished;
+        if (CONST_COLOR) {
+          const float weight = T * (1.0f - e.alpha);
+          const float mm = tukey_power_ladder(e.enter * pre_multi, ladder_p);
+          dx = fmaf(2.0f * weight * mm, dz, dx);
+          dy = fmaf(2.0f * weight, dw, dy);
+          dz += weight;
+          dw = fmaf(weight, mm, dw);
+          T *= e.alpha;
+          finished = T < 1.0f / 255.0f;
+        } else {
+          logT -= e.tau;
+          T *= e.alpha;
+          const float dens = rec[5].w;
+          const float m1 = dens * (e.exit + e.enter) * 0.5f;
+          dx = fmaf(2.0f * m1, dz, dx);
+          dy = fmaf(2.0f * dens, dw, dy);
+          dz += dens;
+          dw += m1;
+          dv = fmaf(dens * dens, e.dt * (1.0f / 3.0f), dv);
+          finished = logT < -5.5f;
+        }
+        if (finished) {
+          active = false;
+          contrib = cur_pos[j] + 1;  // entries walked, the terminating one included
+          bits = 0;
         }
       }
     }
     __syncwarp();
-    if (hit_ids) {  // append the batch's entries that were hit, in list order
-      const unsigned m = lane16 < n_cur ? hb[lane16] : 0u;
-      const unsigned nzb = (__ballot_sync(0xffffffffu, m != 0u) >> (16 * half)) & 0xFFFFu;
-      if (m) {
-        const int64_t slot = hbase + n_hit + __popc(nzb & below);
+    if (hit_ids && n_cur > 0) {  // append the batch to the hit list
+      if (lane16 < n_cur) {
         const int id = batch_id[warp][half][buf][lane16];
-        hit_ids[slot] = id;
-        hit_masks[slot] = (uint16_t)m;
-        tet_flags[id] = 1;  // this tet receives a gradient
+        hit_ids[hbase + n_ent + lane16] = id;
+        tet_flags[id] = 1;  // this tet's record-gradient row is cleared and read by the backward pass
       }
-      n_hit += __popc(nzb);
+      hit_masks[mbase + n_ent + lane16] = (uint16_t)hitbits;  // n_ent is a multiple of 16 here
+      n_ent += n_cur;
     }
-    __syncwarp();
-    fetching = __ballot_sync(0xffffffffu, active) & half_mask;
+    act16 = (__ballot_sync(FULL, active) >> (16 * half)) & 0xFFFFu;
+    fetching = act16 != 0;
     buf = nb;
     n_cur = take;
   }
   cp_async_wait<0>();
   if (active) contrib = u.len;  // walked the whole list
 
-  if (hit_counts && lane16 == 0 && unit < n_units) hit_counts[(int64_t)u.tile * u.subs + u.sub] = n_hit;
+  if (hit_counts && lane16 == 0 && unit < n_units) hit_counts[(int64_t)u.tile * u.subs + u.sub] = n_ent;
   if (u.inside) {
     if (CONST_COLOR) {
       out_img[pix] = make_float4(sr, sg, sb, T);
@@ -639,6 +732,7 @@ k_backward(const int2* __restrict__ ranges, const float4* __restrict__ records, 
   __shared__ int stage_id[kWarpsPerBlock][2][2][kChunk];
   __shared__ unsigned stage_mask[kWarpsPerBlock][2][2][kChunk];  // pixels of the tile that hit the entry (forward)
   __shared__ __align__(16) float reduce_buf[kWarpsPerBlock][2 * (kChunk * 20 + 16)];
+  __shared__ __align__(16) uint32_t lane_bits[kWarpsPerBlock][2][kChunk];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int half = lane >> 4, lane16 = lane & 15;
   const int64_t unit = ((int64_t)blockIdx.x * kWarpsPerBlock + warp) * 2 + half;
@@ -661,44 +755,51 @@ k_backward(const int2* __restrict__ ranges, const float4* __restrict__ records, 
   }
   const float min_t = rcam.min_t;
 
-  // The half-warp walks its hit list (written by the forward pass: the entries some pixel of
-  // these 16 hit, in list order, with tet id and pixel mask) from the last entry to the first.
+  // The half-warp walks its hit list (written by the forward pass: the batches it evaluated, each
+  // with its tet ids and, per pixel, the bit set of the batch entries the pixel hit) from the last
+  // entry to the first.  Batch c holds entries [16 c, 16 c + 16) of the list, the last one fewer.
   const int64_t hbase = (int64_t)u.start * u.subs + (int64_t)u.sub * u.len;
+  const int64_t mbase = hbase + 16 * ((int64_t)u.tile * u.subs + u.sub);
   const int nmax = unit < n_units ? min(__ldg(hit_counts + (int64_t)u.tile * u.subs + u.sub), u.len) : 0;
   const int nchunks = (nmax + kChunk - 1) / kChunk;
   const int max_chunks = max(nchunks, __shfl_xor_sync(0xffffffffu, nchunks, 16));
 
-  // chunk k of this half (k = 0 is the LAST chunk of its hit list) sits in buffer k&1
-  // Tet id and hit mask this lane stages for chunk k+1, loaded while chunk k is issued.
+  // chunk k of this half (k = 0 is the LAST batch of its hit list) sits in buffer k&1
+  // Tet id and per-pixel bits this lane loads for chunk k+1, fetched while chunk k is issued.
   int id_next = 0;
-  unsigned mask_next = 0;
+  unsigned bits_next = 0;
   {
     const int e0 = (nchunks - 1) * kChunk + lane16;
-    if (nchunks >= 1 && e0 < nmax) {
-      id_next = __ldg(hit_ids + hbase + e0);
-      mask_next = __ldg(hit_masks + hbase + e0);
+    if (nchunks >= 1) {
+      if (e0 < nmax) id_next = __ldg(hit_ids + hbase + e0);
+      bits_next = __ldg(hit_masks + mbase + e0);
     }
   }
   auto issue = [&](int k) {
     int c = nchunks - 1 - k;
+    unsigned bits = 0u;
+    int id = 0;
     if (c >= 0) {
-      int e = c * kChunk + lane16;
-      const int id = id_next;
-      const unsigned m = e < nmax ? mask_next : 0u;
-      if (c >= 1) {  // entry e - kChunk is always below nmax
-        id_next = __ldg(hit_ids + hbase + e - kChunk);
-        mask_next = __ldg(hit_masks + hbase + e - kChunk);
+      id = id_next;
+      bits = bits_next;
+      if (c >= 1) {  // batch c - 1 is a full batch
+        const int e = (c - 1) * kChunk + lane16;
+        id_next = __ldg(hit_ids + hbase + e);
+        bits_next = __ldg(hit_masks + mbase + e);
       }
-      stage_id[warp][half][k & 1][lane16] = id;
-      stage_mask[warp][half][k & 1][lane16] = m;
-      if (m) {
-        const float4* src = records + kRecStride * (int64_t)id;
-        float4* dst = stage[warp][half][k & 1] + lane16 * 6;
+    }
+    // per-pixel bit sets -> per-entry pixel masks (lane j gets the mask of entry j of the batch)
+    lane_bits[warp][half][lane16] = bits;
+    __syncwarp();
+    const unsigned m = transpose_masks(lane_bits[warp][half], lane16);
+    __syncwarp();
+    stage_id[warp][half][k & 1][lane16] = id;
+    stage_mask[warp][half][k & 1][lane16] = m;
+    if (m) {
+      const float4* src = records + kRecStride * (int64_t)id;
+      float4* dst = stage[warp][half][k & 1] + lane16 * 6;
 #pragma unroll
-        for (int q = 0; q < 6; ++q) cp_async16(dst + q, src + q);
-      }
-    } else {
-      stage_mask[warp][half][k & 1][lane16] = 0u;
+      for (int q = 0; q < 6; ++q) cp_async16(dst + q, src + q);
     }
     cp_async_commit();
   };
@@ -858,6 +959,257 @@ k_backward(const int2* __restrict__ ranges, const float4* __restrict__ records, 
       }
     }
     __syncwarp();
+  }
+  cp_async_wait<0>();
+}
+
+// ----------------------------------------------------------------------------
+// Backward, per-pixel walk
+// ----------------------------------------------------------------------------
+// The hit lists give every pixel the bit set of the batch entries it hit, so every lane
+// walks its own bits from the last to the first and no lane idles on an entry its pixel
+// missed.  Lanes of a half-warp are then on different entries at the same time, and
+// the per-entry sums over the pixels can no longer be formed by a lock-step transpose.
+// Instead, per round: every lane with a hit writes its 16 gradient values as a row to
+// shared memory with a tag (entry, entering plane, exit plane); then lane c adds up
+// column c of the rows, run by run of equal tags, and adds each run's sum to the
+// entry's accumulator in shared memory - column c of every accumulator belongs to lane c
+// alone, so plain loads and stores do (shared-memory float atomics serialise on equal
+// addresses, which is the common case here).  After the batch the accumulators go to the
+// record-gradient rows with 128-bit reductions and are cleared.
+constexpr int kBwdWarps = 2;     // warps per block
+constexpr int kRowStride = 20;   // floats per gradient row (16 used; 80 bytes keep the 128-bit stores apart)
+constexpr int kAccStride = 40;   // floats per accumulator: 4 planes as entering plane, 4 as exit plane, 8 colour fields
+constexpr uint32_t kNoTag = 0xFFFFFFFFu;
+
+struct __align__(16) BwdShared {  // per half-warp
+  float4 stage[2][kBatch * kStageStride];
+  float acc[kBatch * kAccStride];
+  float rows[16 * kRowStride];
+  uint32_t tags[16];
+  int ids[2][kBatch];
+};
+
+__global__ void __launch_bounds__(kBwdWarps * 32, 7)
+k_backward_px(const int2* __restrict__ ranges, const float4* __restrict__ records, RmCamera rcam,
+              const float2* __restrict__ jitter, const float4* __restrict__ out_img,
+              const float* __restrict__ dist_img, const int32_t* __restrict__ hit_counts,
+              const int32_t* __restrict__ hit_ids, const uint16_t* __restrict__ hit_masks,
+              const float4* __restrict__ g_img, const float* __restrict__ g_dist, float* __restrict__ grec, int subs,
+              int64_t n_units) {
+  __shared__ BwdShared shm[kBwdWarps][2];
+  constexpr unsigned FULL = 0xffffffffu;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int half = lane >> 4, lane16 = lane & 15;
+  const int64_t unit = ((int64_t)blockIdx.x * kBwdWarps + warp) * 2 + half;
+  Unit u = make_unit(rcam, ranges, unit, n_units, subs, lane16);
+  BwdShared& S = shm[warp][half];
+
+  f3 d = {0.f, 0.f, 1.f};
+  const int64_t pix = (int64_t)u.y * rcam.image_width + u.x;
+  float logT = 0.f, sz = 0.f, sw = 0.f;
+  float gr = 0.f, gg = 0.f, gb = 0.f, glogT = 0.f, gx = 0.f, gy = 0.f, gz = 0.f, gw = 0.f, gv = 0.f;
+  if (u.inside) {
+    float2 j = __ldg(jitter + pix);
+    d = ray_direction(rcam, (float)u.x + j.x, (float)u.y + j.y);
+    logT = __ldg(out_img + pix).w;
+    sz = __ldg(dist_img + 5 * pix + 2);
+    sw = __ldg(dist_img + 5 * pix + 3);
+    float4 g4 = __ldg(g_img + pix);
+    gr = g4.x; gg = g4.y; gb = g4.z; glogT = g4.w;
+    const float* gd = g_dist + 5 * pix;
+    gx = __ldg(gd); gy = __ldg(gd + 1); gz = __ldg(gd + 2); gw = __ldg(gd + 3); gv = __ldg(gd + 4);
+  }
+  const float min_t = rcam.min_t;
+
+  // column ownership of this lane in the reduction: lanes 0-3 own component c of every plane in its
+  // role as entering plane, lanes 4-7 the same for the exit plane, lanes 8-15 one colour field each
+  const int tag_shift = lane16 < 4 ? 8 : 12;
+  const uint32_t tag_mask = lane16 < 8 ? 7u : 0u;
+  const int acc_base = lane16 < 4 ? lane16 : (lane16 < 8 ? 16 + (lane16 - 4) : 32 + (lane16 - 8));
+
+  const int64_t hbase = (int64_t)u.start * u.subs + (int64_t)u.sub * u.len;
+  const int64_t mbase = hbase + 16 * ((int64_t)u.tile * u.subs + u.sub);
+  const int nmax = unit < n_units ? min(__ldg(hit_counts + (int64_t)u.tile * u.subs + u.sub), u.len) : 0;
+  const int nchunks = (nmax + kBatch - 1) / kBatch;
+  const int max_chunks = max(nchunks, __shfl_xor_sync(FULL, nchunks, 16));
+
+  {
+    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = lane16; i < kBatch * kAccStride / 4; i += 16) reinterpret_cast<float4*>(S.acc)[i] = z;
+  }
+
+  // batch k of this half (k = 0 is the LAST batch of its hit list) sits in buffer k&1
+  int id_next = 0;
+  uint32_t bits_next = 0;
+  if (nchunks >= 1) {
+    const int e0 = (nchunks - 1) * kBatch + lane16;
+    if (e0 < nmax) id_next = __ldg(hit_ids + hbase + e0);
+    bits_next = __ldg(hit_masks + mbase + e0);
+  }
+  auto issue = [&](int k, uint32_t& bits_out, int& n_out) {
+    const int c = nchunks - 1 - k;
+    bits_out = 0u;
+    n_out = 0;
+    if (c >= 0) {
+      const int id = id_next;
+      bits_out = bits_next;
+      n_out = min(kBatch, nmax - c * kBatch);
+      if (c >= 1) {  // batch c - 1 is a full batch
+        const int e = (c - 1) * kBatch + lane16;
+        id_next = __ldg(hit_ids + hbase + e);
+        bits_next = __ldg(hit_masks + mbase + e);
+      }
+      if (lane16 < n_out) {
+        S.ids[k & 1][lane16] = id;
+        const float4* src = records + kRecStride * (int64_t)id;
+        float4* dst = S.stage[k & 1] + lane16 * kStageStride;
+#pragma unroll
+        for (int q = 0; q < 6; ++q) cp_async16(dst + q, src + q);
+      }
+    }
+    cp_async_commit();
+  };
+
+  uint32_t bits_cur = 0, bits_ahead = 0;
+  int n_cur = 0, n_ahead = 0;
+  issue(0, bits_cur, n_cur);
+  for (int k = 0; k < max_chunks; ++k) {
+    issue(k + 1, bits_ahead, n_ahead);
+    cp_async_wait<1>();
+    __syncwarp();
+    const float4* cur = S.stage[k & 1];
+    uint32_t bits = bits_cur;
+    while (__any_sync(FULL, bits != 0u)) {
+      uint32_t tag = kNoTag;
+      if (bits) {
+        const int j = 31 - __clz(bits);
+        bits ^= 1u << j;
+        const float4* rec = cur + j * kStageStride;
+        const float4 pl[4] = {rec[0], rec[1], rec[2], rec[3]};
+        Eval ev;
+        // same arithmetic as the forward pass, so the test succeeds again
+        if (slab_test<true>(pl, d, min_t, ev) && integrate(rec, d, min_t, ev)) {
+          const float4 cbv = rec[5];
+          const float dens = cbv.w;
+          // undo: state before this tet
+          logT += ev.tau;
+          const float Tp = __expf(fminf(logT, 46.0517f));
+          const float m0 = dens, m1 = dens * (ev.exit + ev.enter) * 0.5f;
+          sz -= m0;
+          sw -= m1;
+          // reverse of the state update
+          const float gcr = gr * Tp, gcg = gg * Tp, gcb = gb * Tp;
+          const float gT = gr * ev.cr + gg * ev.cg + gb * ev.cb;
+          const float g_a = -glogT;
+          const float g_m1 = 2.0f * sz * gx + gw;
+          const float g_m0 = 2.0f * sw * gy + gz;
+          float g_dens = g_m0 + g_m1 * (ev.exit + ev.enter) * 0.5f + gv * 2.0f * dens * ev.dt * (1.0f / 3.0f);
+          float g_exit = g_m1 * dens * 0.5f, g_enter = g_exit;
+          if (ev.exit - ev.enter > 0.0f) {
+            float kk = gv * dens * dens * (1.0f / 3.0f);
+            g_exit += kk;
+            g_enter -= kk;
+          }
+          glogT = fmaf(gT, Tp, glogT);
+          gz = fmaf(2.0f * m1, gx, gz);
+          gw = fmaf(2.0f * m0, gy, gw);
+          // reverse of the segment integral
+          const float cxr = cbv.x + ev.ox, cxg = cbv.y + ev.ox, cxb = cbv.z + ev.ox;
+          const float cer = cbv.x + ev.oe, ceg = cbv.y + ev.oe, ceb = cbv.z + ev.oe;
+          const float g_w0 = gcr * cxr + gcg * cxg + gcb * cxb;
+          const float g_w1 = gcr * cer + gcg * ceg + gcb * ceb;
+          const float G = gcr + gcg + gcb;
+          const float wsum = ev.w0 + ev.w1;
+          const float g_ox = ev.w0 * G, g_oe = ev.w1 * G;
+          const float g_gd = g_ox * (ev.exit + min_t) + g_oe * (ev.enter + min_t);
+          g_exit = fmaf(g_ox, ev.gd, g_exit);
+          g_enter = fmaf(g_oe, ev.gd, g_enter);
+          const float g_phi = g_w0 - g_w1;
+          const float dphi = -__fdividef(ev.w0, ev.tau);  // d phi / d tau = (alpha - phi) / tau = -w0 / tau
+          const float g_tau = g_phi * dphi + g_w0 * ev.alpha + g_a;
+          g_dens = fmaf(g_tau, ev.dt, g_dens);
+          const float g_dt = g_tau * dens;
+          if (ev.exit - ev.enter > 0.0f) {
+            g_exit += g_dt;
+            g_enter -= g_dt;
+          }
+          float g_tx = 0.0f, g_te = 0.0f;
+          if (ev.tx > ev.enter) g_tx = g_exit; else g_enter += g_exit;
+          if (ev.te > 0.0f) g_te = g_enter;
+          // planes: t = -D/den - min_t  =>  dt/dD = -1/den, dt/dn = (D/den^2) d
+          float4 ve = make_float4(0.f, 0.f, 0.f, 0.f), vx = ve;
+          int pe = 0, px = 0;  // a plane without a gradient receives zeros
+          if (g_te != 0.0f && ev.ie >= 0) {
+            const float4 p = rec[ev.ie];
+            const float r = __fdividef(1.0f, p.x * d.x + p.y * d.y + p.z * d.z);
+            const float kn = g_te * p.w * r * r;
+            ve = make_float4(kn * d.x, kn * d.y, kn * d.z, -g_te * r);
+            pe = ev.ie;
+          }
+          if (g_tx != 0.0f && ev.ix >= 0) {
+            const float4 p = rec[ev.ix];
+            const float r = __fdividef(1.0f, p.x * d.x + p.y * d.y + p.z * d.z);
+            const float kn = g_tx * p.w * r * r;
+            vx = make_float4(kn * d.x, kn * d.y, kn * d.z, -g_tx * r);
+            px = ev.ix;
+          }
+          float4* row4 = reinterpret_cast<float4*>(S.rows + lane16 * kRowStride);
+          row4[0] = ve;
+          row4[1] = vx;
+          row4[2] = make_float4(g_gd * d.x, g_gd * d.y, g_gd * d.z, g_ox + g_oe);
+          row4[3] = make_float4(wsum * gcr, wsum * gcg, wsum * gcb, g_dens);
+          tag = (uint32_t)j | ((uint32_t)pe << 8) | ((uint32_t)px << 12);
+        }
+      }
+      S.tags[lane16] = tag;
+      __syncwarp();
+      {
+        // lane c sums column c of the rows, run by run of equal tags
+        const uint4 t0 = reinterpret_cast<const uint4*>(S.tags)[0], t1 = reinterpret_cast<const uint4*>(S.tags)[1],
+                    t2 = reinterpret_cast<const uint4*>(S.tags)[2], t3 = reinterpret_cast<const uint4*>(S.tags)[3];
+        const uint32_t tg[16] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w,
+                                 t2.x, t2.y, t2.z, t2.w, t3.x, t3.y, t3.z, t3.w};
+        uint32_t run = kNoTag;
+        float sum = 0.0f;
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+          const uint32_t t = tg[r];
+          if (t != run) {
+            if (run != kNoTag) {
+              float* a = S.acc + (run & 0xFFu) * kAccStride + acc_base + ((run >> tag_shift) & tag_mask) * 4;
+              *a += sum;
+            }
+            run = t;
+            sum = 0.0f;
+          }
+          if (t != kNoTag) sum += S.rows[r * kRowStride + lane16];
+        }
+        if (run != kNoTag) {
+          float* a = S.acc + (run & 0xFFu) * kAccStride + acc_base + ((run >> tag_shift) & tag_mask) * 4;
+          *a += sum;
+        }
+      }
+      __syncwarp();
+    }
+    // the batch's accumulators go to the record-gradient rows and are cleared
+    {
+      const int* ids = S.ids[k & 1];
+      float4* acc4 = reinterpret_cast<float4*>(S.acc);
+      const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int q = lane16; q < n_cur * (kAccStride / 4); q += 16) {
+        const int j = q / (kAccStride / 4), part = q - j * (kAccStride / 4);
+        const float4 a = acc4[q];
+        if (a.x != 0.f || a.y != 0.f || a.z != 0.f || a.w != 0.f) {
+          float4* row = reinterpret_cast<float4*>(grec + (int64_t)ids[j] * 24);
+          atomicAdd(row + (part < 4 ? part : part - 4), a);  // parts 0-3 and 4-7: planes 0-3; 8, 9: colour fields
+          acc4[q] = z;
+        }
+      }
+    }
+    __syncwarp();
+    bits_cur = bits_ahead;
+    n_cur = n_ahead;
   }
   cp_async_wait<0>();
 }
@@ -1137,12 +1489,12 @@ static inline void unit_grid(const RmCamera* cam, int* subs, int64_t* n_units, u
   *blocks = (unsigned)((*n_units + per_block - 1) / per_block);
 }
 
-int rm_launch_pack(const int32_t* indices, const float* vertices, const float* cell, int64_t T, const RmCamera* cam,
-                   const int32_t* tiles_touched, float* records, cudaStream_t st) {
+int rm_launch_pack(const int32_t* indices, const float* vertices, const float* cell, int64_t T, int64_t V,
+                   const RmCamera* cam, const int32_t* tiles_touched, float* records, cudaStream_t st) {
   if (T == 0) return RM_OK;
   RmProfScope prof("k_pack_records", st);
-  rm::k_pack_records<<<(unsigned)((T + rm::kPackThreads - 1) / rm::kPackThreads), rm::kPackThreads, 0, st>>>(indices, vertices, cell, T, *cam, tiles_touched,
-                                                                  reinterpret_cast<float4*>(records));
+  rm_count_launch(), rm::k_pack_records<<<(unsigned)((T + rm::kPackThreads - 1) / rm::kPackThreads), rm::kPackThreads, 0, st>>>(
+      indices, vertices, cell, T, V, *cam, tiles_touched, reinterpret_cast<float4*>(records));
   RM_CUDA_CHECK(cudaPeekAtLastError());
   return RM_OK;
 }
@@ -1156,7 +1508,7 @@ int rm_launch_forward(const int32_t* list, const int32_t* ranges, const float* r
   unit_grid(cam, &subs, &n_units, &blocks);
   if (n_units == 0) return RM_OK;
   RmProfScope prof("k_forward", st);
-  rm::k_forward<false><<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
+  rm_count_launch(), rm::k_forward<false><<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
       list, reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam,
       reinterpret_cast<const float2*>(jitter), reinterpret_cast<float4*>(out_img), dist_img, n_contrib,
       hits ? hits->counts : nullptr, hits ? hits->ids : nullptr, hits ? hits->masks : nullptr,
@@ -1174,7 +1526,7 @@ int rm_launch_forward_constant_color(const int32_t* list, const int32_t* ranges,
   unit_grid(cam, &subs, &n_units, &blocks);
   if (n_units == 0) return RM_OK;
   RmProfScope prof("k_forward<constant colour>", st);
-  rm::k_forward<true><<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
+  rm_count_launch(), rm::k_forward<true><<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
       list, reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam, nullptr,
       reinterpret_cast<float4*>(out_img), dist_img, n_contrib, nullptr, nullptr, nullptr, nullptr, subs, n_units,
       pre_multi, ladder_p);
@@ -1194,7 +1546,7 @@ int rm_launch_tet_err(const int32_t* list, const int32_t* ranges, const float* r
   unit_grid(cam, &subs, &n_units, &blocks);
   if (n_units == 0) return RM_OK;
   RmProfScope prof("k_tet_err", st);
-  rm::k_tet_err<<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
+  rm_count_launch(), rm::k_tet_err<<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
       list, reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam, pixel_err,
       ssim_err, tet_err, tet_count, subs, n_units);
   RM_CUDA_CHECK(cudaPeekAtLastError());
@@ -1212,7 +1564,7 @@ int rm_launch_backward(const int32_t* list, const int32_t* ranges, const float* 
   if (T == 0) return RM_OK;
   {
     RmProfScope prof("k_clear_flagged_rows", st);
-    rm::k_clear_flagged_rows<<<(unsigned)(((T + 3) / 4 + 255) / 256), 256, 0, st>>>(
+    rm_count_launch(), rm::k_clear_flagged_rows<<<(unsigned)(((T + 3) / 4 + 255) / 256), 256, 0, st>>>(
         hits->tet_flags, T, reinterpret_cast<float4*>(grec));
   }
   int subs;
@@ -1221,13 +1573,22 @@ int rm_launch_backward(const int32_t* list, const int32_t* ranges, const float* 
   unit_grid(cam, &subs, &n_units, &blocks);
   if (n_units > 0) {
     RmProfScope prof("k_backward", st);
-    rm::k_backward<<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
-        reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam,
-        reinterpret_cast<const float2*>(jitter), reinterpret_cast<const float4*>(out_img), dist_img, hits->counts,
-        hits->ids, hits->masks, reinterpret_cast<const float4*>(g_img), g_dist, grec, subs, n_units);
+    static const bool lockstep = getenv("RM_BACKWARD_LOCKSTEP") != nullptr;
+    if (lockstep) {
+      rm_count_launch(), rm::k_backward<<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
+          reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam,
+          reinterpret_cast<const float2*>(jitter), reinterpret_cast<const float4*>(out_img), dist_img, hits->counts,
+          hits->ids, hits->masks, reinterpret_cast<const float4*>(g_img), g_dist, grec, subs, n_units);
+    } else {
+      const int64_t per_block = rm::kBwdWarps * 2;
+      rm_count_launch(), rm::k_backward_px<<<(unsigned)((n_units + per_block - 1) / per_block), rm::kBwdWarps * 32, 0, st>>>(
+          reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam,
+          reinterpret_cast<const float2*>(jitter), reinterpret_cast<const float4*>(out_img), dist_img, hits->counts,
+          hits->ids, hits->masks, reinterpret_cast<const float4*>(g_img), g_dist, grec, subs, n_units);
+    }
   }
   RmProfScope prof2("k_backward_finish", st);
-  rm::k_backward_finish<<<(unsigned)((T + rm::kFinishThreads - 1) / rm::kFinishThreads), rm::kFinishThreads, 0, st>>>(indices, vertices, cell, T, *cam,
+  rm_count_launch(), rm::k_backward_finish<<<(unsigned)((T + rm::kFinishThreads - 1) / rm::kFinishThreads), rm::kFinishThreads, 0, st>>>(indices, vertices, cell, T, *cam,
                                                                      reinterpret_cast<const float4*>(grec),
                                                                      hits->tet_flags, vgrad, cgrad);
   RM_CUDA_CHECK(cudaPeekAtLastError());
@@ -1258,8 +1619,12 @@ extern "C" int rm_backward_static_scratch(const int32_t* sorted_tetra_idx, const
                                           const float* vertices, const float* cell_values, int64_t n_tets,
                                           int64_t n_vertices, float* vertices_grad, float* cell_values_grad,
                                           void* stream) {
-  if (n_tets < 0 || n_vertices < 0 || !cam) return RM_ERR_INVALID_ARG;
+  // the same host-side checks as rm_backward, before anything touches the device
+  rm_clear_last_error();
   if (n_tets > RM_STATIC_SCRATCH_MAX_TETS) return RM_ERR_STATIC_SCRATCH;
+  int rc = rm_check_cam(cam);
+  if (rc) return rc;
+  if (n_tets < 0 || n_vertices < 0) return RM_ERR_INVALID_ARG;
   if (!tile_ranges || !ray_jitter || !output_img || !distortion_img || !hits || !hits->counts || !hits->ids ||
       !hits->masks || !hits->tet_flags || !grad_output_img || !grad_distortion_img || !vertices_grad)
     return RM_ERR_INVALID_ARG;
@@ -1267,13 +1632,9 @@ extern "C" int rm_backward_static_scratch(const int32_t* sorted_tetra_idx, const
   (void)n_contributors;
   if (n_tets > 0 && (!indices || !vertices || !cell_values || !cell_values_grad || !records))
     return RM_ERR_INVALID_ARG;
-  if (cam->image_height <= 0 || cam->image_width <= 0 || cam->tile_height <= 0 || cam->tile_width <= 0 ||
-      cam->tile_row_begin < 0 || cam->tile_row_end > cam->grid_height || cam->tile_row_begin > cam->tile_row_end)
-    return RM_ERR_INVALID_ARG;
-  auto misaligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) != 0; };
-  if (misaligned(output_img) || misaligned(grad_output_img) || misaligned(records) || misaligned(indices))
+  if (!rm_aligned16(output_img) || !rm_aligned16(grad_output_img) || !rm_aligned16(records) || !rm_aligned16(indices))
     return RM_ERR_WORKSPACE;
-  int rc = rm_bind_device(vertices_grad);  // makes the device that owns the buffers current
+  rc = rm_bind_device(vertices_grad);  // makes the device that owns the buffers current
   if (rc) return rc;
   // Set-up, once per device, with that device current: the array's name is a
   // host-side handle, the kernels need its device address.
@@ -1294,20 +1655,25 @@ extern "C" int rm_backward_static_scratch(const int32_t* sorted_tetra_idx, const
   // The array keeps the previous call's sums: clear the rows this call accumulates into.
   RM_CUDA_CHECK(cudaMemsetAsync(vertices_grad, 0, sizeof(float) * 3 * (size_t)n_vertices, st));
   if (n_tets == 0) return RM_OK;
-  rm::k_clear_flagged_rows<<<(unsigned)(((n_tets + 3) / 4 + 255) / 256), 256, 0, st>>>(hits->tet_flags, n_tets,
-                                                                                 reinterpret_cast<float4*>(scratch));
+  {
+    RmProfScope prof("k_clear_flagged_rows", st);
+    rm_count_launch(), rm::k_clear_flagged_rows<<<(unsigned)(((n_tets + 3) / 4 + 255) / 256), 256, 0, st>>>(
+        hits->tet_flags, n_tets, reinterpret_cast<float4*>(scratch));
+  }
   int subs;
   int64_t n_units;
   unsigned blocks;
   unit_grid(cam, &subs, &n_units, &blocks);
   if (n_units > 0) {
-    rm::k_backward<<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
+    RmProfScope prof("k_backward", st);
+    rm_count_launch(), rm::k_backward<<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
         reinterpret_cast<const int2*>(tile_ranges), reinterpret_cast<const float4*>(records), *cam,
         reinterpret_cast<const float2*>(ray_jitter), reinterpret_cast<const float4*>(output_img), distortion_img,
         hits->counts, hits->ids, hits->masks, reinterpret_cast<const float4*>(grad_output_img), grad_distortion_img,
         scratch, subs, n_units);
   }
-  rm::k_backward_finish<<<(unsigned)((n_tets + rm::kFinishThreads - 1) / rm::kFinishThreads), rm::kFinishThreads, 0, st>>>(
+  RmProfScope prof2("k_backward_finish", st);
+  rm_count_launch(), rm::k_backward_finish<<<(unsigned)((n_tets + rm::kFinishThreads - 1) / rm::kFinishThreads), rm::kFinishThreads, 0, st>>>(
       indices, vertices, cell_values, n_tets, *cam, reinterpret_cast<const float4*>(scratch), hits->tet_flags,
       vertices_grad, cell_values_grad);
   RM_CUDA_CHECK(cudaPeekAtLastError());

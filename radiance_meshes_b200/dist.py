@@ -116,19 +116,30 @@ def combine_band_images(local_image, band, tile_height, group=None, bands=None):
     return out
 
 
-def render_view_parallel(render_backward_fn, views, rank, world_size, group=None):
+def render_view_parallel(render_backward_fn, views, rank, world_size, group=None, zero_like=None):
     """Each rank renders views[rank::world_size] and the gradients are summed.
 
     render_backward_fn(view) -> (image, vertices_grad, cell_values_grad).
     Returns (list of local images, vertices_grad, cell_values_grad) with the
     gradients summed over all views of all ranks.
+
+    With fewer views than ranks some ranks have nothing to render but still have to join the
+    collective: `zero_like` = (tensor shaped like vertices_grad, tensor shaped like
+    cell_values_grad) tells them what to contribute.  Without it the call raises on EVERY
+    rank before any collective is entered (all ranks see the same `views`), instead of
+    leaving the ranks that do have views blocked in the all-reduce.
     """
+    if len(views) < world_size and zero_like is None:
+        raise ValueError(f"{len(views)} view(s) for {world_size} ranks: pass zero_like=(vertices_grad-like, "
+                         "cell_values_grad-like) so that ranks without a view can join the gradient sum")
     images, vg, cg = [], None, None
     for v in views[rank::world_size]:
         img, g_v, g_c = render_backward_fn(v)
         images.append(img)
         vg = g_v.clone() if vg is None else vg + g_v
         cg = g_c.clone() if cg is None else cg + g_c
+    if vg is None:
+        vg, cg = torch.zeros_like(zero_like[0]), torch.zeros_like(zero_like[1])
     allreduce_gradients([vg, cg], group)
     return images, vg, cg
 

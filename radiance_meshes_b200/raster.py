@@ -104,6 +104,8 @@ def read_info(ctx):
     if status & _lib.RM_STATUS_NAN_VERTEX:
         # same message as the reference's assert (tile_shader_slang.py:78)
         raise AssertionError("Tensor contains NaN values!")
+    if status & _lib.RM_STATUS_BAD_INDEX:
+        raise IndexError("rm_b200: indices name a vertex outside [0, n_vertices)")
     if status & _lib.RM_STATUS_KEY_OVERFLOW or n_keys > 2**31 - 1:
         raise RuntimeError(f"rm_b200: {n_keys} (tile, tet) pairs exceed the int32 range of the tile lists")
     return n_keys, n_visible
@@ -135,8 +137,8 @@ def pack_records(indices, vertices, cell_values, cam, tiles_touched=None):
     T = indices.shape[0]
     with torch.cuda.device(dev):
         records = torch.empty((T, _lib.RM_RECORD_FLOATS), dtype=torch.float32, device=dev)
-        _lib.check(lib.rm_pack_records(_ptr(indices), _ptr(vertices), _ptr(cell_values), T, cam.ref,
-                                       _ptr(tiles_touched), _ptr(records), _stream(dev)))
+        _lib.check(lib.rm_pack_records(_ptr(indices), _ptr(vertices), _ptr(cell_values), T, vertices.shape[0],
+                                       cam.ref, _ptr(tiles_touched), _ptr(records), _stream(dev)))
     return records
 
 
@@ -150,7 +152,7 @@ def hit_list_ref(hits):
 
 def forward(sorted_idx, tile_ranges, records, cam, ray_jitter, want_hit_masks=True):
     """Returns (output_img, distortion_img, n_contributors, hits); hits = (counts int32 [G*S], ids int32 [N*S],
-    masks int16 [N*S], tet_flags uint8 [T]) are the hit lists backward() walks, None if not requested."""
+    masks int16 [N*S + 16*G*S], tet_flags uint8 [T]) are the hit lists backward() walks, None if not requested."""
     lib = _lib.load()
     dev = records.device
     H, W = cam.c.image_height, cam.c.image_width
@@ -167,7 +169,7 @@ def forward(sorted_idx, tile_ranges, records, cam, ray_jitter, want_hit_masks=Tr
             units = cam.c.grid_height * cam.c.grid_width * groups
             hits = (alloc((units,), dtype=torch.int32, device=dev),
                     torch.empty((slots,), dtype=torch.int32, device=dev),
-                    torch.empty((slots,), dtype=torch.int16, device=dev),
+                    torch.empty((slots + 16 * units,), dtype=torch.int16, device=dev),
                     torch.zeros((max(int(records.shape[0]), 1),), dtype=torch.uint8, device=dev))
         _lib.check(lib.rm_forward(_ptr(sorted_idx), _ptr(tile_ranges), _ptr(records), cam.ref, _ptr(ray_jitter),
                                   _ptr(output_img), _ptr(distortion_img), _ptr(n_contributors), hit_list_ref(hits),

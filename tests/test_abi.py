@@ -53,3 +53,33 @@ def test_render_grid_and_util():
     assert len(tensors) == 2 and plain["b"] == 3
     back = recombine_tensors(plain, tensors)
     assert set(back) == set(d) and back["a"] is d["a"]
+
+
+def test_bad_camera_is_rejected_before_any_launch(cuda_lib):
+    """Host-side argument checks run before anything touches a device: a camera with NULL arrays, or
+    a tile grid that does not match the image, returns RM_ERR_INVALID_ARG from every entry point that
+    takes a camera (checked here where it matters most, the entry point with library-owned scratch)."""
+    import ctypes as C
+    from radiance_meshes_b200 import _lib
+    fake = C.c_void_p(0x1000)  # never dereferenced: the call must fail first
+    hits = C.byref(_lib.RmHitList(fake, fake, fake, fake))
+
+    def call(cam, n_tets=8):
+        return cuda_lib.rm_backward_static_scratch(fake, fake, fake, C.byref(cam), fake, fake, fake, fake, hits, fake,
+                                                   fake, fake, fake, fake, n_tets, 4, fake, fake, None)
+
+    cam = _lib.RmCamera()
+    cam.image_height = cam.image_width = 16
+    cam.tile_height = cam.tile_width = 4
+    cam.grid_height = cam.grid_width = 4
+    cam.tile_row_end = 4
+    assert call(cam) == _lib.RM_ERR_INVALID_ARG  # the four device arrays are NULL
+    cam.world_view_transform = cam.K = cam.cam_pos = cam.distortion_params = 0x1000
+    cam.grid_width = 5  # does not match ceil(16 / 4)
+    assert call(cam) == _lib.RM_ERR_INVALID_ARG
+    cam.grid_width = 4
+    cam.tile_row_end = 5  # band outside the grid
+    assert call(cam) == _lib.RM_ERR_INVALID_ARG
+    cam.tile_row_end = 4
+    assert call(cam, n_tets=_lib.RM_STATIC_SCRATCH_MAX_TETS + 1) == _lib.RM_ERR_STATIC_SCRATCH
+    assert cuda_lib.rm_launch_count() >= 0

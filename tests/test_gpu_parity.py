@@ -255,21 +255,15 @@ def test_distorted_perspective_camera(oracle, cuda_lib):
 
 
 def test_fisheye_camera(oracle, cuda_lib):
-    # fisheye projection uses acos/sin/cos, whose CUDA and libm results may differ in
-    # the last bit: rectangles are compared with a one-tile slack on a tiny share of
-    # tets, images where the tile lists agree
-    from radiance_meshes_b200.render import render, tcam_to_device
+    # fisheye projection: acos/sin are evaluated as the same fixed double-precision series on both
+    # sides, so rectangles and tile lists are bit-exact like the pinhole ones; image and gradients
+    # within the usual tolerances (the ray directions use the fast sine/cosine)
     pts, tets, cell = scene_util.small_scene(300, seed=43)
     H, W = 48, 48
-    tcam = scene_util.camera(H=H, W=W, tile=4, fov=100.0, camera_type=1)
-    jit = scene_util.jitter(H, W, 12)
-    ref = oracle.render(tets, pts, cell, tcam, jit)
-    got = gpu_render(pts, tets, cell, tcam, jit)
-    diff = np.abs(got["rect"] - ref["project"]["rect"]).max(-1)
-    assert diff.max() <= 1 and (diff > 0).mean() < 0.01
-    if (diff == 0).all():
-        np.testing.assert_array_equal(got["sorted_tetra_idx"], ref["sorted_idx"])
-        assert rel_l2(got["image"], ref["output_img"]) <= IMG_TOL
+    for fov, dist in ((100.0, None), (140.0, (0.02, -0.01, 0.001, 0.002))):
+        tcam = scene_util.camera(H=H, W=W, tile=4, fov=fov, camera_type=1, distortion=dist)
+        ref, got = check_against_oracle(oracle, pts, tets, cell, tcam, scene_util.jitter(H, W, 12))
+        assert ref["sorted_idx"].shape[0] > 1000
 
 
 def test_densification_statistics(oracle, cuda_lib):

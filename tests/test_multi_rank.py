@@ -64,6 +64,14 @@ def _worker(rank, world, port, results):
             out, vg, cg, _, _ = _oracle_render_backward(O, pts, tets, cell, _view(view))
             return torch.from_numpy(out), torch.from_numpy(vg), torch.from_numpy(cg)
         images, vg, cg = rmdist.render_view_parallel(rb, [0, 1, 2, 3], rank, world)
+        # --- fewer views than ranks: rank 1 has nothing to render and contributes zeros of the right shape;
+        # without the shapes every rank raises before any collective
+        one_img, vg1, cg1 = rmdist.render_view_parallel(rb, [2], rank, world, zero_like=(vg, cg))
+        try:
+            rmdist.render_view_parallel(rb, [2], rank, world)
+            raised = False
+        except ValueError:
+            raised = True
         # --- band split of view 0
         tcam = _view(0)
         pr = O.project(tets, pts, tcam)
@@ -81,6 +89,7 @@ def _worker(rank, world, port, results):
         rmdist.allreduce_gradients([a, b])
         rmdist.allreduce_gradients(separate)
         results[rank] = dict(vg=vg.numpy(), cg=cg.numpy(), n_images=len(images), full=full.numpy(), band=band,
+                             vg1=vg1.numpy(), cg1=cg1.numpy(), n_images1=len(one_img), raised=raised,
                              weights=weights.numpy(), flat=flat.numpy(), covering=rmdist._covering_view([a, b]).numel(),
                              separate=[t.numpy() for t in separate])
     finally:
@@ -104,6 +113,12 @@ def test_two_rank_view_parallel_and_band_split(oracle):
         assert results[r]["n_images"] == 2
         np.testing.assert_allclose(results[r]["vg"], vg_ref, rtol=1e-5, atol=1e-5 * np.abs(vg_ref).max())
         np.testing.assert_allclose(results[r]["cg"], cg_ref, rtol=1e-5, atol=1e-5 * np.abs(cg_ref).max())
+    # one view on two ranks: both ranks end with that view's gradients
+    _, vg2, cg2, _, _ = _oracle_render_backward(oracle, pts, tets, cell, _view(2))
+    for r in range(world):
+        assert results[r]["n_images1"] == (1 if r == 0 else 0) and results[r]["raised"]
+        np.testing.assert_allclose(results[r]["vg1"], vg2, rtol=1e-5, atol=1e-5 * np.abs(vg2).max())
+        np.testing.assert_allclose(results[r]["cg1"], cg2, rtol=1e-5, atol=1e-5 * np.abs(cg2).max())
     # band split: the combined image equals the single-rank image bit for bit
     full_ref, _, _, idx_full, ranges_full = _oracle_render_backward(oracle, pts, tets, cell, _view(0))
     np.testing.assert_array_equal(results[0]["full"], full_ref)
