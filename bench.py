@@ -302,7 +302,9 @@ def run_gpu(args):
     tcam = tcam_to_device(tcam_np, dev)
     T, V = sc["indices"].shape[0], sc["vertices"].shape[0]
 
-    ar_events = []
+    # gradients are summed over the ranks inside the backward pass: every finished range of tets is
+    # all-reduced on a communication stream while the next range is being finished
+    reducer = rmdist.OverlappedGradientSum(chunks=args.reduce_chunks)
 
     def step(inp, reduce=True, time_allreduce=False):
         v = inp["vertices"].requires_grad_(True)
@@ -310,15 +312,13 @@ def run_gpu(args):
         v.grad = None
         c.grad = None
         pkg = render(inp["indices"], v, c, tcam, inp["jitter"])
-        torch.autograd.backward([pkg["image"], pkg["distortion_img"]], [inp["g_img"], inp["g_dist"]])
         if reduce and world > 1:
-            if time_allreduce:
-                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a0.record()
-            rmdist.allreduce_gradients([v.grad, c.grad])
-            if time_allreduce:
-                a1.record()
-                ar_events.append((a0, a1))
+            reducer.timing = time_allreduce
+            reducer.install()
+        try:
+            torch.autograd.backward([pkg["image"], pkg["distortion_img"]], [inp["g_img"], inp["g_dist"]])
+        finally:
+            reducer.remove()
         return pkg, v.grad, c.grad
 
     def barrier():
@@ -363,7 +363,9 @@ def run_gpu(args):
     allreduce = None
     rank_ms = [ms_local]
     if world > 1:
-        ar_ms = float(np.mean([a.elapsed_time(b) for a, b in ar_events]))
+        torch.cuda.synchronize()
+        ar_ms = float(sum(a.elapsed_time(b) for a, b in reducer.events)) / args.steps
+        reducer.events.clear()
         ar_bytes = (vg.numel() + cg.numel()) * 4
         t = torch.tensor([ms_local, ar_ms], device=dev, dtype=torch.float64)
         allr = [torch.empty_like(t) for _ in range(world)]
@@ -374,8 +376,11 @@ def run_gpu(args):
         ar_min = min(ar_all)
         allreduce = dict(bytes=ar_bytes, ms_min_over_ranks=ar_min, ms_max_over_ranks=max(ar_all),
                          bus_gbs=2 * (world - 1) / world * ar_bytes / (ar_min * 1e-3) / 1e9,
-                         note="CUDA events around the NCCL all-reduce of both gradients inside every timed step; the "
-                              "minimum over ranks is the collective itself, the rest is waiting for the slowest view")
+                         chunks=args.reduce_chunks,
+                         note="sum per step of the CUDA-event durations of the NCCL all-reduces (one per finished range "
+                              "of tets plus the vertex gradients), issued on a communication stream inside the backward "
+                              "pass; the minimum over ranks is the collectives themselves, the rest is waiting for the "
+                              "slowest view")
 
     # ---- per-kernel times: a separate short loop with the library's event profiling on ----
     _lib.profile_read()
@@ -443,8 +448,15 @@ def run_gpu(args):
 
     def e2e_step():
         # host buffers in, host buffers out; the copies overlap this frame's kernels on two copy streams
-        pipe.step(host, out_host, tcam, reduce_gradients=rmdist.allreduce_gradients)
+        if world > 1:
+            reducer.timing = False
+            reducer.install()
+        try:
+            pipe.step(host, out_host, tcam)
+        finally:
+            reducer.remove()
 
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     for _ in range(max(1, min(args.warmup, 3))):
         e2e_step()
     barrier()
@@ -467,10 +479,13 @@ def run_gpu(args):
         for i in range(n):
             if i >= 2:
                 pipe2.wait(tickets[i - 2])
-            tickets.append(pipe2.submit(host, outs2[i % 2], tcam, reduce_gradients=rmdist.allreduce_gradients))
+            tickets.append(pipe2.submit(host, outs2[i % 2], tcam))
         for t in tickets[-2:]:
             pipe2.wait(t)
 
+    if world > 1:
+        reducer.timing = False
+        reducer.install()
     stream_frames(max(2, min(args.warmup, 3)))
     barrier()
     e0.record()
@@ -479,6 +494,7 @@ def run_gpu(args):
     e1.record()
     barrier()
     e2e_stream_ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    reducer.remove()
     del pipe2, outs2
 
     # ---- densification statistics (the next row after the fwd+bwd path), timed separately ----
@@ -781,6 +797,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="config3", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--reduce-chunks", type=int, default=4,
+                    help="ranges of tets whose gradients are all-reduced while the next range is finished (N > 1)")
     ap.add_argument("--mode", default="views", choices=["views", "bands"],
                     help="views: one view per GPU, fwd+bwd, gradients all-reduced (the headline metric); "
                          "bands: one 4K frame split by tile-row bands, forward only")

@@ -193,6 +193,25 @@ int rm_backward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, con
                 float* grad_records, float* vertices_grad, float* cell_values_grad, void* stream);
 
 /*
+ * The two halves of rm_backward, for callers that want to start work on finished gradients early (a
+ * multi-GPU job sums the cell-value gradients of one range of tets over the ranks while the next
+ * range is still being finished).  No counterpart in the reference, which is single-GPU.
+ *   rm_backward_integrate: zeroes vertices_grad, clears the record-gradient rows of flagged tets and
+ *     accumulates the record gradients of the whole frame (the pixel walk).
+ *   rm_backward_finish: the per-tet chain rule for tets [tet_begin, tet_end): writes rows
+ *     [tet_begin, tet_end) of cell_values_grad[T,7] and adds to vertices_grad[V,3], which is complete
+ *     once every tet has been finished.  Ranges whose begin is a multiple of 256 keep the stores wide.
+ * rm_backward is rm_backward_integrate followed by rm_backward_finish(0, n_tets).
+ */
+int rm_backward_integrate(const int32_t* tile_ranges, const float* records, const RmCamera* cam,
+                          const float* ray_jitter, const float* output_img, const float* distortion_img,
+                          const RmHitList* hits, const float* grad_output_img, const float* grad_distortion_img,
+                          int64_t n_tets, int64_t n_vertices, float* grad_records, float* vertices_grad, void* stream);
+int rm_backward_finish(const int32_t* indices, const float* vertices, const float* cell_values, int64_t tet_begin,
+                       int64_t tet_end, int64_t n_tets, const RmCamera* cam, const float* grad_records,
+                       const RmHitList* hits, float* vertices_grad, float* cell_values_grad, void* stream);
+
+/*
  * Feature activation of a frozen model, the step before the rasterizer on the
  * rendering path.  Replaces activate_output (utils/model_util.py:93-105, with
  * offset_normalize :81-91 and eval_sh utils/eval_sh_py.py:121-179; callers

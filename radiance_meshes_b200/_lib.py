@@ -18,7 +18,8 @@ RM_STATUS_BAD_INDEX = 4
 SYMBOLS = ["rm_strerror", "rm_version", "rm_bin_workspace_bytes", "rm_list_scratch_bytes", "rm_project_and_bin", "rm_build_tile_lists",
            "rm_pack_records", "rm_forward", "rm_backward", "rm_vertex_backward", "rm_profile_enable",
            "rm_profile_read", "rm_backward_static_scratch", "rm_tet_err",
-           "rm_activate_output", "rm_forward_constant_color", "rm_launch_count"]
+           "rm_activate_output", "rm_forward_constant_color", "rm_launch_count",
+           "rm_backward_integrate", "rm_backward_finish"]
 RM_STATIC_SCRATCH_MAX_TETS = 131072
 RM_ERR_STATIC_SCRATCH = -5
 RM_ERR_INVALID_ARG = -1
@@ -69,6 +70,8 @@ def load():
     hits = C.POINTER(RmHitList)
     lib.rm_forward.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, hits, vp]
     lib.rm_backward.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, hits, vp, vp, vp, vp, vp, i64, i64, vp, vp, vp, vp]
+    lib.rm_backward_integrate.argtypes = [vp, vp, cam, vp, vp, vp, hits, vp, vp, i64, i64, vp, vp, vp]
+    lib.rm_backward_finish.argtypes = [vp, vp, vp, i64, i64, i64, cam, vp, hits, vp, vp, vp]
     lib.rm_vertex_backward.argtypes = [vp, vp, i64, i64, cam, vp, vp, vp, vp, vp]
     lib.rm_backward_static_scratch.argtypes = [vp, vp, vp, cam, vp, vp, vp, vp, hits, vp, vp, vp, vp, vp, i64, i64, vp, vp,
                                                vp]

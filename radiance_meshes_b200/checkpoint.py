@@ -96,3 +96,79 @@ class FrozenScene:
         with torch.no_grad():
             return activate_output(camera_center, self.density, self.rgb, self.gradient, self.sh, self.indices,
                                    self.circumcenters, self.vertices, self.max_sh_deg, self.max_sh_deg)
+
+
+# ---------------------------------------------------------------------------
+# ckpt.ply: the mesh export of models/base_model.py:107-151 (save2ply)
+# ---------------------------------------------------------------------------
+# The reference writes it through the un-vendored `tinyplypy` package and holds no reader for it
+# in its tree, so the byte-level header of its files cannot be checked here.  The layout below is
+# the standard binary little-endian PLY with the element and property names save2ply uses:
+#   element vertex:       x y z (float32)
+#   element tetrahedron:  indices (list of 4 int32), s (density), grd_x grd_y grd_z,
+#                         sh_0_r sh_0_g sh_0_b (degree-0 SH = (rgb - 0.5) / C0), sh_i_r sh_i_g sh_i_b
+SH_C0 = 0.28209479177387814
+
+
+def write_ply(path, vertices, indices, density, grd, rgb, sh_rest):
+    """vertices[V,3] f32, indices[T,4] i32, density[T], grd[T,3], rgb[T,3] (base colour at vertex 0,
+    before activation), sh_rest[T,K,3]."""
+    import numpy as np
+    v = np.ascontiguousarray(np.asarray(vertices, np.float32))
+    idx = np.ascontiguousarray(np.asarray(indices, np.int32))
+    T, K = idx.shape[0], int(np.asarray(sh_rest).shape[1])
+    names = ["s", "grd_x", "grd_y", "grd_z", "sh_0_r", "sh_0_g", "sh_0_b"]
+    names += [f"sh_{i + 1}_{c}" for i in range(K) for c in "rgb"]
+    cols = np.concatenate([np.asarray(density, np.float32).reshape(T, 1), np.asarray(grd, np.float32).reshape(T, 3),
+                           (np.asarray(rgb, np.float32).reshape(T, 3) - 0.5) / SH_C0,
+                           np.asarray(sh_rest, np.float32).reshape(T, 3 * K)], axis=1).astype("<f4")
+    rec = np.zeros(T, dtype=[("n", "u1"), ("idx", "<i4", (4,)), ("f", "<f4", (cols.shape[1],))])
+    rec["n"], rec["idx"], rec["f"] = 4, idx, cols
+    header = ["ply", "format binary_little_endian 1.0", f"element vertex {v.shape[0]}", "property float x",
+              "property float y", "property float z", f"element tetrahedron {T}", "property list uchar int indices"]
+    header += [f"property float {n}" for n in names] + ["end_header"]
+    path = Path(path)
+    path.parent.mkdir(parents=True, exist_ok=True)
+    with open(path, "wb") as f:
+        f.write(("\n".join(header) + "\n").encode("ascii"))
+        f.write(v.astype("<f4").tobytes())
+        f.write(rec.tobytes())
+
+
+def read_ply(path):
+    """Inverse of write_ply.  Returns dict(vertices, indices, density, grd, rgb, sh_rest) as NumPy arrays."""
+    import numpy as np
+    with open(path, "rb") as f:
+        data = f.read()
+    end = data.index(b"end_header\n") + len(b"end_header\n")
+    lines = data[:end].decode("ascii").split("\n")
+    if lines[0] != "ply" or "binary_little_endian" not in lines[1]:
+        raise ValueError(f"{path}: not a binary little-endian PLY file")
+    counts, props, cur = {}, {}, None
+    for ln in lines[2:]:
+        parts = ln.split()
+        if parts[:1] == ["element"]:
+            cur = parts[1]
+            counts[cur] = int(parts[2])
+            props[cur] = []
+        elif parts[:1] == ["property"]:
+            props[cur].append(parts[1:])
+    if [p[-1] for p in props.get("vertex", [])] != ["x", "y", "z"] or "tetrahedron" not in props:
+        raise ValueError(f"{path}: expected elements `vertex` (x y z) and `tetrahedron`")
+    tp = props["tetrahedron"]
+    if tp[0] != ["list", "uchar", "int", "indices"] or any(p[0] != "float" for p in tp[1:]):
+        raise ValueError(f"{path}: unexpected tetrahedron properties")
+    names = [p[1] for p in tp[1:]]
+    V, T = counts["vertex"], counts["tetrahedron"]
+    v = np.frombuffer(data, "<f4", 3 * V, end).reshape(V, 3)
+    rec = np.frombuffer(data, np.dtype([("n", "u1"), ("idx", "<i4", (4,)), ("f", "<f4", (len(names),))]), T,
+                        end + 12 * V)
+    if T and not (rec["n"] == 4).all():
+        raise ValueError(f"{path}: a tetrahedron does not have 4 indices")
+    col = {n: rec["f"][:, i] for i, n in enumerate(names)}
+    K = (len(names) - 7) // 3
+    sh_rest = np.stack([np.stack([col[f"sh_{i + 1}_{c}"] for c in "rgb"], -1) for i in range(K)], 1) if K else \
+        np.zeros((T, 0, 3), np.float32)
+    return dict(vertices=v.copy(), indices=rec["idx"].copy(), density=col["s"].copy(),
+                grd=np.stack([col["grd_x"], col["grd_y"], col["grd_z"]], -1),
+                rgb=np.stack([col["sh_0_r"], col["sh_0_g"], col["sh_0_b"]], -1) * SH_C0 + 0.5, sh_rest=sh_rest)

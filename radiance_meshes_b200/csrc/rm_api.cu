@@ -24,9 +24,11 @@ int rm_launch_forward(const int32_t*, const int32_t*, const float*, const RmCame
                       int32_t*, const RmHitList*, cudaStream_t);
 int rm_launch_forward_constant_color(const int32_t*, const int32_t*, const float*, const RmCamera*, float, float,
                                      float*, float*, int32_t*, cudaStream_t);
-int rm_launch_backward(const int32_t*, const int32_t*, const float*, const RmCamera*, const float*, const float*,
-                       const float*, const int32_t*, const RmHitList*, const float*, const float*, const int32_t*,
-                       const float*, const float*, int64_t, int64_t, float*, float*, float*, cudaStream_t);
+int rm_launch_backward_integrate(const int32_t*, const float*, const RmCamera*, const float*, const float*, const float*,
+                                 const RmHitList*, const float*, const float*, int64_t, int64_t, float*, float*,
+                                 cudaStream_t);
+int rm_launch_backward_finish(const int32_t*, const float*, const float*, int64_t, int64_t, const RmCamera*,
+                              const float*, const RmHitList*, float*, float*, cudaStream_t);
 
 int rm_launch_tet_err(const int32_t*, const int32_t*, const float*, const RmCamera*, const float*, const float*,
                       int64_t, float*, int32_t*, cudaStream_t);
@@ -263,30 +265,72 @@ int rm_forward_constant_color(const int32_t* sorted_tetra_idx, const int32_t* ti
                                           static_cast<cudaStream_t>(stream));
 }
 
-int rm_backward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, const float* records,
-                const RmCamera* cam, const float* ray_jitter, const float* output_img,
-                const float* distortion_img, const int32_t* n_contributors, const RmHitList* hits,
-                const float* grad_output_img, const float* grad_distortion_img, const int32_t* indices,
-                const float* vertices, const float* cell_values, int64_t n_tets, int64_t n_vertices,
-                float* grad_records, float* vertices_grad, float* cell_values_grad, void* stream) {
-  g_last_error[0] = 0;
+static int check_backward_args(const int32_t* tile_ranges, const float* records, const RmCamera* cam,
+                               const float* ray_jitter, const float* output_img, const float* distortion_img,
+                               const RmHitList* hits, const float* grad_output_img, const float* grad_distortion_img,
+                               int64_t n_tets, int64_t n_vertices, const float* grad_records,
+                               const float* vertices_grad) {
   int rc = rm_check_cam(cam);
   if (rc) return rc;
   if (n_tets < 0 || n_vertices < 0) return RM_ERR_INVALID_ARG;
   if (!tile_ranges || !ray_jitter || !output_img || !distortion_img || !hits || !hits->counts || !hits->ids ||
       !hits->masks || !hits->tet_flags || !grad_output_img || !grad_distortion_img || !vertices_grad)
     return RM_ERR_INVALID_ARG;
-  if (n_tets > 0 && (!indices || !vertices || !cell_values || !grad_records || !cell_values_grad || !records))
-    return RM_ERR_INVALID_ARG;
-  if (!rm_aligned16(output_img) || !rm_aligned16(grad_output_img) || !rm_aligned16(records) || !rm_aligned16(grad_records) ||
-      !rm_aligned16(indices))
+  if (n_tets > 0 && (!grad_records || !records)) return RM_ERR_INVALID_ARG;
+  if (!rm_aligned16(output_img) || !rm_aligned16(grad_output_img) || !rm_aligned16(records) ||
+      !rm_aligned16(grad_records))
     return RM_ERR_WORKSPACE;
+  return RM_OK;
+}
+
+int rm_backward_integrate(const int32_t* tile_ranges, const float* records, const RmCamera* cam,
+                          const float* ray_jitter, const float* output_img, const float* distortion_img,
+                          const RmHitList* hits, const float* grad_output_img, const float* grad_distortion_img,
+                          int64_t n_tets, int64_t n_vertices, float* grad_records, float* vertices_grad, void* stream) {
+  g_last_error[0] = 0;
+  int rc = check_backward_args(tile_ranges, records, cam, ray_jitter, output_img, distortion_img, hits,
+                               grad_output_img, grad_distortion_img, n_tets, n_vertices, grad_records, vertices_grad);
+  if (rc) return rc;
   rc = rm_bind_device(vertices_grad);
   if (rc) return rc;
-  return rm_launch_backward(sorted_tetra_idx, tile_ranges, records, cam, ray_jitter, output_img, distortion_img,
-                            n_contributors, hits, grad_output_img, grad_distortion_img, indices, vertices, cell_values,
-                            n_tets, n_vertices, grad_records, vertices_grad, cell_values_grad,
-                            static_cast<cudaStream_t>(stream));
+  return rm_launch_backward_integrate(tile_ranges, records, cam, ray_jitter, output_img, distortion_img, hits,
+                                      grad_output_img, grad_distortion_img, n_tets, n_vertices, grad_records,
+                                      vertices_grad, static_cast<cudaStream_t>(stream));
+}
+
+int rm_backward_finish(const int32_t* indices, const float* vertices, const float* cell_values, int64_t tet_begin,
+                       int64_t tet_end, int64_t n_tets, const RmCamera* cam, const float* grad_records,
+                       const RmHitList* hits, float* vertices_grad, float* cell_values_grad, void* stream) {
+  g_last_error[0] = 0;
+  int rc = rm_check_cam(cam);
+  if (rc) return rc;
+  if (tet_begin < 0 || tet_end < tet_begin || tet_end > n_tets) return RM_ERR_INVALID_ARG;
+  if (tet_end == tet_begin) return RM_OK;
+  if (!indices || !vertices || !cell_values || !grad_records || !hits || !hits->tet_flags || !vertices_grad ||
+      !cell_values_grad)
+    return RM_ERR_INVALID_ARG;
+  if (!rm_aligned16(indices) || !rm_aligned16(grad_records)) return RM_ERR_WORKSPACE;
+  rc = rm_bind_device(vertices_grad);
+  if (rc) return rc;
+  return rm_launch_backward_finish(indices, vertices, cell_values, tet_begin, tet_end, cam, grad_records, hits,
+                                   vertices_grad, cell_values_grad, static_cast<cudaStream_t>(stream));
+}
+
+int rm_backward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, const float* records,
+                const RmCamera* cam, const float* ray_jitter, const float* output_img,
+                const float* distortion_img, const int32_t* n_contributors, const RmHitList* hits,
+                const float* grad_output_img, const float* grad_distortion_img, const int32_t* indices,
+                const float* vertices, const float* cell_values, int64_t n_tets, int64_t n_vertices,
+                float* grad_records, float* vertices_grad, float* cell_values_grad, void* stream) {
+  (void)sorted_tetra_idx;
+  (void)n_contributors;  // the hit lists already stop at every pixel's last contributor
+  int rc = rm_backward_integrate(tile_ranges, records, cam, ray_jitter, output_img, distortion_img, hits,
+                                 grad_output_img, grad_distortion_img, n_tets, n_vertices, grad_records, vertices_grad,
+                                 stream);
+  if (rc) return rc;
+  if (n_tets > 0 && (!indices || !vertices || !cell_values || !cell_values_grad)) return RM_ERR_INVALID_ARG;
+  return rm_backward_finish(indices, vertices, cell_values, 0, n_tets, n_tets, cam, grad_records, hits, vertices_grad,
+                            cell_values_grad, stream);
 }
 
 int rm_activate_output(const float* camera_center, const float* density, const float* rgb, const float* grd,

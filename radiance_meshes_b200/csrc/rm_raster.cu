@@ -32,8 +32,6 @@
 //     a per-tet row; a per-tet kernel then applies the chain rule to vertices and
 //     cell values (12 vertex atomics per tet instead of 19 atomics per pixel hit).
 
-#include <stdlib.h>
-
 #include "rm_common.cuh"
 
 namespace rm {
@@ -494,7 +492,7 @@ __device__ __forceinline__ uint32_t transpose_masks(const uint32_t* __restrict__
 // termination when the transmittance falls below 1/255; out_img = (r, g, b, transmittance) and
 // dist_img has four channels.
 template <bool CONST_COLOR>
-__global__ void __launch_bounds__(kWarpsPerBlock * 32, 4)
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, 5)
 k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, const float4* __restrict__ records,
           RmCamera rcam, const float2* __restrict__ jitter, float4* __restrict__ out_img,
           float* __restrict__ dist_img, int32_t* __restrict__ n_contrib, int32_t* __restrict__ hit_counts,
@@ -964,257 +962,6 @@ k_backward(const int2* __restrict__ ranges, const float4* __restrict__ records, 
 }
 
 // ----------------------------------------------------------------------------
-// Backward, per-pixel walk
-// ----------------------------------------------------------------------------
-// The hit lists give every pixel the bit set of the batch entries it hit, so every lane
-// walks its own bits from the last to the first and no lane idles on an entry its pixel
-// missed.  Lanes of a half-warp are then on different entries at the same time, and
-// the per-entry sums over the pixels can no longer be formed by a lock-step transpose.
-// Instead, per round: every lane with a hit writes its 16 gradient values as a row to
-// shared memory with a tag (entry, entering plane, exit plane); then lane c adds up
-// column c of the rows, run by run of equal tags, and adds each run's sum to the
-// entry's accumulator in shared memory - column c of every accumulator belongs to lane c
-// alone, so plain loads and stores do (shared-memory float atomics serialise on equal
-// addresses, which is the common case here).  After the batch the accumulators go to the
-// record-gradient rows with 128-bit reductions and are cleared.
-constexpr int kBwdWarps = 2;     // warps per block
-constexpr int kRowStride = 20;   // floats per gradient row (16 used; 80 bytes keep the 128-bit stores apart)
-constexpr int kAccStride = 40;   // floats per accumulator: 4 planes as entering plane, 4 as exit plane, 8 colour fields
-constexpr uint32_t kNoTag = 0xFFFFFFFFu;
-
-struct __align__(16) BwdShared {  // per half-warp
-  float4 stage[2][kBatch * kStageStride];
-  float acc[kBatch * kAccStride];
-  float rows[16 * kRowStride];
-  uint32_t tags[16];
-  int ids[2][kBatch];
-};
-
-__global__ void __launch_bounds__(kBwdWarps * 32, 7)
-k_backward_px(const int2* __restrict__ ranges, const float4* __restrict__ records, RmCamera rcam,
-              const float2* __restrict__ jitter, const float4* __restrict__ out_img,
-              const float* __restrict__ dist_img, const int32_t* __restrict__ hit_counts,
-              const int32_t* __restrict__ hit_ids, const uint16_t* __restrict__ hit_masks,
-              const float4* __restrict__ g_img, const float* __restrict__ g_dist, float* __restrict__ grec, int subs,
-              int64_t n_units) {
-  __shared__ BwdShared shm[kBwdWarps][2];
-  constexpr unsigned FULL = 0xffffffffu;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int half = lane >> 4, lane16 = lane & 15;
-  const int64_t unit = ((int64_t)blockIdx.x * kBwdWarps + warp) * 2 + half;
-  Unit u = make_unit(rcam, ranges, unit, n_units, subs, lane16);
-  BwdShared& S = shm[warp][half];
-
-  f3 d = {0.f, 0.f, 1.f};
-  const int64_t pix = (int64_t)u.y * rcam.image_width + u.x;
-  float logT = 0.f, sz = 0.f, sw = 0.f;
-  float gr = 0.f, gg = 0.f, gb = 0.f, glogT = 0.f, gx = 0.f, gy = 0.f, gz = 0.f, gw = 0.f, gv = 0.f;
-  if (u.inside) {
-    float2 j = __ldg(jitter + pix);
-    d = ray_direction(rcam, (float)u.x + j.x, (float)u.y + j.y);
-    logT = __ldg(out_img + pix).w;
-    sz = __ldg(dist_img + 5 * pix + 2);
-    sw = __ldg(dist_img + 5 * pix + 3);
-    float4 g4 = __ldg(g_img + pix);
-    gr = g4.x; gg = g4.y; gb = g4.z; glogT = g4.w;
-    const float* gd = g_dist + 5 * pix;
-    gx = __ldg(gd); gy = __ldg(gd + 1); gz = __ldg(gd + 2); gw = __ldg(gd + 3); gv = __ldg(gd + 4);
-  }
-  const float min_t = rcam.min_t;
-
-  // column ownership of this lane in the reduction: lanes 0-3 own component c of every plane in its
-  // role as entering plane, lanes 4-7 the same for the exit plane, lanes 8-15 one colour field each
-  const int tag_shift = lane16 < 4 ? 8 : 12;
-  const uint32_t tag_mask = lane16 < 8 ? 7u : 0u;
-  const int acc_base = lane16 < 4 ? lane16 : (lane16 < 8 ? 16 + (lane16 - 4) : 32 + (lane16 - 8));
-
-  const int64_t hbase = (int64_t)u.start * u.subs + (int64_t)u.sub * u.len;
-  const int64_t mbase = hbase + 16 * ((int64_t)u.tile * u.subs + u.sub);
-  const int nmax = unit < n_units ? min(__ldg(hit_counts + (int64_t)u.tile * u.subs + u.sub), u.len) : 0;
-  const int nchunks = (nmax + kBatch - 1) / kBatch;
-  const int max_chunks = max(nchunks, __shfl_xor_sync(FULL, nchunks, 16));
-
-  {
-    const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int i = lane16; i < kBatch * kAccStride / 4; i += 16) reinterpret_cast<float4*>(S.acc)[i] = z;
-  }
-
-  // batch k of this half (k = 0 is the LAST batch of its hit list) sits in buffer k&1
-  int id_next = 0;
-  uint32_t bits_next = 0;
-  if (nchunks >= 1) {
-    const int e0 = (nchunks - 1) * kBatch + lane16;
-    if (e0 < nmax) id_next = __ldg(hit_ids + hbase + e0);
-    bits_next = __ldg(hit_masks + mbase + e0);
-  }
-  auto issue = [&](int k, uint32_t& bits_out, int& n_out) {
-    const int c = nchunks - 1 - k;
-    bits_out = 0u;
-    n_out = 0;
-    if (c >= 0) {
-      const int id = id_next;
-      bits_out = bits_next;
-      n_out = min(kBatch, nmax - c * kBatch);
-      if (c >= 1) {  // batch c - 1 is a full batch
-        const int e = (c - 1) * kBatch + lane16;
-        id_next = __ldg(hit_ids + hbase + e);
-        bits_next = __ldg(hit_masks + mbase + e);
-      }
-      if (lane16 < n_out) {
-        S.ids[k & 1][lane16] = id;
-        const float4* src = records + kRecStride * (int64_t)id;
-        float4* dst = S.stage[k & 1] + lane16 * kStageStride;
-#pragma unroll
-        for (int q = 0; q < 6; ++q) cp_async16(dst + q, src + q);
-      }
-    }
-    cp_async_commit();
-  };
-
-  uint32_t bits_cur = 0, bits_ahead = 0;
-  int n_cur = 0, n_ahead = 0;
-  issue(0, bits_cur, n_cur);
-  for (int k = 0; k < max_chunks; ++k) {
-    issue(k + 1, bits_ahead, n_ahead);
-    cp_async_wait<1>();
-    __syncwarp();
-    const float4* cur = S.stage[k & 1];
-    uint32_t bits = bits_cur;
-    while (__any_sync(FULL, bits != 0u)) {
-      uint32_t tag = kNoTag;
-      if (bits) {
-        const int j = 31 - __clz(bits);
-        bits ^= 1u << j;
-        const float4* rec = cur + j * kStageStride;
-        const float4 pl[4] = {rec[0], rec[1], rec[2], rec[3]};
-        Eval ev;
-        // same arithmetic as the forward pass, so the test succeeds again
-        if (slab_test<true>(pl, d, min_t, ev) && integrate(rec, d, min_t, ev)) {
-          const float4 cbv = rec[5];
-          const float dens = cbv.w;
-          // undo: state before this tet
-          logT += ev.tau;
-          const float Tp = __expf(fminf(logT, 46.0517f));
-          const float m0 = dens, m1 = dens * (ev.exit + ev.enter) * 0.5f;
-          sz -= m0;
-          sw -= m1;
-          // reverse of the state update
-          const float gcr = gr * Tp, gcg = gg * Tp, gcb = gb * Tp;
-          const float gT = gr * ev.cr + gg * ev.cg + gb * ev.cb;
-          const float g_a = -glogT;
-          const float g_m1 = 2.0f * sz * gx + gw;
-          const float g_m0 = 2.0f * sw * gy + gz;
-          float g_dens = g_m0 + g_m1 * (ev.exit + ev.enter) * 0.5f + gv * 2.0f * dens * ev.dt * (1.0f / 3.0f);
-          float g_exit = g_m1 * dens * 0.5f, g_enter = g_exit;
-          if (ev.exit - ev.enter > 0.0f) {
-            float kk = gv * dens * dens * (1.0f / 3.0f);
-            g_exit += kk;
-            g_enter -= kk;
-          }
-          glogT = fmaf(gT, Tp, glogT);
-          gz = fmaf(2.0f * m1, gx, gz);
-          gw = fmaf(2.0f * m0, gy, gw);
-          // reverse of the segment integral
-          const float cxr = cbv.x + ev.ox, cxg = cbv.y + ev.ox, cxb = cbv.z + ev.ox;
-          const float cer = cbv.x + ev.oe, ceg = cbv.y + ev.oe, ceb = cbv.z + ev.oe;
-          const float g_w0 = gcr * cxr + gcg * cxg + gcb * cxb;
-          const float g_w1 = gcr * cer + gcg * ceg + gcb * ceb;
-          const float G = gcr + gcg + gcb;
-          const float wsum = ev.w0 + ev.w1;
-          const float g_ox = ev.w0 * G, g_oe = ev.w1 * G;
-          const float g_gd = g_ox * (ev.exit + min_t) + g_oe * (ev.enter + min_t);
-          g_exit = fmaf(g_ox, ev.gd, g_exit);
-          g_enter = fmaf(g_oe, ev.gd, g_enter);
-          const float g_phi = g_w0 - g_w1;
-          const float dphi = -__fdividef(ev.w0, ev.tau);  // d phi / d tau = (alpha - phi) / tau = -w0 / tau
-          const float g_tau = g_phi * dphi + g_w0 * ev.alpha + g_a;
-          g_dens = fmaf(g_tau, ev.dt, g_dens);
-          const float g_dt = g_tau * dens;
-          if (ev.exit - ev.enter > 0.0f) {
-            g_exit += g_dt;
-            g_enter -= g_dt;
-          }
-          float g_tx = 0.0f, g_te = 0.0f;
-          if (ev.tx > ev.enter) g_tx = g_exit; else g_enter += g_exit;
-          if (ev.te > 0.0f) g_te = g_enter;
-          // planes: t = -D/den - min_t  =>  dt/dD = -1/den, dt/dn = (D/den^2) d
-          float4 ve = make_float4(0.f, 0.f, 0.f, 0.f), vx = ve;
-          int pe = 0, px = 0;  // a plane without a gradient receives zeros
-          if (g_te != 0.0f && ev.ie >= 0) {
-            const float4 p = rec[ev.ie];
-            const float r = __fdividef(1.0f, p.x * d.x + p.y * d.y + p.z * d.z);
-            const float kn = g_te * p.w * r * r;
-            ve = make_float4(kn * d.x, kn * d.y, kn * d.z, -g_te * r);
-            pe = ev.ie;
-          }
-          if (g_tx != 0.0f && ev.ix >= 0) {
-            const float4 p = rec[ev.ix];
-            const float r = __fdividef(1.0f, p.x * d.x + p.y * d.y + p.z * d.z);
-            const float kn = g_tx * p.w * r * r;
-            vx = make_float4(kn * d.x, kn * d.y, kn * d.z, -g_tx * r);
-            px = ev.ix;
-          }
-          float4* row4 = reinterpret_cast<float4*>(S.rows + lane16 * kRowStride);
-          row4[0] = ve;
-          row4[1] = vx;
-          row4[2] = make_float4(g_gd * d.x, g_gd * d.y, g_gd * d.z, g_ox + g_oe);
-          row4[3] = make_float4(wsum * gcr, wsum * gcg, wsum * gcb, g_dens);
-          tag = (uint32_t)j | ((uint32_t)pe << 8) | ((uint32_t)px << 12);
-        }
-      }
-      S.tags[lane16] = tag;
-      __syncwarp();
-      {
-        // lane c sums column c of the rows, run by run of equal tags
-        const uint4 t0 = reinterpret_cast<const uint4*>(S.tags)[0], t1 = reinterpret_cast<const uint4*>(S.tags)[1],
-                    t2 = reinterpret_cast<const uint4*>(S.tags)[2], t3 = reinterpret_cast<const uint4*>(S.tags)[3];
-        const uint32_t tg[16] = {t0.x, t0.y, t0.z, t0.w, t1.x, t1.y, t1.z, t1.w,
-                                 t2.x, t2.y, t2.z, t2.w, t3.x, t3.y, t3.z, t3.w};
-        uint32_t run = kNoTag;
-        float sum = 0.0f;
-#pragma unroll
-        for (int r = 0; r < 16; ++r) {
-          const uint32_t t = tg[r];
-          if (t != run) {
-            if (run != kNoTag) {
-              float* a = S.acc + (run & 0xFFu) * kAccStride + acc_base + ((run >> tag_shift) & tag_mask) * 4;
-              *a += sum;
-            }
-            run = t;
-            sum = 0.0f;
-          }
-          if (t != kNoTag) sum += S.rows[r * kRowStride + lane16];
-        }
-        if (run != kNoTag) {
-          float* a = S.acc + (run & 0xFFu) * kAccStride + acc_base + ((run >> tag_shift) & tag_mask) * 4;
-          *a += sum;
-        }
-      }
-      __syncwarp();
-    }
-    // the batch's accumulators go to the record-gradient rows and are cleared
-    {
-      const int* ids = S.ids[k & 1];
-      float4* acc4 = reinterpret_cast<float4*>(S.acc);
-      const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int q = lane16; q < n_cur * (kAccStride / 4); q += 16) {
-        const int j = q / (kAccStride / 4), part = q - j * (kAccStride / 4);
-        const float4 a = acc4[q];
-        if (a.x != 0.f || a.y != 0.f || a.z != 0.f || a.w != 0.f) {
-          float4* row = reinterpret_cast<float4*>(grec + (int64_t)ids[j] * 24);
-          atomicAdd(row + (part < 4 ? part : part - 4), a);  // parts 0-3 and 4-7: planes 0-3; 8, 9: colour fields
-          acc4[q] = z;
-        }
-      }
-    }
-    __syncwarp();
-    bits_cur = bits_ahead;
-    n_cur = n_ahead;
-  }
-  cp_async_wait<0>();
-}
-
-// ----------------------------------------------------------------------------
 // Densification statistics (slang/alphablend_shader_interp.slang:433-599,
 // internal/render_err.py:119-150): the forward walk again, from the pixel centres,
 // with the pixel state starting at log-transmittance 1 as the reference has it;
@@ -1398,12 +1145,13 @@ constexpr int kFinishThreads = 256;
 
 __global__ void __launch_bounds__(kFinishThreads)
 k_backward_finish(const int32_t* __restrict__ indices, const float* __restrict__ vertices,
-                  const float* __restrict__ cell, int64_t T, RmCamera rcam, const float4* __restrict__ grec,
-                  const uint8_t* __restrict__ tet_flags, float* __restrict__ vgrad, float* __restrict__ cgrad) {
+                  const float* __restrict__ cell, int64_t t_begin, int64_t T, RmCamera rcam,
+                  const float4* __restrict__ grec, const uint8_t* __restrict__ tet_flags, float* __restrict__ vgrad,
+                  float* __restrict__ cgrad) {
   // the block's cell-value gradient rows (7 floats per tet) leave through shared memory as
   // contiguous 16-byte stores
   __shared__ __align__(16) float rows[kFinishThreads * 7];
-  const int64_t g0 = (int64_t)blockIdx.x * kFinishThreads;
+  const int64_t g0 = t_begin + (int64_t)blockIdx.x * kFinishThreads;  // tets [t_begin, T) are handled by this launch
   const int64_t g = g0 + threadIdx.x;
   float* co = rows + 7 * threadIdx.x;
   float4 q[6];
@@ -1553,13 +1301,12 @@ int rm_launch_tet_err(const int32_t* list, const int32_t* ranges, const float* r
   return RM_OK;
 }
 
-int rm_launch_backward(const int32_t* list, const int32_t* ranges, const float* records, const RmCamera* cam,
-                       const float* jitter, const float* out_img, const float* dist_img, const int32_t* n_contrib,
-                       const RmHitList* hits, const float* g_img, const float* g_dist, const int32_t* indices,
-                       const float* vertices, const float* cell, int64_t T, int64_t V, float* grec, float* vgrad,
-                       float* cgrad, cudaStream_t st) {
-  (void)list;
-  (void)n_contrib;  // the hit lists already stop at every pixel's last contributor
+// Everything of the backward pass except the per-tet chain rule: clears vertices_grad and the
+// record-gradient rows of flagged tets, then accumulates the record gradients.
+int rm_launch_backward_integrate(const int32_t* ranges, const float* records, const RmCamera* cam, const float* jitter,
+                                 const float* out_img, const float* dist_img, const RmHitList* hits, const float* g_img,
+                                 const float* g_dist, int64_t T, int64_t V, float* grec, float* vgrad,
+                                 cudaStream_t st) {
   RM_CUDA_CHECK(cudaMemsetAsync(vgrad, 0, sizeof(float) * 3 * (size_t)V, st));
   if (T == 0) return RM_OK;
   {
@@ -1573,24 +1320,25 @@ int rm_launch_backward(const int32_t* list, const int32_t* ranges, const float* 
   unit_grid(cam, &subs, &n_units, &blocks);
   if (n_units > 0) {
     RmProfScope prof("k_backward", st);
-    static const bool lockstep = getenv("RM_BACKWARD_LOCKSTEP") != nullptr;
-    if (lockstep) {
-      rm_count_launch(), rm::k_backward<<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
-          reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam,
-          reinterpret_cast<const float2*>(jitter), reinterpret_cast<const float4*>(out_img), dist_img, hits->counts,
-          hits->ids, hits->masks, reinterpret_cast<const float4*>(g_img), g_dist, grec, subs, n_units);
-    } else {
-      const int64_t per_block = rm::kBwdWarps * 2;
-      rm_count_launch(), rm::k_backward_px<<<(unsigned)((n_units + per_block - 1) / per_block), rm::kBwdWarps * 32, 0, st>>>(
-          reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam,
-          reinterpret_cast<const float2*>(jitter), reinterpret_cast<const float4*>(out_img), dist_img, hits->counts,
-          hits->ids, hits->masks, reinterpret_cast<const float4*>(g_img), g_dist, grec, subs, n_units);
-    }
+    rm_count_launch(), rm::k_backward<<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
+        reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam,
+        reinterpret_cast<const float2*>(jitter), reinterpret_cast<const float4*>(out_img), dist_img, hits->counts,
+        hits->ids, hits->masks, reinterpret_cast<const float4*>(g_img), g_dist, grec, subs, n_units);
   }
-  RmProfScope prof2("k_backward_finish", st);
-  rm_count_launch(), rm::k_backward_finish<<<(unsigned)((T + rm::kFinishThreads - 1) / rm::kFinishThreads), rm::kFinishThreads, 0, st>>>(indices, vertices, cell, T, *cam,
-                                                                     reinterpret_cast<const float4*>(grec),
-                                                                     hits->tet_flags, vgrad, cgrad);
+  RM_CUDA_CHECK(cudaPeekAtLastError());
+  return RM_OK;
+}
+
+// The chain rule from record gradients to vertices and cell values for tets [t_begin, t_end).
+int rm_launch_backward_finish(const int32_t* indices, const float* vertices, const float* cell, int64_t t_begin,
+                              int64_t t_end, const RmCamera* cam, const float* grec, const RmHitList* hits,
+                              float* vgrad, float* cgrad, cudaStream_t st) {
+  if (t_end <= t_begin) return RM_OK;
+  RmProfScope prof("k_backward_finish", st);
+  rm_count_launch(), rm::k_backward_finish<<<(unsigned)((t_end - t_begin + rm::kFinishThreads - 1) / rm::kFinishThreads),
+                                            rm::kFinishThreads, 0, st>>>(
+      indices, vertices, cell, t_begin, t_end, *cam, reinterpret_cast<const float4*>(grec), hits->tet_flags, vgrad,
+      cgrad);
   RM_CUDA_CHECK(cudaPeekAtLastError());
   return RM_OK;
 }
@@ -1674,7 +1422,7 @@ extern "C" int rm_backward_static_scratch(const int32_t* sorted_tetra_idx, const
   }
   RmProfScope prof2("k_backward_finish", st);
   rm_count_launch(), rm::k_backward_finish<<<(unsigned)((n_tets + rm::kFinishThreads - 1) / rm::kFinishThreads), rm::kFinishThreads, 0, st>>>(
-      indices, vertices, cell_values, n_tets, *cam, reinterpret_cast<const float4*>(scratch), hits->tet_flags,
+      indices, vertices, cell_values, 0, n_tets, *cam, reinterpret_cast<const float4*>(scratch), hits->tet_flags,
       vertices_grad, cell_values_grad);
   RM_CUDA_CHECK(cudaPeekAtLastError());
   return RM_OK;

@@ -48,6 +48,68 @@ def allreduce_gradients(grads, group=None):
     return grads
 
 
+class OverlappedGradientSum:
+    """Sums the rasterizer's gradients over the ranks while its backward pass is still running.
+
+    The backward pass finishes the cell-value gradients range by range (raster.set_gradient_sink);
+    every finished range is all-reduced on a communication stream while the next range is being
+    finished on the compute stream, the vertex gradients (which every range adds to) last.  After
+    the backward pass returns, the compute stream has been made to wait for the last collective, so
+    the gradients a caller sees are the sums.  Use as a context manager around the backward call, or
+    install()/remove() around a training loop.
+    """
+
+    def __init__(self, group=None, chunks=4, device=None):
+        self.group = group
+        self.chunks = chunks
+        self.device = device
+        self.comm = None
+        self.events = []   # (start, end) CUDA events of every collective, if timing is on
+        self.timing = False
+
+    def _active(self):
+        return dist.is_available() and dist.is_initialized() and dist.get_world_size(self.group) > 1
+
+    def __call__(self, t):
+        if not self._active():
+            return
+        cur = torch.cuda.current_stream(t.device)
+        if self.comm is None:
+            self.comm = torch.cuda.Stream(t.device)
+        ready = torch.cuda.Event()
+        ready.record(cur)
+        self.comm.wait_event(ready)
+        with torch.cuda.stream(self.comm):
+            if self.timing:
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(self.comm)
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+            if self.timing:
+                b.record(self.comm)
+                self.events.append((a, b))
+        t.record_stream(self.comm)
+
+    def done(self):
+        if self.comm is not None:
+            torch.cuda.current_stream(self.comm.device).wait_stream(self.comm)
+
+    def install(self):
+        from . import raster
+        raster.set_gradient_sink(self, self.chunks)
+        return self
+
+    def remove(self):
+        from . import raster
+        raster.set_gradient_sink(None)
+
+    def __enter__(self):
+        return self.install()
+
+    def __exit__(self, *exc):
+        self.remove()
+        return False
+
+
 def tile_row_bands(grid_height, world_size, row_weights=None):
     """Split tile rows [0, grid_height) into world_size contiguous bands.
 

@@ -177,6 +177,19 @@ def forward(sorted_idx, tile_ranges, records, cam, ray_jitter, want_hit_masks=Tr
     return output_img, distortion_img, n_contributors, hits
 
 
+# Optional consumer of finished gradients, set by a multi-GPU job (dist.OverlappedGradientSum.install): the
+# backward pass then finishes the tets in `chunks` ranges and hands every finished range of cell_values_grad,
+# and vertices_grad at the end, to `sink` while the next range is still being finished.
+_gradient_sink = None
+
+
+def set_gradient_sink(sink, chunks=4):
+    """sink(tensor) is called on the backward pass's stream, in order, with views of the two gradients as
+    they become final; sink.done() once at the end.  None removes it."""
+    global _gradient_sink
+    _gradient_sink = None if sink is None else (sink, max(1, int(chunks)))
+
+
 def backward(sorted_idx, tile_ranges, records, cam, ray_jitter, output_img, distortion_img, n_contributors,
              hits, grad_output_img, grad_distortion_img, indices, vertices, cell_values):
     lib = _lib.load()
@@ -192,11 +205,29 @@ def backward(sorted_idx, tile_ranges, records, cam, ray_jitter, output_img, dist
         cell_grad = flat[off:].view(T, 7)
         if off > 3 * V:
             flat[3 * V:off].zero_()
-        _lib.check(lib.rm_backward(_ptr(sorted_idx), _ptr(tile_ranges), _ptr(records), cam.ref, _ptr(ray_jitter),
-                                   _ptr(output_img), _ptr(distortion_img), _ptr(n_contributors), hit_list_ref(hits),
-                                   _ptr(grad_output_img), _ptr(grad_distortion_img), _ptr(indices), _ptr(vertices),
-                                   _ptr(cell_values), T, V, _ptr(grad_records), _ptr(vertices_grad), _ptr(cell_grad),
-                                   _stream(dev)))
+        href = hit_list_ref(hits)
+        st = _stream(dev)
+        _lib.check(lib.rm_backward_integrate(_ptr(tile_ranges), _ptr(records), cam.ref, _ptr(ray_jitter),
+                                             _ptr(output_img), _ptr(distortion_img), href, _ptr(grad_output_img),
+                                             _ptr(grad_distortion_img), T, V, _ptr(grad_records), _ptr(vertices_grad),
+                                             st))
+        sink = _gradient_sink
+        n_chunks = sink[1] if sink is not None and T >= 4096 else 1
+        step = -(-T // n_chunks)
+        step = -(-step // 256) * 256  # range starts on multiples of 256 tets
+        t0 = 0
+        while True:
+            t1 = min(t0 + step, T)
+            _lib.check(lib.rm_backward_finish(_ptr(indices), _ptr(vertices), _ptr(cell_values), t0, t1, T, cam.ref,
+                                              _ptr(grad_records), href, _ptr(vertices_grad), _ptr(cell_grad), st))
+            if sink is not None and t1 > t0:
+                sink[0](cell_grad[t0:t1])
+            t0 = t1
+            if t0 >= T:
+                break
+        if sink is not None:
+            sink[0](vertices_grad)
+            sink[0].done()
     return vertices_grad, cell_grad
 
 

@@ -79,3 +79,36 @@ def test_cell_values_from_checkpoint_gpu(tmp_path):
                               sc.sh.cpu().numpy(), sc.indices.cpu().numpy(), sc.circumcenters.cpu().numpy(),
                               sc.vertices.cpu().numpy(), 3)
     np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-5)
+
+
+def test_ply_round_trip(tmp_path):
+    """ckpt.ply with the element and property names of models/base_model.py:107-151."""
+    import numpy as np
+    from radiance_meshes_b200 import checkpoint
+    rng = np.random.default_rng(5)
+    V, T, K = 40, 57, 8
+    vertices = rng.normal(size=(V, 3)).astype(np.float32)
+    indices = rng.integers(0, V, (T, 4)).astype(np.int32)
+    density = rng.uniform(0, 3, T).astype(np.float32)
+    grd = rng.normal(size=(T, 3)).astype(np.float32)
+    rgb = rng.uniform(0, 1, (T, 3)).astype(np.float32)
+    sh = rng.normal(size=(T, K, 3)).astype(np.float32)
+    path = tmp_path / "sub" / "ckpt.ply"
+    checkpoint.write_ply(path, vertices, indices, density, grd, rgb, sh)
+    head = open(path, "rb").read(1200).decode("latin1")
+    assert head.startswith("ply\nformat binary_little_endian 1.0\nelement vertex 40\n")
+    for name in ("element tetrahedron 57", "property list uchar int indices", "property float s",
+                 "property float grd_z", "property float sh_0_r", "property float sh_8_b"):
+        assert name in head
+    back = checkpoint.read_ply(path)
+    np.testing.assert_array_equal(back["vertices"], vertices)
+    np.testing.assert_array_equal(back["indices"], indices)
+    np.testing.assert_array_equal(back["density"], density)
+    np.testing.assert_array_equal(back["grd"], grd)
+    np.testing.assert_array_equal(back["sh_rest"], sh)
+    np.testing.assert_allclose(back["rgb"], rgb, atol=1e-6)
+    # degree 0 only, no tets
+    checkpoint.write_ply(tmp_path / "e.ply", vertices, np.zeros((0, 4), np.int32), np.zeros(0), np.zeros((0, 3)),
+                         np.zeros((0, 3)), np.zeros((0, 0, 3)))
+    e = checkpoint.read_ply(tmp_path / "e.ply")
+    assert e["indices"].shape == (0, 4) and e["sh_rest"].shape == (0, 0, 3)
