@@ -156,6 +156,10 @@ def cpu_baseline(sc, tcam, jitter, g_img, g_dist, tile_rows=8):
     t_fwd = time.time() - t0
     # pixels the reference algorithm itself decides by rounding carry no upstream gradient on either side
     keep = ~O.sensitive_pixels(idx, ranges, sc["indices"], sc["vertices"], sc["cell_values"], tcam, jitter, tol=2e-5)
+    # pixels whose termination (log-transmittance against the -5.5 cut-off) is decided within 1e-2: one tet more
+    # or less is walked there, which moves the alpha channel by that tet's whole optical depth
+    cut = (O.sensitive_pixels(idx, ranges, sc["indices"], sc["vertices"], sc["cell_values"], tcam, jitter, tol=2e-3,
+                              flags=True) & 2) != 0
     band = np.zeros((H, W), bool)
     band[rows[0]:rows[1]] = True
     gm = (keep & band)[..., None]
@@ -171,8 +175,64 @@ def cpu_baseline(sc, tcam, jitter, g_img, g_dist, tile_rows=8):
                          f"project(all tets) {t_proj:.2f}s scaled by the band's share, lists {t_lists:.2f}s, "
                          f"forward {t_fwd:.2f}s, backward {t_bwd:.2f}s"))
     ref = dict(rows=rows, tile_rows=(r0, r1), project=pr, idx=idx, ranges=ranges, out=out, dist=dist, keep=keep,
+               cut=cut,
                g_img=g_img_b, g_dist=g_dist_b, vg=vg, cg=cg)
     return entry, ref
+
+
+LIST_BUILD_KERNELS = ("rank_tets_radix_sort(12 launches)", "rank_order_scan(4 launches)", "tile_ranges(6 launches)",
+                      "k_block_start_ranks+k_region_hist1", "k_radix_rowscan+k_region_scatter(pass 1)",
+                      "k_region_hist2", "k_radix_rowscan+k_region_scatter(pass 2)", "k_region_layout", "k_fine_count",
+                      "k_fine_cursors", "k_fine_write")
+
+
+def time_reference_sort(torch, pkg, tcam_np, kernel_ms):
+    """Keys as generate_keys emits them (slang/tile_shader.slang:49-97: tet order, rows then columns of the
+    rectangle, key = tile << 32 | sortable(depth)), sorted by the reference's sort_by_keys
+    (sort_by_keys/sort_by_keys.cu:9-53) with the bit count of tile_shader_slang.py:57-59."""
+    from oracle import build_ref
+    try:
+        mod = build_ref.load_prebuilt()
+    except Exception as e:  # a prebuilt extension that does not load on this box
+        return dict(unavailable=f"oracle/_ref extension failed to load: {e}")
+    if mod is None:
+        return dict(unavailable="oracle/_ref/ref_sort_by_keys.so was not built (oracle/build_ref.py needs the reference "
+                                "checkout)")
+    dev = pkg["rect"].device
+    gw, gh = tcam_np["grid_width"], tcam_np["grid_height"]
+    rect = pkg["rect"].to(torch.int64)
+    w = rect[:, 2] - rect[:, 0]
+    tt = (w * (rect[:, 3] - rect[:, 1])) * pkg["mask"]
+    N = int(tt.sum().item())
+    tet = torch.repeat_interleave(torch.arange(rect.shape[0], device=dev), tt)
+    first = torch.cumsum(tt, 0) - tt
+    local = torch.arange(N, device=dev, dtype=torch.int64) - first[tet]
+    del first
+    wt = w[tet]
+    tile = (rect[tet, 1] + local // wt) * gw + rect[tet, 0] + local % wt
+    del local, wt
+    bits = pkg["vs_tetra"][:, 2].contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    sortable = torch.where(bits >= 0x80000000, (~bits) & 0xFFFFFFFF, bits ^ 0x80000000)
+    keys = (tile << 32) | sortable[tet]
+    ids = tet.to(torch.int32)
+    del tile, tet
+    msb = int(gw * gh).bit_length()
+    times = []
+    vals = None
+    for _ in range(4):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        _, vals = mod.sort_by_keys(keys, ids, msb)
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    same = bool(torch.equal(vals, pkg["sorted_tetra_idx"]))
+    ours = sum(kernel_ms.get(k, 0.0) for k in LIST_BUILD_KERNELS)
+    return dict(pairs=N, key_bits=32 + msb, reference_sort_ms=float(min(times[1:])),
+                this_library_list_build_ms=ours, values_equal_sorted_tetra_idx=same,
+                note="reference: CUB DeviceRadixSort::SortPairs of N (int64 key, int32 id) pairs incl. its cudaMalloc/"
+                     "cudaFree (key generation and tile ranges not included); this library: rank sort of the tets + "
+                     "tile ranges + region sort + mask expansion, i.e. everything between projection and the lists")
 
 
 def rel_l2(a, b):
@@ -200,16 +260,25 @@ def band_parity(ref, tcam_np, render_frame):
         o_seg = ref["idx"][o_rng[nz[0], 0]:o_rng[nz[-1], 1]]
         lists_ok = bool(np.array_equal(g_seg, o_seg))
     keep = ref["keep"][y0:y1]
+    settled = ~ref["cut"][y0:y1]
+    gi, oi = got["image"][y0:y1], ref["out"][y0:y1]
+    big = np.abs(gi - oi).max(-1) > 1e-3 * (np.abs(oi).max(-1) + 1e-3)
     return dict(rows=[int(y0), int(y1)], band_list_entries=int(o_len.sum()),
                 rect_and_depth_bit_exact_all_tets=rect_ok, tile_lists_bit_exact=lists_ok,
-                image_rel_l2=rel_l2(got["image"][y0:y1], ref["out"][y0:y1]),
+                image_rel_l2=rel_l2(gi[settled], oi[settled]), rgb_rel_l2_all_pixels=rel_l2(gi[..., :3], oi[..., :3]),
+                image_rel_l2_all_pixels=rel_l2(gi, oi), pixels_with_undecided_termination=float(1.0 - settled.mean()),
+                pixels_differing_1e3=dict(settled=float((big & settled).mean()), undecided=float((big & ~settled).mean())),
                 distortion_rel_l2=rel_l2(got["distortion_img"][y0:y1][keep], ref["dist"][y0:y1][keep]),
                 vertices_grad_rel_l2=rel_l2(got["vertices_grad"], ref["vg"]),
                 cell_grad_rel_l2=rel_l2(got["cell_grad"], ref["cg"]),
                 rounding_decided_pixels=float(1.0 - keep.mean()),
                 tolerances=dict(image=1e-4, gradients=1e-3),
-                note="GPU full frame vs CPU oracle on the band; upstream gradients zero outside the band and on "
-                     "pixels the reference algorithm decides by rounding")
+                note="GPU full frame vs CPU oracle on the band.  image_rel_l2: all four channels on the pixels whose "
+                     "termination is settled (log-transmittance never within 1e-2 of the -5.5 cut-off; elsewhere one "
+                     "tet more or less is walked and the alpha channel moves by its whole optical depth); the colour "
+                     "channels are also given on all pixels.  Distortion moments and gradients: on the pixels the "
+                     "reference algorithm does not itself decide by rounding (grazing contacts, cut-off within 1e-4), "
+                     "upstream gradients zero outside the band and on those pixels")
 
 
 def run_reference(args):
@@ -583,6 +652,13 @@ def run_gpu(args):
                                   "of this implementation, forward and backward)")
             del bctx, sidx, recs, hits, counts, masks, flags, slots, bits, owner, within, ncontrib
 
+    # ---- the reference's own GPU sort (CUB DeviceRadixSort behind sort_by_keys.cu, built unchanged from the
+    # reference checkout by oracle/build_ref.py) on the keys of this frame: timed beside this library's list
+    # build, and its value array must equal sorted_tetra_idx (a second pin of the tile-list order)
+    reference_sort = None
+    if rank == 0 and world == 1:
+        reference_sort = time_reference_sort(torch, pkg, tcam_np, kernel_ms)
+
     # ---- parity of the benchmarked frame itself against the CPU oracle, on the oracle's band of rows
     cpu_entry, parity = None, None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -668,6 +744,7 @@ def run_gpu(args):
         gpu_launches=int(launches), ms_per_step_median=ms_median,
         rank_step_ms=dict(min=min(rank_ms), median=float(np.median(rank_ms)), max=max(rank_ms)),
         allreduce=allreduce, parity=parity, parity_multi=parity_multi, hit_stats=hit_stats,
+        reference_sort=reference_sort,
         fp32_pipe=fp32_pipe,
         roofline=roofline,
         frame_roofline=dict(algorithmic_bytes=frame_bytes, achieved=frame_bytes / (ms_step * 1e-3) / 1e9,

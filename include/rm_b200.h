@@ -299,6 +299,23 @@ int rm_profile_read(char* names, size_t names_bytes, float* ms, int max_records)
  * library's launches inside it. */
 int64_t rm_launch_count(void);
 
+/*
+ * Bounds-checked build of the library (compiled with -DRM_BOUNDS_CHECK; the tests' stand-in for a
+ * memory checker, no counterpart in the reference).  In that build every index that depends on data
+ * - list cursors, hit-list slots, ids read from lists and the rows they address - is compared with the
+ * extent of its array before the access; a violation sets a bit of a status word and the access is
+ * skipped, nothing traps.
+ *   rm_debug_bounds_checked: 1 in the checked build, 0 otherwise (the other two are no-ops then).
+ *   rm_debug_set_extent(which, n): extent of a caller-owned array of the integration stages, whose
+ *     entry points carry no lengths: 0 list entries, 1 tets, 2 vertices, 3 hit-list id slots,
+ *     4 hit-list mask slots, 5 hit-list units.
+ *   rm_debug_bounds_status: waits for the device, returns the status word and clears it (bit = access
+ *     site; 0 = every checked access was inside its array).
+ */
+int rm_debug_bounds_checked(void);
+void rm_debug_set_extent(int which, int64_t n);
+uint32_t rm_debug_bounds_status(void);
+
 #ifdef __cplusplus
 }
 #endif

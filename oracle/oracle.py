@@ -178,15 +178,18 @@ def backward(sorted_idx, tile_ranges, indices, vertices, cell_values, tcam, jitt
     return vg, cg
 
 
-def sensitive_pixels(sorted_idx, tile_ranges, indices, vertices, cell_values, tcam, jitter, tol=1e-4, nthreads=0):
-    """Boolean [H,W] mask of pixels decided by rounding in the reference algorithm itself."""
+def sensitive_pixels(sorted_idx, tile_ranges, indices, vertices, cell_values, tcam, jitter, tol=1e-4, nthreads=0,
+                     flags=False):
+    """Boolean [H,W] mask of pixels decided by rounding in the reference algorithm itself.  With flags=True
+    the uint8 flags instead: bit 0 = a grazing ray/tet contact, bit 1 = a log-transmittance within tol (relative)
+    of the termination cut-off."""
     sorted_idx, tile_ranges, indices, vertices, cell_values, jitter = _fb_args(
         np.float32, sorted_idx, tile_ranges, indices, vertices, cell_values, jitter)
     cam = make_camera(tcam)
     mask = np.zeros((cam.image_height, cam.image_width), np.uint8)
     lib().or_sensitive_pixels(_p(sorted_idx), _p(tile_ranges), _p(indices), _p(vertices), _p(cell_values),
                               C.byref(cam), _p(jitter), _p(mask), C.c_float(tol), C.c_int(nthreads))
-    return mask.astype(bool)
+    return mask if flags else mask.astype(bool)
 
 
 def tet_err(sorted_idx, tile_ranges, indices, vertices, cell_values, tcam, pixel_err, ssim_err, nthreads=0):

@@ -994,11 +994,11 @@ int or_sensitive_pixels(const int32_t* sorted_idx, const int32_t* tile_ranges, c
         else tx = std::fmin(tx, tt);
       }
       float chord = tx - std::fmax(te, 0.f);
-      if (t.density > 0.f && std::fabs(chord) <= tol * std::fmax(1.f, std::fabs(tx))) flag = 1;
+      if (t.density > 0.f && std::fabs(chord) <= tol * std::fmax(1.f, std::fabs(tx))) flag |= 1;  // grazing contact
       Ctrl<float> c;
       if (evaluate_tet(t, o, d, c) && c.a > 0.f) {
         update_state(s, c);
-        if (std::fabs(s.logT + 5.5f) <= tol * 5.5f) flag = 1;
+        if (std::fabs(s.logT + 5.5f) <= tol * 5.5f) flag |= 2;  // termination decided within tol
         if (s.logT < -5.5f) break;
       }
     }

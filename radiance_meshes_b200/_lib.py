@@ -6,7 +6,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "librm_b200.so")
+# RM_B200_LIBRARY selects another build of the same library (the tests load the bounds-checked one)
+LIB_PATH = os.environ.get("RM_B200_LIBRARY") or os.path.join(_HERE, "librm_b200.so")
 
 RM_RECORD_FLOATS = 36
 RM_GRAD_RECORD_FLOATS = 24
@@ -19,7 +20,8 @@ SYMBOLS = ["rm_strerror", "rm_version", "rm_bin_workspace_bytes", "rm_list_scrat
            "rm_pack_records", "rm_forward", "rm_backward", "rm_vertex_backward", "rm_profile_enable",
            "rm_profile_read", "rm_backward_static_scratch", "rm_tet_err",
            "rm_activate_output", "rm_forward_constant_color", "rm_launch_count",
-           "rm_backward_integrate", "rm_backward_finish"]
+           "rm_backward_integrate", "rm_backward_finish", "rm_debug_bounds_checked", "rm_debug_set_extent",
+           "rm_debug_bounds_status"]
 RM_STATIC_SCRATCH_MAX_TETS = 131072
 RM_ERR_STATIC_SCRATCH = -5
 RM_ERR_INVALID_ARG = -1
@@ -82,6 +84,9 @@ def load():
     lib.rm_profile_enable.argtypes = [C.c_int]
     lib.rm_profile_read.argtypes = [C.c_char_p, sz, C.POINTER(C.c_float), C.c_int]
     lib.rm_launch_count.restype = C.c_int64
+    lib.rm_debug_set_extent.restype = None
+    lib.rm_debug_set_extent.argtypes = [C.c_int, i64]
+    lib.rm_debug_bounds_status.restype = C.c_uint32
     for name in SYMBOLS:
         getattr(lib, name)
     _lib = lib
@@ -91,6 +96,29 @@ def load():
 def check(rc):
     if rc != 0:
         raise RuntimeError(f"rm_b200: {load().rm_strerror(rc).decode()} (code {rc})")
+
+
+_checked = None
+
+
+def bounds_checked():
+    """True if the loaded library is the bounds-checked build."""
+    global _checked
+    if _checked is None:
+        _checked = bool(load().rm_debug_bounds_checked())
+    return _checked
+
+
+def set_extents(**extents):
+    """Bounds-checked build only: extents of caller-owned arrays (list, tets, verts, hit_ids, hit_masks, units)."""
+    order = ("list", "tets", "verts", "hit_ids", "hit_masks", "units")
+    lib = load()
+    for k, v in extents.items():
+        lib.rm_debug_set_extent(order.index(k), int(v))
+
+
+def bounds_status():
+    return int(load().rm_debug_bounds_status())
 
 
 def launch_count():

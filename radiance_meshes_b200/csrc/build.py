@@ -26,37 +26,48 @@ def _nvcc():
     return "nvcc"
 
 
-def needs_build():
-    if not os.path.exists(TARGET):
+def _target(variant):
+    return TARGET if variant is None else os.path.join(PKG, f"librm_b200_{variant}.so")
+
+
+def needs_build(variant=None):
+    target = _target(variant)
+    if not os.path.exists(target):
         return True
-    t = os.path.getmtime(TARGET)
+    t = os.path.getmtime(target)
     srcs = [os.path.join(HERE, u) for u, _ in UNITS] + HEADERS + [os.path.abspath(__file__)]
     return any(os.path.getmtime(s) > t for s in srcs)
 
 
-def build(force=False, verbose=False, ptxas_info=False):
-    if not force and not needs_build():
-        return TARGET
+def build(force=False, verbose=False, ptxas_info=False, variant=None):
+    """variant=None: the library.  variant="check": the bounds-checked build (-DRM_BOUNDS_CHECK), written to
+    librm_b200_check.so and loaded by the tests through RM_B200_LIBRARY."""
+    assert variant in (None, "check")
+    target = _target(variant)
+    if not force and not needs_build(variant):
+        return target
     nvcc = _nvcc()
-    objdir = os.path.join(HERE, "build")
+    objdir = os.path.join(HERE, "build" if variant is None else f"build_{variant}")
     os.makedirs(objdir, exist_ok=True)
+    defines = ["-DRM_BOUNDS_CHECK"] if variant == "check" else []
     objs = []
     for unit, extra in UNITS:
         obj = os.path.join(objdir, unit.replace(".cu", ".o"))
         cmd = [nvcc, "-std=c++17", "-O3", "-lineinfo", *ARCH, "-I", INCLUDE, "-I", HERE, "-Xcompiler", "-fPIC",
-               *extra, "-c", os.path.join(HERE, unit), "-o", obj]
+               *defines, *extra, "-c", os.path.join(HERE, unit), "-o", obj]
         if ptxas_info:
             cmd[1:1] = ["-Xptxas", "-v"]
         if verbose:
             print(" ".join(cmd), flush=True)
         subprocess.check_call(cmd)
         objs.append(obj)
-    cmd = [nvcc, "-shared", *ARCH, "-o", TARGET, *objs]
+    cmd = [nvcc, "-shared", *ARCH, "-o", target, *objs]
     if verbose:
         print(" ".join(cmd), flush=True)
     subprocess.check_call(cmd)
-    return TARGET
+    return target
 
 
 if __name__ == "__main__":
-    build(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas" in sys.argv)
+    build(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas" in sys.argv,
+          variant="check" if "--check" in sys.argv else None)

@@ -36,6 +36,8 @@ int rm_launch_tet_err(const int32_t*, const int32_t*, const float*, const RmCame
 int rm_launch_activate(const float*, const float*, const float*, const float*, const void*, int, const int32_t*,
                        const float*, const float*, int64_t, int, int, float*, cudaStream_t);
 
+void rm_debug_extent_raster(int which, long long n);
+
 static thread_local char g_last_error[256] = "";
 
 // ---- optional per-kernel timing ---------------------------------------------
@@ -129,6 +131,16 @@ const char* rm_strerror(int code) {
 int rm_version(void) { return 101; }
 
 int64_t rm_launch_count(void) { return (int64_t)g_launches.load(std::memory_order_relaxed); }
+
+int rm_debug_bounds_checked(void) {
+#ifdef RM_BOUNDS_CHECK
+  return 1;
+#else
+  return 0;
+#endif
+}
+void rm_debug_set_extent(int which, int64_t n) { rm_debug_extent_raster(which, (long long)n); }
+uint32_t rm_debug_bounds_status(void) { return rm_bounds_status_raster() | rm_bounds_status_binning(); }
 
 void rm_profile_enable(int on) {
   std::lock_guard<std::mutex> lk(g_prof_mu);

@@ -257,6 +257,7 @@ k_radix_scatter(const uint32_t* __restrict__ keys_in, const uint32_t* __restrict
   for (int lp = threadIdx.x; lp < n_block; lp += kSortThreads) {
     const uint2 pr = sbuf[lp];
     const uint32_t g = dbase[(pr.x >> shift) & (kRadix - 1)] + (uint32_t)lp;
+    if (!RM_INDEX_OK(g, RM_X_TETS, 13)) continue;
     keys_out[g] = pr.x;
     vals_out[g] = pr.y;
   }
@@ -484,6 +485,7 @@ k_region_hist1(const uint32_t* __restrict__ cum, const uint32_t* __restrict__ st
   for (int jl = threadIdx.x; jl < cnt; jl += kBinThreads) {
     uint32_t region, tet;
     item_region(jl, j0, r0, before, win, own, order, rect, reg_w, region, tet);
+    if (!(RM_INDEX_OK(region, RM_X_REGIONS, 11) && RM_INDEX_OK(tet, RM_X_TETS, 13))) continue;
     pairs_out[j0 + jl] = make_uint2(tet, region);  // generated once; the scatter passes read them back
     atomicAdd(&h[region & (bins - 1)], 1u);
     if (n_regions_smem) atomicAdd(&rh[region], 1u);
@@ -647,6 +649,7 @@ k_region_scatter(const uint2* __restrict__ pairs, int64_t n, int shift, uint32_t
   for (int lp = threadIdx.x; lp < cntItems; lp += kBinThreads) {
     const uint2 p2 = sbuf[lp];
     const uint32_t g = dbase[(p2.y >> shift) & (bins - 1)] + (uint32_t)lp;
+    if (!RM_INDEX_OK(g, RM_X_PAIRS, 9)) continue;
     if (final) entries[g] = region_entry(p2.x, p2.y, rect, reg_w);
     else pairs_out[g] = p2;
   }
@@ -678,7 +681,8 @@ k_region_layout(const uint32_t* __restrict__ region_count, uint32_t n_regions, u
     const uint32_t ex_c = block_exclusive_scan<1024>(q, &total, sm);
     if (r < n_regions) {
       chunk_base[r] = carry_c + ex_c;
-      for (uint32_t k = 0; k < q; ++k) chunk_region[carry_c + ex_c + k] = r;
+      for (uint32_t k = 0; k < q; ++k)
+        if (RM_INDEX_OK(carry_c + ex_c + k, RM_X_CHUNKS, 10)) chunk_region[carry_c + ex_c + k] = r;
     }
     carry_c += total;
   }
@@ -710,11 +714,14 @@ __device__ __forceinline__ bool chunk_span(uint32_t chunk, const uint32_t* __res
                                            const uint32_t* __restrict__ chunk_region, uint32_t n_regions,
                                            ChunkSpan* sp) {
   if (chunk >= chunk_base[n_regions]) return false;
+  if (!RM_INDEX_OK(chunk, RM_X_CHUNKS, 10)) return false;
   const uint32_t r = chunk_region[chunk];
+  if (!RM_INDEX_OK(r, RM_X_REGIONS, 11)) return false;
   const uint32_t k = chunk - chunk_base[r];
   sp->region = r;
   sp->begin = region_start[r] + k * kChunk;
   sp->end = min(sp->begin + (uint32_t)kChunk, region_start[r + 1]);
+  if (sp->end > sp->begin && !RM_INDEX_OK(sp->end - 1, RM_X_PAIRS, 9)) return false;
   return true;
 }
 
@@ -746,7 +753,8 @@ k_fine_cursors(const uint32_t* __restrict__ chunk_base, uint32_t n_regions, int 
   if (r >= n_regions) return;
   const int gy = (int)(r / (uint32_t)reg_w), gx = (int)(r - (uint32_t)gy * (uint32_t)reg_w);
   const int tx = gx * kRegW + (lane & (kRegW - 1)), ty = gy * kRegH + (lane >> kRegShiftX);
-  uint32_t pos = (tx < grid_w && ty < grid_h) ? tile_start[(int64_t)ty * grid_w + tx] : 0u;
+  uint32_t pos = (tx < grid_w && ty < grid_h && RM_INDEX_OK((int64_t)ty * grid_w + tx, RM_X_TILES, 12))
+                     ? tile_start[(int64_t)ty * grid_w + tx] : 0u;
   const uint32_t q1 = chunk_base[r + 1];
   constexpr int kBatch = 8;  // independent loads in flight per step of the serial scan
   for (uint32_t q = chunk_base[r]; q < q1; q += kBatch) {
@@ -790,7 +798,7 @@ k_fine_write(const uint2* __restrict__ entries, const uint32_t* __restrict__ reg
       const uint32_t pos = __shfl_sync(0xffffffffu, c, l) + __popc(col & lt);
       // pos < n_keys always holds when the masks agree with the tile populations; the test keeps a
       // disagreement from writing outside the list array
-      if (covers && pos < n_keys) sorted_idx[pos] = (int32_t)en.x;
+      if (covers && pos < n_keys && RM_INDEX_OK(pos, RM_X_LIST, 8)) sorted_idx[pos] = (int32_t)en.x;
       if (lane == l) appended = __popc(col);
     }
     c += appended;
@@ -898,6 +906,8 @@ int rm_launch_bin_finish(int64_t T, const RmCamera* cam, const int32_t* rect, in
   uint32_t* tstart = reinterpret_cast<uint32_t*>(b + L.tile_start);
   unsigned long long* total_keys = reinterpret_cast<unsigned long long*>(b + L.total_keys);
 
+  rm_set_extent(RM_X_TETS, T, st);
+  rm_set_extent(RM_X_TILES, G, st);
   // 1. rank tets by (depth bits, id): 4 stable passes; result ends in buffer 0
   if (T > 0) {
     RmProfScope prof("rank_tets_radix_sort(12 launches)", st);
@@ -998,6 +1008,12 @@ int rm_launch_build_lists(const int32_t* rect, const int32_t* tile_ranges, int64
   if (n_region_keys < 1 || n_region_keys > n_keys || !make_list_plan(n_region_keys, gh, gw, &P))
     return RM_ERR_INVALID_ARG;
   if (P.total > scratch_bytes || (reinterpret_cast<uintptr_t>(scratch) & 255)) return RM_ERR_WORKSPACE;
+  rm_set_extent(RM_X_TETS, T, st);
+  rm_set_extent(RM_X_TILES, G, st);
+  rm_set_extent(RM_X_LIST, n_keys, st);
+  rm_set_extent(RM_X_PAIRS, n_region_keys, st);
+  rm_set_extent(RM_X_CHUNKS, P.max_chunks, st);
+  rm_set_extent(RM_X_REGIONS, P.n_regions, st);
   char* b = static_cast<char*>(ws);
   const uint32_t* order = reinterpret_cast<uint32_t*>(b + L.ord_a);
   const uint32_t* cum = reinterpret_cast<uint32_t*>(b + L.cum);
@@ -1076,3 +1092,5 @@ int rm_launch_build_lists(const int32_t* rect, const int32_t* tile_ranges, int64
   RM_CUDA_CHECK(cudaPeekAtLastError());
   return RM_OK;
 }
+
+unsigned rm_bounds_status_binning() { return rm_take_bounds_status(); }

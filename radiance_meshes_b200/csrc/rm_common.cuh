@@ -37,6 +37,54 @@ struct RmProfScope {
   ~RmProfScope() { rm_prof_end(st); }
 };
 
+// ---------------------------------------------------------------------------
+// Bounds-checked build (-DRM_BOUNDS_CHECK), used by the tests in place of a memory checker: every
+// index that depends on data (list cursors, hit-list slots, ids read from lists, rows addressed by
+// them) is tested against the extent of its array before the access; a violation sets a bit of a
+// status word that rm_debug_bounds_status() returns and the access is skipped - nothing traps.  The
+// extents are set by the host launchers before each launch.  In the normal build the macros vanish.
+// ---------------------------------------------------------------------------
+enum RmExtent {
+  RM_X_LIST = 0,      // sorted_tetra_idx entries
+  RM_X_TETS,          // records / record-gradient rows / tet_flags / per-tet outputs
+  RM_X_VERTS,         // vertices
+  RM_X_HIT_IDS,       // hit-list id slots
+  RM_X_HIT_MASKS,     // hit-list mask slots
+  RM_X_UNITS,         // hit-list counts
+  RM_X_PAIRS,         // (region, tet) pairs / sorted region entries
+  RM_X_CHUNKS,        // chunks of the level-2 list build
+  RM_X_REGIONS,       // regions
+  RM_X_TILES,         // tiles
+  RM_X_COUNT
+};
+#ifdef RM_BOUNDS_CHECK
+static __device__ long long g_rm_extent[RM_X_COUNT];
+static __device__ unsigned g_rm_bounds_status;
+// site: a small number naming the access, reported as bit (site & 31)
+#define RM_INDEX_OK(i, which, site) rm_index_ok((long long)(i), g_rm_extent[which], (site))
+static __device__ __forceinline__ bool rm_index_ok(long long i, long long n, int site) {
+  if ((unsigned long long)i < (unsigned long long)n) return true;
+  atomicOr(&g_rm_bounds_status, 1u << (site & 31));
+  return false;
+}
+static inline void rm_set_extent(int which, long long n, cudaStream_t st) {
+  cudaMemcpyToSymbolAsync(g_rm_extent, &n, sizeof(n), sizeof(long long) * (size_t)which, cudaMemcpyHostToDevice, st);
+}
+static inline unsigned rm_take_bounds_status() {
+  unsigned v = 0, z = 0;
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(&v, g_rm_bounds_status, sizeof(v));
+  cudaMemcpyToSymbol(g_rm_bounds_status, &z, sizeof(z));
+  return v;
+}
+#else
+#define RM_INDEX_OK(i, which, site) true
+static inline void rm_set_extent(int, long long, cudaStream_t) {}
+static inline unsigned rm_take_bounds_status() { return 0; }
+#endif
+unsigned rm_bounds_status_raster();
+unsigned rm_bounds_status_binning();
+
 namespace rm {
 
 constexpr int kRecordFloats = RM_RECORD_FLOATS;

@@ -278,6 +278,23 @@ k_project(const int32_t* __restrict__ indices, int64_t T, const float* __restric
     f3 mn, mx;
     const bool simple = cam.type == 0 && dist_norm2(cam) < 1e-9f && cs[0].z > 1e-4f && cs[1].z > 1e-4f &&
                         cs[2].z > 1e-4f && cs[3].z > 1e-4f;
+    if (simple && (cam.row0 > 0 || cam.row1 < cam.grid_h)) {
+      // Band pre-test: a tet whose four projected vertices all lie more than a pixel above the band's
+      // first pixel row, or more than a pixel below its last, ends with an empty rectangle after the
+      // clamp below; it is culled here, before the extent and the fp64 circumsphere.  The comparison
+      // py < y is made without the division (Z > 0): fy*Y + (cy - y)*Z < 0; its rounding error is far
+      // below the one-pixel margin wherever py is near y.
+      const float c_lo = cam.K[5] - (float(cam.row0 * cam.tile_h) - 1.0f);
+      const float c_hi = cam.K[5] - (float(cam.row1 * cam.tile_h) + 1.0f);
+      bool above = true, below = true;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float a = cam.K[4] * cs[k].y;
+        above = above && (a + c_lo * cs[k].z < 0.0f);
+        below = below && (a + c_hi * cs[k].z > 0.0f);
+      }
+      if (above || below) break;
+    }
     if (simple) find_extent_unclipped(cs, mn, mx, cam);
     else find_extent(cs, mn, mx, cam);
     if (mx.z <= 0.0f) break;

@@ -118,18 +118,31 @@ k_pack_records(const int32_t* __restrict__ indices, const float* __restrict__ ve
                      __ldg(D + 3) * __ldg(D + 3);
     bool ok = rcam.camera_type == 0 && d2 < 1e-9f;
     float px[4], py[4];
+    // Bound of the fp32 rounding error of the projected vertices, in pixels: the camera-space
+    // coordinates are sums of four products (error <= 4 * 2^-24 * sum of magnitudes), and the error of
+    // X/Z grows with 1/Z, so vertices near the camera plane project with errors far above the 0.01
+    // pixel margin of the hull tests.  The lines are moved outwards by the bound (two end points per
+    // line); a tet whose bound reaches half a pixel, or with a vertex behind the near plane, is not culled.
+    float perr = 0.0f;
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       float X = __ldg(W + 0) * v[k].x + __ldg(W + 1) * v[k].y + __ldg(W + 2) * v[k].z + __ldg(W + 3);
       float Y = __ldg(W + 4) * v[k].x + __ldg(W + 5) * v[k].y + __ldg(W + 6) * v[k].z + __ldg(W + 7);
       float Z = __ldg(W + 8) * v[k].x + __ldg(W + 9) * v[k].y + __ldg(W + 10) * v[k].z + __ldg(W + 11);
+      const float u4 = 2.4e-7f;
+      const float eX = u4 * (fabsf(__ldg(W + 0) * v[k].x) + fabsf(__ldg(W + 1) * v[k].y) + fabsf(__ldg(W + 2) * v[k].z) + fabsf(__ldg(W + 3)));
+      const float eY = u4 * (fabsf(__ldg(W + 4) * v[k].x) + fabsf(__ldg(W + 5) * v[k].y) + fabsf(__ldg(W + 6) * v[k].z) + fabsf(__ldg(W + 7)));
+      const float eZ = u4 * (fabsf(__ldg(W + 8) * v[k].x) + fabsf(__ldg(W + 9) * v[k].y) + fabsf(__ldg(W + 10) * v[k].z) + fabsf(__ldg(W + 11)));
       ok = ok && Z > 1e-3f;
+      const float iz = 1.0f / Z;
       px[k] = fx * (X / Z) + cx;
       py[k] = fy * (Y / Z) + cy;
-      // A vertex just in front of the camera projects to coordinates whose fp32 rounding (and that of
-      // the line offsets built from them) exceeds the 0.01 pixel margin of the tests: no cull then.
-      ok = ok && fabsf(px[k]) <= 1e4f && fabsf(py[k]) <= 1e4f;
+      const float ex = fabsf(fx) * iz * (eX + fabsf(X * iz) * eZ) + 4e-7f * (fabsf(px[k]) + fabsf(cx));
+      const float ey = fabsf(fy) * iz * (eY + fabsf(Y * iz) * eZ) + 4e-7f * (fabsf(py[k]) + fabsf(cy));
+      perr = fmaxf(perr, ex + ey);
     }
+    const float margin = 2.0f * perr;
+    ok = ok && margin < 0.5f;
     // Edge lines of the convex hull of the four projected vertices, a*x + b*y + c >= 0
     // inside, (a, b) of unit length.  A vertex pair is a hull edge iff the other two
     // vertices lie on one side of its line; a tet projects to a quadrilateral (4 such
@@ -153,7 +166,7 @@ k_pack_records(const int32_t* __restrict__ indices, const float* __restrict__ ve
           const float inv = (pos ? 1.0f : -1.0f) / len;
           nx *= inv;
           ny *= inv;
-          const float cc = -(nx * px[a] + ny * py[a]);
+          const float cc = -(nx * px[a] + ny * py[a]) + margin;
 #pragma unroll
           for (int q = 0; q < 4; ++q) {  // slot `ne`, without dynamic indexing
             if (q == ne) { la[q] = nx; lb[q] = ny; lc[q] = cc; }
@@ -395,6 +408,7 @@ __device__ __forceinline__ Unit make_unit(const RmCamera& c, const int2* __restr
   int2 rg = __ldg(ranges + u.tile);
   u.start = rg.x;
   u.len = rg.y - rg.x;
+  if (u.len > 0 && !(RM_INDEX_OK(rg.x, RM_X_LIST, 0) && RM_INDEX_OK(rg.y - 1, RM_X_LIST, 0))) u.len = 0;
   return u;
 }
 
@@ -550,6 +564,8 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
   int qa_h = 0, qa_n = 0, qb_h = 0, qb_n = 0;  // ring heads and fill levels (the same in all lanes of the half)
   int id_e = (fetching && lane16 < u.len) ? __ldg(list + u.start + lane16) : -1;
   int id_n = (fetching && kBatch + lane16 < u.len) ? __ldg(list + u.start + kBatch + lane16) : -1;
+  if (id_e >= 0 && !RM_INDEX_OK(id_e, RM_X_TETS, 1)) id_e = -1;
+  if (id_n >= 0 && !RM_INDEX_OK(id_n, RM_X_TETS, 1)) id_n = -1;
   const float qnan = __int_as_float(0x7fc00000);
   float4 hq0 = make_float4(qnan, qnan, qnan, qnan), hq1 = hq0, hq2 = hq0;
   if (id_e >= 0) {
@@ -592,6 +608,7 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
             hq2 = __ldg(src_rec + 8);
           }
           id_n = (src + kBatch + lane16 < u.len) ? __ldg(list + u.start + src + kBatch + lane16) : -1;
+          if (id_n >= 0 && !RM_INDEX_OK(id_n, RM_X_TETS, 1)) id_n = -1;
         }
         continue;
       }
@@ -687,12 +704,13 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
     }
     __syncwarp();
     if (hit_ids && n_cur > 0) {  // append the batch to the hit list
-      if (lane16 < n_cur) {
+      if (lane16 < n_cur && RM_INDEX_OK(hbase + n_ent + lane16, RM_X_HIT_IDS, 2)) {
         const int id = batch_id[warp][half][buf][lane16];
         hit_ids[hbase + n_ent + lane16] = id;
         tet_flags[id] = 1;  // this tet's record-gradient row is cleared and read by the backward pass
       }
-      hit_masks[mbase + n_ent + lane16] = (uint16_t)hitbits;  // n_ent is a multiple of 16 here
+      if (RM_INDEX_OK(mbase + n_ent + lane16, RM_X_HIT_MASKS, 3))
+        hit_masks[mbase + n_ent + lane16] = (uint16_t)hitbits;  // n_ent is a multiple of 16 here
       n_ent += n_cur;
     }
     act16 = (__ballot_sync(FULL, active) >> (16 * half)) & 0xFFFFu;
@@ -703,7 +721,8 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
   cp_async_wait<0>();
   if (active) contrib = u.len;  // walked the whole list
 
-  if (hit_counts && lane16 == 0 && unit < n_units) hit_counts[(int64_t)u.tile * u.subs + u.sub] = n_ent;
+  if (hit_counts && lane16 == 0 && unit < n_units && RM_INDEX_OK((int64_t)u.tile * u.subs + u.sub, RM_X_UNITS, 4))
+    hit_counts[(int64_t)u.tile * u.subs + u.sub] = n_ent;
   if (u.inside) {
     if (CONST_COLOR) {
       out_img[pix] = make_float4(sr, sg, sb, T);
@@ -758,7 +777,11 @@ k_backward(const int2* __restrict__ ranges, const float4* __restrict__ records, 
   // entry to the first.  Batch c holds entries [16 c, 16 c + 16) of the list, the last one fewer.
   const int64_t hbase = (int64_t)u.start * u.subs + (int64_t)u.sub * u.len;
   const int64_t mbase = hbase + 16 * ((int64_t)u.tile * u.subs + u.sub);
-  const int nmax = unit < n_units ? min(__ldg(hit_counts + (int64_t)u.tile * u.subs + u.sub), u.len) : 0;
+  int nmax = (unit < n_units && RM_INDEX_OK((int64_t)u.tile * u.subs + u.sub, RM_X_UNITS, 4))
+                 ? min(__ldg(hit_counts + (int64_t)u.tile * u.subs + u.sub), u.len) : 0;
+  if (nmax > 0 && !(RM_INDEX_OK(hbase + nmax - 1, RM_X_HIT_IDS, 2) &&
+                    RM_INDEX_OK(mbase + (nmax + kChunk - 1) / kChunk * kChunk - 1, RM_X_HIT_MASKS, 3)))
+    nmax = 0;
   const int nchunks = (nmax + kChunk - 1) / kChunk;
   const int max_chunks = max(nchunks, __shfl_xor_sync(0xffffffffu, nchunks, 16));
 
@@ -789,7 +812,8 @@ k_backward(const int2* __restrict__ ranges, const float4* __restrict__ records, 
     // per-pixel bit sets -> per-entry pixel masks (lane j gets the mask of entry j of the batch)
     lane_bits[warp][half][lane16] = bits;
     __syncwarp();
-    const unsigned m = transpose_masks(lane_bits[warp][half], lane16);
+    unsigned m = transpose_masks(lane_bits[warp][half], lane16);
+    if (m && !RM_INDEX_OK(id, RM_X_TETS, 1)) m = 0u;  // an id outside the tet table: the entry is dropped
     __syncwarp();
     stage_id[warp][half][k & 1][lane16] = id;
     stage_mask[warp][half][k & 1][lane16] = m;
@@ -1008,6 +1032,7 @@ k_tet_err(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
 
   if (fetching && lane16 < u.len) {
     int id = __ldg(list + u.start + lane16);
+    if (!RM_INDEX_OK(id, RM_X_TETS, 6)) id = 0;
     stage_id[warp][half][0][lane16] = id;
     const float4* src = records + kRecStride * (int64_t)id;
 #pragma unroll
@@ -1018,6 +1043,7 @@ k_tet_err(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
   }
   cp_async_commit();
   int id_next = (fetching && kChunk + lane16 < u.len) ? __ldg(list + u.start + kChunk + lane16) : 0;
+  if (!RM_INDEX_OK(id_next, RM_X_TETS, 6)) id_next = 0;
 
   for (int c = 0; c < max_chunks; ++c) {
     float4* cur = stage[warp][half][c & 1];
@@ -1037,6 +1063,7 @@ k_tet_err(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
       }
       cp_async_commit();
       if (fetching && e + kChunk < u.len) id_next = __ldg(list + u.start + e + kChunk);
+      if (!RM_INDEX_OK(id_next, RM_X_TETS, 6)) id_next = 0;
     }
     cp_async_wait<1>();
     __syncwarp();
@@ -1169,6 +1196,9 @@ k_backward_finish(const int32_t* __restrict__ indices, const float* __restrict__
   } else {
   f3 cam = {__ldg(rcam.cam_pos), __ldg(rcam.cam_pos + 1), __ldg(rcam.cam_pos + 2)};
   int4 id = __ldg(reinterpret_cast<const int4*>(indices) + g);
+  if (!(RM_INDEX_OK(id.x, RM_X_VERTS, 5) && RM_INDEX_OK(id.y, RM_X_VERTS, 5) && RM_INDEX_OK(id.z, RM_X_VERTS, 5) &&
+        RM_INDEX_OK(id.w, RM_X_VERTS, 5)))
+    id = make_int4(0, 0, 0, 0);
   const int vid[4] = {id.x, id.y, id.z, id.w};
   f3 v[4] = {load3(vertices, id.x), load3(vertices, id.y), load3(vertices, id.z), load3(vertices, id.w)};
   PlaneSetup p;
@@ -1426,4 +1456,14 @@ extern "C" int rm_backward_static_scratch(const int32_t* sorted_tetra_idx, const
       vertices_grad, cell_values_grad);
   RM_CUDA_CHECK(cudaPeekAtLastError());
   return RM_OK;
+}
+
+// Bounds-checked build: extents of the caller-owned arrays of the integration stages (the entry points
+// of these stages carry no array lengths) and the status word of this translation unit.
+unsigned rm_bounds_status_raster() { return rm_take_bounds_status(); }
+void rm_debug_extent_raster(int which, long long n) {
+  if (which >= 0 && which < RM_X_COUNT) rm_set_extent(which, n, nullptr);
+#ifdef RM_BOUNDS_CHECK
+  cudaDeviceSynchronize();
+#endif
 }

@@ -171,6 +171,10 @@ def forward(sorted_idx, tile_ranges, records, cam, ray_jitter, want_hit_masks=Tr
                     torch.empty((slots,), dtype=torch.int32, device=dev),
                     torch.empty((slots + 16 * units,), dtype=torch.int16, device=dev),
                     torch.zeros((max(int(records.shape[0]), 1),), dtype=torch.uint8, device=dev))
+        if _lib.bounds_checked():
+            _lib.set_extents(list=sorted_idx.shape[0], tets=records.shape[0],
+                             hit_ids=hits[1].shape[0] if hits else 0, hit_masks=hits[2].shape[0] if hits else 0,
+                             units=hits[0].shape[0] if hits else 0)
         _lib.check(lib.rm_forward(_ptr(sorted_idx), _ptr(tile_ranges), _ptr(records), cam.ref, _ptr(ray_jitter),
                                   _ptr(output_img), _ptr(distortion_img), _ptr(n_contributors), hit_list_ref(hits),
                                   _stream(dev)))
@@ -207,6 +211,9 @@ def backward(sorted_idx, tile_ranges, records, cam, ray_jitter, output_img, dist
             flat[3 * V:off].zero_()
         href = hit_list_ref(hits)
         st = _stream(dev)
+        if _lib.bounds_checked():
+            _lib.set_extents(list=sorted_idx.shape[0], tets=T, verts=V, hit_ids=hits[1].shape[0],
+                             hit_masks=hits[2].shape[0], units=hits[0].shape[0])
         _lib.check(lib.rm_backward_integrate(_ptr(tile_ranges), _ptr(records), cam.ref, _ptr(ray_jitter),
                                              _ptr(output_img), _ptr(distortion_img), href, _ptr(grad_output_img),
                                              _ptr(grad_distortion_img), T, V, _ptr(grad_records), _ptr(vertices_grad),
@@ -249,6 +256,8 @@ def tet_err(sorted_idx, tile_ranges, records, cam, pixel_err, ssim_err, n_tets):
     with torch.cuda.device(dev):
         err = torch.empty((n_tets, 16), dtype=torch.float32, device=dev)
         cnt = torch.empty((n_tets, 2), dtype=torch.int32, device=dev)
+        if _lib.bounds_checked():
+            _lib.set_extents(list=sorted_idx.shape[0], tets=n_tets)
         _lib.check(lib.rm_tet_err(_ptr(sorted_idx), _ptr(tile_ranges), _ptr(records), cam.ref, _ptr(pixel_err),
                                   _ptr(ssim_err), n_tets, _ptr(err), _ptr(cnt), _stream(dev)))
     return err, cnt
