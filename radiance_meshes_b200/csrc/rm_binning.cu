@@ -46,6 +46,10 @@ __device__ __forceinline__ uint32_t scan_value(const uint32_t* __restrict__ in, 
   if (rect) return regions_touched(__ldg(rect + gather[i]));
   return gather ? in[gather[i]] : in[i];
 }
+// number of valid items: n, or the device-side count if one is given (the visible tets, known only on the device)
+__device__ __forceinline__ int64_t valid_items(int64_t n, const int32_t* __restrict__ n_dev) {
+  return n_dev ? min(n, (int64_t)__ldg(n_dev)) : n;
+}
 
 constexpr int kScanThreads = 256;
 constexpr int kScanItems = 16;
@@ -82,16 +86,17 @@ __device__ __forceinline__ uint32_t block_exclusive_scan(uint32_t v, uint32_t* t
 
 __global__ void __launch_bounds__(kScanThreads)
 k_scan_block_sums(const uint32_t* __restrict__ in, const uint32_t* __restrict__ gather,
-                  const int4* __restrict__ rect, int64_t n, uint32_t* __restrict__ bsum,
-                  uint32_t* __restrict__ values_out) {
+                  const int4* __restrict__ rect, int64_t n, const int32_t* __restrict__ n_dev,
+                  uint32_t* __restrict__ bsum, uint32_t* __restrict__ values_out) {
   __shared__ uint32_t sm[kScanThreads / 32 + 1];
   int64_t base = (int64_t)blockIdx.x * kScanTile;
+  const int64_t nv = valid_items(n, n_dev);
   uint32_t s = 0;
 #pragma unroll
   for (int k = 0; k < kScanItems; ++k) {
     int64_t i = base + k * kScanThreads + threadIdx.x;
     if (i < n) {
-      const uint32_t v = scan_value(in, gather, rect, i);
+      const uint32_t v = i < nv ? scan_value(in, gather, rect, i) : 0u;
       if (values_out) values_out[i] = v;  // gathered once: the apply pass reads these in place
       s += v;
     }
@@ -143,6 +148,53 @@ k_scan_apply(const uint32_t* in, const uint32_t* __restrict__ gather, const int4
 }
 
 // ---------------------------------------------------------------------------
+// Stable compaction of the (key, value) pairs whose key is not 0xFFFFFFFF (the visible tets) to the
+// front of the output arrays: block counts -> k_scan_sums -> scatter with the block's own scan.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kScanThreads)
+k_compact_count(const uint32_t* __restrict__ keys, int64_t n, uint32_t* __restrict__ bsum) {
+  __shared__ uint32_t sm[kScanThreads / 32 + 1];
+  const int64_t base = (int64_t)blockIdx.x * kScanTile + (int64_t)threadIdx.x * kScanItems;
+  uint32_t s = 0;
+#pragma unroll
+  for (int k = 0; k < kScanItems; ++k) {
+    const int64_t i = base + k;
+    s += (i < n && keys[i] != 0xFFFFFFFFu) ? 1u : 0u;
+  }
+  uint32_t total;
+  block_exclusive_scan<kScanThreads>(s, &total, sm);
+  if (threadIdx.x == 0) bsum[blockIdx.x] = total;
+}
+
+__global__ void __launch_bounds__(kScanThreads)
+k_compact_scatter(const uint32_t* __restrict__ keys, const uint32_t* __restrict__ vals, int64_t n,
+                  const uint32_t* __restrict__ bsum, uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out) {
+  __shared__ uint32_t sm[kScanThreads / 32 + 1];
+  // blocked arrangement (thread t owns kScanItems consecutive items), so that the order is kept
+  const int64_t base = (int64_t)blockIdx.x * kScanTile + (int64_t)threadIdx.x * kScanItems;
+  uint32_t key[kScanItems];
+  uint32_t s = 0;
+#pragma unroll
+  for (int k = 0; k < kScanItems; ++k) {
+    const int64_t i = base + k;
+    key[k] = i < n ? keys[i] : 0xFFFFFFFFu;
+    s += key[k] != 0xFFFFFFFFu ? 1u : 0u;
+  }
+  uint32_t total;
+  uint32_t pos = block_exclusive_scan<kScanThreads>(s, &total, sm) + bsum[blockIdx.x];
+#pragma unroll
+  for (int k = 0; k < kScanItems; ++k) {
+    if (key[k] != 0xFFFFFFFFu) {
+      if (RM_INDEX_OK(pos, RM_X_TETS, 13)) {
+        keys_out[pos] = key[k];
+        vals_out[pos] = vals[base + k];
+      }
+      ++pos;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // LSD radix sort of (uint32 key, uint32 value) pairs, 8 bits per pass, stable.
 // Per pass: block histograms -> per-digit row scan -> stable scatter.
 // ---------------------------------------------------------------------------
@@ -155,8 +207,10 @@ constexpr int kSortWarps = kSortThreads / 32;
 constexpr int kWarpSpan = 32 * kSortItems;  // consecutive keys owned by one warp
 
 __global__ void __launch_bounds__(kSortThreads)
-k_radix_hist(const uint32_t* __restrict__ keys, int64_t n, int shift, uint32_t* __restrict__ hist, int nblk) {
+k_radix_hist(const uint32_t* __restrict__ keys, int64_t n_max, const int32_t* __restrict__ n_dev, int shift,
+             uint32_t* __restrict__ hist, int nblk) {
   __shared__ uint32_t h[kRadix];
+  const int64_t n = valid_items(n_max, n_dev);
   for (int i = threadIdx.x; i < kRadix; i += kSortThreads) h[i] = 0;
   __syncthreads();
   int64_t base = (int64_t)blockIdx.x * kSortTile;
@@ -192,9 +246,11 @@ __device__ __forceinline__ void local_layout(uint32_t bins, uint32_t* cnt, uint3
 // Stable scatter of one pass.  The block's pairs are first reordered by digit in shared
 // memory, so that the global stores of one digit's run are contiguous.
 __global__ void __launch_bounds__(kSortThreads, 3)
-k_radix_scatter(const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in, int64_t n, int shift,
-                const uint32_t* __restrict__ hist, const uint32_t* __restrict__ digit_total, int nblk,
-                uint32_t* __restrict__ keys_out, uint32_t* __restrict__ vals_out) {
+k_radix_scatter(const uint32_t* __restrict__ keys_in, const uint32_t* __restrict__ vals_in, int64_t n_max,
+                const int32_t* __restrict__ n_dev, int shift, const uint32_t* __restrict__ hist,
+                const uint32_t* __restrict__ digit_total, int nblk, uint32_t* __restrict__ keys_out,
+                uint32_t* __restrict__ vals_out) {
+  const int64_t n = valid_items(n_max, n_dev);
   __shared__ uint2 sbuf[kSortTile];
   __shared__ uint32_t cnt[kSortWarps * kRadix];  // per-warp digit counts -> offsets
   __shared__ uint32_t dbase[kRadix];
@@ -861,8 +917,10 @@ int rm_launch_bin_prepare(int64_t T, const RmCamera* cam, void* ws, size_t ws_by
   BinLayout L = make_layout(T, G, gh, gw);
   if (L.total > ws_bytes) return RM_ERR_WORKSPACE;
   char* b = static_cast<char*>(ws);
-  *depth_keys = reinterpret_cast<uint32_t*>(b + L.keys_a);
-  *order_in = reinterpret_cast<uint32_t*>(b + L.ord_a);
+  // a band-restricted frame compacts the visible tets from buffer b to buffer a before ranking them
+  const bool banded = cam->tile_row_begin > 0 || cam->tile_row_end < gh;
+  *depth_keys = reinterpret_cast<uint32_t*>(b + (banded ? L.keys_b : L.keys_a));
+  *order_in = reinterpret_cast<uint32_t*>(b + (banded ? L.ord_b : L.ord_a));
   *tile_diff = reinterpret_cast<int32_t*>(b + L.tile_diff);
   RM_CUDA_CHECK(cudaMemsetAsync(b + L.tile_diff, 0, 4 * (size_t)(gh + 1) * (gw + 1), st));
   RM_CUDA_CHECK(cudaMemsetAsync(b + L.cursor, 0, 4 * (size_t)(G + 1), st));
@@ -870,8 +928,8 @@ int rm_launch_bin_prepare(int64_t T, const RmCamera* cam, void* ws, size_t ws_by
   return RM_OK;
 }
 
-static int launch_scan(const uint32_t* in, const uint32_t* gather, const int4* rect, int64_t n, uint32_t* bsum,
-                       uint32_t* out, int inclusive, unsigned long long* total64, cudaStream_t st) {
+static int launch_scan(const uint32_t* in, const uint32_t* gather, const int4* rect, int64_t n, const int32_t* n_dev,
+                       uint32_t* bsum, uint32_t* out, int inclusive, unsigned long long* total64, cudaStream_t st) {
   if (n <= 0) {
     if (total64) RM_CUDA_CHECK(cudaMemsetAsync(total64, 0, 8, st));
     return RM_OK;
@@ -879,7 +937,8 @@ static int launch_scan(const uint32_t* in, const uint32_t* gather, const int4* r
   int64_t nb = (n + rm::kScanTile - 1) / rm::kScanTile;
   // with a gather the values are fetched once, left in `out`, and scanned there in place
   const bool stash = gather != nullptr;
-  rm_count_launch(), rm::k_scan_block_sums<<<(unsigned)nb, rm::kScanThreads, 0, st>>>(in, gather, rect, n, bsum, stash ? out : nullptr);
+  rm_count_launch(), rm::k_scan_block_sums<<<(unsigned)nb, rm::kScanThreads, 0, st>>>(in, gather, rect, n, n_dev, bsum,
+                                                                                       stash ? out : nullptr);
   rm_count_launch(), rm::k_scan_sums<<<1, 1024, 0, st>>>(bsum, nb, total64);
   if (stash) rm_count_launch(), rm::k_scan_apply<<<(unsigned)nb, rm::kScanThreads, 0, st>>>(out, nullptr, nullptr, n, bsum, out, inclusive);
   else rm_count_launch(), rm::k_scan_apply<<<(unsigned)nb, rm::kScanThreads, 0, st>>>(in, gather, rect, n, bsum, out, inclusive);
@@ -908,16 +967,31 @@ int rm_launch_bin_finish(int64_t T, const RmCamera* cam, const int32_t* rect, in
 
   rm_set_extent(RM_X_TETS, T, st);
   rm_set_extent(RM_X_TILES, G, st);
-  // 1. rank tets by (depth bits, id): 4 stable passes; result ends in buffer 0
+  // 1. rank the tets by (depth bits, id): four stable radix passes that start and end in buffer 0; culled
+  //    tets carry key 0xFFFFFFFF and sort last.  A band-restricted frame sees a fraction of the tets, and
+  //    every rank of a band-split job would still sort all T of them: there k_project left its pairs in
+  //    buffer 1, a stable compaction moves the visible ones to the front of buffer 0, and the passes run over
+  //    those only (their number is known on the device: info->n_visible).  Ranks past the visible tets then
+  //    hold nothing that later stages read.
   if (T > 0) {
-    RmProfScope prof("rank_tets_radix_sort(12 launches)", st);
+    RmProfScope prof("rank_tets_radix_sort", st);
+    const bool banded = cam->tile_row_begin > 0 || cam->tile_row_end < gh;
+    const int32_t* n_sort = banded ? &info->n_visible : nullptr;
+    if (banded) {
+      const int64_t nbc = (T + rm::kScanTile - 1) / rm::kScanTile;
+      rm_count_launch(), rm::k_compact_count<<<(unsigned)nbc, rm::kScanThreads, 0, st>>>(keys[1], T, bsum);
+      rm_count_launch(), rm::k_scan_sums<<<1, 1024, 0, st>>>(bsum, nbc, nullptr);
+      rm_count_launch(), rm::k_compact_scatter<<<(unsigned)nbc, rm::kScanThreads, 0, st>>>(keys[1], ord[1], T, bsum, keys[0],
+                                                                                   ord[0]);
+    }
     for (int pass = 0; pass < 4; ++pass) {
       int src = pass & 1, dst = src ^ 1;
       int shift = pass * rm::kRadixBits;
-      rm_count_launch(), rm::k_radix_hist<<<L.nblk_sort, rm::kSortThreads, 0, st>>>(keys[src], T, shift, hist, L.nblk_sort);
+      rm_count_launch(), rm::k_radix_hist<<<L.nblk_sort, rm::kSortThreads, 0, st>>>(keys[src], T, n_sort, shift, hist,
+                                                                              L.nblk_sort);
       rm_count_launch(), rm::k_radix_rowscan<<<rm::kRadix, 1024, 0, st>>>(hist, L.nblk_sort, dtot);
-      rm_count_launch(), rm::k_radix_scatter<<<L.nblk_sort, rm::kSortThreads, 0, st>>>(keys[src], ord[src], T, shift, hist, dtot,
-                                                                   L.nblk_sort, keys[dst], ord[dst]);
+      rm_count_launch(), rm::k_radix_scatter<<<L.nblk_sort, rm::kSortThreads, 0, st>>>(
+          keys[src], ord[src], T, n_sort, shift, hist, dtot, L.nblk_sort, keys[dst], ord[dst]);
     }
     RM_CUDA_CHECK(cudaPeekAtLastError());
   }
@@ -928,7 +1002,7 @@ int rm_launch_bin_finish(int64_t T, const RmCamera* cam, const int32_t* rect, in
     rm_count_launch(), rm::k_diff_prefix_x<<<(gh + 1 + rows_per_block - 1) / rows_per_block, 32 * rows_per_block, 0, st>>>(diff, gh, gw);
     rm_count_launch(), rm::k_diff_prefix_y<<<(gw + rows_per_block - 1) / rows_per_block, 32 * rows_per_block, 0, st>>>(diff, gh, gw,
                                                                                                   tcount);
-    int rc = launch_scan(tcount, nullptr, nullptr, G, bsum, tstart, 0, total_keys, st);
+    int rc = launch_scan(tcount, nullptr, nullptr, G, nullptr, bsum, tstart, 0, total_keys, st);
     if (rc) return rc;
     rm_count_launch(), rm::k_write_ranges<<<(unsigned)((G + 255) / 256), 256, 0, st>>>(tcount, tstart, G,
                                                                     reinterpret_cast<int2*>(tile_ranges));
@@ -938,7 +1012,8 @@ int rm_launch_bin_finish(int64_t T, const RmCamera* cam, const int32_t* rect, in
   //    have an empty rectangle and sort last)
   {
     RmProfScope prof("rank_order_scan(4 launches)", st);
-    int rc = launch_scan(nullptr, ord[0], reinterpret_cast<const int4*>(rect), T, bsum, cum, 1, total_keys + 1, st);
+    int rc = launch_scan(nullptr, ord[0], reinterpret_cast<const int4*>(rect), T, &info->n_visible, bsum, cum, 1,
+                         total_keys + 1, st);
     if (rc) return rc;
     rm_count_launch(), rm::k_finish_info<<<1, 1, 0, st>>>(info, total_keys);
     RM_CUDA_CHECK(cudaPeekAtLastError());

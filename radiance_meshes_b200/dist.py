@@ -148,6 +148,23 @@ def row_weights_from_rects(rect_tile_space, tiles_touched, grid_height):
     return torch.cumsum(diff, 0)[:grid_height]
 
 
+def row_weights_from_walk(n_contributors, rect_tile_space, tiles_touched, grid_height, tile_height, walk_share=0.75):
+    """Work per tile row for balancing bands, from the previous frame of a sequence: the list entries its
+    pixels walked (n_contributors[H,W], what the integration kernel's time follows) blended with the row's
+    (tile, tet) pairs (what the list build's time follows).  `walk_share` is the integration kernel's share of
+    a frame's time.  Every rank computes the same weights from the same tensors."""
+    nc = n_contributors.reshape(n_contributors.shape[0], -1).to(torch.float64).sum(1)
+    H = nc.shape[0]
+    pad = grid_height * tile_height - H
+    if pad > 0:
+        nc = torch.cat([nc, torch.zeros(pad, dtype=nc.dtype, device=nc.device)])
+    walk = nc.reshape(grid_height, tile_height).sum(1)
+    pairs = row_weights_from_rects(rect_tile_space, tiles_touched, grid_height).to(torch.float64)
+    walk = walk / walk.sum().clamp_min(1.0)
+    pairs = pairs / pairs.sum().clamp_min(1.0)
+    return walk_share * walk + (1.0 - walk_share) * pairs
+
+
 def combine_band_images(local_image, band, tile_height, group=None, bands=None):
     """Full image from per-rank band images.
 
