@@ -1,10 +1,10 @@
 """Constant-colour debug renderer, drop-in for the reference module of the same name
-(delaunay_rasterization/internal/alphablend_tiled_slang.py:16-192), forward only.
+(delaunay_rasterization/internal/alphablend_tiled_slang.py:16-192).
 
 `render_constant_color` is what utils/train_util.py:164-186 (`render_debug`) calls to turn
-a per-tet scalar or colour into an image.  The reference also differentiates this renderer
-(its `AlphaBlendTiledRender.backward`); nothing in its training or evaluation code asks for
-those gradients, and the backward pass is not built here: requesting it raises.
+a per-tet scalar or colour into an image.  `AlphaBlendTiledRender` is differentiable in the
+vertices and in rgbs, with the reference's formulation of the backward pass
+(slang/alphablend_shader.slang:186-277).
 """
 import torch
 
@@ -41,14 +41,38 @@ class AlphaBlendTiledRender(torch.autograd.Function):
                 raster._ptr(sorted_tetra_idx), raster._ptr(tile_ranges), raster._ptr(records), cam.ref,
                 float(pre_multi), float(ladder_p), raster._ptr(output_img), raster._ptr(distortion_img),
                 raster._ptr(n_contributors), raster._stream(dev)))
-        ctx.n_contributors = n_contributors
+        ctx.save_for_backward(sorted_tetra_idx, tile_ranges, indices, vertices.detach().contiguous().float(), cell,
+                              records, output_img, distortion_img, n_contributors)
+        ctx.cam = cam
+        ctx.scalars = (float(pre_multi), float(ladder_p))
         return output_img, distortion_img
 
     @staticmethod
     def backward(ctx, grad_output_img, grad_distortion_img):
-        raise NotImplementedError(
-            "rm_b200: the constant-colour debug renderer is forward-only; render under torch.no_grad() "
-            "(the differentiable path is alphablend_tiled_slang_interp.AlphaBlendTiledRender)")
+        (sorted_tetra_idx, tile_ranges, indices, verts, cell, records, output_img, distortion_img,
+         n_contributors) = ctx.saved_tensors
+        dev = verts.device
+        T, V = indices.shape[0], verts.shape[0]
+        pre_multi, ladder_p = ctx.scalars
+        lib = _lib.load()
+        idx32 = indices.contiguous().to(torch.int32)
+        g_img = grad_output_img.contiguous().float()
+        g_dist = grad_distortion_img.contiguous().float()
+        with torch.cuda.device(dev):
+            grad_records = torch.empty((T, _lib.RM_GRAD_RECORD_FLOATS), dtype=torch.float32, device=dev)
+            flags = torch.empty((max(T, 1),), dtype=torch.uint8, device=dev)
+            vertices_grad = torch.empty((V, 3), dtype=torch.float32, device=dev)
+            cell_grad = torch.empty((T, 7), dtype=torch.float32, device=dev)
+            if _lib.bounds_checked():
+                _lib.set_extents(list=sorted_tetra_idx.shape[0], tets=T, verts=V)
+            _lib.check(lib.rm_backward_constant_color(
+                raster._ptr(sorted_tetra_idx), raster._ptr(tile_ranges), raster._ptr(records), ctx.cam.ref, pre_multi,
+                ladder_p, raster._ptr(output_img), raster._ptr(distortion_img), raster._ptr(n_contributors),
+                raster._ptr(g_img), raster._ptr(g_dist), raster._ptr(idx32), raster._ptr(verts), raster._ptr(cell), T, V,
+                raster._ptr(grad_records), raster._ptr(flags), raster._ptr(vertices_grad), raster._ptr(cell_grad),
+                raster._stream(dev)))
+        rgbs_grad = torch.cat([cell_grad[:, 1:4], cell_grad[:, 0:1]], dim=1)
+        return None, None, None, vertices_grad, rgbs_grad, None, None, None, None
 
 
 def render_constant_color(indices, vertices, rgbs_fn, camera, cell_values=None, tile_size=16, min_t=0.1):
@@ -65,9 +89,8 @@ def render_constant_color(indices, vertices, rgbs_fn, camera, cell_values=None, 
     sorted_tetra_idx, tile_ranges, vs_tetra, circumcenter, mask, _ = vertex_and_tile_shader(
         indices, vertices, tcam, render_grid)
     rgbs = cell_values
-    with torch.no_grad():
-        image_rgb, distortion_img = AlphaBlendTiledRender.apply(
-            sorted_tetra_idx, tile_ranges, indices, vertices, rgbs, render_grid, tcam, 100, -0.1)
+    image_rgb, distortion_img = AlphaBlendTiledRender.apply(
+        sorted_tetra_idx, tile_ranges, indices, vertices, rgbs, render_grid, tcam, 100, -0.1)
     return {
         "render": image_rgb.permute(2, 0, 1)[:3, ...],
         "viewspace_points": vs_tetra,

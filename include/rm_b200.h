@@ -176,6 +176,23 @@ int rm_forward_constant_color(const int32_t* sorted_tetra_idx, const int32_t* ti
                               float* distortion_img, int32_t* n_contributors, void* stream);
 
 /*
+ * Backward pass of the constant-colour debug renderer.  Replaces splat_tiled.bwd / bwd_alpha_blend of
+ * slang/alphablend_shader.slang:186-277 (host side alphablend_tiled_slang.py:131-192), with the reference's
+ * formulation: pairs with alpha < 1/255 skipped, the state in front of a tet recovered by undoing the update.
+ *   records and cell_values: as passed to rm_forward_constant_color (cell values (density, r, g, b, 0, 0, 0));
+ *   output_img, distortion_img, n_contributors: what that call wrote; grad_distortion_img[H,W,4];
+ *   grad_records[T, RM_GRAD_RECORD_FLOATS] and tet_flags[T] are caller-provided scratch (filled here);
+ *   vertices_grad[V,3] and cell_values_grad[T,7] = gradients of (density, r, g, b, -, -, -) are fully written.
+ */
+int rm_backward_constant_color(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, const float* records,
+                               const RmCamera* cam, float pre_multi, float ladder_p, const float* output_img,
+                               const float* distortion_img, const int32_t* n_contributors,
+                               const float* grad_output_img, const float* grad_distortion_img, const int32_t* indices,
+                               const float* vertices, const float* cell_values, int64_t n_tets, int64_t n_vertices,
+                               float* grad_records, uint8_t* tet_flags, float* vertices_grad, float* cell_values_grad,
+                               void* stream);
+
+/*
  * Backward integration.  Replaces splat_tiled.bwd / bwd_alpha_blend
  * (slang/alphablend_shader_interp.slang:273-369, host side
  * alphablend_tiled_slang_interp.py:70-112).

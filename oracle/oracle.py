@@ -155,6 +155,47 @@ def forward_constant_color(sorted_idx, tile_ranges, indices, vertices, rgbs, tca
     return out, dist, nc
 
 
+def _cc_args(dtype, sorted_idx, tile_ranges, indices, vertices, rgbs):
+    return (np.ascontiguousarray(_np(sorted_idx), np.int32), np.ascontiguousarray(_np(tile_ranges), np.int32),
+            np.ascontiguousarray(_np(indices), np.int32), np.ascontiguousarray(_np(vertices), dtype),
+            np.ascontiguousarray(_np(rgbs), dtype))
+
+
+def forward_constant_color_f64(sorted_idx, tile_ranges, indices, vertices, rgbs, tcam, pre_multi=100.0, ladder_p=-0.1):
+    """The same forward pass in float64 (for finite-difference checks of the backward pass)."""
+    sorted_idx, tile_ranges, indices, vertices, rgbs = _cc_args(np.float64, sorted_idx, tile_ranges, indices, vertices,
+                                                                rgbs)
+    cam = make_camera(tcam)
+    H, W = cam.image_height, cam.image_width
+    out, dist, nc = np.zeros((H, W, 4)), np.zeros((H, W, 4)), np.zeros((H, W), np.int32)
+    rc = lib().or_forward_constant_color_f64(_p(sorted_idx), _p(tile_ranges), _p(indices), _p(vertices), _p(rgbs),
+                                             C.byref(cam), C.c_double(pre_multi), C.c_double(ladder_p), _p(out),
+                                             _p(dist), _p(nc), C.c_int(0))
+    assert rc == 0
+    return out, dist, nc
+
+
+def backward_constant_color(sorted_idx, tile_ranges, indices, vertices, rgbs, tcam, out_img, dist_img, n_contrib,
+                            g_img, g_dist, pre_multi=100.0, ladder_p=-0.1, dtype=np.float32, nthreads=0,
+                            min_alpha=1.0 / 255.0):
+    """Backward of the constant-colour renderer as the reference runs it (slang/alphablend_shader.slang:186-277).
+    Returns (vertices_grad[V,3], rgbs_grad[T,4])."""
+    sorted_idx, tile_ranges, indices, vertices, rgbs = _cc_args(dtype, sorted_idx, tile_ranges, indices, vertices, rgbs)
+    cam = make_camera(tcam)
+    arrs = [np.ascontiguousarray(_np(a), dtype) for a in (out_img, dist_img, g_img, g_dist)]
+    nc = np.ascontiguousarray(_np(n_contrib), np.int32)
+    vg, rg = np.zeros_like(vertices), np.zeros_like(rgbs)
+    if dtype == np.float32:
+        fn, ft = lib().or_backward_constant_color, C.c_float
+    else:
+        fn, ft = lib().or_backward_constant_color_f64, C.c_double
+    rc = fn(_p(sorted_idx), _p(tile_ranges), _p(indices), _p(vertices), _p(rgbs), C.byref(cam), ft(pre_multi),
+            ft(ladder_p), _p(arrs[0]), _p(arrs[1]), _p(nc), _p(arrs[2]), _p(arrs[3]), _p(vg), _p(rg), ft(min_alpha),
+            C.c_int(nthreads))
+    assert rc == 0
+    return vg, rg
+
+
 def backward(sorted_idx, tile_ranges, indices, vertices, cell_values, tcam, jitter, out_img, dist_img, n_contrib,
              g_img, g_dist, rows=None, nthreads=0, dtype=np.float32):
     """Stage 6. Returns (vertices_grad[V,3], cell_values_grad[T,7])."""

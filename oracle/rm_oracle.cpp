@@ -901,16 +901,49 @@ int or_backward_f64(const int32_t* sorted_idx, const int32_t* tile_ranges, const
 // alpha 0 and an unwritten distance; its weight is 0).  out_img = (r, g, b,
 // transmittance), dist_img has 4 channels.
 // ---------------------------------------------------------------------------
-static inline float tukey_power_ladder(float x, float p) {
-  float xp = std::fabs(x);
-  float xs = xp / std::fmax(1.0754944e-20f, std::fabs(p - 1.0f));
-  float sgn = x > 0.0f ? 1.0f : (x < 0.0f ? -1.0f : 0.0f);
-  return sgn * std::fabs(p - 1.0f) / p * (std::pow(xs + 1.0f, p) - 1.0f);
+extern "C++" {
+template <class F>
+static inline F tukey_power_ladder(F x, F p) {
+  F xp = std::fabs(x);
+  F xs = xp / std::fmax(F(1.0754944e-20f), std::fabs(p - F(1)));
+  F sgn = x > F(0) ? F(1) : (x < F(0) ? F(-1) : F(0));
+  return sgn * std::fabs(p - F(1)) / p * (std::pow(xs + F(1), p) - F(1));
 }
-int or_forward_constant_color(const int32_t* sorted_idx, const int32_t* tile_ranges, const int32_t* indices,
-                              const float* vertices, const float* rgbs, const OrCamera* ocam, float pre_multi,
-                              float ladder_p, float* out_img, float* dist_img, int32_t* n_contrib, int nthreads) {
-  Cam<float> cam = load_cam<float>(ocam);
+// d ladder / dx = (|x|/|p-1| + 1)^(p-1)  (the sign factors cancel; 0 at x = 0 as sign(0) = 0 there)
+template <class F>
+static inline F tukey_power_ladder_dx(F x, F p) {
+  if (x == F(0)) return F(0);
+  F q = std::fmax(F(1.0754944e-20f), std::fabs(p - F(1)));
+  return std::fabs(p - F(1)) / q * std::pow(std::fabs(x) / q + F(1), p - F(1));
+}
+
+// What evaluate_tetra (slang/utils.slang:160-186) returns for one (ray, tet) pair of the constant-colour renderer.
+template <class F>
+struct CtrlCC {
+  bool hit;
+  F alpha, enter, dt, te, tx;
+  int ie, ix;
+  Planes<F> pl;
+  V3<F> v[4];
+};
+template <class F>
+inline void evaluate_cc(int64_t id, const int32_t* indices, const F* vertices, const F* rgbs, V3<F> o, V3<F> d,
+                        CtrlCC<F>& c) {
+  for (int k = 0; k < 4; ++k) c.v[k] = load_v(vertices, indices[4 * id + k]);
+  make_planes(c.v, o, c.pl);
+  c.hit = intersect(c.pl, d, c.te, c.tx, c.ie, c.ix);
+  c.alpha = F(0);
+  if (!c.hit) return;
+  c.enter = std::fmax(c.te, F(0));
+  c.dt = std::fmax(std::fabs(c.tx - c.enter), F(0));
+  c.alpha = safe_clip(F(1) - safe_exp(-rgbs[4 * id + 3] * c.dt), F(0), F(1));
+}
+
+template <class F>
+int forward_cc_impl(const int32_t* sorted_idx, const int32_t* tile_ranges, const int32_t* indices, const F* vertices,
+                    const F* rgbs, const OrCamera* ocam, F pre_multi, F ladder_p, F* out_img, F* dist_img,
+                    int32_t* n_contrib, int nthreads) {
+  Cam<F> cam = load_cam<F>(ocam);
   const int H = cam.H, W = cam.Wd;
 #ifdef _OPENMP
   if (nthreads > 0) omp_set_num_threads(nthreads);
@@ -920,41 +953,181 @@ int or_forward_constant_color(const int32_t* sorted_idx, const int32_t* tile_ran
     int y = int(p / W), x = int(p % W);
     int tile = (y / cam.tile_h) * cam.grid_w + (x / cam.tile_w);
     int64_t s0 = tile_ranges[2 * tile], s1 = tile_ranges[2 * tile + 1];
-    V3<float> o, d;
-    get_ray(cam, float(x) + 0.5f, float(y) + 0.5f, o, d);
-    float r = 0.f, g = 0.f, b = 0.f, T = 1.f;
-    float dx = 0.f, dy = 0.f, dz = 0.f, dw = 0.f;
+    V3<F> o, d;
+    get_ray(cam, F(x) + F(0.5), F(y) + F(0.5), o, d);
+    F r = 0, g = 0, b = 0, T = 1;
+    F dx = 0, dy = 0, dz = 0, dw = 0;
     int contrib = 0;
     for (int64_t j = s0; j < s1; ++j) {
       ++contrib;
       const int64_t id = sorted_idx[j];
-      V3<float> v[4];
-      for (int k = 0; k < 4; ++k) v[k] = load_v(vertices, indices[4 * id + k]);
-      Planes<float> pl;
-      make_planes(v, o, pl);
-      float te, tx;
-      int ie, ix;
-      if (!intersect(pl, d, te, tx, ie, ix)) continue;
-      const float enter = std::fmax(te, 0.0f);
-      const float dt = std::fmax(std::fabs(tx - enter), 0.0f);
-      const float alpha = safe_clip(1.0f - safe_exp(-rgbs[4 * id + 3] * dt), 0.0f, 1.0f);
-      const float weight = T * alpha;
-      const float m = tukey_power_ladder(enter * pre_multi, ladder_p);
-      dx = dx + 2.0f * weight * m * dz;
-      dy = dy + 2.0f * weight * dw;
+      CtrlCC<F> c;
+      evaluate_cc(id, indices, vertices, rgbs, o, d, c);
+      if (!c.hit) continue;
+      const F weight = T * c.alpha;
+      const F m = tukey_power_ladder(c.enter * pre_multi, ladder_p);
+      dx = dx + F(2) * weight * m * dz;
+      dy = dy + F(2) * weight * dw;
       dz = dz + weight;
       dw = dw + weight * m;
-      r += alpha * rgbs[4 * id + 0] * T;
-      g += alpha * rgbs[4 * id + 1] * T;
-      b += alpha * rgbs[4 * id + 2] * T;
-      T = T * (1.0f - alpha);
-      if (T < 1.0f / 255.0f) break;
+      r += c.alpha * rgbs[4 * id + 0] * T;
+      g += c.alpha * rgbs[4 * id + 1] * T;
+      b += c.alpha * rgbs[4 * id + 2] * T;
+      T = T * (F(1) - c.alpha);
+      if (T < F(1) / F(255)) break;
     }
     out_img[4 * p + 0] = r; out_img[4 * p + 1] = g; out_img[4 * p + 2] = b; out_img[4 * p + 3] = T;
     dist_img[4 * p + 0] = dx; dist_img[4 * p + 1] = dy; dist_img[4 * p + 2] = dz; dist_img[4 * p + 3] = dw;
     n_contrib[p] = contrib;
   }
   return 0;
+}
+
+// Backward of the constant-colour renderer as the reference runs it (slang/alphablend_shader.slang:186-277,
+// host side alphablend_tiled_slang.py:131-192), quirks included:
+//   * entries whose alpha is below 1/255 are skipped here although the forward pass blended them (:246);
+//   * the state before a tet is recovered by undoing the update: transmittance by a division, replaced by 1
+//     when 1 - alpha < 1e-3 (:63-75); the distortion state with the weight (transmittance AFTER the tet) * alpha
+//     (:97-103), not the weight the forward pass used;
+//   * the derivatives are then those of update_alpha_out and evaluate_tetra at that recovered state.
+// With min_alpha = 0 (nothing skipped), alphas away from 1 and no upstream gradient on the distortion image this is
+// the true gradient of the forward pass, which the tests check by finite differences in float64; with the
+// reference's 1/255 the skipped pairs lose their (not small) vertex-gradient terms, as in the reference.
+template <class F>
+int backward_cc_impl(const int32_t* sorted_idx, const int32_t* tile_ranges, const int32_t* indices, const F* vertices,
+                     const F* rgbs, const OrCamera* ocam, F pre_multi, F ladder_p, const F* out_img,
+                     const F* dist_img, const int32_t* n_contrib, const F* g_img, const F* g_dist, F* vgrad,
+                     F* rgbs_grad, F min_alpha, int nthreads) {
+  Cam<F> cam = load_cam<F>(ocam);
+  const int H = cam.H, W = cam.Wd;
+#ifdef _OPENMP
+  if (nthreads > 0) omp_set_num_threads(nthreads);
+#endif
+#pragma omp parallel for schedule(dynamic, 16)
+  for (int64_t p = 0; p < (int64_t)H * W; ++p) {
+    int y = int(p / W), x = int(p % W);
+    int tile = (y / cam.tile_h) * cam.grid_w + (x / cam.tile_w);
+    int64_t s0 = tile_ranges[2 * tile], s1 = tile_ranges[2 * tile + 1];
+    V3<F> o, d;
+    get_ray(cam, F(x) + F(0.5), F(y) + F(0.5), o, d);
+    F r = out_img[4 * p], g = out_img[4 * p + 1], b = out_img[4 * p + 2], T = out_img[4 * p + 3];
+    F sx = dist_img[4 * p], sy = dist_img[4 * p + 1], sz = dist_img[4 * p + 2], sw = dist_img[4 * p + 3];
+    F dr = g_img[4 * p], dg = g_img[4 * p + 1], db = g_img[4 * p + 2], dT = g_img[4 * p + 3];
+    F ddx = g_dist[4 * p], ddy = g_dist[4 * p + 1], ddz = g_dist[4 * p + 2], ddw = g_dist[4 * p + 3];
+    const int nc = n_contrib[p];
+    for (int64_t j = s1 - 1; j >= s0; --j) {
+      if (j - s0 >= nc) continue;
+      const int64_t id = sorted_idx[j];
+      CtrlCC<F> c;
+      evaluate_cc(id, indices, vertices, rgbs, o, d, c);
+      if (!c.hit || c.alpha < min_alpha) continue;  // the reference: min_alpha = 1/255
+      const F a = c.alpha;
+      const V3<F> col = {rgbs[4 * id], rgbs[4 * id + 1], rgbs[4 * id + 2]};
+      const F m = tukey_power_ladder(c.enter * pre_multi, ladder_p);
+      // ---- undo_alpha_out
+      const F w_u = T * a;  // the transmittance AFTER the tet
+      const F T_prev = (F(1) - a < F(1e-3f)) ? F(1) : safe_div(T, F(1) - a);
+      r -= a * col.x * T_prev;
+      g -= a * col.y * T_prev;
+      b -= a * col.z * T_prev;
+      T = T_prev;
+      sz = sz - w_u;
+      sw = sw - w_u * m;
+      sx = sx - F(2) * w_u * m * sz;
+      sy = sy - F(2) * w_u * sw;
+      // ---- reverse of update_alpha_out at (recovered state, ctrl)
+      const F weight = T * a;
+      F g_crgb_x = dr * T, g_crgb_y = dg * T, g_crgb_z = db * T;  // wrt ctrl.rgb = alpha * colour
+      F g_Tprev = dr * a * col.x + dg * a * col.y + db * a * col.z + dT * (F(1) - a);
+      F g_a = -dT * T;
+      const F g_weight = ddx * F(2) * m * sz + ddy * F(2) * sw + ddz + ddw * m;
+      const F g_m = ddx * F(2) * weight * sz + ddw * weight;
+      const F ddz_prev = ddz + ddx * F(2) * weight * m;
+      const F ddw_prev = ddw + ddy * F(2) * weight;
+      g_Tprev += g_weight * a;
+      g_a += g_weight * T;
+      dT = g_Tprev;
+      ddz = ddz_prev;
+      ddw = ddw_prev;
+      F g_enter = g_m * tukey_power_ladder_dx(c.enter * pre_multi, ladder_p) * pre_multi;
+      // ---- reverse of evaluate_tetra: rgba = (alpha * colour, alpha), alpha = clip(1 - exp(-density * dt), 0, 1)
+      const F g_alpha = g_a + g_crgb_x * col.x + g_crgb_y * col.y + g_crgb_z * col.z;
+      const V3<F> g_col = {g_crgb_x * a, g_crgb_y * a, g_crgb_z * a};
+      const F dens = rgbs[4 * id + 3];
+      const F inner = F(1) - safe_exp(-dens * c.dt);
+      const F g_tau = (inner > F(0) && inner < F(1)) ? g_alpha * safe_exp(-dens * c.dt) : F(0);  // clip passes its interior
+      const F g_dens = g_tau * c.dt;
+      const F g_dt = g_tau * dens;
+      F g_tx = F(0);
+      if (c.tx - c.enter > F(0)) { g_tx += g_dt; g_enter -= g_dt; }
+      else if (c.tx - c.enter < F(0)) { g_tx -= g_dt; g_enter += g_dt; }
+      const F g_te = c.te > F(0) ? g_enter : F(0);
+      // ---- reverse of the plane intersection (as in the interpolating renderer)
+      V3<F> gv[4] = {{0, 0, 0}, {0, 0, 0}, {0, 0, 0}, {0, 0, 0}};
+      static const int fa[4][4] = {{0, 1, 2, 3}, {0, 1, 3, 2}, {0, 2, 3, 1}, {1, 2, 3, 0}};
+      for (int pass = 0; pass < 2; ++pass) {
+        int i = pass == 0 ? c.ie : c.ix;
+        F gt = pass == 0 ? g_te : g_tx;
+        if (i < 0 || gt == F(0)) continue;
+        F den = dot(c.pl.n[i], d);
+        F g_dist = -gt / den;
+        F g_den = gt * c.pl.d[i] / (den * den);
+        V3<F> bb = c.v[fa[i][0]];
+        V3<F> g_n = (bb - o) * (-g_dist) + d * g_den;
+        V3<F> g_b = c.pl.n[i] * (-g_dist);
+        V3<F> e1 = c.v[fa[i][1]] - bb, e2 = c.v[fa[i][2]] - bb;
+        V3<F> g_raw = g_n * F(c.pl.sgn[i]);
+        V3<F> g_e1 = cross(e2, g_raw);
+        V3<F> g_e2 = cross(g_raw, e1);
+        gv[fa[i][1]] = gv[fa[i][1]] + g_e1;
+        gv[fa[i][2]] = gv[fa[i][2]] + g_e2;
+        gv[fa[i][0]] = gv[fa[i][0]] + g_b - g_e1 - g_e2;
+      }
+      for (int k = 0; k < 4; ++k) {
+        int64_t vi = indices[4 * id + k];
+        atomic_add(&vgrad[3 * vi + 0], gv[k].x);
+        atomic_add(&vgrad[3 * vi + 1], gv[k].y);
+        atomic_add(&vgrad[3 * vi + 2], gv[k].z);
+      }
+      atomic_add(&rgbs_grad[4 * id + 0], g_col.x);
+      atomic_add(&rgbs_grad[4 * id + 1], g_col.y);
+      atomic_add(&rgbs_grad[4 * id + 2], g_col.z);
+      atomic_add(&rgbs_grad[4 * id + 3], g_dens);
+    }
+  }
+  return 0;
+}
+
+}  // extern "C++"
+
+int or_forward_constant_color(const int32_t* sorted_idx, const int32_t* tile_ranges, const int32_t* indices,
+                              const float* vertices, const float* rgbs, const OrCamera* ocam, float pre_multi,
+                              float ladder_p, float* out_img, float* dist_img, int32_t* n_contrib, int nthreads) {
+  return forward_cc_impl<float>(sorted_idx, tile_ranges, indices, vertices, rgbs, ocam, pre_multi, ladder_p, out_img,
+                                dist_img, n_contrib, nthreads);
+}
+int or_forward_constant_color_f64(const int32_t* sorted_idx, const int32_t* tile_ranges, const int32_t* indices,
+                                  const double* vertices, const double* rgbs, const OrCamera* ocam, double pre_multi,
+                                  double ladder_p, double* out_img, double* dist_img, int32_t* n_contrib,
+                                  int nthreads) {
+  return forward_cc_impl<double>(sorted_idx, tile_ranges, indices, vertices, rgbs, ocam, pre_multi, ladder_p, out_img,
+                                 dist_img, n_contrib, nthreads);
+}
+int or_backward_constant_color(const int32_t* sorted_idx, const int32_t* tile_ranges, const int32_t* indices,
+                               const float* vertices, const float* rgbs, const OrCamera* ocam, float pre_multi,
+                               float ladder_p, const float* out_img, const float* dist_img, const int32_t* n_contrib,
+                               const float* g_img, const float* g_dist, float* vgrad, float* rgbs_grad,
+                               float min_alpha, int nthreads) {
+  return backward_cc_impl<float>(sorted_idx, tile_ranges, indices, vertices, rgbs, ocam, pre_multi, ladder_p, out_img,
+                                 dist_img, n_contrib, g_img, g_dist, vgrad, rgbs_grad, min_alpha, nthreads);
+}
+int or_backward_constant_color_f64(const int32_t* sorted_idx, const int32_t* tile_ranges, const int32_t* indices,
+                                   const double* vertices, const double* rgbs, const OrCamera* ocam, double pre_multi,
+                                   double ladder_p, const double* out_img, const double* dist_img,
+                                   const int32_t* n_contrib, const double* g_img, const double* g_dist, double* vgrad,
+                                   double* rgbs_grad, double min_alpha, int nthreads) {
+  return backward_cc_impl<double>(sorted_idx, tile_ranges, indices, vertices, rgbs, ocam, pre_multi, ladder_p, out_img,
+                                  dist_img, n_contrib, g_img, g_dist, vgrad, rgbs_grad, min_alpha, nthreads);
 }
 
 // Pixels whose result is decided by floating-point rounding in the reference

@@ -32,6 +32,9 @@ int rm_launch_backward_finish(const int32_t*, const float*, const float*, int64_
 
 int rm_launch_tet_err(const int32_t*, const int32_t*, const float*, const RmCamera*, const float*, const float*,
                       int64_t, float*, int32_t*, cudaStream_t);
+int rm_launch_backward_constant_color(const int32_t*, const int32_t*, const float*, const RmCamera*, float, float,
+                                      const float*, const float*, const int32_t*, const float*, const float*, int64_t,
+                                      int64_t, float*, uint8_t*, float*, cudaStream_t);
 
 int rm_launch_activate(const float*, const float*, const float*, const float*, const void*, int, const int32_t*,
                        const float*, const float*, int64_t, int, int, float*, cudaStream_t);
@@ -293,6 +296,39 @@ static int check_backward_args(const int32_t* tile_ranges, const float* records,
       !rm_aligned16(grad_records))
     return RM_ERR_WORKSPACE;
   return RM_OK;
+}
+
+int rm_backward_constant_color(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, const float* records,
+                               const RmCamera* cam, float pre_multi, float ladder_p, const float* output_img,
+                               const float* distortion_img, const int32_t* n_contributors,
+                               const float* grad_output_img, const float* grad_distortion_img, const int32_t* indices,
+                               const float* vertices, const float* cell_values, int64_t n_tets, int64_t n_vertices,
+                               float* grad_records, uint8_t* tet_flags, float* vertices_grad, float* cell_values_grad,
+                               void* stream) {
+  g_last_error[0] = 0;
+  int rc = rm_check_cam(cam);
+  if (rc) return rc;
+  if (n_tets < 0 || n_vertices < 0 || ladder_p == 0.0f) return RM_ERR_INVALID_ARG;
+  if (!tile_ranges || !output_img || !distortion_img || !n_contributors || !grad_output_img || !grad_distortion_img ||
+      !vertices_grad)
+    return RM_ERR_INVALID_ARG;
+  if (n_tets > 0 && (!sorted_tetra_idx || !records || !indices || !vertices || !cell_values || !grad_records ||
+                     !tet_flags || !cell_values_grad))
+    return RM_ERR_INVALID_ARG;
+  if (!rm_aligned16(output_img) || !rm_aligned16(distortion_img) || !rm_aligned16(grad_output_img) ||
+      !rm_aligned16(grad_distortion_img) || !rm_aligned16(records) || !rm_aligned16(grad_records) ||
+      !rm_aligned16(indices))
+    return RM_ERR_WORKSPACE;
+  rc = rm_bind_device(vertices_grad);
+  if (rc) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  rc = rm_launch_backward_constant_color(sorted_tetra_idx, tile_ranges, records, cam, pre_multi, ladder_p, output_img,
+                                         distortion_img, n_contributors, grad_output_img, grad_distortion_img, n_tets,
+                                         n_vertices, grad_records, tet_flags, vertices_grad, st);
+  if (rc) return rc;
+  RmHitList flags_only = {nullptr, nullptr, nullptr, tet_flags};
+  return rm_launch_backward_finish(indices, vertices, cell_values, 0, n_tets, cam, grad_records, &flags_only,
+                                   vertices_grad, cell_values_grad, st);
 }
 
 int rm_backward_integrate(const int32_t* tile_ranges, const float* records, const RmCamera* cam,

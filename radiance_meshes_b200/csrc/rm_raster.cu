@@ -1143,6 +1143,104 @@ k_tet_err(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
   cp_async_wait<0>();
 }
 
+// ----------------------------------------------------------------------------
+// Backward of the constant-colour debug renderer, as the reference runs it
+// (slang/alphablend_shader.slang:186-277, host side alphablend_tiled_slang.py:131-192): every pixel
+// walks its tile list from its last contributor to the first; pairs with alpha < 1/255 are skipped
+// (although the forward pass blended them); the state before a tet is recovered by undoing the update
+// (transmittance by a division, replaced by 1 when 1 - alpha < 1e-3; distortion state with the weight
+// (transmittance after the tet) * alpha); the derivatives of update_alpha_out and evaluate_tetra are taken
+// at that recovered state.  A debug path: one lane per pixel, records read straight from global memory,
+// gradients added to the record-gradient rows with 128-bit reductions (the reference issues 16 scalar
+// atomics per hit); k_backward_finish then applies the chain rule to vertices and (r, g, b, density).
+// ----------------------------------------------------------------------------
+__device__ __forceinline__ float tukey_power_ladder_dx(float x, float p) {
+  if (x == 0.0f) return 0.0f;
+  const float q = fmaxf(fabsf(p - 1.0f), 1.0754944e-20f);
+  return fabsf(p - 1.0f) / q * __powf(fabsf(x) / q + 1.0f, p - 1.0f);
+}
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+k_backward_cc(const int32_t* __restrict__ list, const int2* __restrict__ ranges, const float4* __restrict__ records,
+              RmCamera rcam, const float4* __restrict__ out_img, const float4* __restrict__ dist_img,
+              const int32_t* __restrict__ n_contrib, const float4* __restrict__ g_img,
+              const float4* __restrict__ g_dist, float pre_multi, float ladder_p, float* __restrict__ grec, int subs,
+              int64_t n_units) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int half = lane >> 4, lane16 = lane & 15;
+  const int64_t unit = ((int64_t)blockIdx.x * kWarpsPerBlock + warp) * 2 + half;
+  Unit u = make_unit(rcam, ranges, unit, n_units, subs, lane16);
+  if (!u.inside) return;
+  const int64_t pix = (int64_t)u.y * rcam.image_width + u.x;
+  const f3 d = ray_direction(rcam, (float)u.x + 0.5f, (float)u.y + 0.5f);
+  const float min_t = rcam.min_t;
+  float4 st = __ldg(out_img + pix);   // r, g, b, transmittance
+  float4 ds = __ldg(dist_img + pix);  // distortion state x, y, z, w
+  float4 gi = __ldg(g_img + pix);
+  float4 gd = __ldg(g_dist + pix);
+  const int last = min(__ldg(n_contrib + pix), u.len);
+  for (int j = last - 1; j >= 0; --j) {
+    const int id = __ldg(list + u.start + j);
+    if (!RM_INDEX_OK(id, RM_X_TETS, 7)) continue;
+    const float4* rec = records + kRecStride * (int64_t)id;
+    const float4 pl[4] = {__ldg(rec), __ldg(rec + 1), __ldg(rec + 2), __ldg(rec + 3)};
+    Eval ev;
+    if (!slab_test<true>(pl, d, min_t, ev)) continue;
+    const float4 cb = __ldg(rec + 5);  // r, g, b, density
+    const float dens = cb.w;
+    const float ex = __expf(-dens * ev.dt);
+    const float a = fminf(fmaxf(1.0f - ex, 0.0f), 1.0f);
+    if (a < 1.0f / 255.0f) continue;
+    const float m = tukey_power_ladder(ev.enter * pre_multi, ladder_p);
+    // undo
+    const float w_u = st.w * a;
+    const float Tp = (1.0f - a < 1e-3f) ? 1.0f : st.w / (1.0f - a);
+    st.x -= a * cb.x * Tp;
+    st.y -= a * cb.y * Tp;
+    st.z -= a * cb.z * Tp;
+    st.w = Tp;
+    ds.z -= w_u;
+    ds.w -= w_u * m;
+    ds.x -= 2.0f * w_u * m * ds.z;
+    ds.y -= 2.0f * w_u * ds.w;
+    // reverse of the update at the recovered state
+    const float weight = Tp * a;
+    const float gcx = gi.x * Tp, gcy = gi.y * Tp, gcz = gi.z * Tp;
+    float g_T = a * (gi.x * cb.x + gi.y * cb.y + gi.z * cb.z) + gi.w * (1.0f - a);
+    float g_a = -gi.w * Tp;
+    const float g_weight = gd.x * 2.0f * m * ds.z + gd.y * 2.0f * ds.w + gd.z + gd.w * m;
+    const float g_m = gd.x * 2.0f * weight * ds.z + gd.w * weight;
+    gd.z = gd.z + gd.x * 2.0f * weight * m;
+    gd.w = gd.w + gd.y * 2.0f * weight;
+    g_T += g_weight * a;
+    g_a += g_weight * Tp;
+    gi.w = g_T;
+    float g_enter = g_m * tukey_power_ladder_dx(ev.enter * pre_multi, ladder_p) * pre_multi;
+    // reverse of evaluate_tetra
+    const float g_alpha = g_a + gcx * cb.x + gcy * cb.y + gcz * cb.z;
+    const float inner = 1.0f - ex;
+    const float g_tau = (inner > 0.0f && inner < 1.0f) ? g_alpha * ex : 0.0f;
+    const float g_dt = g_tau * dens;
+    float g_tx = 0.0f;
+    if (ev.tx - ev.enter > 0.0f) { g_tx = g_dt; g_enter -= g_dt; }
+    const float g_te = ev.te > 0.0f ? g_enter : 0.0f;
+    float4* row = reinterpret_cast<float4*>(grec + (int64_t)id * 24);
+    if (g_te != 0.0f && ev.ie >= 0) {
+      const float4 p = pl[ev.ie];
+      const float r = __fdividef(1.0f, p.x * d.x + p.y * d.y + p.z * d.z);
+      const float kn = g_te * p.w * r * r;
+      atomicAdd(row + ev.ie, make_float4(kn * d.x, kn * d.y, kn * d.z, -g_te * r));
+    }
+    if (g_tx != 0.0f && ev.ix >= 0) {
+      const float4 p = pl[ev.ix];
+      const float r = __fdividef(1.0f, p.x * d.x + p.y * d.y + p.z * d.z);
+      const float kn = g_tx * p.w * r * r;
+      atomicAdd(row + ev.ix, make_float4(kn * d.x, kn * d.y, kn * d.z, -g_tx * r));
+    }
+    atomicAdd(row + 5, make_float4(gcx * a, gcy * a, gcz * a, g_tau * ev.dt));
+  }
+}
+
 // Clears the record-gradient rows (6 float4 each) of the tets flagged by the forward pass.
 __global__ void __launch_bounds__(256)
 k_clear_flagged_rows(const uint8_t* __restrict__ tet_flags, int64_t T, float4* __restrict__ grec) {
@@ -1308,6 +1406,32 @@ int rm_launch_forward_constant_color(const int32_t* list, const int32_t* ranges,
       list, reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam, nullptr,
       reinterpret_cast<float4*>(out_img), dist_img, n_contrib, nullptr, nullptr, nullptr, nullptr, subs, n_units,
       pre_multi, ladder_p);
+  RM_CUDA_CHECK(cudaPeekAtLastError());
+  return RM_OK;
+}
+
+int rm_launch_backward_constant_color(const int32_t* list, const int32_t* ranges, const float* records,
+                                      const RmCamera* cam, float pre_multi, float ladder_p, const float* out_img,
+                                      const float* dist_img, const int32_t* n_contrib, const float* g_img,
+                                      const float* g_dist, int64_t T, int64_t V, float* grec, uint8_t* tet_flags,
+                                      float* vgrad, cudaStream_t st) {
+  RM_CUDA_CHECK(cudaMemsetAsync(vgrad, 0, sizeof(float) * 3 * (size_t)V, st));
+  if (T == 0) return RM_OK;
+  // every tet may receive a gradient here (the forward pass of this renderer keeps no hit lists)
+  RM_CUDA_CHECK(cudaMemsetAsync(grec, 0, sizeof(float) * 24 * (size_t)T, st));
+  RM_CUDA_CHECK(cudaMemsetAsync(tet_flags, 1, (size_t)T, st));
+  int subs;
+  int64_t n_units;
+  unsigned blocks;
+  unit_grid(cam, &subs, &n_units, &blocks);
+  if (n_units > 0) {
+    RmProfScope prof("k_backward<constant colour>", st);
+    rm_count_launch(), rm::k_backward_cc<<<blocks, rm::kWarpsPerBlock * 32, 0, st>>>(
+        list, reinterpret_cast<const int2*>(ranges), reinterpret_cast<const float4*>(records), *cam,
+        reinterpret_cast<const float4*>(out_img), reinterpret_cast<const float4*>(dist_img), n_contrib,
+        reinterpret_cast<const float4*>(g_img), reinterpret_cast<const float4*>(g_dist), pre_multi, ladder_p, grec, subs,
+        n_units);
+  }
   RM_CUDA_CHECK(cudaPeekAtLastError());
   return RM_OK;
 }

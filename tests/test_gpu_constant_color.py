@@ -70,20 +70,35 @@ def test_render_constant_color_matches_oracle(oracle, cuda_lib, tile):
     assert rel_l2(d_got[same_walk], dist[same_walk]) <= 1e-4
 
 
-def test_backward_is_refused(cuda_lib):
+@pytest.mark.parametrize("tile", [16, 4])
+def test_backward_against_oracle(oracle, cuda_lib, tile):
+    """Gradients of the constant-colour renderer (vertices and rgbs) against the oracle's restatement of the
+    reference's backward pass, upstream gradients on the image and on the distortion moments."""
     from delaunay_rasterization.internal.alphablend_tiled_slang import AlphaBlendTiledRender
     from delaunay_rasterization.internal.render_grid import RenderGrid
     from delaunay_rasterization.internal.tile_shader_slang import vertex_and_tile_shader
     from radiance_meshes_b200.render import tcam_to_device
-    pts, tets, cell = scene_util.small_scene(100, seed=2)
-    tcam = scene_util.camera(H=32, W=32, tile=16)
+    pts, tets, cell = scene_util.small_scene(300, seed=12, zero_frac=0.2)
+    H, W = 48, 64
+    tcam = scene_util.camera(H=H, W=W, tile=tile)
+    rng = np.random.default_rng(8)
+    rgbs = np.concatenate([rng.uniform(0, 1, (tets.shape[0], 3)), 2.0 * cell[:, :1]], axis=1).astype(np.float32)
+    g_img = rng.normal(size=(H, W, 4)).astype(np.float32)
+    g_dist = (1e-3 * rng.normal(size=(H, W, 4))).astype(np.float32)
     dev = torch.device("cuda:0")
     idx = torch.tensor(tets, device=dev, dtype=torch.int32)
-    v = torch.tensor(pts, device=dev)
-    rgbs = torch.rand((tets.shape[0], 4), device=dev, requires_grad=True)
-    grid = RenderGrid(32, 32, tile_height=16, tile_width=16)
+    v = torch.tensor(pts, device=dev, requires_grad=True)
+    r = torch.tensor(rgbs, device=dev, requires_grad=True)
+    grid = RenderGrid(H, W, tile_height=tile, tile_width=tile)
     tdev = tcam_to_device(tcam, dev)
-    sidx, ranges, *_ = vertex_and_tile_shader(idx, v, tdev, grid)
-    img, dimg = AlphaBlendTiledRender.apply(sidx, ranges, idx, v, rgbs, grid, tdev, 100, -0.1)
-    with pytest.raises(NotImplementedError):
-        img.sum().backward()
+    sidx, ranges, *_ = vertex_and_tile_shader(idx, v.detach(), tdev, grid)
+    img, dimg = AlphaBlendTiledRender.apply(sidx, ranges, idx, v, r, grid, tdev, 100, -0.1)
+    ((img * torch.tensor(g_img, device=dev)).sum() + (dimg * torch.tensor(g_dist, device=dev)).sum()).backward()
+    pr = oracle.project(tets, pts, tcam)
+    ref_idx, ref_ranges = oracle.build_lists(pr["tiles_touched"], pr["rect"], pr["vs_tetra"], tcam["grid_height"],
+                                             tcam["grid_width"])
+    out, dist, nc = oracle.forward_constant_color(ref_idx, ref_ranges, tets, pts, rgbs, tcam)
+    vg, rg = oracle.backward_constant_color(ref_idx, ref_ranges, tets, pts, rgbs, tcam, out, dist, nc, g_img, g_dist)
+    assert np.abs(vg).max() > 0 and np.abs(rg).max() > 0
+    assert rel_l2(r.grad.cpu().numpy(), rg) <= 1e-3
+    assert rel_l2(v.grad.cpu().numpy(), vg) <= 1e-3

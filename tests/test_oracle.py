@@ -223,3 +223,51 @@ def test_circumspheres_against_reference_torch_geometry(oracle):
         ref = ((g["eye"] - t["circumcenter"][i]) ** 2).sum() - t["radius"][i] ** 2
         assert abs(p - ref) <= 1e-12 * max(1.0, abs(ref))
         assert np.abs(c - t["circumcenter"][i]).max() <= 1e-12 * max(1.0, t["radius"][i])
+
+
+def test_constant_color_backward_against_finite_differences(oracle):
+    """The oracle's constant-colour backward pass (the reference's formulation, undo included) is the gradient of
+    its forward pass when no pair is skipped (min_alpha = 0; the reference skips alpha < 1/255 in the backward pass
+    only, which drops vertex-gradient terms that are not small), alphas stay away from 1 and the loss reads the
+    image only; checked in float64."""
+    pts, tets, cell = scene_util.small_scene(60, seed=2, mu=-0.5, sigma=0.4, zero_frac=0.0)
+    rng = np.random.default_rng(4)
+    rgbs = np.concatenate([rng.uniform(0.1, 0.9, (tets.shape[0], 3)), rng.uniform(0.8, 2.5, (tets.shape[0], 1))], 1)
+    H = W = 12
+    tcam = scene_util.camera(H=H, W=W, tile=4)
+    pr = oracle.project(tets, pts, tcam)
+    idx, ranges = oracle.build_lists(pr["tiles_touched"], pr["rect"], pr["vs_tetra"], tcam["grid_height"],
+                                     tcam["grid_width"])
+    v64, r64 = pts.astype(np.float64), rgbs.astype(np.float64)
+    g_img = rng.normal(size=(H, W, 4))
+    g_img[..., 3] *= 0.3
+
+    def loss(v, r):
+        out, _, _ = oracle.forward_constant_color_f64(idx, ranges, tets, v, r, tcam)
+        return float((out * g_img).sum())
+
+    out, dist, nc = oracle.forward_constant_color_f64(idx, ranges, tets, v64, r64, tcam)
+    vg, rg = oracle.backward_constant_color(idx, ranges, tets, v64, r64, tcam, out, dist, nc, g_img,
+                                            np.zeros((H, W, 4)), dtype=np.float64, min_alpha=0.0)
+    assert np.abs(rg).max() > 0 and np.abs(vg).max() > 0
+    # the reference's cut changes the result visibly (which is why the check above runs without it)
+    vg_ref, rg_ref = oracle.backward_constant_color(idx, ranges, tets, v64, r64, tcam, out, dist, nc, g_img,
+                                                    np.zeros((H, W, 4)), dtype=np.float64)
+    assert np.abs(rg_ref - rg).max() < 0.05 * np.abs(rg).max()
+    eps = 1e-6
+    order = np.argsort(-np.abs(rg).sum(1))[:6]
+    for t in order:
+        for k in range(4):
+            rp, rm = r64.copy(), r64.copy()
+            rp[t, k] += eps
+            rm[t, k] -= eps
+            fd = (loss(v64, rp) - loss(v64, rm)) / (2 * eps)
+            assert abs(fd - rg[t, k]) <= 1e-5 * max(1.0, abs(fd)), (t, k, fd, rg[t, k])
+    vorder = np.argsort(-np.abs(vg).sum(1))[:5]
+    for vi in vorder:
+        for k in range(3):
+            vp, vm = v64.copy(), v64.copy()
+            vp[vi, k] += eps
+            vm[vi, k] -= eps
+            fd = (loss(vp, r64) - loss(vm, r64)) / (2 * eps)
+            assert abs(fd - vg[vi, k]) <= 1e-4 * max(1.0, abs(fd)), (vi, k, fd, vg[vi, k])
