@@ -164,3 +164,28 @@ def test_tile_row_bands_partition():
     bands = rmdist.tile_row_bands(100, 4, w)
     sums = [w[a:b].sum() for a, b in bands]
     assert max(sums) - min(sums) <= 1.0 and sum(sums) == 20
+
+
+def test_row_weights_from_walk_balance_bands():
+    """Band weights from the previous frame: walk lengths blended with pair counts, normalised."""
+    H, W, th, gh = 22, 8, 4, 6                      # a ragged last tile row (22 = 5*4 + 2)
+    nc = torch.zeros((H, W, 1), dtype=torch.int32)
+    nc[4:8] = 10                                    # tile row 1 walks a lot
+    nc[20:22] = 5                                   # the ragged row a little
+    rect = torch.tensor([[0, 0, 2, 1], [0, 1, 2, 3], [0, 5, 1, 6], [0, 0, 0, 0]], dtype=torch.int32)
+    tt = torch.tensor([2, 4, 1, 0], dtype=torch.int32)
+    w = rmdist.row_weights_from_walk(nc, rect, tt, gh, th, walk_share=0.75).numpy()
+    assert w.shape == (gh,) and abs(w.sum() - 1.0) < 1e-12
+    walk = np.array([0, 10 * 4 * W, 0, 0, 0, 5 * 2 * W], float)
+    pairs = np.array([2, 2, 2, 0, 0, 1], float)
+    np.testing.assert_allclose(w, 0.75 * walk / walk.sum() + 0.25 * pairs / pairs.sum(), rtol=1e-12)
+    bands = rmdist.tile_row_bands(gh, 2, w)
+    assert bands[0][1] <= 2                         # the heavy row ends the first band early
+
+
+def test_overlapped_gradient_sum_is_inert_without_a_process_group():
+    s = rmdist.OverlappedGradientSum(chunks=3)
+    t = torch.ones(4)
+    s(t)                                            # no process group: nothing happens, no CUDA needed
+    s.done()
+    assert torch.equal(t, torch.ones(4)) and s.comm is None
