@@ -820,15 +820,16 @@ def run_bands(args):
         n_pairs, _ = raster.read_info(bctx)
         sidx = raster.build_tile_lists(bctx, n_pairs)
         recs = raster.pack_records(bctx["indices"], bctx["vertices"], cell, bctx["cam"], bctx["tiles_touched"])
-        _, _, ncontrib, _ = raster.forward(sidx, bctx["tile_ranges"], recs, bctx["cam"], jit, want_hit_masks=False)
+        _, _, ncontrib, hits = raster.forward(sidx, bctx["tile_ranges"], recs, bctx["cam"], jit)
         weights = rmdist.row_weights_from_walk(ncontrib, bctx["rect"], bctx["tiles_touched"], grid.grid_height,
-                                               tile).cpu().numpy()
-        del sidx, recs, ncontrib, bctx
+                                               tile, walk_share=0.7, hit_counts=hits[0], tile_width=tile).cpu().numpy()
+        del sidx, recs, ncontrib, bctx, hits
     band = rmdist.tile_row_bands(grid.grid_height, world, weights)[rank]
 
     def band_fn(b):
         t = dict(tcam)
         t["tile_rows"] = b
+        t["band_rows_only"] = True  # only the band's rows are read (combine_band_images)
         return render(ind, ver, cell, t, jit)["image"]
 
     def step():
@@ -879,6 +880,27 @@ def run_bands(args):
     kernel_ms = {}
     for name, t_ms in _lib.profile_read():
         kernel_ms[name] = kernel_ms.get(name, 0.0) + t_ms
+    # where a band's time goes on every rank: its kernels, the gather of the bands, and how long the host
+    # needs to enqueue one frame (a band's kernels are short; the host must not become the limit)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    with torch.no_grad():
+        barrier()
+        t_host = time.perf_counter()
+        ev[0].record()
+        local = band_fn(band) if band[1] > band[0] else band_fn((0, 0))
+        ev[1].record()
+        rmdist.combine_band_images(local, band, tile, bands=rmdist.tile_row_bands(grid.grid_height, world, weights))
+        ev[2].record()
+        t_host = (time.perf_counter() - t_host) * 1e3
+        torch.cuda.synchronize()
+    mine = torch.tensor([ev[0].elapsed_time(ev[1]), ev[1].elapsed_time(ev[2]), t_host, sum(kernel_ms.values()),
+                         kernel_ms.get("k_forward<constant colour>", kernel_ms.get("k_forward", 0.0))],
+                        device=dev, dtype=torch.float64)
+    per_rank = [mine]
+    if world > 1:
+        per_rank = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(per_rank, mine)
+    per_rank = [[round(float(x), 3) for x in t.tolist()] for t in per_rank]
     barrier()
     if rank == 0:
         line = dict(metric="fwd Mpix/s, one 3840x2160 frame split in tile-row bands", value=H * W / (ms * 1e-3) / 1e6,
@@ -889,6 +911,9 @@ def run_bands(args):
                                 tile_tet_pairs=n_pairs, band_rows_rank0=list(band),
                                 l2_policy="inputs larger than L2"),
                     clocks=clocks, parity_multi=parity_multi,
+                    per_rank_ms=dict(columns=["render the band (device)", "gather the bands (device)",
+                                              "host time to enqueue both", "sum of this library's kernels", "k_forward"],
+                                     rows=per_rank),
                     kernel_ms_rank0={k: round(v, 4) for k, v in sorted(kernel_ms.items(), key=lambda kv: -kv[1])})
         print(json.dumps(line), flush=True)
     if world > 1:

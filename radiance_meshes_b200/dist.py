@@ -148,17 +148,31 @@ def row_weights_from_rects(rect_tile_space, tiles_touched, grid_height):
     return torch.cumsum(diff, 0)[:grid_height]
 
 
-def row_weights_from_walk(n_contributors, rect_tile_space, tiles_touched, grid_height, tile_height, walk_share=0.75):
-    """Work per tile row for balancing bands, from the previous frame of a sequence: the list entries its
-    pixels walked (n_contributors[H,W], what the integration kernel's time follows) blended with the row's
-    (tile, tet) pairs (what the list build's time follows).  `walk_share` is the integration kernel's share of
-    a frame's time.  Every rank computes the same weights from the same tensors."""
-    nc = n_contributors.reshape(n_contributors.shape[0], -1).to(torch.float64).sum(1)
-    H = nc.shape[0]
-    pad = grid_height * tile_height - H
-    if pad > 0:
-        nc = torch.cat([nc, torch.zeros(pad, dtype=nc.dtype, device=nc.device)])
-    walk = nc.reshape(grid_height, tile_height).sum(1)
+def row_weights_from_walk(n_contributors, rect_tile_space, tiles_touched, grid_height, tile_height, walk_share=0.75,
+                          hit_counts=None, tile_width=None):
+    """Work per tile row for balancing bands, from the previous frame of a sequence, blended from what the
+    integration kernel's time follows and the row's (tile, tet) pairs (what the list build's time follows);
+    `walk_share` is the integration kernel's share of a frame's time.  Every rank computes the same weights
+    from the same tensors.
+
+    The integration term per tile: with `hit_counts` (RmHitList.counts of the previous frame) and `tile_width`,
+    4 * (entries examined = the longest walk among the tile's pixels) + 90 * (entries evaluated), the
+    instruction counts of the two phases of the forward kernel; without them the sum of the pixels' walk lengths."""
+    H, W = n_contributors.shape[0], n_contributors.shape[1]
+    nc = n_contributors.reshape(H, W).to(torch.float64)
+    pad_h = grid_height * tile_height - H
+    if pad_h > 0:
+        nc = torch.cat([nc, torch.zeros((pad_h, W), dtype=nc.dtype, device=nc.device)])
+    if hit_counts is not None and tile_width is not None:
+        grid_width = -(-W // tile_width)
+        pad_w = grid_width * tile_width - W
+        if pad_w > 0:
+            nc = torch.cat([nc, torch.zeros((nc.shape[0], pad_w), dtype=nc.dtype, device=nc.device)], dim=1)
+        examined = nc.reshape(grid_height, tile_height, grid_width, tile_width).amax(dim=(1, 3))
+        evaluated = hit_counts.to(torch.float64).reshape(grid_height, grid_width, -1).sum(-1)
+        walk = (4.0 * examined + 90.0 * evaluated).sum(1)
+    else:
+        walk = nc.sum(1).reshape(grid_height, tile_height).sum(1)
     pairs = row_weights_from_rects(rect_tile_space, tiles_touched, grid_height).to(torch.float64)
     walk = walk / walk.sum().clamp_min(1.0)
     pairs = pairs / pairs.sum().clamp_min(1.0)

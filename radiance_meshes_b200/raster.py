@@ -52,6 +52,8 @@ class CameraArgs:
         c.grid_width = int(tcam["grid_width"])
         r0, r1 = tile_rows if tile_rows is not None else tcam.get("tile_rows", (0, c.grid_height))
         c.tile_row_begin, c.tile_row_end = int(r0), int(r1)
+        # a band-restricted call zero-fills the image rows outside its band unless the caller reads the band only
+        self.band_rows_only = bool(tcam.get("band_rows_only", False))
         self.c = c
 
     @property
@@ -157,7 +159,7 @@ def forward(sorted_idx, tile_ranges, records, cam, ray_jitter, want_hit_masks=Tr
     dev = records.device
     H, W = cam.c.image_height, cam.c.image_width
     full = cam.c.tile_row_begin == 0 and cam.c.tile_row_end == cam.c.grid_height
-    alloc = torch.empty if full else torch.zeros
+    alloc = torch.empty if (full or cam.band_rows_only) else torch.zeros
     with torch.cuda.device(dev):
         output_img = alloc((H, W, 4), dtype=torch.float32, device=dev)
         distortion_img = alloc((H, W, 5), dtype=torch.float32, device=dev)

@@ -181,6 +181,14 @@ def test_row_weights_from_walk_balance_bands():
     np.testing.assert_allclose(w, 0.75 * walk / walk.sum() + 0.25 * pairs / pairs.sum(), rtol=1e-12)
     bands = rmdist.tile_row_bands(gh, 2, w)
     assert bands[0][1] <= 2                         # the heavy row ends the first band early
+    # with the previous frame's hit counts: 4 * entries examined + 90 * entries evaluated per tile
+    counts = torch.zeros((gh, 2), dtype=torch.int32)  # two tiles per row (W = 8, tile 4), one unit per tile
+    counts[1] = torch.tensor([3, 1])
+    counts[5] = torch.tensor([0, 2])
+    w2 = rmdist.row_weights_from_walk(nc, rect, tt, gh, th, walk_share=0.75, hit_counts=counts.reshape(-1),
+                                      tile_width=4).numpy()
+    walk2 = np.array([0, 4 * 20 + 90 * 4, 0, 0, 0, 4 * 10 + 90 * 2], float)
+    np.testing.assert_allclose(w2, 0.75 * walk2 / walk2.sum() + 0.25 * pairs / pairs.sum(), rtol=1e-12)
 
 
 def test_overlapped_gradient_sum_is_inert_without_a_process_group():
