@@ -711,8 +711,8 @@ def run_gpu(args):
                         unit="GB/s", frac=(achieved / peak) if achieved else None, traffic=traffic,
                         traffic_source=traffic_src,
                         kernel_ms=kernel_ms[dominant], algorithmic_bytes=bytes_alg,
-                        note="issue-bound kernel (about 16 pixel evaluations per staged record): the HBM fraction is low by "
-                             "construction")
+                        note="the kernel is bound by instruction issue (ncu: 72 % of the issue slots, DRAM at 3 %), so its HBM "
+                             "fraction is low by construction; `fp32_pipe` is its second roofline")
     frame_bytes = sum(alg.values())
     # Second roofline: the integration kernels are bound by the fp32 pipes, not by HBM.  Pair evaluations x
     # 170 flop (slab test + segment integral) against 148 SMs x 128 lanes x 2 flop at the sampled SM clock.

@@ -18,13 +18,15 @@
 //     distance by min_t*(n_i.d), so the per-(pixel,tet) work drops from four
 //     cross products to four dot products.
 //   * A half-warp owns 16 pixels of one tile; a warp therefore walks two tile
-//     lists in lock-step.  Forward: the list is examined 16 entries at a time
-//     (hull lines against the box of the half-warp's samples); candidates queue
-//     up in shared memory and are staged 16 at a time with 128-bit cp.async
-//     copies, double buffered, so both half-warps evaluate equally long batches.
-//     A half-warp stops as soon as all of its pixels have terminated.  Every
-//     entry that some pixel hit is appended, with the mask of those pixels, to
-//     the half-warp's hit list.
+//     lists side by side.  Forward: the list is examined 16 entries at a time
+//     (hull lines against the box of the half-warp's samples); survivors are
+//     tested against each of the 16 sample positions, which gives the mask of
+//     pixels a tet can cover; entries with a non-empty mask are staged 16 at a
+//     time with 128-bit cp.async copies, double buffered, and every lane then
+//     walks only the staged entries that cover its pixel.  A half-warp stops as
+//     soon as all of its pixels have terminated.  Every evaluated batch is
+//     appended, with the per-pixel bit sets of the entries that were hit, to the
+//     half-warp's hit list.
 //   * Backward walks the hit lists back to front and accumulates gradients with
 //     respect to 16 of the 24 record fields per hit (entering plane, exit plane,
 //     colour fields): the 16 pixels' values are summed through a shared-memory
