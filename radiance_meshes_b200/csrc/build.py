@@ -61,10 +61,13 @@ def build(force=False, verbose=False, ptxas_info=False, variant=None):
             print(" ".join(cmd), flush=True)
         subprocess.check_call(cmd)
         objs.append(obj)
-    cmd = [nvcc, "-shared", *ARCH, "-o", target, *objs]
+    # link beside the target and rename: a reader never sees a half-written library
+    tmp = target + f".tmp{os.getpid()}"
+    cmd = [nvcc, "-shared", *ARCH, "-o", tmp, *objs]
     if verbose:
         print(" ".join(cmd), flush=True)
     subprocess.check_call(cmd)
+    os.replace(tmp, target)
     return target
 
 

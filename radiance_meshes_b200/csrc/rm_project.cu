@@ -158,10 +158,14 @@ __device__ __forceinline__ void find_extent(const f3 tet[4], f3& mn, f3& mx, con
 
 // Extent of a tet that lies entirely in front of the near plane, seen by an
 // undistorted pinhole camera.  The general routine then clips nothing and samples
-// every directed face edge a->b at its two ends, a + (b-a)*0 and a + (b-a)*1; the
-// first is the vertex itself (up to the sign of a zero, which no later step can
-// see), so 4 vertex projections and 12 end samples give the same minima and
-// maxima as its 24 projections, without loops or local arrays.
+// every directed face edge a->b at its two ends, a + (b-a)*0 and a + (b-a)*1.  The
+// first is the vertex a itself (up to the sign of a zero, which no later step can
+// see).  The second equals b bit for bit unless the subtraction or the addition
+// rounded, which happens for about one sample in forty; its projection is then
+// already among the four vertex projections.  So the four vertices are projected,
+// the twelve end samples are formed and compared with their vertex, and only the
+// ones that differ are projected as well: the same minima and maxima as the 24
+// projections of the general routine.
 __device__ __forceinline__ void find_extent_unclipped(const f3 cs[4], f3& mn, f3& mx, const DevCam& c) {
   const float BIG = 1e20f;
   mn = {BIG, BIG, BIG};
@@ -173,19 +177,29 @@ __device__ __forceinline__ void find_extent_unclipped(const f3 cs[4], f3& mn, f3
     mn = {fminf(mn.x, px), fminf(mn.y, py), fminf(mn.z, p.z)};
     mx = {fmaxf(mx.x, px), fmaxf(mx.y, py), fmaxf(mx.z, p.z)};
   };
-  // One pass per face (a, b, c) = (0,1,2) (0,2,3) (0,3,1) (1,3,2): vertex number `face` and the end
-  // samples of the directed edges a->b, b->c, c->a.  The loop is kept rolled (the vertices are picked
-  // with selects, not indexed) so that the kernel stays small enough for the instruction cache.
-#pragma unroll 1
-  for (int face = 0; face < 4; ++face) {
-    const f3 a = face == 3 ? cs[1] : cs[0];
-    const f3 b = face == 0 ? cs[1] : (face == 1 ? cs[2] : cs[3]);
-    const f3 cc = face == 0 ? cs[2] : (face == 1 ? cs[3] : (face == 2 ? cs[1] : cs[2]));
-    const f3 own = face == 0 ? cs[0] : (face == 1 ? cs[1] : (face == 2 ? cs[2] : cs[3]));
-    add(own);
+  add(cs[0]);
+  add(cs[1]);
+  add(cs[2]);
+  add(cs[3]);
+  // directed edges of the faces (0,1,2) (0,2,3) (0,3,1) (1,3,2), two bits per end point
+  constexpr unsigned kFrom = 0u | (1u << 2) | (2u << 4) | (0u << 6) | (2u << 8) | (3u << 10) | (0u << 12) | (3u << 14) |
+                             (1u << 16) | (1u << 18) | (3u << 20) | (2u << 22);
+  constexpr unsigned kTo = 1u | (2u << 2) | (0u << 4) | (2u << 6) | (3u << 8) | (0u << 10) | (3u << 12) | (1u << 14) |
+                           (0u << 16) | (3u << 18) | (2u << 20) | (1u << 22);
+  unsigned pending = 0;
+#pragma unroll
+  for (int e = 0; e < 12; ++e) {
+    const f3 a = cs[(kFrom >> (2 * e)) & 3u], b = cs[(kTo >> (2 * e)) & 3u];
+    const f3 s_ = lerp3(a, b, 1.0f);
+    if (s_.x != b.x || s_.y != b.y || s_.z != b.z) pending |= 1u << e;
+  }
+  while (pending) {
+    const int e = __ffs(pending) - 1;
+    pending &= pending - 1;
+    const unsigned ia = (kFrom >> (2 * e)) & 3u, ib = (kTo >> (2 * e)) & 3u;
+    const f3 a = ia == 0 ? cs[0] : (ia == 1 ? cs[1] : (ia == 2 ? cs[2] : cs[3]));
+    const f3 b = ib == 0 ? cs[0] : (ib == 1 ? cs[1] : (ib == 2 ? cs[2] : cs[3]));
     add(lerp3(a, b, 1.0f));
-    add(lerp3(b, cc, 1.0f));
-    add(lerp3(cc, a, 1.0f));
   }
 }
 
