@@ -1283,7 +1283,10 @@ k_backward_finish(const int32_t* __restrict__ indices, const float* __restrict__
   float* co = rows + 7 * threadIdx.x;
   float4 q[6];
   bool any = false;
+  int4 id = make_int4(0, 0, 0, 0);
   if (g < T && tet_flags[g]) {  // rows of tets without a hit were neither cleared nor written
+    // the vertex ids travel with the gradient row: one dependent round trip less before the vertex gathers
+    id = __ldg(reinterpret_cast<const int4*>(indices) + g);
 #pragma unroll
     for (int k = 0; k < 6; ++k) {
       q[k] = __ldg(grec + 6 * g + k);
@@ -1295,7 +1298,6 @@ k_backward_finish(const int32_t* __restrict__ indices, const float* __restrict__
     for (int k = 0; k < 7; ++k) co[k] = 0.0f;
   } else {
   f3 cam = {__ldg(rcam.cam_pos), __ldg(rcam.cam_pos + 1), __ldg(rcam.cam_pos + 2)};
-  int4 id = __ldg(reinterpret_cast<const int4*>(indices) + g);
   if (!(RM_INDEX_OK(id.x, RM_X_VERTS, 5) && RM_INDEX_OK(id.y, RM_X_VERTS, 5) && RM_INDEX_OK(id.z, RM_X_VERTS, 5) &&
         RM_INDEX_OK(id.w, RM_X_VERTS, 5)))
     id = make_int4(0, 0, 0, 0);
