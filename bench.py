@@ -633,17 +633,7 @@ def run_gpu(args):
             _, _, ncontrib, hits = raster.forward(sidx, bctx["tile_ranges"], recs, bctx["cam"], d["jitter"])
             counts, _, masks, flags = hits
             counts64 = counts.to(torch.int64)
-            nbatch = (counts64 + 15) // 16
-            start = bctx["tile_ranges"][:, 0].to(torch.int64)
-            mbase = start + 16 * torch.arange(counts.shape[0], device=dev, dtype=torch.int64)  # 4x4 tiles: one unit per tile
-            first = torch.cumsum(nbatch, 0) - nbatch
-            total_b = int(nbatch.sum().item())
-            owner = torch.repeat_interleave(torch.arange(counts.shape[0], device=dev), nbatch)
-            within = torch.arange(total_b, device=dev, dtype=torch.int64) - first[owner]
-            slots = (mbase[owner] + 16 * within)[:, None] + torch.arange(16, device=dev, dtype=torch.int64)[None, :]
-            bits = masks[slots.reshape(-1)].to(torch.int32) & 0xFFFF
-            pop16 = torch.tensor([bin(i).count("1") for i in range(65536)], device=dev, dtype=torch.int32)
-            pixel_hits = int(pop16[bits.long()].to(torch.int64).sum().item())
+            pixel_hits = int(rmdist.pixel_hits_per_unit(counts, masks, bctx["tile_ranges"]).sum().item())  # 4x4 tiles
             hit_stats = dict(list_entries=nk, walked_pixel_entries=int(ncontrib.to(torch.int64).sum().item()),
                              recorded_entries=int(counts64.sum().item()), pixel_hits=pixel_hits,
                              tets_with_gradient=int(flags.to(torch.int64).sum().item()),
@@ -652,7 +642,7 @@ def run_gpu(args):
                              note="walked_pixel_entries = sum of n_contributors (the reference's pair evaluations, "
                                   "forward); pixel_hits = (pixel, tet) pairs with a contribution (the pair evaluations "
                                   "of this implementation, forward and backward)")
-            del bctx, sidx, recs, hits, counts, masks, flags, slots, bits, owner, within, ncontrib
+            del bctx, sidx, recs, hits, counts, masks, flags, ncontrib
 
     # ---- the reference's own GPU sort (CUB DeviceRadixSort behind sort_by_keys.cu, built unchanged from the
     # reference checkout by oracle/build_ref.py) on the keys of this frame: timed beside this library's list
@@ -821,8 +811,10 @@ def run_bands(args):
         sidx = raster.build_tile_lists(bctx, n_pairs)
         recs = raster.pack_records(bctx["indices"], bctx["vertices"], cell, bctx["cam"], bctx["tiles_touched"])
         _, _, ncontrib, hits = raster.forward(sidx, bctx["tile_ranges"], recs, bctx["cam"], jit)
+        px_hits = rmdist.pixel_hits_per_unit(hits[0], hits[2], bctx["tile_ranges"])
         weights = rmdist.row_weights_from_walk(ncontrib, bctx["rect"], bctx["tiles_touched"], grid.grid_height,
-                                               tile, walk_share=0.7, hit_counts=hits[0], tile_width=tile).cpu().numpy()
+                                               tile, walk_share=0.7, hit_counts=hits[0], tile_width=tile,
+                                               pixel_hits=px_hits).cpu().numpy()
         del sidx, recs, ncontrib, bctx, hits
     band = rmdist.tile_row_bands(grid.grid_height, world, weights)[rank]
 

@@ -148,16 +148,46 @@ def row_weights_from_rects(rect_tile_space, tiles_touched, grid_height):
     return torch.cumsum(diff, 0)[:grid_height]
 
 
+_POP16 = {}
+
+
+def pixel_hits_per_unit(hit_counts, hit_masks, tile_ranges, units_per_tile=1):
+    """(pixel, entry) hits of every hit-list unit of the previous frame: the population count of the per-pixel
+    bit sets the forward pass recorded (RmHitList.masks), summed per unit.  Returns int64 [G * units_per_tile]."""
+    dev = hit_counts.device
+    lut = _POP16.get(dev)
+    if lut is None:
+        lut = _POP16[dev] = torch.tensor([bin(i).count("1") for i in range(65536)], device=dev, dtype=torch.int64)
+    counts = hit_counts.to(torch.int64)
+    S = units_per_tile
+    n_units = counts.shape[0]
+    nbatch = (counts + 15) // 16
+    unit = torch.arange(n_units, device=dev, dtype=torch.int64)
+    start = tile_ranges[:, 0].to(torch.int64)
+    length = (tile_ranges[:, 1] - tile_ranges[:, 0]).to(torch.int64)
+    base = start[unit // S] * S + (unit % S) * length[unit // S] + 16 * unit  # first mask slot of the unit
+    owner = torch.repeat_interleave(unit, nbatch)
+    first = torch.cumsum(nbatch, 0) - nbatch
+    within = torch.arange(int(nbatch.sum().item()), device=dev, dtype=torch.int64) - first[owner]
+    slots = (base[owner] + 16 * within)[:, None] + torch.arange(16, device=dev, dtype=torch.int64)[None, :]
+    bits = hit_masks[slots.reshape(-1)].to(torch.int64) & 0xFFFF
+    per_batch = lut[bits].reshape(-1, 16).sum(1)
+    out = torch.zeros(n_units, dtype=torch.int64, device=dev)
+    out.index_add_(0, owner, per_batch)
+    return out
+
+
 def row_weights_from_walk(n_contributors, rect_tile_space, tiles_touched, grid_height, tile_height, walk_share=0.75,
-                          hit_counts=None, tile_width=None):
+                          hit_counts=None, tile_width=None, pixel_hits=None):
     """Work per tile row for balancing bands, from the previous frame of a sequence, blended from what the
     integration kernel's time follows and the row's (tile, tet) pairs (what the list build's time follows);
     `walk_share` is the integration kernel's share of a frame's time.  Every rank computes the same weights
     from the same tensors.
 
     The integration term per tile: with `hit_counts` (RmHitList.counts of the previous frame) and `tile_width`,
-    4 * (entries examined = the longest walk among the tile's pixels) + 90 * (entries evaluated), the
-    instruction counts of the two phases of the forward kernel; without them the sum of the pixels' walk lengths."""
+    4 * (entries examined = the longest walk among the tile's pixels) + 20 * (entries evaluated) + 5.5 *
+    (pixel hits, `pixel_hits_per_unit`; 90 * entries evaluated if those are not given) - the instruction counts of the
+    phases of the forward kernel; without them the sum of the pixels' walk lengths."""
     H, W = n_contributors.shape[0], n_contributors.shape[1]
     nc = n_contributors.reshape(H, W).to(torch.float64)
     pad_h = grid_height * tile_height - H
@@ -170,7 +200,11 @@ def row_weights_from_walk(n_contributors, rect_tile_space, tiles_touched, grid_h
             nc = torch.cat([nc, torch.zeros((nc.shape[0], pad_w), dtype=nc.dtype, device=nc.device)], dim=1)
         examined = nc.reshape(grid_height, tile_height, grid_width, tile_width).amax(dim=(1, 3))
         evaluated = hit_counts.to(torch.float64).reshape(grid_height, grid_width, -1).sum(-1)
-        walk = (4.0 * examined + 90.0 * evaluated).sum(1)
+        if pixel_hits is not None:
+            hits = pixel_hits.to(torch.float64).reshape(grid_height, grid_width, -1).sum(-1)
+            walk = (4.0 * examined + 20.0 * evaluated + 5.5 * hits).sum(1)
+        else:
+            walk = (4.0 * examined + 90.0 * evaluated).sum(1)
     else:
         walk = nc.sum(1).reshape(grid_height, tile_height).sum(1)
     pairs = row_weights_from_rects(rect_tile_space, tiles_touched, grid_height).to(torch.float64)

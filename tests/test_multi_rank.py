@@ -197,3 +197,19 @@ def test_overlapped_gradient_sum_is_inert_without_a_process_group():
     s(t)                                            # no process group: nothing happens, no CUDA needed
     s.done()
     assert torch.equal(t, torch.ones(4)) and s.comm is None
+
+
+def test_pixel_hits_per_unit_reads_the_hit_list_layout():
+    """Mask slots of unit q start at start(tile)*S + s*len(tile) + 16*q, 16 per batch of 16 recorded entries."""
+    ranges = torch.tensor([[0, 5], [5, 45], [0, 0]], dtype=torch.int32)      # three tiles, one unit each
+    counts = torch.tensor([3, 20, 0], dtype=torch.int32)                    # 1 batch, 2 batches, none
+    masks = torch.full((45 + 16 * 3,), 0x7FFF, dtype=torch.int16)           # unwritten slots hold anything
+    masks[0 + 0:0 + 16] = 0
+    masks[0] = 0b0101                                                        # tile 0: two hits of pixel 0
+    masks[3] = 0b0001
+    b1 = 5 + 16 * 1
+    masks[b1:b1 + 32] = 0
+    masks[b1 + 2] = -1                                                       # 0xFFFF: 16 hits
+    masks[b1 + 16 + 15] = 0b0100_0000_0000_0001
+    got = rmdist.pixel_hits_per_unit(counts, masks, ranges)
+    assert got.tolist() == [3, 18, 0]
