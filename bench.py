@@ -816,7 +816,7 @@ def run_bands(args):
                                                tile, walk_share=0.7, hit_counts=hits[0], tile_width=tile,
                                                pixel_hits=px_hits).cpu().numpy()
         del sidx, recs, ncontrib, bctx, hits
-    band = rmdist.tile_row_bands(grid.grid_height, world, weights)[rank]
+    bands = rmdist.tile_row_bands(grid.grid_height, world, weights)
 
     def band_fn(b):
         t = dict(tcam)
@@ -826,7 +826,7 @@ def run_bands(args):
 
     def step():
         with torch.no_grad():
-            full, _ = rmdist.render_band_split(band_fn, grid.grid_height, tile, rank, world, row_weights=weights)
+            full, _ = rmdist.render_band_split(band_fn, grid.grid_height, tile, rank, world, bands=bands)
         return full
 
     def barrier():
@@ -834,6 +834,24 @@ def run_bands(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    # the bands adapt to the measured time of the previous frames, as a renderer in a sequence would: a few
+    # untimed frames, each followed by new cuts from the all-gathered device times of the ranks' bands
+    rebalanced = 0
+    if world > 1:
+        for _ in range(4):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            with torch.no_grad():
+                a.record()
+                band_fn(bands[rank] if bands[rank][1] > bands[rank][0] else (0, 0))
+                b.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([a.elapsed_time(b)], device=dev, dtype=torch.float64)
+            ts = [torch.empty_like(t) for _ in range(world)]
+            dist.all_gather(ts, t)
+            bands = rmdist.rebalance_bands(bands, [float(x.item()) for x in ts], weights)
+            rebalanced += 1
+    band = bands[rank]
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -881,7 +899,7 @@ def run_bands(args):
         ev[0].record()
         local = band_fn(band) if band[1] > band[0] else band_fn((0, 0))
         ev[1].record()
-        rmdist.combine_band_images(local, band, tile, bands=rmdist.tile_row_bands(grid.grid_height, world, weights))
+        rmdist.combine_band_images(local, band, tile, bands=bands)
         ev[2].record()
         t_host = (time.perf_counter() - t_host) * 1e3
         torch.cuda.synchronize()
@@ -900,7 +918,7 @@ def run_bands(args):
                     higher_is_better=True, scaling="strong", vs_baseline=None, dtype="f32", data="synthetic",
                     config=dict(workload=f"{args.workload} mesh ({sc['indices'].shape[0]} tets), 3840x2160, fov 90, "
                                          f"tile 4, forward only, {world} tile-row band(s)",
-                                tile_tet_pairs=n_pairs, band_rows_rank0=list(band),
+                                tile_tet_pairs=n_pairs, bands=[list(b) for b in bands], rebalanced_frames=rebalanced,
                                 l2_policy="inputs larger than L2"),
                     clocks=clocks, parity_multi=parity_multi,
                     per_rank_ms=dict(columns=["render the band (device)", "gather the bands (device)",

@@ -136,6 +136,22 @@ def tile_row_bands(grid_height, world_size, row_weights=None):
     return [(cuts[k], cuts[k + 1]) for k in range(world_size)]
 
 
+def rebalance_bands(bands, times, row_weights):
+    """New bands from the measured time of the current ones (a renderer in a sequence does this between
+    frames).  Rank r took times[r] for bands[r]; its time is spread over its rows in proportion to
+    row_weights, and the new cuts are placed where the running time crosses k/N of the total.  Every rank
+    calls this with the same (all-gathered) times and gets the same bands."""
+    w = np.asarray(row_weights, np.float64).reshape(-1)
+    gh = w.shape[0]
+    dens = np.zeros(gh, np.float64)
+    for (a, b), t in zip(bands, times):
+        if b > a:
+            ww = w[a:b]
+            tot = ww.sum()
+            dens[a:b] = float(t) * (ww / tot if tot > 0 else np.full(b - a, 1.0 / (b - a)))
+    return tile_row_bands(gh, len(bands), dens)
+
+
 def row_weights_from_rects(rect_tile_space, tiles_touched, grid_height):
     """Work per tile row from the per-tet rectangles: sum over tets of the rectangle
     width for every row the rectangle covers (a difference array over rows)."""
@@ -271,13 +287,16 @@ def render_view_parallel(render_backward_fn, views, rank, world_size, group=None
     return images, vg, cg
 
 
-def render_band_split(render_band_fn, grid_height, tile_height, rank, world_size, row_weights=None, group=None):
+def render_band_split(render_band_fn, grid_height, tile_height, rank, world_size, row_weights=None, group=None,
+                      bands=None):
     """One frame split over the ranks by tile-row bands.
 
     render_band_fn((row_begin, row_end)) -> full-size image whose band rows are valid.
+    `bands`: the bands to use (e.g. from rebalance_bands); else they are cut from row_weights.
     Returns (full image on every rank, this rank's band).
     """
-    bands = tile_row_bands(grid_height, world_size, row_weights)
+    if bands is None:
+        bands = tile_row_bands(grid_height, world_size, row_weights)
     band = bands[rank]
     if band[1] > band[0]:
         local = render_band_fn(band)

@@ -213,3 +213,17 @@ def test_pixel_hits_per_unit_reads_the_hit_list_layout():
     masks[b1 + 16 + 15] = 0b0100_0000_0000_0001
     got = rmdist.pixel_hits_per_unit(counts, masks, ranges)
     assert got.tolist() == [3, 18, 0]
+
+
+def test_rebalance_bands_moves_rows_from_the_slow_rank():
+    w = np.ones(100)
+    bands = rmdist.tile_row_bands(100, 4, w)
+    assert bands == [(0, 25), (25, 50), (50, 75), (75, 100)]
+    new = rmdist.rebalance_bands(bands, [1.0, 3.0, 1.0, 1.0], w)     # rank 1 took three times as long
+    assert new[0][0] == 0 and new[-1][1] == 100 and all(new[k][1] == new[k + 1][0] for k in range(3))
+    assert new[1][1] - new[1][0] < 25 and new[0][1] > 25               # its band shrinks, its neighbours grow
+    # time per row: 0.04, 0.12, 0.04, 0.04 -> total 6; cuts at 1.5, 3.0, 4.5 -> rows 30, 42.5, 62.5
+    for (a, b), (ea, eb) in zip(new, [(0, 30), (30, 42), (42, 63), (63, 100)]):
+        assert abs(a - ea) <= 1 and abs(b - eb) <= 1
+    same = rmdist.rebalance_bands(bands, [1.0, 1.0, 1.0, 1.0], w)
+    assert all(abs(a - ea) <= 1 and abs(b - eb) <= 1 for (a, b), (ea, eb) in zip(same, bands))
