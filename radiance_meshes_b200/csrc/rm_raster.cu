@@ -34,6 +34,7 @@
 //     a per-tet row; a per-tet kernel then applies the chain rule to vertices and
 //     cell values (12 vertex atomics per tet instead of 19 atomics per pixel hit).
 
+#include <type_traits>
 #include "rm_common.cuh"
 
 namespace rm {
@@ -376,6 +377,7 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 
 constexpr int kWarpsPerBlock = 4;
 constexpr int kChunk = 16;  // records staged per half-warp per round
+constexpr int kBwdGroup = 3;        // entries with disjoint pixel masks the backward walk takes in one step
 constexpr int kTileSumMinHits = 4;  // fewer hit pixels in a tile: every pixel adds its own values with atomics
 
 struct Unit {
@@ -741,7 +743,7 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
 // ----------------------------------------------------------------------------
 // Backward
 // ----------------------------------------------------------------------------
-__global__ void __launch_bounds__(kWarpsPerBlock * 32, 4)
+__global__ void __launch_bounds__(kWarpsPerBlock * 32, 5)
 k_backward(const int2* __restrict__ ranges, const float4* __restrict__ records, RmCamera rcam,
            const float2* __restrict__ jitter, const float4* __restrict__ out_img, const float* __restrict__ dist_img,
            const int32_t* __restrict__ hit_counts, const int32_t* __restrict__ hit_ids,
@@ -835,20 +837,42 @@ k_backward(const int2* __restrict__ ranges, const float4* __restrict__ records, 
     const float4* cur = stage[warp][half][k & 1];
     const int* cur_id = stage_id[warp][half][k & 1];
     const unsigned* cur_mask = stage_mask[warp][half][k & 1];
-    // Both halves step in lock-step through their own hit entries, last entry
-    // first; a half that runs out idles.
+    // Both halves step in lock-step through their own hit entries, last entry first; a half
+    // that runs out idles.  Up to kBwdGroup entries that follow one another and whose pixel
+    // masks are disjoint are taken in ONE step: every pixel belongs to at most one of them, so
+    // its back-to-front order is untouched, and lanes the first entry would leave idle evaluate
+    // the next one.
     unsigned todo = (__ballot_sync(0xffffffffu, cur_mask[lane16] != 0u) >> (16 * half)) & 0xFFFFu;
-    const int steps = max(__popc(todo), __shfl_xor_sync(0xffffffffu, __popc(todo), 16));
-    for (int step = 0; step < steps; ++step) {
-      int j = 0;
-      bool in_range = false;
-      if (todo) {
-        j = 31 - __clz(todo);
-        todo &= ~(1u << j);
-        in_range = true;
+    while (__any_sync(0xffffffffu, todo != 0u)) {
+      int mem[kBwdGroup];            // batch positions of the step's entries
+      unsigned mem_mask[kBwdGroup];  // and their pixel masks (0: slot unused)
+      unsigned covered = 0u;
+      {
+        bool open = true;
+#pragma unroll
+        for (int g = 0; g < kBwdGroup; ++g) {
+          mem[g] = 0;
+          mem_mask[g] = 0u;
+          if (open && todo) {
+            const int c = 31 - __clz(todo);
+            const unsigned mc = cur_mask[c];
+            if (g == 0 || (mc & covered) == 0u) {
+              mem[g] = c;
+              mem_mask[g] = mc;
+              covered |= mc;
+              todo &= ~(1u << c);
+            } else {
+              open = false;
+            }
+          }
+        }
       }
+      int j = mem[0];  // the entry this lane evaluates
+#pragma unroll
+      for (int g = 1; g < kBwdGroup; ++g)
+        if ((mem_mask[g] >> lane16) & 1u) j = mem[g];
       const float4* rec = cur + j * 6;
-      bool hit = in_range && ((cur_mask[j] >> lane16) & 1u);
+      bool hit = (covered >> lane16) & 1u;
       Eval ev;
       if (hit) {  // same arithmetic as the forward pass, so the test succeeds again
         const float4 pl[4] = {rec[0], rec[1], rec[2], rec[3]};
@@ -938,48 +962,66 @@ k_backward(const int2* __restrict__ ranges, const float4* __restrict__ records, 
           v[15] = g_dens;
         }
       }
-      // Reduction over the pixels of a tile.  If every contributing lane of a half
-      // enters through the same face and leaves through the same face, and enough
-      // lanes hit, the 16 sums are formed first (shared-memory transpose, one atomic
-      // per lane); otherwise each hit lane adds its own 16 values.
-      const unsigned my_hits = (hits >> (16 * half)) & 0xFFFFu;
-      const unsigned e_lanes = (__ballot_sync(0xffffffffu, pe >= 0) >> (16 * half)) & 0xFFFFu;
-      const unsigned x_lanes = (__ballot_sync(0xffffffffu, px >= 0) >> (16 * half)) & 0xFFFFu;
-      const int src_e = e_lanes ? (__ffs(e_lanes) - 1) + 16 * half : lane;
-      const int src_x = x_lanes ? (__ffs(x_lanes) - 1) + 16 * half : lane;
-      const int pe_ref = __shfl_sync(0xffffffffu, pe, src_e);
-      const int px_ref = __shfl_sync(0xffffffffu, px, src_x);
-      const bool odd = (pe >= 0 && pe != pe_ref) || (px >= 0 && px != px_ref);
-      const bool sum_over_tile =
-          __ballot_sync(0xffffffffu, odd || (my_hits != 0 && __popc(my_hits) < kTileSumMinHits)) == 0;
-      if (sum_over_tile) {
-        // transpose through shared memory: every lane stores its 16 values as a row (stride 20
-        // floats keeps the 128-bit stores aligned and the column reads free of bank conflicts),
-        // then lane l adds up column l
-        float* rb = reduce_buf[warp] + half * (kChunk * 20 + 16);
-        float4* row4 = reinterpret_cast<float4*>(rb + lane16 * 20);
-        row4[0] = make_float4(v[0], v[1], v[2], v[3]);
-        row4[1] = make_float4(v[4], v[5], v[6], v[7]);
-        row4[2] = make_float4(v[8], v[9], v[10], v[11]);
-        row4[3] = make_float4(v[12], v[13], v[14], v[15]);
-        __syncwarp();
-        float sum = 0.0f;
+      // Reduction over the pixels of a tile, entry by entry of the step.  If every contributing
+      // lane of a half enters through the same face and leaves through the same face, and enough
+      // lanes hit, the 16 sums are formed first (shared-memory transpose, one atomic per lane);
+      // otherwise each hit lane adds its own 16 values.  `GROUPED` = a half took several entries
+      // in this step: the lanes of the other entries then count as lanes without a hit.
+      auto reduce_entry = [&](auto grouped, int g) {
+        constexpr bool GROUPED = decltype(grouped)::value;
+        const bool hit_g = GROUPED ? hit && ((mem_mask[g] >> lane16) & 1u) : hit;
+        const unsigned my_hits =
+            ((GROUPED ? __ballot_sync(0xffffffffu, hit_g) : hits) >> (16 * half)) & 0xFFFFu;
+        const unsigned e_lanes = (__ballot_sync(0xffffffffu, hit_g && pe >= 0) >> (16 * half)) & 0xFFFFu;
+        const unsigned x_lanes = (__ballot_sync(0xffffffffu, hit_g && px >= 0) >> (16 * half)) & 0xFFFFu;
+        const int src_e = e_lanes ? (__ffs(e_lanes) - 1) + 16 * half : lane;
+        const int src_x = x_lanes ? (__ffs(x_lanes) - 1) + 16 * half : lane;
+        const int pe_ref = __shfl_sync(0xffffffffu, pe, src_e);
+        const int px_ref = __shfl_sync(0xffffffffu, px, src_x);
+        const bool odd = hit_g && ((pe >= 0 && pe != pe_ref) || (px >= 0 && px != px_ref));
+        const bool sum_over_tile =
+            __ballot_sync(0xffffffffu, odd || (my_hits != 0 && __popc(my_hits) < kTileSumMinHits)) == 0;
+        if (sum_over_tile) {
+          if (GROUPED && __ballot_sync(0xffffffffu, my_hits != 0u) == 0u) return;
+          // transpose through shared memory: every lane stores its 16 values as a row (stride 20
+          // floats keeps the 128-bit stores aligned and the column reads free of bank conflicts),
+          // then lane l adds up column l
+          float* rb = reduce_buf[warp] + half * (kChunk * 20 + 16);
+          float4* row4 = reinterpret_cast<float4*>(rb + lane16 * 20);
+          const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
+          row4[0] = (!GROUPED || hit_g) ? make_float4(v[0], v[1], v[2], v[3]) : z4;
+          row4[1] = (!GROUPED || hit_g) ? make_float4(v[4], v[5], v[6], v[7]) : z4;
+          row4[2] = (!GROUPED || hit_g) ? make_float4(v[8], v[9], v[10], v[11]) : z4;
+          row4[3] = (!GROUPED || hit_g) ? make_float4(v[12], v[13], v[14], v[15]) : z4;
+          __syncwarp();
+          float sum = 0.0f;
 #pragma unroll
-        for (int r = 0; r < kChunk; ++r) sum += rb[r * 20 + lane16];
-        __syncwarp();
-        if (my_hits && sum != 0.0f) {
-          float* row = grec + (int64_t)cur_id[j] * 24;
-          const int f = lane16;
-          const int dst = f < 4 ? 4 * pe_ref + f : (f < 8 ? 4 * px_ref + (f - 4) : f + 8);
-          if (dst >= 0) atomicAdd(row + dst, sum);
+          for (int r = 0; r < kChunk; ++r) sum += rb[r * 20 + lane16];
+          __syncwarp();
+          if (my_hits && sum != 0.0f) {
+            float* row = grec + (int64_t)cur_id[mem[g]] * 24;
+            const int f = lane16;
+            const int dst = f < 4 ? 4 * pe_ref + f : (f < 8 ? 4 * px_ref + (f - 4) : f + 8);
+            if (dst >= 0) atomicAdd(row + dst, sum);
+          }
+        } else if (hit_g) {
+          // 128-bit reductions: a plane's four sums and the colour sums are 16-byte aligned
+          float4* row = reinterpret_cast<float4*>(grec + (int64_t)cur_id[j] * 24);
+          if (pe >= 0) atomicAdd(row + pe, make_float4(v[0], v[1], v[2], v[3]));
+          if (px >= 0) atomicAdd(row + px, make_float4(v[4], v[5], v[6], v[7]));
+          atomicAdd(row + 4, make_float4(v[8], v[9], v[10], v[11]));
+          atomicAdd(row + 5, make_float4(v[12], v[13], v[14], v[15]));
         }
-      } else if (hit) {
-        // 128-bit reductions: a plane's four sums and the colour sums are 16-byte aligned
-        float4* row = reinterpret_cast<float4*>(grec + (int64_t)cur_id[j] * 24);
-        if (pe >= 0) atomicAdd(row + pe, make_float4(v[0], v[1], v[2], v[3]));
-        if (px >= 0) atomicAdd(row + px, make_float4(v[4], v[5], v[6], v[7]));
-        atomicAdd(row + 4, make_float4(v[8], v[9], v[10], v[11]));
-        atomicAdd(row + 5, make_float4(v[12], v[13], v[14], v[15]));
+      };
+      static_assert(kBwdGroup >= 2, "the step takes at least two entries");
+      if (!__any_sync(0xffffffffu, mem_mask[1] != 0u)) {
+        reduce_entry(std::false_type{}, 0);
+      } else {
+#pragma unroll
+        for (int g = 0; g < kBwdGroup; ++g) {
+          if (g > 1 && !__any_sync(0xffffffffu, mem_mask[g] != 0u)) break;
+          reduce_entry(std::true_type{}, g);
+        }
       }
     }
     __syncwarp();

@@ -9,12 +9,6 @@ import torch
 
 from . import _lib
 
-# launches of this library's kernels (memsets not counted) per call, for bench accounting
-LAUNCHES_PROJECT_AND_BIN = 1 + 12 + 2 + 3 + 1 + 3 + 1
-LAUNCHES_BUILD_LISTS = 11
-LAUNCHES_FORWARD = 2
-LAUNCHES_BACKWARD = 3
-
 
 def _ptr(t):
     return None if t is None else C.c_void_p(t.data_ptr())
