@@ -295,35 +295,34 @@ struct Eval {
 // of den, not from den < 0.  0/0 is NaN, which fmaxf/fminf drop (the reference ignores
 // that plane too).
 // TRACK = true (backward) also reports which plane produced each distance: the first
-// plane, in index order, whose distance equals the chain's result (what a running
-// "strictly greater / strictly smaller" update would have kept).
+// plane, in index order, whose distance equals the chain's result.  It runs the chains
+// as "strictly greater / strictly smaller" updates that carry the index along; these
+// leave the same values as fmaxf/fminf (a NaN never compares greater or smaller).
 template <bool TRACK>
 __device__ __forceinline__ bool slab_test(const float4 (&rec)[4], f3 d, float min_t, Eval& e) {
   // Distances are first taken from the camera position (u = -D/den) and shifted
   // by min_t afterwards: t = -(D + min_t*den)/den = u - min_t.
   float ue = -1e30f, ux = 1e30f;
-  float us[4];
-  bool ent[4];
+  int ie = -1, ix = -1;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const float4 p = rec[i];
     const float den = p.x * d.x + p.y * d.y + p.z * d.z;
     const float u = __fdividef(-p.w, den);
-    ent[i] = __float_as_int(den) < 0;  // sign bit: -0 bounds the entry, +0 the exit
-    us[i] = u;
-    ue = fmaxf(ue, ent[i] ? u : -1e30f);
-    ux = fminf(ux, ent[i] ? 1e30f : u);
+    const bool ent = __float_as_int(den) < 0;  // sign bit: -0 bounds the entry, +0 the exit
+    if (TRACK) {
+      const bool later = ent && u > ue, sooner = !ent && u < ux;
+      ue = later ? u : ue;
+      ie = later ? i : ie;
+      ux = sooner ? u : ux;
+      ix = sooner ? i : ix;
+    } else {
+      ue = fmaxf(ue, ent ? u : -1e30f);
+      ux = fminf(ux, ent ? 1e30f : u);
+    }
   }
   const float te = ue - min_t, tx = ux - min_t;
   if (!(te <= tx) || tx <= 0.0f) return false;
-  int ie = -1, ix = -1;
-  if (TRACK) {
-#pragma unroll
-    for (int i = 3; i >= 0; --i) {
-      if (ent[i] && us[i] == ue) ie = i;
-      if (!ent[i] && us[i] == ux) ix = i;
-    }
-  }
   e.te = te; e.tx = tx; e.ie = ie; e.ix = ix;
   e.enter = fmaxf(te, 0.0f);
   e.exit = fmaxf(tx, e.enter);
