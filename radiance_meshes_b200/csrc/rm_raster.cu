@@ -27,7 +27,8 @@
 //     soon as all of its pixels have terminated.  Every evaluated batch is
 //     appended, with the per-pixel bit sets of the entries that were hit, to the
 //     half-warp's hit list.
-//   * Backward walks the hit lists back to front and accumulates gradients with
+//   * Backward walks the hit lists back to front, up to three consecutive entries
+//     with disjoint pixel masks per step, and accumulates gradients with
 //     respect to 16 of the 24 record fields per hit (entering plane, exit plane,
 //     colour fields): the 16 pixels' values are summed through a shared-memory
 //     transpose when they share both faces, else added with 128-bit atomics, into
