@@ -373,7 +373,24 @@ def run_gpu(args):
 
     # gradients are summed over the ranks inside the backward pass: every finished range of tets is
     # all-reduced on a communication stream while the next range is being finished
-    reducer = rmdist.OverlappedGradientSum(chunks=args.reduce_chunks)
+    reducer = rmdist.OverlappedGradientSum(chunks=args.reduce_chunks or 4)
+    transport, transport_note = "nccl", None
+    if world > 1 and (args.reduce == "multimem" or (args.reduce == "auto" and world >= 8)):
+        # the sums formed by the NVSwitch (multimem kernels of this library on a symmetric-memory buffer) where
+        # every rank can set that up, NCCL's all-reduce otherwise; measured on this pool, the switch path wins
+        # at 8 ranks (0.72 against 1.06 ms per step), ties at 4 and loses to NCCL's ring at 2
+        ok = 0
+        mm = rmdist.MultimemGradientSum(chunks=args.reduce_chunks or 2)
+        try:
+            ok = int(mm.prepare((3 * V + 3) // 4 * 4 + 7 * T, dev))
+        except Exception as e:  # no symmetric memory or no multicast on this box
+            transport_note = f"{type(e).__name__}: {str(e)[:160]}"
+        flag = torch.tensor([ok], device=dev, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 1:
+            reducer, transport = mm, "multimem"
+        elif args.reduce == "multimem":
+            raise RuntimeError(f"--reduce multimem: not available here ({transport_note})")
 
     def step(inp, reduce=True, time_allreduce=False):
         v = inp["vertices"].requires_grad_(True)
@@ -435,6 +452,10 @@ def run_gpu(args):
         torch.cuda.synchronize()
         ar_ms = float(sum(a.elapsed_time(b) for a, b in reducer.events)) / args.steps
         reducer.events.clear()
+        mm_kernel_ms = None
+        if getattr(reducer, "kernel_events", None):
+            mm_kernel_ms = float(sum(a.elapsed_time(b) for a, b in reducer.kernel_events)) / args.steps
+            reducer.kernel_events.clear()
         ar_bytes = (vg.numel() + cg.numel()) * 4
         t = torch.tensor([ms_local, ar_ms], device=dev, dtype=torch.float64)
         allr = [torch.empty_like(t) for _ in range(world)]
@@ -445,11 +466,28 @@ def run_gpu(args):
         ar_min = min(ar_all)
         allreduce = dict(bytes=ar_bytes, ms_min_over_ranks=ar_min, ms_max_over_ranks=max(ar_all),
                          bus_gbs=2 * (world - 1) / world * ar_bytes / (ar_min * 1e-3) / 1e9,
-                         chunks=args.reduce_chunks,
-                         note="sum per step of the CUDA-event durations of the NCCL all-reduces (one per finished range "
-                              "of tets plus the vertex gradients), issued on a communication stream inside the backward "
-                              "pass; the minimum over ranks is the collectives themselves, the rest is waiting for the "
-                              "slowest view")
+                         chunks=reducer.chunks, transport=transport, transport_note=transport_note,
+                         multimem_kernel_ms_rank0=mm_kernel_ms,
+                         note="sum per step of the CUDA-event durations of the sums over the ranks (one per finished "
+                              "range of tets plus the vertex gradients), issued on a communication stream inside the "
+                              "backward pass; transport nccl: NCCL all-reduces; multimem: a one-element NCCL "
+                              "all-reduce as barrier + this library's k_multimem_sum per range; the minimum over ranks "
+                              "is the collectives themselves, the rest is waiting for the slowest view")
+
+    # ---- per-rank time of the same step without the sum over the ranks: what each view costs on its own
+    rank_compute_ms = None
+    if world > 1:
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        c0.record()
+        for _ in range(5):
+            step(d, reduce=False)
+        c1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([c0.elapsed_time(c1) / 5], device=dev, dtype=torch.float64)
+        allc = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(allc, t)
+        rank_compute_ms = [round(float(x.item()), 3) for x in allc]
 
     # ---- per-kernel times: a separate short loop with the library's event profiling on ----
     _lib.profile_read()
@@ -737,7 +775,7 @@ def run_gpu(args):
         if e2e_stream_ms else None,
         gpu_launches=int(launches), ms_per_step_median=ms_median,
         rank_step_ms=dict(min=min(rank_ms), median=float(np.median(rank_ms)), max=max(rank_ms)),
-        allreduce=allreduce, parity=parity, parity_multi=parity_multi, hit_stats=hit_stats,
+        allreduce=allreduce, rank_compute_ms=rank_compute_ms, parity=parity, parity_multi=parity_multi, hit_stats=hit_stats,
         reference_sort=reference_sort,
         fp32_pipe=fp32_pipe,
         roofline=roofline,
@@ -941,8 +979,13 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--lean", action="store_true",
                     help="only the device-resident arm, its per-kernel times and the multi-GPU parity check")
-    ap.add_argument("--reduce-chunks", type=int, default=4,
-                    help="ranges of tets whose gradients are all-reduced while the next range is finished (N > 1)")
+    ap.add_argument("--reduce-chunks", type=int, default=None,
+                    help="ranges of tets whose gradients are summed over the ranks while the next range is finished "
+                         "(N > 1); default 4 with NCCL, 2 with the multimem kernels")
+    ap.add_argument("--reduce", default="auto", choices=["auto", "nccl", "multimem"],
+                    help="how the gradients are summed over the ranks (N > 1): NCCL all-reduce, or this library's "
+                         "multimem kernels through the NVSwitch; auto = multimem at 8 or more ranks where every rank can "
+                         "set it up, else NCCL")
     ap.add_argument("--mode", default="views", choices=["views", "bands"],
                     help="views: one view per GPU, fwd+bwd, gradients all-reduced (the headline metric); "
                          "bands: one 4K frame split by tile-row bands, forward only")

@@ -298,6 +298,21 @@ int rm_backward_static_scratch(const int32_t* sorted_tetra_idx, const int32_t* t
                                void* stream);
 
 /*
+ * Sum of floats [float_begin, float_end) of a buffer over the `world` GPUs of one NVSwitch domain,
+ * in place on every GPU, for multi-GPU jobs that render one view per GPU and sum the gradients (no
+ * counterpart in the reference, which is single-GPU).  `multicast_buffer` is the NVLink MULTICAST
+ * address of the buffer: every rank holds the buffer at the same offset of a symmetric allocation
+ * bound to one multicast object (e.g. torch.distributed._symmetric_memory: empty(), rendezvous(),
+ * multicast_ptr).  Rank `rank` launches one kernel that pulls the sum of its 1/world slice through
+ * the switch (multimem.ld_reduce) and stores it to all GPUs (multimem.st).  Both bounds must be
+ * multiples of 4 floats and the address 16-byte aligned.  The kernel waits for nothing; the caller
+ * orders it on `stream`: a barrier among the ranks after the last write to the range and before this
+ * call, and another after it before any rank reads the sums.
+ */
+int rm_multimem_sum(float* multicast_buffer, int64_t float_begin, int64_t float_end, int rank, int world,
+                    void* stream);
+
+/*
  * Optional per-kernel timing, a measurement aid with no counterpart in the
  * reference (which only has commented-out wall-clock prints,
  * alphablend_tiled_slang.py:39-40).  While enabled, every kernel launch of the

@@ -21,7 +21,7 @@ SYMBOLS = ["rm_strerror", "rm_version", "rm_bin_workspace_bytes", "rm_list_scrat
            "rm_profile_read", "rm_backward_static_scratch", "rm_tet_err",
            "rm_activate_output", "rm_forward_constant_color", "rm_launch_count",
            "rm_backward_integrate", "rm_backward_finish", "rm_debug_bounds_checked", "rm_debug_set_extent",
-           "rm_debug_bounds_status", "rm_backward_constant_color"]
+           "rm_debug_bounds_status", "rm_backward_constant_color", "rm_multimem_sum"]
 RM_STATIC_SCRATCH_MAX_TETS = 131072
 RM_ERR_STATIC_SCRATCH = -5
 RM_ERR_INVALID_ARG = -1
@@ -79,6 +79,7 @@ def load():
                                                vp]
     lib.rm_tet_err.argtypes = [vp, vp, vp, cam, vp, vp, i64, vp, vp, vp]
     lib.rm_activate_output.argtypes = [vp, vp, vp, vp, vp, C.c_int, vp, vp, vp, i64, C.c_int, C.c_int, vp, vp]
+    lib.rm_multimem_sum.argtypes = [vp, i64, i64, C.c_int, C.c_int, vp]
     lib.rm_forward_constant_color.argtypes = [vp, vp, vp, cam, C.c_float, C.c_float, vp, vp, vp, vp]
     lib.rm_backward_constant_color.argtypes = [vp, vp, vp, cam, C.c_float, C.c_float, vp, vp, vp, vp, vp, vp, vp, vp,
                                                i64, i64, vp, vp, vp, vp, vp]

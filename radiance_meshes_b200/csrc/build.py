@@ -14,7 +14,7 @@ PKG = os.path.dirname(HERE)
 INCLUDE = os.path.join(os.path.dirname(PKG), "include")
 TARGET = os.path.join(PKG, "librm_b200.so")
 UNITS = [("rm_project.cu", ["-fmad=false"]), ("rm_binning.cu", []), ("rm_raster.cu", []), ("rm_activate.cu", []),
-         ("rm_api.cu", [])]
+         ("rm_multimem.cu", []), ("rm_api.cu", [])]
 HEADERS = [os.path.join(HERE, "rm_common.cuh"), os.path.join(INCLUDE, "rm_b200.h")]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 

@@ -36,6 +36,7 @@ int rm_launch_backward_constant_color(const int32_t*, const int32_t*, const floa
                                       const float*, const float*, const int32_t*, const float*, const float*, int64_t,
                                       int64_t, float*, uint8_t*, float*, cudaStream_t);
 
+int rm_launch_multimem_sum(float*, int64_t, int64_t, int, int, cudaStream_t);
 int rm_launch_activate(const float*, const float*, const float*, const float*, const void*, int, const int32_t*,
                        const float*, const float*, int64_t, int, int, float*, cudaStream_t);
 
@@ -379,6 +380,19 @@ int rm_backward(const int32_t* sorted_tetra_idx, const int32_t* tile_ranges, con
   if (n_tets > 0 && (!indices || !vertices || !cell_values || !cell_values_grad)) return RM_ERR_INVALID_ARG;
   return rm_backward_finish(indices, vertices, cell_values, 0, n_tets, n_tets, cam, grad_records, hits, vertices_grad,
                             cell_values_grad, stream);
+}
+
+int rm_multimem_sum(float* multicast_buffer, int64_t float_begin, int64_t float_end, int rank, int world,
+                    void* stream) {
+  g_last_error[0] = 0;
+  if (!multicast_buffer || world < 1 || rank < 0 || rank >= world || float_begin < 0 || float_end < float_begin ||
+      (float_begin & 3) || (float_end & 3))
+    return RM_ERR_INVALID_ARG;
+  if (!rm_aligned16(multicast_buffer)) return RM_ERR_WORKSPACE;
+  if (float_end == float_begin) return RM_OK;
+  // a multicast address belongs to no single device: the caller's current device launches
+  return rm_launch_multimem_sum(multicast_buffer, float_begin, float_end, rank, world,
+                                static_cast<cudaStream_t>(stream));
 }
 
 int rm_activate_output(const float* camera_center, const float* density, const float* rgb, const float* grd,

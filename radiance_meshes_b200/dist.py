@@ -110,6 +110,88 @@ class OverlappedGradientSum:
         return False
 
 
+class MultimemGradientSum(OverlappedGradientSum):
+    """OverlappedGradientSum with the sums formed by the NVSwitch instead of NCCL's all-reduce kernels.
+
+    The backward pass writes its gradients into a symmetric-memory buffer that is bound to an NVLink
+    multicast object (torch.distributed._symmetric_memory).  For every finished range this rank's kernel
+    (rm_multimem_sum) pulls the sum of its 1/N slice through the switch and stores it to all GPUs; a
+    one-element NCCL all-reduce in front of it is the barrier that tells every rank the others have written
+    the range, and one more at the end that all slices have been stored.  The sums are then copied out of
+    the buffer, which the next backward pass reuses.  prepare() is collective and must be called by every
+    rank (outside the backward pass) before the first use; it returns False where multicast is missing."""
+
+    def __init__(self, group=None, chunks=2, device=None):
+        super().__init__(group, chunks, device)
+        self.buf = None
+        self.mc = 0
+        self.token = None
+        self.kernel_events = []  # (start, end) of every rm_multimem_sum launch, if timing is on
+
+    def prepare(self, n_floats, device):
+        import torch.distributed._symmetric_memory as symm
+        group = self.group if self.group is not None else dist.group.WORLD
+        n4 = (int(n_floats) + 3) // 4 * 4
+        buf = symm.empty(n4, dtype=torch.float32, device=device)
+        buf.zero_()
+        handle = symm.rendezvous(buf, group)
+        if not handle.multicast_ptr:
+            return False
+        self.buf, self.mc, self._handle = buf, int(handle.multicast_ptr), handle
+        self.token = torch.zeros(1, dtype=torch.float32, device=device)
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        torch.cuda.synchronize(device)
+        return True
+
+    def allocate(self, n_floats, device):
+        if self.buf is None or not self._active() or self.buf.numel() < n_floats or self.buf.device != device:
+            return None
+        return self.buf[:n_floats]
+
+    def _owns(self, t):
+        return self.buf is not None and t.device == self.buf.device and \
+            0 <= t.data_ptr() - self.buf.data_ptr() <= 4 * (self.buf.numel() - t.numel())
+
+    def __call__(self, t):
+        if not self._active():
+            return
+        if not self._owns(t):  # gradients in ordinary memory: NCCL sums them
+            return super().__call__(t)
+        from . import _lib
+        begin = (t.data_ptr() - self.buf.data_ptr()) // 4
+        end = (begin + t.numel() + 3) // 4 * 4  # the buffer is padded with zeros to a multiple of 4 floats
+        assert begin % 4 == 0
+        cur = torch.cuda.current_stream(t.device)
+        if self.comm is None:
+            self.comm = torch.cuda.Stream(t.device)
+        ready = torch.cuda.Event()
+        ready.record(cur)
+        self.comm.wait_event(ready)
+        with torch.cuda.stream(self.comm):
+            if self.timing:
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(self.comm)
+            dist.all_reduce(self.token, op=dist.ReduceOp.SUM, group=self.group)  # every rank has written the range
+            if self.timing:
+                m = torch.cuda.Event(enable_timing=True)
+                m.record(self.comm)
+            _lib.check(_lib.load().rm_multimem_sum(self.mc, begin, end, self.rank, self.world,
+                                                   self.comm.cuda_stream))
+            if self.timing:
+                b.record(self.comm)
+                self.events.append((a, b))
+                self.kernel_events.append((m, b))
+
+    def done(self):
+        if self.comm is not None and self.buf is not None and self._active():
+            with torch.cuda.stream(self.comm):
+                dist.all_reduce(self.token, op=dist.ReduceOp.SUM, group=self.group)  # every slice has been stored
+        super().done()
+
+    def export(self, flat):
+        return flat.clone() if self._owns(flat) else flat
+
+
 def tile_row_bands(grid_height, world_size, row_weights=None):
     """Split tile rows [0, grid_height) into world_size contiguous bands.
 

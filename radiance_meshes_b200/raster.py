@@ -184,8 +184,12 @@ _gradient_sink = None
 
 
 def set_gradient_sink(sink, chunks=4):
-    """sink(tensor) is called on the backward pass's stream, in order, with views of the two gradients as
-    they become final; sink.done() once at the end.  None removes it."""
+    """sink(tensor) is called on the backward pass's stream, in order, with contiguous ranges of the flat
+    gradient buffer (vertex gradients first in memory, padded to 4 floats, then the cell-value gradients) as
+    they become final: ranges of the cell-value gradients first, the vertex gradients last; sink.done() once
+    at the end.  Optional methods: sink.allocate(n_floats, device) -> a float32 tensor the gradients are
+    written to (or None for an ordinary allocation), sink.export(flat) -> the tensor handed to the caller
+    after done().  None removes the sink."""
     global _gradient_sink
     _gradient_sink = None if sink is None else (sink, max(1, int(chunks)))
 
@@ -200,7 +204,12 @@ def backward(sorted_idx, tile_ranges, records, cam, ray_jitter, output_img, dist
         # both gradients live in one allocation (the second one 16-byte aligned), so that a multi-GPU
         # job can sum them over the ranks with a single all-reduce (dist.allreduce_gradients)
         off = (3 * V + 3) // 4 * 4
-        flat = torch.empty((off + 7 * T,), dtype=torch.float32, device=dev)
+        sink = _gradient_sink
+        flat = None
+        if sink is not None and hasattr(sink[0], "allocate"):  # a sink may want the gradients in memory of its own
+            flat = sink[0].allocate(off + 7 * T, dev)
+        if flat is None:
+            flat = torch.empty((off + 7 * T,), dtype=torch.float32, device=dev)
         vertices_grad = flat[:3 * V].view(V, 3)
         cell_grad = flat[off:].view(T, 7)
         if off > 3 * V:
@@ -214,7 +223,6 @@ def backward(sorted_idx, tile_ranges, records, cam, ray_jitter, output_img, dist
                                              _ptr(output_img), _ptr(distortion_img), href, _ptr(grad_output_img),
                                              _ptr(grad_distortion_img), T, V, _ptr(grad_records), _ptr(vertices_grad),
                                              st))
-        sink = _gradient_sink
         n_chunks = sink[1] if sink is not None and T >= 4096 else 1
         step = -(-T // n_chunks)
         step = -(-step // 256) * 256  # range starts on multiples of 256 tets
@@ -229,8 +237,12 @@ def backward(sorted_idx, tile_ranges, records, cam, ray_jitter, output_img, dist
             if t0 >= T:
                 break
         if sink is not None:
-            sink[0](vertices_grad)
+            sink[0](flat[:off])
             sink[0].done()
+            if hasattr(sink[0], "export"):  # the sums leave the sink's memory before its next use
+                flat = sink[0].export(flat)
+                vertices_grad = flat[:3 * V].view(V, 3)
+                cell_grad = flat[off:].view(T, 7)
     return vertices_grad, cell_grad
 
 

@@ -83,3 +83,20 @@ def test_bad_camera_is_rejected_before_any_launch(cuda_lib):
     cam.tile_row_end = 4
     assert call(cam, n_tets=_lib.RM_STATIC_SCRATCH_MAX_TETS + 1) == _lib.RM_ERR_STATIC_SCRATCH
     assert cuda_lib.rm_launch_count() >= 0
+
+
+def test_multimem_sum_rejects_bad_ranges_before_any_launch(cuda_lib):
+    """rm_multimem_sum checks its arguments on the host: NULL or misaligned address, a range that is not a
+    multiple of 4 floats, a rank outside the group.  An empty range is a no-op.  Nothing is launched."""
+    import ctypes as C
+    from radiance_meshes_b200 import _lib
+    fake = C.c_void_p(0x10000)  # never dereferenced
+    call = cuda_lib.rm_multimem_sum
+    assert call(None, 0, 16, 0, 2, None) == _lib.RM_ERR_INVALID_ARG
+    assert call(fake, 2, 16, 0, 2, None) == _lib.RM_ERR_INVALID_ARG
+    assert call(fake, 0, 18, 0, 2, None) == _lib.RM_ERR_INVALID_ARG
+    assert call(fake, 16, 0, 0, 2, None) == _lib.RM_ERR_INVALID_ARG
+    assert call(fake, 0, 16, 2, 2, None) == _lib.RM_ERR_INVALID_ARG
+    assert call(fake, 0, 16, 0, 0, None) == _lib.RM_ERR_INVALID_ARG
+    assert call(C.c_void_p(0x10004), 0, 16, 0, 2, None) != 0
+    assert call(fake, 16, 16, 1, 2, None) == 0

@@ -199,6 +199,17 @@ def test_overlapped_gradient_sum_is_inert_without_a_process_group():
     assert torch.equal(t, torch.ones(4)) and s.comm is None
 
 
+def test_multimem_gradient_sum_is_inert_without_a_process_group():
+    """Without a process group (or before prepare()) it owns no buffer: the backward pass allocates as
+    usual, ranges pass through untouched and export() hands the same tensor back."""
+    s = rmdist.MultimemGradientSum(chunks=2)
+    assert s.allocate(16, torch.device("cpu")) is None
+    t = torch.ones(8)
+    s(t)
+    s.done()
+    assert s.export(t) is t and torch.equal(t, torch.ones(8)) and s.comm is None
+
+
 def test_pixel_hits_per_unit_reads_the_hit_list_layout():
     """Mask slots of unit q start at start(tile)*S + s*len(tile) + 16*q, 16 per batch of 16 recorded entries."""
     ranges = torch.tensor([[0, 5], [5, 45], [0, 0]], dtype=torch.int32)      # three tiles, one unit each
