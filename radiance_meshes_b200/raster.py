@@ -184,10 +184,10 @@ _gradient_sink = None
 
 
 def set_gradient_sink(sink, chunks=4):
-    """sink(tensor) is called on the backward pass's stream, in order, with contiguous ranges of the flat
-    gradient buffer (vertex gradients first in memory, padded to 4 floats, then the cell-value gradients) as
-    they become final: ranges of the cell-value gradients first, the vertex gradients last; sink.done() once
-    at the end.  Optional methods: sink.allocate(n_floats, device) -> a float32 tensor the gradients are
+    """sink(tensor) is called on the backward pass's stream, in order, with views of the two gradients as
+    they become final: ranges of rows of the cell-value gradients first, the vertex gradients last;
+    sink.done() once at the end.  Both gradients live in one buffer (vertex gradients first, zero-padded to a
+    multiple of 4 floats, then the cell-value gradients), so the views are contiguous ranges of it.  Optional methods: sink.allocate(n_floats, device) -> a float32 tensor the gradients are
     written to (or None for an ordinary allocation), sink.export(flat) -> the tensor handed to the caller
     after done().  None removes the sink."""
     global _gradient_sink
@@ -237,7 +237,7 @@ def backward(sorted_idx, tile_ranges, records, cam, ray_jitter, output_img, dist
             if t0 >= T:
                 break
         if sink is not None:
-            sink[0](flat[:off])
+            sink[0](vertices_grad)
             sink[0].done()
             if hasattr(sink[0], "export"):  # the sums leave the sink's memory before its next use
                 flat = sink[0].export(flat)
