@@ -371,6 +371,11 @@ __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
   uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
 }
+// The hull edge lines of a record (bytes 96..143) are wanted soon: start their way into the caches.
+__device__ __forceinline__ void prefetch_hull_lines(const float4* rec) {
+  asm volatile("prefetch.global.L1 [%0];\n" ::"l"(rec + 6));
+  asm volatile("prefetch.global.L1 [%0];\n" ::"l"(rec + 8));
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
@@ -570,6 +575,9 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
   int id_n = (fetching && kBatch + lane16 < u.len) ? __ldg(list + u.start + kBatch + lane16) : -1;
   if (id_e >= 0 && !RM_INDEX_OK(id_e, RM_X_TETS, 1)) id_e = -1;
   if (id_n >= 0 && !RM_INDEX_OK(id_n, RM_X_TETS, 1)) id_n = -1;
+  int id_n2 = (fetching && 2 * kBatch + lane16 < u.len) ? __ldg(list + u.start + 2 * kBatch + lane16) : -1;
+  if (id_n2 >= 0 && !RM_INDEX_OK(id_n2, RM_X_TETS, 1)) id_n2 = -1;
+  if (id_n >= 0) prefetch_hull_lines(records + kRecStride * (int64_t)id_n);
   const float qnan = __int_as_float(0x7fc00000);
   float4 hq0 = make_float4(qnan, qnan, qnan, qnan), hq1 = hq0, hq2 = hq0;
   if (id_e >= 0) {
@@ -611,8 +619,11 @@ k_forward(const int32_t* __restrict__ list, const int2* __restrict__ ranges, con
             hq1 = __ldg(src_rec + 7);
             hq2 = __ldg(src_rec + 8);
           }
-          id_n = (src + kBatch + lane16 < u.len) ? __ldg(list + u.start + src + kBatch + lane16) : -1;
-          if (id_n >= 0 && !RM_INDEX_OK(id_n, RM_X_TETS, 1)) id_n = -1;
+          // the id two batches ahead arrived a step ago: its hull lines are asked for now and read in the next step
+          id_n = id_n2;
+          if (id_n >= 0) prefetch_hull_lines(records + kRecStride * (int64_t)id_n);
+          id_n2 = (src + 2 * kBatch + lane16 < u.len) ? __ldg(list + u.start + src + 2 * kBatch + lane16) : -1;
+          if (id_n2 >= 0 && !RM_INDEX_OK(id_n2, RM_X_TETS, 1)) id_n2 = -1;
         }
         continue;
       }
