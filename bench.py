@@ -379,15 +379,10 @@ def run_gpu(args):
         # the sums formed by the NVSwitch (multimem kernels of this library on a symmetric-memory buffer) where
         # every rank can set that up, NCCL's all-reduce otherwise; measured on this pool, the switch path wins
         # at 8 ranks (0.72 against 1.06 ms per step), ties at 4 and loses to NCCL's ring at 2
-        ok = 0
         mm = rmdist.MultimemGradientSum(chunks=args.reduce_chunks or 2)
-        try:
-            ok = int(mm.prepare((3 * V + 3) // 4 * 4 + 7 * T, dev))
-        except Exception as e:  # no symmetric memory or no multicast on this box
-            transport_note = f"{type(e).__name__}: {str(e)[:160]}"
-        flag = torch.tensor([ok], device=dev, dtype=torch.int32)
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        if int(flag.item()) == 1:
+        ok = int(mm.prepare((3 * V + 3) // 4 * 4 + 7 * T, dev))  # collective; False on every rank if one cannot
+        transport_note = mm.unavailable
+        if ok:
             reducer, transport = mm, "multimem"
         elif args.reduce == "multimem":
             raise RuntimeError(f"--reduce multimem: not available here ({transport_note})")

@@ -127,15 +127,40 @@ class MultimemGradientSum(OverlappedGradientSum):
         self.mc = 0
         self.token = None
         self.kernel_events = []  # (start, end) of every rm_multimem_sum launch, if timing is on
+        self.unavailable = None  # after prepare() returned False: why, on this rank
 
     def prepare(self, n_floats, device):
         import torch.distributed._symmetric_memory as symm
         group = self.group if self.group is not None else dist.group.WORLD
         n4 = (int(n_floats) + 3) // 4 * 4
-        buf = symm.empty(n4, dtype=torch.float32, device=device)
-        buf.zero_()
-        handle = symm.rendezvous(buf, group)
-        if not handle.multicast_ptr:
+        # every rank first says whether it can allocate symmetric memory with multicast at all; the collective
+        # rendezvous is entered only if all can, so a rank that cannot never leaves the others waiting in it
+        buf, reason = None, None
+        try:
+            from torch._C._distributed_c10d import _SymmetricMemory
+            if not _SymmetricMemory.has_multicast_support(torch._C._autograd.DeviceType.CUDA,
+                                                          torch.device(device).index or 0):
+                reason = "no multicast support on this device"
+            else:
+                buf = symm.empty(n4, dtype=torch.float32, device=device)
+                buf.zero_()
+        except Exception as e:
+            buf, reason = None, f"{type(e).__name__}: {str(e)[:160]}"
+        self.unavailable = reason
+        flag = torch.tensor([0 if buf is None else 1], dtype=torch.int32, device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if int(flag.item()) == 0:
+            return False
+        handle = None
+        try:
+            handle = symm.rendezvous(buf, group)
+            if not handle.multicast_ptr:
+                handle, self.unavailable = None, "rendezvous returned no multicast address"
+        except Exception as e:  # e.g. the processes may not exchange memory handles in this container
+            self.unavailable = f"{type(e).__name__}: {str(e)[:160]}"
+        flag.fill_(0 if handle is None else 1)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if int(flag.item()) == 0:
             return False
         self.buf, self.mc, self._handle = buf, int(handle.multicast_ptr), handle
         self.token = torch.zeros(1, dtype=torch.float32, device=device)
