@@ -88,7 +88,13 @@ def _worker(rank, world, port, results):
         separate = [torch.full((3,), float(rank + 1)), torch.full((2, 2), 10.0 * (rank + 1))]
         rmdist.allreduce_gradients([a, b])
         rmdist.allreduce_gradients(separate)
-        results[rank] = dict(vg=vg.numpy(), cg=cg.numpy(), n_images=len(images), full=full.numpy(), band=band,
+        # --- the switch-side gradient sum needs CUDA symmetric memory with multicast: on these CPU ranks every
+        # rank learns that together (no rank is left waiting in the rendezvous) and the NCCL-style class is used
+        mm = rmdist.MultimemGradientSum(chunks=2)
+        mm_ok = mm.prepare(64, torch.device("cpu"))
+        mm_alloc = mm.allocate(64, torch.device("cpu"))
+        results[rank] = dict(mm_ok=mm_ok, mm_reason=mm.unavailable, mm_alloc_none=mm_alloc is None,
+                             vg=vg.numpy(), cg=cg.numpy(), n_images=len(images), full=full.numpy(), band=band,
                              vg1=vg1.numpy(), cg1=cg1.numpy(), n_images1=len(one_img), raised=raised,
                              weights=weights.numpy(), flat=flat.numpy(), covering=rmdist._covering_view([a, b]).numel(),
                              separate=[t.numpy() for t in separate])
@@ -119,6 +125,8 @@ def test_two_rank_view_parallel_and_band_split(oracle):
         assert results[r]["n_images1"] == (1 if r == 0 else 0) and results[r]["raised"]
         np.testing.assert_allclose(results[r]["vg1"], vg2, rtol=1e-5, atol=1e-5 * np.abs(vg2).max())
         np.testing.assert_allclose(results[r]["cg1"], cg2, rtol=1e-5, atol=1e-5 * np.abs(cg2).max())
+    for r in range(world):
+        assert results[r]["mm_ok"] is False and results[r]["mm_reason"] and results[r]["mm_alloc_none"]
     # band split: the combined image equals the single-rank image bit for bit
     full_ref, _, _, idx_full, ranges_full = _oracle_render_backward(oracle, pts, tets, cell, _view(0))
     np.testing.assert_array_equal(results[0]["full"], full_ref)
