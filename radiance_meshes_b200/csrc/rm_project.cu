@@ -248,7 +248,7 @@ __device__ __forceinline__ float clipf(float v, float lo, float hi) { return fma
 //   depth_keys[g]  sortable depth bits, 0xFFFFFFFF for culled tets
 //   order_in[g]    g
 //   tile_diff      2-D difference array of tile coverage ((gh+1) x (gw+1) int32)
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 k_project(const int32_t* __restrict__ indices, int64_t T, const float* __restrict__ vertices, int64_t V,
           RmCamera rcam, int32_t* __restrict__ tiles_touched, int4* __restrict__ rect, float* __restrict__ vs_tetra,
           float* __restrict__ circumcenter, uint32_t* __restrict__ depth_keys, uint32_t* __restrict__ order_in,
