@@ -75,7 +75,7 @@ constexpr int kPackThreads = 128;
 
 // One thread per tet builds the record in registers; the block then writes its
 // records through shared memory so that the global stores are contiguous.
-__global__ void __launch_bounds__(kPackThreads)
+__global__ void __launch_bounds__(kPackThreads, 8)
 k_pack_records(const int32_t* __restrict__ indices, const float* __restrict__ vertices,
                const float* __restrict__ cell, int64_t T, int64_t V, RmCamera rcam,
                const int32_t* __restrict__ tiles_touched, float4* __restrict__ records) {
